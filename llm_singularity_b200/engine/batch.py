@@ -1,0 +1,150 @@
+"""StepEntry and StepContext: one step's batch, flattened for the kernels.
+
+A step is a list of entries ``(request, its next tokens, wanted places)``:
+portions of prompts beside single decoded tokens, cut anywhere.  All entries are
+flattened into one token stream ``[T]``; per token the context carries its
+position and its request's index, per request where its tokens start in the
+stream, how long its sequence is after this step, and which block-table row is
+its own.  The reference builds the same arrays per forward, in separate passes
+for prompts and decode tokens, with five ``cudaMalloc`` and a per-token copy of
+the block table (models/llama/llama_model.cpp:306-400,434-500); here it is one
+packed int32 buffer and one host-to-device copy per step.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Hashable, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+
+@dataclass
+class StepEntry:
+    request: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = field(default_factory=list)   # places among ``tokens``
+
+
+class StepContext:
+    """Device arrays (int32) and host mirrors describing one step's batch."""
+
+    # device
+    token_ids: torch.Tensor      # [T]
+    positions: torch.Tensor      # [T]  absolute position of each token in its sequence
+    token_req: torch.Tensor      # [T]  index of the token's request within this step
+    q_start: torch.Tensor        # [R+1] first token of each request in the stream
+    kv_len: torch.Tensor         # [R]  sequence length after this step
+    table_rows: torch.Tensor     # [R]  the request's row in block tables and state
+    want_rows: torch.Tensor      # [W]  stream indices whose logits are wanted
+    # host
+    n_tokens: int
+    n_requests: int
+    n_wanted: int
+    h_q_len: np.ndarray
+    h_kv_len: np.ndarray
+    max_q_len: int
+    max_kv_len: int
+
+
+class ContextBuilder:
+    """Packs step metadata into one pinned buffer and copies it to the device once."""
+
+    RING = 4
+
+    def __init__(self, device, max_tokens: int, max_requests: int, max_table_updates: int = 0):
+        self.device = torch.device(device)
+        self.max_tokens = max_tokens
+        self.max_requests = max_requests
+        cap = 4 * max_tokens + 3 * max_requests + 1 + 2 * max(max_table_updates, 1024) + 64
+        self._cap = cap
+        self._cuda = self.device.type == "cuda"
+        self._host = [torch.empty(cap, dtype=torch.int32, pin_memory=self._cuda)
+                      for _ in range(self.RING)]
+        self._dev = [torch.empty(cap, dtype=torch.int32, device=self.device)
+                     for _ in range(self.RING)]
+        self._events = [None] * self.RING
+        self._turn = 0
+
+    def _grow(self, n: int) -> None:
+        cap = max(n, 2 * self._cap)
+        self._cap = cap
+        if self._cuda:
+            torch.cuda.synchronize(self.device)
+        self._host = [torch.empty(cap, dtype=torch.int32, pin_memory=self._cuda)
+                      for _ in range(self.RING)]
+        self._dev = [torch.empty(cap, dtype=torch.int32, device=self.device)
+                     for _ in range(self.RING)]
+        self._events = [None] * self.RING
+
+    def build(self, tokens: List[Sequence[int]], starts: List[int], rows: List[int],
+              wants: List[Sequence[int]], extra: Optional[List[np.ndarray]] = None):
+        """``tokens[r]`` are request r's new tokens, ``starts[r]`` how many it already
+        holds, ``rows[r]`` its block-table row, ``wants[r]`` places among its tokens.
+        ``extra`` are further int32 arrays to ride along; returns (ctx, extra on device)."""
+        R = len(tokens)
+        q_len = np.fromiter((len(t) for t in tokens), dtype=np.int32, count=R)
+        if R == 0 or (q_len <= 0).any():
+            raise ValueError("a step needs at least one entry, and every entry at least one token")
+        T = int(q_len.sum())
+        q_start = np.zeros(R + 1, dtype=np.int32)
+        np.cumsum(q_len, out=q_start[1:])
+        starts_a = np.asarray(starts, dtype=np.int32)
+        kv_len = starts_a + q_len
+        want_rows: List[int] = []
+        for r in range(R):
+            for w in wants[r]:
+                if not 0 <= w < q_len[r]:
+                    raise ValueError(f"entry {r}: wanted place {w} outside its {q_len[r]} tokens")
+                want_rows.append(int(q_start[r]) + int(w))
+        W = len(want_rows)
+        extra = extra or []
+        n = 3 * T + (R + 1) + 2 * R + W + sum(len(e) for e in extra)
+        if n > self._cap:
+            self._grow(n)
+
+        i = self._turn
+        self._turn = (self._turn + 1) % self.RING
+        if self._events[i] is not None:
+            self._events[i].synchronize()
+        host = self._host[i].numpy()
+        o = 0
+
+        def put(arr):
+            nonlocal o
+            a = o
+            host[o:o + len(arr)] = arr
+            o += len(arr)
+            return a, o
+
+        flat = np.concatenate([np.asarray(t, dtype=np.int32) for t in tokens])
+        token_req = np.repeat(np.arange(R, dtype=np.int32), q_len)
+        positions = np.arange(T, dtype=np.int32) - np.repeat(q_start[:-1] - starts_a, q_len)
+        s_tok = put(flat)
+        s_pos = put(positions)
+        s_req = put(token_req)
+        s_qs = put(q_start)
+        s_kv = put(kv_len)
+        s_rows = put(np.asarray(rows, dtype=np.int32))
+        s_want = put(np.asarray(want_rows, dtype=np.int32))
+        s_extra = [put(e) for e in extra]
+
+        dev = self._dev[i]
+        dev[:o].copy_(self._host[i][:o], non_blocking=True)
+        if self._cuda:
+            ev = torch.cuda.Event()
+            ev.record()
+            self._events[i] = ev
+
+        ctx = StepContext()
+        ctx.token_ids = dev[s_tok[0]:s_tok[1]]
+        ctx.positions = dev[s_pos[0]:s_pos[1]]
+        ctx.token_req = dev[s_req[0]:s_req[1]]
+        ctx.q_start = dev[s_qs[0]:s_qs[1]]
+        ctx.kv_len = dev[s_kv[0]:s_kv[1]]
+        ctx.table_rows = dev[s_rows[0]:s_rows[1]]
+        ctx.want_rows = dev[s_want[0]:s_want[1]]
+        ctx.n_tokens, ctx.n_requests, ctx.n_wanted = T, R, W
+        ctx.h_q_len, ctx.h_kv_len = q_len, kv_len
+        ctx.max_q_len, ctx.max_kv_len = int(q_len.max()), int(kv_len.max())
+        return ctx, [dev[a:b] for a, b in s_extra]

@@ -1,0 +1,157 @@
+"""ModelRunner: the model, its cache and the one step function.
+
+``step(entries)`` takes a batch of (request, its next tokens, wanted places),
+portions of prompts beside single decoded tokens, cut anywhere; it runs only the
+tokens it is given, as one batch, against the cache earlier steps left, and
+returns the logits at the wanted places as a device tensor ``[wanted, vocab]``
+in the order of the entries and of their wanted places.  The scheduler, the
+Python entry point and trace replay all drive this same function.
+
+The reference's counterpart runs prompts and decode tokens as two forwards and
+returns host vectors (models/llama/llama_model.cpp:298-726; app/main.cpp:295-337).
+"""
+from __future__ import annotations
+
+from typing import Dict, Hashable, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager
+from ..config.specs import ModelSpec
+from ..models.decoder import DecoderModel
+from ..parts.base import Runtime
+from ..registry import architecture_of, read_config_json
+from ..weights.loader import load_checkpoint
+from .batch import ContextBuilder, StepContext, StepEntry
+
+
+class OutOfPages(RuntimeError):
+    """The cache pool cannot hold the tokens a step brings."""
+
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
+           "float32": torch.float32, "fp32": torch.float32}
+
+
+def parse_dtype(dtype) -> torch.dtype:
+    if isinstance(dtype, torch.dtype):
+        return dtype
+    try:
+        return _DTYPES[str(dtype)]
+    except KeyError:
+        raise ValueError(f"dtype must be one of {sorted(_DTYPES)}, got {dtype!r}") from None
+
+
+def _build_model(spec: ModelSpec, rt: Runtime, arch=None):
+    build = getattr(arch, "build", None) if arch is not None else None
+    return build(spec, rt) if build else DecoderModel(spec, rt)
+
+
+def expected_tensors_of(spec: ModelSpec) -> Dict[str, Tuple[Tuple[int, ...], str, str]]:
+    """Checkpoint name -> (shape, role, init) of every tensor a model of ``spec`` needs."""
+    shell = DecoderModel(spec, Runtime("cpu", torch.float32, ops=object()))
+    return {n: (ps.shape, ps.role, ps.init) for n, (_, _, ps) in shell.expected_tensors().items()}
+
+
+class ModelRunner:
+    def __init__(self, model_dir: Optional[str] = None, *, config=None,
+                 tensors: Optional[Dict[str, torch.Tensor]] = None,
+                 dtype="bfloat16", device="cuda:0", page_size: int = 16,
+                 num_pages: int = 1024, max_requests: int = 64,
+                 max_tokens_per_step: int = 2048, max_model_len: Optional[int] = None,
+                 ops=None, verbose: bool = False):
+        """Either ``model_dir`` (config.json + safetensors) or ``config`` + ``tensors``
+        (checkpoint names -> tensors, e.g. from ``random_tensors``)."""
+        self.dtype = parse_dtype(dtype)
+        arch = None
+        if config is None:
+            cfg_dict = read_config_json(model_dir)
+            arch = architecture_of(cfg_dict)
+            config = arch.config_cls.from_dict(cfg_dict)
+        self.config = config
+        self.spec: ModelSpec = config.to_model_spec()
+        self.rt = Runtime(device, self.dtype, ops=ops, page_size=page_size)
+        self.model = _build_model(self.spec, self.rt, arch)
+        if ops is None:
+            # compile (first call) and load what this model needs; raises if it cannot
+            self.rt.ops.prepare(self.model.required_kernels() + ["sampling", "cache_table"],
+                                verbose=verbose)
+
+        expected = self.model.expected_tensors()
+        if tensors is None:
+            tensors = load_checkpoint(
+                model_dir, {n: (ps.shape, ps.role) for n, (_, _, ps) in expected.items()},
+                self.spec.ignorable)
+        self.model.load_tensors(tensors)
+
+        self.page_size = page_size
+        if max_model_len is None:
+            max_model_len = num_pages * page_size
+        self.max_model_len = max_model_len
+        self.max_requests = max_requests
+        self.max_tokens_per_step = max_tokens_per_step
+        self.cache = CacheManager(self.model.cache_specs(), page_size, num_pages, max_requests,
+                                  -(-max_model_len // page_size), rt=self.rt)
+        self._ctx = ContextBuilder(self.rt.device, max_tokens_per_step, max_requests)
+        self.steps = 0
+        self.tokens_run = 0
+
+    @property
+    def vocab_size(self) -> int:
+        return self.spec.head.vocab_size
+
+    # ---------------------------------------------------------------- requests
+    def open(self, request: Hashable) -> bool:
+        """Admit ``request`` (a slot for its block-table row and state); False if none is free."""
+        return self.cache.open(request) is not None
+
+    def close(self, request: Hashable) -> None:
+        """The request is finished: what it holds is given back."""
+        self.cache.close(request)
+
+    # -------------------------------------------------------------------- step
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        cache = self.cache
+        starts = [cache.length(e.request) for e in entries]
+        seen = set()
+        for e in entries:
+            if e.request in seen:
+                raise ValueError(f"request {e.request!r} appears twice in one step")
+            seen.add(e.request)
+        reserved: List[Tuple[Hashable, int]] = []
+        for e, s in zip(entries, starts):
+            new_len = s + len(e.tokens)
+            if new_len > self.max_model_len:
+                raise OutOfPages(f"request {e.request!r}: {new_len} tokens exceed the "
+                                 f"engine's max_model_len {self.max_model_len}")
+            if not cache.reserve(e.request, new_len):
+                raise OutOfPages(
+                    f"request {e.request!r} needs {cache.pages_needed(e.request, new_len)} more "
+                    f"pages, {cache.free_pages()} are free")
+        ctx = self.prepare_context(entries, starts)
+        logits = self.model.forward(ctx, cache)
+        for e, s in zip(entries, starts):
+            cache.commit(e.request, s + len(e.tokens))
+        self.steps += 1
+        self.tokens_run += ctx.n_tokens
+        return logits
+
+    def prepare_context(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> StepContext:
+        """Build the step's device metadata and bring the device block tables up to date."""
+        cache = self.cache
+        extra: List[np.ndarray] = []
+        for gi in range(len(cache.groups)):
+            ups = cache.take_updates(gi)
+            # later writes to one cell win: keep the last value per cell
+            last = dict(ups)
+            extra.append(np.fromiter(last.keys(), dtype=np.int32, count=len(last)))
+            extra.append(np.fromiter(last.values(), dtype=np.int32, count=len(last)))
+        ctx, dev_extra = self._ctx.build(
+            [e.tokens for e in entries], list(starts),
+            [cache.slot(e.request) for e in entries], [e.want for e in entries], extra)
+        for gi, g in enumerate(cache.groups):
+            idx, val = dev_extra[2 * gi], dev_extra[2 * gi + 1]
+            if idx.numel():
+                self.rt.ops.scatter_i32(g.dev_table, idx, val)
+        return ctx

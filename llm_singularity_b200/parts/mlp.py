@@ -1,0 +1,42 @@
+"""Dense gated feed-forward: ``down( act(gate(x)) * up(x) )``, no bias.
+
+Reference: two products, ``silu(g) * u`` with ``silu(g) = g / (1 + exp(-g))``,
+then the down product (models/llama/llama_model.cpp:634-649;
+kernels/src/activations.cu:11-21).  Here gate and up are one product against the
+row-wise concatenation ``[Wgate; Wup]`` and the activation kernel reads both
+halves of each output row; the activation is evaluated in 32-bit.
+"""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from .base import ParamSpec, Part, register_feed_forward
+
+
+@register_feed_forward("gated_mlp")
+class GatedMLP(Part):
+    kernels = ("gemm", "activation")
+
+    def __init__(self, spec, rt):
+        super().__init__(spec, rt)
+        if spec.activation != "silu":
+            raise ValueError(f"activation '{spec.activation}' is not implemented (silu only)")
+
+    @classmethod
+    def params(cls, spec) -> Dict[str, ParamSpec]:
+        H, I = spec.hidden_size, spec.intermediate_size
+        return {"gate_proj": ParamSpec((I, H)), "up_proj": ParamSpec((I, H)),
+                "down_proj": ParamSpec((H, I))}
+
+    def load(self, tensors):
+        self.w_gate_up = torch.cat([tensors["gate_proj"], tensors["up_proj"]], dim=0).contiguous()
+        self.w_down = tensors["down_proj"].contiguous()
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        ops = self.rt.ops
+        gate_up = ops.linear(x, self.w_gate_up)                 # [T, 2I]
+        act = self.rt.empty(x.shape[0], self.spec.intermediate_size)
+        ops.swiglu(gate_up, act)
+        return ops.linear(act, self.w_down)
