@@ -1,0 +1,35 @@
+// SwiGLU on a fused gate/up product: out[t, i] = silu(gu[t, i]) * gu[t, I + i],
+// silu(g) = g / (1 + exp(-g)), evaluated in 32-bit.
+//
+// Replaces silu_mul_kernel of the reference (kernels/src/activations.cu:11-21), which
+// reads two separate fp32 buffers.
+#include "common.cuh"
+
+LSB_DEFINE_STATUS()
+
+template <typename T>
+__global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out,
+                              int inter, long long total) {
+    long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (; idx < total; idx += stride) {
+        const long long t = idx / inter;
+        const int i = (int)(idx - t * inter);
+        const T* row = gate_up + t * 2 * (long long)inter;
+        const float g = lsb_to_float(row[i]);
+        const float u = lsb_to_float(row[inter + i]);
+        out[idx] = lsb_from_float<T>(g / (1.f + expf(-g)) * u);
+    }
+}
+
+LSB_API int lsb_swiglu(const void* gate_up, void* out, int dtype, int tokens, int inter,
+                       cudaStream_t stream) {
+    const long long total = (long long)tokens * inter;
+    if (total <= 0) return 0;
+    const int threads = 256;
+    long long blocks = (total + threads - 1) / threads;
+    if (blocks > 148 * 32) blocks = 148 * 32;
+    LSB_DISPATCH_DTYPE(dtype, (swiglu_kernel<T><<<(int)blocks, threads, 0, stream>>>(
+        (const T*)gate_up, (T*)out, inter, total)));
+    return LSB_LAUNCH_CHECK();
+}

@@ -119,7 +119,10 @@ class ModelRunner:
             if e.request in seen:
                 raise ValueError(f"request {e.request!r} appears twice in one step")
             seen.add(e.request)
-        reserved: List[Tuple[Hashable, int]] = []
+        V = self.spec.embedding.vocab_size
+        for e in entries:
+            if len(e.tokens) and not (0 <= min(e.tokens) and max(e.tokens) < V):
+                raise ValueError(f"request {e.request!r}: token id outside [0, {V})")
         for e, s in zip(entries, starts):
             new_len = s + len(e.tokens)
             if new_len > self.max_model_len:
@@ -136,6 +139,13 @@ class ModelRunner:
         self.steps += 1
         self.tokens_run += ctx.n_tokens
         return logits
+
+    def check_kernels(self) -> None:
+        """Raise if a kernel recorded a fault (a page not held, a token outside the table).
+        Synchronises the device."""
+        check = getattr(self.rt.ops, "check_status", None)
+        if check is not None:
+            check()
 
     def prepare_context(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> StepContext:
         """Build the step's device metadata and bring the device block tables up to date."""

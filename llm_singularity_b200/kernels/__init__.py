@@ -1,0 +1,285 @@
+"""Kernel entry points: checked Python wrappers over the compiled sm_100a libraries.
+
+Every function here launches hand-written CUDA on the current stream of its
+tensors' device.  There is no CPU path and no fallback: a tensor that is not on
+a CUDA device, or a library that cannot be compiled or loaded, raises.  Shapes,
+dtypes, contiguity and size limits are checked here, before the launch, so that
+a size a kernel does not take is refused with a message and never computed
+wrongly.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Dict, Iterable, Optional
+
+import torch
+
+from . import build as _build
+
+_libs: Dict[str, ctypes.CDLL] = {}
+
+_F32, _BF16 = 0, 1
+_STATUS_TEXT = {
+    1: "a block-table entry outside the page pool was met (page not held by the request)",
+    2: "a token id outside the vocabulary was met",
+    3: "a row index outside its tensor was met",
+    4: "a bounded wait inside a kernel ran out",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+# ------------------------------------------------------------------ loading
+def prepare(names: Iterable[str], verbose: bool = False) -> None:
+    """Compile (if needed) and load the named libraries; raises if that is impossible."""
+    names = [n for n in dict.fromkeys(names) if n not in _libs]
+    if not names:
+        return
+    paths = _build.ensure_built(names, verbose=verbose)
+    for n in names:
+        try:
+            _libs[n] = ctypes.CDLL(paths[n])
+        except OSError as e:
+            raise KernelError(f"cannot load kernel library '{n}' from {paths[n]}: {e}") from None
+        _libs[n].lsb_error_string.restype = ctypes.c_char_p
+
+
+def loaded_libraries() -> Dict[str, str]:
+    return {n: lib._name for n, lib in _libs.items()}
+
+
+def _lib(name: str) -> ctypes.CDLL:
+    if name not in _libs:
+        prepare([name])
+    return _libs[name]
+
+
+def check_status() -> None:
+    """Read (and clear) every loaded library's status word; raises if a kernel recorded a fault.
+    Synchronises the device."""
+    for n, lib in _libs.items():
+        code = ctypes.c_int(0)
+        rc = lib.lsb_take_status(ctypes.byref(code))
+        if rc != 0:
+            raise KernelError(f"{n}: reading the status word failed: "
+                              f"{lib.lsb_error_string(rc).decode()}")
+        if code.value != 0:
+            raise KernelError(f"{n}: {_STATUS_TEXT.get(code.value, f'status {code.value}')}")
+
+
+def _call(libname: str, fn: str, *args) -> None:
+    lib = _lib(libname)
+    rc = getattr(lib, fn)(*args)
+    if rc != 0:
+        raise KernelError(f"{fn} failed: {lib.lsb_error_string(rc).decode()} (code {rc})")
+
+
+# ------------------------------------------------------------------- helpers
+def _dt(t: torch.Tensor) -> int:
+    if t.dtype == torch.float32:
+        return _F32
+    if t.dtype == torch.bfloat16:
+        return _BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, got {t.dtype}")
+
+
+def _req(t: torch.Tensor, name: str, dtype=None, dim: Optional[int] = None, contiguous=True):
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise KernelError(f"{name} must be a CUDA tensor (there is no CPU path)")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    if dim is not None and t.dim() != dim:
+        raise KernelError(f"{name} must have {dim} dims, got shape {tuple(t.shape)}")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    return t
+
+
+def _p(t: Optional[torch.Tensor]):
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _stream(t: torch.Tensor):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+_i = ctypes.c_int
+_ll = ctypes.c_longlong
+_f = ctypes.c_float
+
+
+# ---------------------------------------------------------------------- ops
+def scatter_i32(dst: torch.Tensor, idx: torch.Tensor, val: torch.Tensor) -> None:
+    """dst.flat[idx[i]] = val[i]."""
+    _req(dst, "dst", torch.int32)
+    _req(idx, "idx", torch.int32, 1)
+    _req(val, "val", torch.int32, 1)
+    if idx.numel() != val.numel():
+        raise KernelError("scatter_i32: idx and val differ in length")
+    _call("cache_table", "lsb_scatter_i32", _p(dst), _p(idx), _p(val), _i(idx.numel()),
+          _ll(dst.numel()), _stream(dst))
+
+
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, :] = float(table[ids[t], :])."""
+    _req(table, "table", dim=2)
+    _req(ids, "ids", torch.int32, 1)
+    _req(out, "out", torch.float32, 2)
+    if out.shape != (ids.shape[0], table.shape[1]):
+        raise KernelError(f"embedding: out is {tuple(out.shape)}, expected "
+                          f"{(ids.shape[0], table.shape[1])}")
+    _call("embedding", "lsb_embedding", _p(table), _i(_dt(table)), _p(ids), _p(out),
+          _i(ids.shape[0]), _i(table.shape[1]), _i(table.shape[0]), _stream(out))
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], weight: torch.Tensor,
+                eps: float, out: torch.Tensor) -> None:
+    """residual += delta (in place, 32-bit); out = rmsnorm(residual) * weight."""
+    _req(residual, "residual", torch.float32, 2)
+    _req(weight, "weight", torch.float32, 1)
+    _req(out, "out", dim=2)
+    T, H = residual.shape
+    if out.shape != (T, H) or weight.shape[0] != H:
+        raise KernelError("add_rmsnorm: shapes of residual, weight and out disagree")
+    if delta is not None:
+        _req(delta, "delta", out.dtype, 2)
+        if delta.shape != (T, H):
+            raise KernelError("add_rmsnorm: delta has another shape than residual")
+    _call("norm", "lsb_add_rmsnorm", _p(residual), _p(delta), _p(weight), _p(out), _i(_dt(out)),
+          _i(T), _i(H), _f(eps), _stream(out))
+
+
+def gather_add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], rows: torch.Tensor,
+                       weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """out[i] = rmsnorm(residual[rows[i]] + delta[rows[i]]) * weight; residual unchanged."""
+    _req(residual, "residual", torch.float32, 2)
+    _req(rows, "rows", torch.int32, 1)
+    _req(weight, "weight", torch.float32, 1)
+    _req(out, "out", dim=2)
+    T, H = residual.shape
+    if out.shape != (rows.shape[0], H) or weight.shape[0] != H:
+        raise KernelError("gather_add_rmsnorm: shapes disagree")
+    if delta is not None:
+        _req(delta, "delta", out.dtype, 2)
+        if delta.shape != (T, H):
+            raise KernelError("gather_add_rmsnorm: delta has another shape than residual")
+    _call("norm", "lsb_gather_add_rmsnorm", _p(residual), _p(delta), _p(rows), _p(weight), _p(out),
+          _i(_dt(out)), _i(rows.shape[0]), _i(T), _i(H), _f(eps), _stream(out))
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """x [M, K] times w [N, K] transposed -> [M, N]; 32-bit accumulation.
+
+    float32 operands run on the CUDA cores in true 32-bit.  bfloat16 operands run on the
+    tensor cores.
+    """
+    _req(x, "x", dim=2)
+    _req(w, "w", x.dtype, 2)
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K:
+        raise KernelError(f"linear: x is {tuple(x.shape)}, w is {tuple(w.shape)}")
+    out_dtype = out_dtype or x.dtype
+    if out_dtype not in (x.dtype, torch.float32):
+        raise KernelError(f"linear: output must be {x.dtype} or float32")
+    if x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16:
+        return torch.matmul(x, w.t())
+    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    _call("gemm", "lsb_gemm_nt", _p(x), _p(w), _p(out), _i(_dt(x)), _i(_dt(out)), _i(M), _i(N), _i(K),
+          _ll(K), _ll(K), _ll(N), _stream(out))
+    return out
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+    _req(gate_up, "gate_up", dim=2)
+    _req(out, "out", gate_up.dtype, 2)
+    T, I = out.shape
+    if gate_up.shape != (T, 2 * I):
+        raise KernelError(f"swiglu: gate_up is {tuple(gate_up.shape)}, out is {tuple(out.shape)}")
+    _call("activation", "lsb_swiglu", _p(gate_up), _p(out), _i(_dt(out)), _i(T), _i(I), _stream(out))
+
+
+def _check_cache(cache, nkv: int, hd: int, dtype) -> None:
+    for name in ("k_pages", "v_pages"):
+        t = _req(getattr(cache, name), name, dtype, 4)
+        if t.shape[1:] != (nkv, cache.page_size, hd):
+            raise KernelError(f"{name} is {tuple(t.shape)}, expected [pages, {nkv}, "
+                              f"{cache.page_size}, {hd}]")
+    _req(cache.block_table, "block_table", torch.int32, 2)
+
+
+def rope_kv_store(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache,
+                  inv_freq: Optional[torch.Tensor], rotary_dim: int, store: bool = True) -> None:
+    """Rotate queries and keys of the fused projection in place and write keys and values
+    of this step's tokens into their cache pages."""
+    _req(qkv, "qkv", dim=2)
+    T = qkv.shape[0]
+    if qkv.shape[1] != (nh + 2 * nkv) * hd:
+        raise KernelError(f"qkv is {tuple(qkv.shape)}, expected [T, {(nh + 2 * nkv) * hd}]")
+    if hd % 2 or rotary_dim % 2 or rotary_dim > hd:
+        raise KernelError(f"rope: head_dim {hd} and rotary_dim {rotary_dim} must be even, "
+                          f"rotary_dim <= head_dim")
+    if rotary_dim:
+        _req(inv_freq, "inv_freq", torch.float32, 1)
+        if inv_freq.shape[0] != rotary_dim // 2:
+            raise KernelError("inv_freq must have rotary_dim / 2 entries")
+    _check_cache(cache, nkv, hd, qkv.dtype)
+    if ctx.n_tokens != T:
+        raise KernelError(f"qkv has {T} rows, the step has {ctx.n_tokens} tokens")
+    _call("rope_cache", "lsb_rope_kv_store", _p(qkv), _i(_dt(qkv)), _i(T), _i(nh), _i(nkv), _i(hd),
+          _p(ctx.positions), _p(ctx.token_req), _p(ctx.table_rows), _p(cache.block_table),
+          _i(cache.block_table.shape[1]), _p(inv_freq if rotary_dim else None), _i(rotary_dim),
+          _p(cache.k_pages), _p(cache.v_pages), _i(cache.page_size), _i(cache.k_pages.shape[0]),
+          _i(1 if store else 0), _stream(qkv))
+
+
+def paged_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache, scale: float,
+                    window: int, out: torch.Tensor) -> None:
+    """Causal attention of this step's query rows over their requests' cached keys and values."""
+    _req(qkv, "qkv", dim=2)
+    _req(out, "out", qkv.dtype, 2)
+    T = qkv.shape[0]
+    if qkv.shape[1] < nh * hd or out.shape != (T, nh * hd):
+        raise KernelError(f"attention: qkv {tuple(qkv.shape)} / out {tuple(out.shape)} do not fit "
+                          f"{nh} heads of {hd}")
+    if hd % 16 or not 16 <= hd <= 256:
+        raise KernelError(f"attention: head_dim must be a multiple of 16 in [16, 256], got {hd}")
+    if nkv <= 0 or nh % nkv:
+        raise KernelError(f"attention: {nh} heads cannot share {nkv} kv heads")
+    if ctx.n_requests > 65535 or nh > 65535:
+        raise KernelError("attention: at most 65535 requests and heads per step")
+    _check_cache(cache, nkv, hd, qkv.dtype)
+    _call("attention", "lsb_paged_attention_generic", _p(qkv), _i(qkv.shape[1]), _p(cache.k_pages),
+          _p(cache.v_pages), _p(ctx.q_start), _p(ctx.kv_len), _p(ctx.table_rows),
+          _p(cache.block_table), _i(cache.block_table.shape[1]), _p(out), _i(_dt(qkv)),
+          _i(ctx.n_requests), _i(ctx.max_q_len), _i(nh), _i(nkv), _i(hd), _i(cache.page_size),
+          _i(cache.k_pages.shape[0]), _f(scale), _i(window), _stream(out))
+
+
+def sample(logits: torch.Tensor, params: torch.Tensor, top_k: torch.Tensor,
+           prev_start: Optional[torch.Tensor], prev_tokens: Optional[torch.Tensor],
+           out: torch.Tensor, work: Optional[torch.Tensor] = None) -> None:
+    """One token per row of ``logits``.  ``params[r] = (temperature, top_p, repetition_penalty,
+    u)``; ``top_k[r]`` (0 = off); ``prev_tokens[prev_start[r]:prev_start[r+1]]`` are the tokens the
+    repetition penalty applies to; ``work`` is scratch shaped like ``logits`` (needed only when
+    a penalty is in use)."""
+    _req(logits, "logits", torch.float32, 2)
+    R, V = logits.shape
+    _req(params, "params", torch.float32, 2)
+    _req(top_k, "top_k", torch.int32, 1)
+    _req(out, "out", torch.int32, 1)
+    if params.shape != (R, 4) or top_k.shape[0] != R or out.shape[0] != R:
+        raise KernelError("sample: per-row arrays do not match the logits")
+    if prev_start is not None:
+        _req(prev_start, "prev_start", torch.int32, 1)
+        _req(prev_tokens, "prev_tokens", torch.int32, 1)
+        if work is None:
+            work = torch.empty_like(logits)
+        _req(work, "work", torch.float32, 2)
+        if work.shape != logits.shape:
+            raise KernelError("sample: work must be shaped like logits")
+    _call("sampling", "lsb_sample", _p(logits), _p(work), _i(R), _i(V), _p(params), _p(top_k),
+          _p(prev_start), _p(prev_tokens), _p(out), _stream(out))
