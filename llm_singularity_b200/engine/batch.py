@@ -42,7 +42,9 @@ class StepContext:
     n_requests: int
     n_wanted: int
     h_q_len: np.ndarray
+    h_q_start: np.ndarray        # [R+1]
     h_kv_len: np.ndarray
+    h_table_rows: np.ndarray
     max_q_len: int
     max_kv_len: int
 
@@ -145,6 +147,7 @@ class ContextBuilder:
         ctx.table_rows = dev[s_rows[0]:s_rows[1]]
         ctx.want_rows = dev[s_want[0]:s_want[1]]
         ctx.n_tokens, ctx.n_requests, ctx.n_wanted = T, R, W
-        ctx.h_q_len, ctx.h_kv_len = q_len, kv_len
+        ctx.h_q_len, ctx.h_kv_len, ctx.h_q_start = q_len, kv_len, q_start
+        ctx.h_table_rows = np.asarray(rows, dtype=np.int32)
         ctx.max_q_len, ctx.max_kv_len = int(q_len.max()), int(kv_len.max())
         return ctx, [dev[a:b] for a, b in s_extra]

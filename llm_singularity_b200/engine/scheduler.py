@@ -1,0 +1,283 @@
+"""Scheduler: admits requests, cuts prompts into portions, decodes, finishes, frees.
+
+Each call of :meth:`Scheduler.schedule` plans one step under a token budget and
+a limit of live requests:
+
+1. every running request whose prompt is done gets its one decode token;
+2. running requests still in their prompt get the next portion, at most
+   ``max_prefill_chunk`` tokens and at most what is left of the budget;
+3. waiting requests are admitted first come, first served (no overtaking), as long
+   as a slot is free and the pools can hold their whole prompt plus one token
+   (pages the prefix cache could give up count as free), and get a first portion.
+
+Pages are reserved here, before the step, for exactly the tokens the step
+brings.  When a reservation fails the prefix cache is asked to evict; if that is
+not enough the most recently admitted running request is preempted: its pages and
+slot are freed and it goes back to the front of the queue with everything it has
+produced so far appended to its prompt, to be recomputed later.  Its sampling
+stream continues where it stopped, so the tokens it yields are the same.  A
+request that could never fit (its prompt plus one token needs more pages than the
+pool has, or exceeds ``max_model_len``) finishes at once with an error status.
+Nothing here is random, so a run can be replayed.
+
+The reference schedules prompts before decode tokens, iterates an unordered map,
+allocates whole prompts at admission, samples after every portion and, when pages
+run out during decoding, silently carries on into page 0
+(core/src/scheduler.cpp:67-272; app/main.cpp:295-337); its stop rules (eos, stop
+ids, max_new_tokens, output includes the stop token; scheduler.cpp:238-266) are
+kept.
+"""
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Deque, Dict, Hashable, List, Optional, Sequence, Tuple
+
+from ..cache.manager import CacheManager
+from ..sampling.params import SamplingParams
+
+
+@dataclass
+class SchedulerConfig:
+    max_batch_size: int = 64            # live requests (reference default, scheduler.h:23)
+    max_tokens_per_batch: int = 512     # tokens per step (scheduler.h:24)
+    max_prefill_chunk: Optional[int] = None
+    stop_token_ids: Tuple[int, ...] = ()
+    max_model_len: int = 1 << 30
+
+
+@dataclass
+class Request:
+    id: Hashable
+    prompt: List[int]
+    max_new_tokens: int
+    sampling: SamplingParams = field(default_factory=SamplingParams)
+    ignore_eos: bool = False
+    # progress
+    tokens: List[int] = field(default_factory=list)      # prompt + generated so far
+    generated: List[int] = field(default_factory=list)
+    computed: int = 0                                    # tokens whose keys/values are cached
+    status: str = "waiting"          # waiting | running | finished | error
+    error: str = ""
+    preemptions: int = 0
+    prefix_path: list = field(default_factory=list)
+
+    def __post_init__(self):
+        if not self.tokens:
+            self.tokens = list(self.prompt)
+
+
+@dataclass
+class ScheduledItem:
+    request: Request
+    start: int                 # == request.computed: position of the first token of the portion
+    tokens: List[int]
+    sample: bool               # the portion ends the known tokens: logits of its last token wanted
+
+
+class Scheduler:
+    def __init__(self, config: SchedulerConfig, cache: CacheManager, prefix_cache=None):
+        self.cfg = config
+        self.cache = cache
+        self.prefix = prefix_cache
+        self.waiting: Deque[Request] = deque()
+        self.running: List[Request] = []          # admission order
+        self.finished: List[Request] = []
+        self.stats = {"steps": 0, "preemptions": 0, "prefill_tokens": 0, "decode_tokens": 0,
+                      "prefix_hit_tokens": 0, "evicted_pages": 0, "admitted": 0, "errors": 0}
+        self._last: List[ScheduledItem] = []
+
+    # ----------------------------------------------------------------- intake
+    def add(self, request: Request) -> None:
+        if not request.prompt:
+            raise ValueError("a request needs at least one prompt token")
+        if request.max_new_tokens < 1:
+            raise ValueError("max_new_tokens must be at least 1")
+        self.waiting.append(request)
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    # ---------------------------------------------------------------- helpers
+    def _free_pages(self) -> int:
+        n = self.cache.free_pages()
+        if self.prefix is not None:
+            n += self.prefix.evictable_pages()
+        return n
+
+    def _reserve(self, req: Request, new_len: int) -> bool:
+        """Pages for ``new_len`` tokens of ``req``, evicting cached prefixes if needed."""
+        if self.cache.reserve(req.id, new_len):
+            return True
+        if self.prefix is not None:
+            need = self.cache.pages_needed(req.id, new_len) - self.cache.free_pages()
+            self.stats["evicted_pages"] += self.prefix.evict(need)
+            return self.cache.reserve(req.id, new_len)
+        return False
+
+    def _release(self, req: Request) -> None:
+        if self.prefix is not None and req.prefix_path:
+            self.prefix.release(req.prefix_path)
+            req.prefix_path = []
+        self.cache.close(req.id)
+
+    def _preempt(self, req: Request) -> None:
+        """Free everything ``req`` holds; it will be recomputed from its tokens so far."""
+        self._release(req)
+        self.running.remove(req)
+        req.computed = 0
+        req.status = "waiting"
+        req.preemptions += 1
+        self.stats["preemptions"] += 1
+        self.waiting.appendleft(req)
+
+    def _fail(self, req: Request, why: str) -> None:
+        req.status, req.error = "error", why
+        self.stats["errors"] += 1
+        self.finished.append(req)
+
+    def _never_fits(self, req: Request) -> Optional[str]:
+        n = len(req.tokens) + 1
+        pool = min(g.pool.num_pages for g in self.cache.groups) if self.cache.groups else 1 << 30
+        if n > self.cfg.max_model_len:
+            return f"{len(req.tokens)} tokens plus one exceed max_model_len {self.cfg.max_model_len}"
+        if self.cache.pages_for(n) > min(pool, self.cache.max_pages):
+            return (f"{len(req.tokens)} tokens plus one need {self.cache.pages_for(n)} pages, "
+                    f"the pool has {pool}")
+        return None
+
+    # --------------------------------------------------------------- schedule
+    def schedule(self) -> List[ScheduledItem]:
+        cfg = self.cfg
+        items: List[ScheduledItem] = []
+        budget = cfg.max_tokens_per_batch
+        chunk_cap = cfg.max_prefill_chunk or cfg.max_tokens_per_batch
+
+        # 1. decode tokens (requests with exactly one token left to run), oldest first; when
+        #    pages run out the youngest running request is preempted (possibly the one asking)
+        for req in list(self.running):
+            if req not in self.running or len(req.tokens) - req.computed != 1:
+                continue
+            if cfg.max_tokens_per_batch - sum(len(it.tokens) for it in items) <= 0:
+                break
+            placed = False
+            while req in self.running:
+                if self._reserve(req, len(req.tokens)):
+                    placed = True
+                    break
+                victim = self.running[-1]
+                items = [it for it in items if it.request is not victim]
+                self._preempt(victim)
+            if placed:
+                items.append(ScheduledItem(req, req.computed, [req.tokens[-1]], True))
+        budget = cfg.max_tokens_per_batch - sum(len(it.tokens) for it in items)
+
+        # 2. next portions of prompts already running (they wait for pages, never preempt)
+        for req in self.running:
+            remaining = len(req.tokens) - req.computed
+            if remaining <= 1 or budget <= 0:
+                continue
+            n = self._fit_portion(req, min(remaining, budget, chunk_cap))
+            if n > 0:
+                items.append(self._portion(req, n))
+                budget -= n
+
+        # 3. admission, first come first served
+        while self.waiting and budget > 0 and len(self.running) < cfg.max_batch_size:
+            req = self.waiting[0]
+            why = self._never_fits(req)
+            if why:
+                self.waiting.popleft()
+                self._fail(req, why)
+                continue
+            path = self.prefix.match(req.tokens) if self.prefix is not None else []
+            need = self.cache.pages_for(len(req.tokens) + 1) - len(path)
+            # pages on the matched path are in use by this request, not evictable for it
+            evictable_on_path = sum(1 for n in path if n.users == 0)
+            if need > self._free_pages() - evictable_on_path:
+                break
+            if self.cache.open(req.id) is None:
+                break
+            self.waiting.popleft()
+            if path:
+                req.computed = self.prefix.adopt(req.id, path)
+                req.prefix_path = path
+                self.stats["prefix_hit_tokens"] += req.computed
+            req.status = "running"
+            self.running.append(req)
+            self.stats["admitted"] += 1
+            n = self._fit_portion(req, min(len(req.tokens) - req.computed, budget, chunk_cap))
+            if n > 0:
+                items.append(self._portion(req, n))
+                budget -= n
+
+        # nothing could move although requests are live: the youngest gives way
+        if not items and self.running:
+            if len(self.running) == 1:
+                req = self.running[0]
+                self._release(req)
+                self.running.remove(req)
+                self._fail(req, "the cache pool cannot hold this request")
+            else:
+                self._preempt(self.running[-1])
+            return self.schedule()
+
+        self._last = items
+        self.stats["steps"] += 1 if items else 0
+        return items
+
+    def _fit_portion(self, req: Request, n: int) -> int:
+        """Largest portion <= n whose pages can be had now (prompts wait rather than preempt)."""
+        if n <= 0:
+            return 0
+        if self._reserve(req, req.computed + n):
+            return n
+        ps = self.cache.page_size
+        have = self.cache.pages_for(req.computed) * ps      # tokens its held pages cover
+        room = have + self._free_pages() * ps - req.computed
+        n = min(n, room)
+        if n > 0 and self._reserve(req, req.computed + n):
+            return n
+        return 0
+
+    def _portion(self, req: Request, n: int) -> ScheduledItem:
+        toks = req.tokens[req.computed:req.computed + n]
+        return ScheduledItem(req, req.computed, toks, req.computed + n == len(req.tokens))
+
+    # ----------------------------------------------------------------- update
+    def update(self, sampled: Dict[Hashable, int]) -> List[Request]:
+        """After the step: advance every scheduled request; ``sampled`` maps the ids of
+        requests whose logits were wanted to their new token.  Returns requests that finished."""
+        done: List[Request] = []
+        for it in self._last:
+            req = it.request
+            req.computed += len(it.tokens)
+            self.cache.commit(req.id, req.computed)      # idempotent if the step function did it
+            if it.sample:
+                if len(it.tokens) == 1 and it.start > 0 and req.generated:
+                    self.stats["decode_tokens"] += 1
+                else:
+                    self.stats["prefill_tokens"] += len(it.tokens)
+                tok = int(sampled[req.id])
+                req.tokens.append(tok)
+                req.generated.append(tok)
+                stop = (not req.ignore_eos and tok in self.cfg.stop_token_ids) \
+                    or len(req.generated) >= req.max_new_tokens \
+                    or len(req.tokens) + 1 > self.cfg.max_model_len
+                if stop:
+                    done.append(req)
+            else:
+                self.stats["prefill_tokens"] += len(it.tokens)
+        for req in done:
+            if self.prefix is not None:
+                self.prefix.insert(req.tokens[:req.computed], req.id)
+            self._release(req)
+            self.running.remove(req)
+            req.status = "finished"
+            self.finished.append(req)
+        self._last = []
+        return done
+
+    def take_finished(self) -> List[Request]:
+        out, self.finished = self.finished, []
+        return out

@@ -1,0 +1,56 @@
+"""Sampler: one token per row of logits, on the device.
+
+Greedy, temperature, top-k, top-p and repetition penalty in the reference's
+order (core/src/sampling.cpp:11-118), done by the ``sampling`` kernel library; the
+host only packs the per-row parameters and the uniform draws.  The reference
+never passes previous tokens to its sampler (app/main.cpp:308-310), which leaves
+its penalty without effect; here the request's generated tokens are passed.
+"""
+from __future__ import annotations
+
+from typing import List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from .params import SamplingParams
+from .rng import uniform
+
+
+class Sampler:
+    def __init__(self, rt):
+        self.rt = rt
+
+    def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams],
+               draw_index: Sequence[int],
+               previous: Optional[Sequence[Sequence[int]]] = None) -> torch.Tensor:
+        """``logits`` [R, V] float32 on the device; ``draw_index[r]`` is how many tokens request
+        r has generated so far (selects its uniform draw); ``previous[r]`` its generated tokens
+        (used only where a repetition penalty is set).  Returns int32 [R] on the device."""
+        R = logits.shape[0]
+        if len(params) != R or len(draw_index) != R:
+            raise ValueError("one SamplingParams and one draw index per row of logits")
+        fl = np.empty((R, 4), dtype=np.float32)
+        tk = np.empty(R, dtype=np.int32)
+        penal = False
+        for r, (p, n) in enumerate(zip(params, draw_index)):
+            fl[r] = (p.temperature, p.top_p, p.repetition_penalty,
+                     0.5 if p.greedy else uniform(p.seed, n))
+            tk[r] = p.top_k
+            penal |= p.repetition_penalty != 1.0
+        dev = self.rt.device
+        d_fl = torch.from_numpy(fl).to(dev, non_blocking=True)
+        d_tk = torch.from_numpy(tk).to(dev, non_blocking=True)
+        d_start = d_prev = None
+        if penal and previous is not None:
+            start = np.zeros(R + 1, dtype=np.int32)
+            flat: List[int] = []
+            for r, prev in enumerate(previous):
+                if params[r].repetition_penalty != 1.0:
+                    flat.extend(prev)
+                start[r + 1] = len(flat)
+            d_start = torch.from_numpy(start).to(dev)
+            d_prev = torch.from_numpy(np.asarray(flat if flat else [0], dtype=np.int32)).to(dev)
+        out = torch.empty(R, dtype=torch.int32, device=dev)
+        self.rt.ops.sample(logits, d_fl, d_tk, d_start, d_prev, out)
+        return out

@@ -12,6 +12,7 @@ from __future__ import annotations
 import json
 import mmap
 import struct
+import warnings
 from typing import Dict, Iterable, Mapping, Tuple
 
 import torch
@@ -89,7 +90,10 @@ class SafetensorsFile:
             n *= s
         if n == 0:
             return torch.empty(shape, dtype=dt)
-        flat = torch.frombuffer(self._map, dtype=dt, count=n, offset=self._data_start + begin)
+        with warnings.catch_warnings():
+            warnings.simplefilter("ignore", UserWarning)      # the map is read-only by design
+            flat = torch.frombuffer(self._map, dtype=dt, count=n,
+                                    offset=self._data_start + begin)
         return flat.view(shape)
 
     def close(self):

@@ -144,37 +144,53 @@ def swiglu_mlp(x, wg, wu, wd):
     return ((g / (1.0 + torch.exp(-g))) * u) @ wd.T
 
 
-def decoder_layer(x, w, i, cfg, positions, inv_freq):
-    """x += attn(norm(x)); x += mlp(norm(x)) (models/llama/llama_model.cpp:502-655)."""
+def _no_rounding(t):
+    return t
+
+
+def bf16_rounding(t):
+    """Round to bfloat16 and back: what storing an activation in bfloat16 does to it."""
+    return t.to(torch.bfloat16).to(t.dtype)
+
+
+def decoder_layer(x, w, i, cfg, positions, inv_freq, rnd=_no_rounding):
+    """x += attn(norm(x)); x += mlp(norm(x)) (models/llama/llama_model.cpp:502-655).
+    ``rnd`` is applied wherever a bfloat16 engine stores an activation (norm output,
+    projections, rotated q/k, attention output, gate/up, activation, down); the residual
+    stream x itself is never rounded."""
     nh, nkv, hd = sizes(cfg)
     eps = cfg.get("rms_norm_eps", 1e-5)
     p = f"model.layers.{i}."
     n = x.shape[0]
-    h = rms_norm(x, w[p + "input_layernorm.weight"], eps)
-    q = (h @ w[p + "self_attn.q_proj.weight"].T).view(n, nh, hd)
-    k = (h @ w[p + "self_attn.k_proj.weight"].T).view(n, nkv, hd)
-    v = (h @ w[p + "self_attn.v_proj.weight"].T).view(n, nkv, hd)
-    q = apply_rope(q, positions, inv_freq)
-    k = apply_rope(k, positions, inv_freq)
-    a = causal_attention(q, k, v, 1.0 / math.sqrt(hd), cfg.get("sliding_window"))
-    x = x + a.reshape(n, nh * hd) @ w[p + "self_attn.o_proj.weight"].T
-    h = rms_norm(x, w[p + "post_attention_layernorm.weight"], eps)
-    return x + swiglu_mlp(h, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"],
-                          w[p + "mlp.down_proj.weight"])
+    h = rnd(rms_norm(x, w[p + "input_layernorm.weight"], eps))
+    q = rnd(h @ w[p + "self_attn.q_proj.weight"].T).view(n, nh, hd)
+    k = rnd(h @ w[p + "self_attn.k_proj.weight"].T).view(n, nkv, hd)
+    v = rnd(h @ w[p + "self_attn.v_proj.weight"].T).view(n, nkv, hd)
+    q = rnd(apply_rope(q, positions, inv_freq))
+    k = rnd(apply_rope(k, positions, inv_freq))
+    a = rnd(causal_attention(q, k, v, 1.0 / math.sqrt(hd), cfg.get("sliding_window")))
+    x = x + rnd(a.reshape(n, nh * hd) @ w[p + "self_attn.o_proj.weight"].T)
+    h = rnd(rms_norm(x, w[p + "post_attention_layernorm.weight"], eps))
+    g = rnd(h @ w[p + "mlp.gate_proj.weight"].T)
+    u = rnd(h @ w[p + "mlp.up_proj.weight"].T)
+    act = rnd((g / (1.0 + torch.exp(-g))) * u)           # same formula as swiglu_mlp
+    return x + rnd(act @ w[p + "mlp.down_proj.weight"].T)
 
 
-def forward_logits(cfg, w, token_ids, dtype=torch.float64):
+def forward_logits(cfg, w, token_ids, dtype=torch.float64, act_round=None):
     """Logits [n, vocab] at every position of one whole sequence
     (models/llama/llama_model.cpp:424-425,502-666; lm_head tied to the embedding when
-    absent, :257-261)."""
+    absent, :257-261).  ``act_round="bfloat16"`` rounds stored activations as a bfloat16
+    engine does, so that such an engine can be held to a tight tolerance."""
+    rnd = bf16_rounding if act_round == "bfloat16" else _no_rounding
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in w.items()}
     nh, nkv, hd = sizes(cfg)
     inv_freq = rope_inv_freq(hd, cfg.get("rope_theta", 10000.0), cfg.get("rope_scaling"))
     positions = list(range(len(token_ids)))
     x = embed(w["model.embed_tokens.weight"], token_ids)
     for i in range(cfg["num_hidden_layers"]):
-        x = decoder_layer(x, w, i, cfg, positions, inv_freq)
-    x = rms_norm(x, w["model.norm.weight"], cfg.get("rms_norm_eps", 1e-5))
+        x = decoder_layer(x, w, i, cfg, positions, inv_freq, rnd)
+    x = rnd(rms_norm(x, w["model.norm.weight"], cfg.get("rms_norm_eps", 1e-5)))
     head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings", False) \
         else w["lm_head.weight"]
     return x @ head.T

@@ -104,3 +104,13 @@ def paged_attention(qkv, nh, nkv, hd, ctx, cache, scale, window, out):
                 s = s.masked_fill(~mask, float("-inf"))
                 w = torch.softmax(s, 0)
                 out[q_start[r] + i, h * hd:(h + 1) * hd] = (w @ V[:, h // group, :]).to(out.dtype)
+
+
+def sample(logits, params, top_k, prev_start, prev_tokens, out, work=None):
+    import plain_llama
+    for r in range(logits.shape[0]):
+        t, p, pen, u = (float(x) for x in params[r])
+        prev = ()
+        if prev_start is not None:
+            prev = prev_tokens[int(prev_start[r]):int(prev_start[r + 1])].tolist()
+        out[r] = plain_llama.sample_plain(logits[r].tolist(), t, int(top_k[r]), p, pen, prev, u)

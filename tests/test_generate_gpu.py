@@ -1,0 +1,131 @@
+"""Generation through the entry point and the command line on the GPU."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+import plain_llama
+import tiny_models
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _engine(model_dir, name, dtype, **kw):
+    from llm_singularity_b200 import Engine
+    opts = dict(dtype=dtype, kv_block_size=tiny_models.PAGE_SIZE[name], num_kv_blocks=64,
+                max_batch_size=4, max_tokens_per_batch=64)
+    opts.update(kw)
+    return Engine(model_dir, **opts)
+
+
+def _greedy_with_margin(cfg, w, prompt, n_new, margin):
+    """Plain greedy tokens, cut at the first step whose top-2 margin is below ``margin``."""
+    toks, out = list(prompt), []
+    for _ in range(n_new):
+        logits = plain_llama.forward_logits(cfg, w, toks)[-1]
+        top = torch.topk(logits, 2).values
+        if float(top[0] - top[1]) < margin:
+            break
+        t = int(torch.argmax(logits))
+        out.append(t); toks.append(t)
+    return out
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_greedy_generation_matches_plain(model_dirs, name, dtype):
+    cfg, w = plain_llama.load_model_dir(model_dirs[name])
+    vocab = tiny_models.CONFIGS[name]["vocab_size"]
+    lengths = (5, 17, 33) if name == "tiny_a" else (1, 9, 40, 70)
+    prompts = [tiny_models.random_tokens(vocab, n, 300 + n) for n in lengths]
+    margin = 1e-4 if dtype == "float32" else 0.05
+    eng = _engine(model_dirs[name], name, dtype, prefill_chunk=24)
+    outs = eng.generate(prompts, max_new_tokens=8, ignore_eos=True)
+    compared = 0
+    for p, o in zip(prompts, outs):
+        # tokens are compared up to the first step at which the plain top-2 margin is inside
+        # the dtype's rounding (a tie there may legitimately fall either way)
+        want = _greedy_with_margin(cfg, w, p, 8, margin)
+        assert len(o) == 8 and o[:len(want)] == want
+        compared += len(want)
+    assert compared >= 8
+    eng.runner.cache.check_invariants()
+
+
+def test_few_pages_preempt_and_still_give_the_same_tokens(model_dirs):
+    name = "tiny_a"
+    prompts = [tiny_models.random_tokens(256, n, 400 + n) for n in (30, 25, 28)]
+    roomy = _engine(model_dirs[name], name, "float32", prefix_cache=False)
+    want = roomy.generate(prompts, max_new_tokens=20, ignore_eos=True)
+    tight = _engine(model_dirs[name], name, "float32", num_kv_blocks=7, prefix_cache=False)
+    got = tight.generate(prompts, max_new_tokens=20, ignore_eos=True)
+    assert tight.stats()["preemptions"] > 0 and got == want
+    tight.runner.cache.check_invariants()
+    assert tight.runner.cache.free_pages() == 7
+
+
+def test_prefix_cache_hits_give_the_same_tokens(model_dirs):
+    name = "tiny_a"
+    shared = tiny_models.random_tokens(256, 48, 9)
+    prompts = [shared + tiny_models.random_tokens(256, 5, i) for i in range(3)]
+    cold = _engine(model_dirs[name], name, "float32", prefix_cache=False)
+    want = [cold.generate([p], max_new_tokens=6, ignore_eos=True)[0] for p in prompts]
+    warm = _engine(model_dirs[name], name, "float32")
+    got = [warm.generate([p], max_new_tokens=6, ignore_eos=True)[0] for p in prompts]
+    assert got == want and warm.stats()["prefix_hit_tokens"] == 2 * 48
+    warm.runner.cache.check_invariants()
+
+
+def test_temperature_sampling_is_reproducible_and_seeded(model_dirs):
+    name = "tiny_b"
+    prompts = [tiny_models.random_tokens(512, n, 500 + n) for n in (1, 9, 40, 70)]
+    kw = dict(max_new_tokens=12, temperature=0.8, ignore_eos=True)
+    a = _engine(model_dirs[name], name, "float32", prefill_chunk=24).generate(prompts, seed=3, **kw)
+    # alone, in another batch composition and with other portions: same tokens per request
+    eng = _engine(model_dirs[name], name, "float32")
+    b = [eng.generate([p], seed=3 + i, **kw)[0] for i, p in enumerate(prompts)]
+    c = _engine(model_dirs[name], name, "float32").generate(prompts, seed=4, **kw)
+    assert a == b and a != c
+    assert len({tuple(x) for x in a}) == 4
+
+
+def test_stop_token_ends_a_request_and_is_part_of_the_output(model_dirs):
+    name = "tiny_a"
+    cfg, w = plain_llama.load_model_dir(model_dirs[name])
+    prompt = tiny_models.random_tokens(256, 12, 1)
+    free = plain_llama.greedy_generate(cfg, w, prompt, 6)
+    # make the third generated token the stop token
+    from llm_singularity_b200 import Engine
+    eng = _engine(model_dirs[name], name, "float32")
+    eng.scheduler.cfg.stop_token_ids = (free[2],)
+    out = eng.generate([prompt], max_new_tokens=6)[0]
+    assert out == free[:free.index(free[2]) + 1]
+
+
+def test_command_line(model_dirs, tmp_path):
+    name = "tiny_a"
+    cfg, w = plain_llama.load_model_dir(model_dirs[name])
+    prompts = [tiny_models.random_tokens(256, n, 600 + n) for n in (4, 11)]
+    (tmp_path / "p.json").write_text(json.dumps(prompts))
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "llm-serve-llama"), "--model-dir", model_dirs[name],
+           "--dtype", "fp32", "--prompt-ids", str(tmp_path / "p.json"), "--max-new-tokens", "5",
+           "--ignore-eos", "--num-kv-blocks", "32", "--max-batch-size", "4", "--stats"]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stderr
+    lines = [json.loads(l) for l in res.stdout.splitlines()]
+    assert [l["tokens"] for l in lines] == [plain_llama.greedy_generate(cfg, w, p, 5) for p in prompts]
+    assert '"stats"' in res.stderr
+    # random-weights mode needs only config.json
+    only_cfg = tmp_path / "cfg"
+    only_cfg.mkdir()
+    (only_cfg / "config.json").write_text(json.dumps(tiny_models.CONFIGS["tiny_b"]))
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "llm-serve-llama"), "--model-dir", str(only_cfg),
+           "--random-weights", "--seed", "7", "--prompt-len", "9", "--num-requests", "3",
+           "--max-new-tokens", "4", "--ignore-eos", "--num-kv-blocks", "32", "--max-batch-size", "4"]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stderr
+    assert [len(json.loads(l)["tokens"]) for l in res.stdout.splitlines()] == [4, 4, 4]

@@ -1,0 +1,397 @@
+"""Each CUDA kernel alone against plain tensor arithmetic, at sizes the engine's tiny models do
+not use: head sizes in steps of 16 up to 256, odd widths and vocabularies, scattered pages."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_llama
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def _tol(dtype, scale=1.0):
+    # float32: accumulation-order noise only; bfloat16: one rounding of the result (2^-8 relative)
+    return (2e-5 if dtype == torch.float32 else 1e-2) * scale
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from llm_singularity_b200 import kernels
+    kernels.prepare(["embedding", "norm", "activation", "cache_table", "rope_cache", "attention",
+                     "gemm", "sampling"])
+    yield kernels
+    kernels.check_status()
+
+
+def _rand(*shape, dtype=torch.float32, seed=0, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype).cuda()
+
+
+# ------------------------------------------------------------------ small ones
+def test_ops_refuse_cpu_tensors(ops):
+    with pytest.raises(ops.KernelError, match="CUDA"):
+        ops.swiglu(torch.zeros(2, 8), torch.zeros(2, 4))
+
+
+def test_scatter_i32(ops):
+    dst = torch.full((5, 7), -1, dtype=torch.int32, device="cuda")
+    idx = torch.tensor([0, 8, 34, 8], dtype=torch.int32, device="cuda")[:3]
+    val = torch.tensor([4, 5, 6], dtype=torch.int32, device="cuda")
+    ops.scatter_i32(dst, idx, val)
+    want = torch.full((35,), -1, dtype=torch.int32)
+    want[[0, 8, 34]] = torch.tensor([4, 5, 6], dtype=torch.int32)
+    assert torch.equal(dst.cpu().view(-1), want)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embedding(ops, dtype):
+    table = _rand(1000, 200, dtype=dtype)
+    ids = torch.tensor([0, 999, 5, 5, 123], dtype=torch.int32, device="cuda")
+    out = torch.empty(5, 200, dtype=torch.float32, device="cuda")
+    ops.embedding(table, ids, out)
+    assert torch.equal(out, table[ids.long()].float())
+
+
+def test_embedding_reports_a_token_outside_the_table(ops):
+    table = _rand(10, 8)
+    out = torch.empty(2, 8, device="cuda")
+    ops.embedding(table, torch.tensor([3, 10], dtype=torch.int32, device="cuda"), out)
+    with pytest.raises(ops.KernelError, match="token id"):
+        ops.check_status()
+    assert torch.equal(out[1], torch.zeros(8, device="cuda")) and torch.equal(out[0], table[3])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [72, 2048, 2049, 5000])
+def test_add_rmsnorm(ops, dtype, hidden):
+    res = _rand(7, hidden, seed=1)
+    delta = _rand(7, hidden, dtype=dtype, seed=2)
+    w = 1 + 0.1 * _rand(hidden, seed=3)
+    eps = 3e-6
+    want_res = res.double() + delta.double()
+    want = plain_llama.rms_norm(want_res, w.double(), eps)
+    out = torch.empty(7, hidden, dtype=dtype, device="cuda")
+    ops.add_rmsnorm(res, delta, w, eps, out)
+    assert torch.allclose(res.double(), want_res, atol=1e-6)          # residual updated in 32-bit
+    assert (out.double() - want).abs().max() <= _tol(dtype, want.abs().max().item())
+    # without a delta the residual is left alone
+    res2 = _rand(3, hidden, seed=4)
+    keep = res2.clone()
+    out2 = torch.empty(3, hidden, dtype=dtype, device="cuda")
+    ops.add_rmsnorm(res2, None, w, eps, out2)
+    assert torch.equal(res2, keep)
+    want2 = plain_llama.rms_norm(keep.double(), w.double(), eps)
+    assert (out2.double() - want2).abs().max() <= _tol(dtype, want2.abs().max().item())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hidden", [200, 4100])
+def test_gather_add_rmsnorm_leaves_the_residual_alone(ops, dtype, hidden):
+    res, delta = _rand(9, hidden, seed=1), _rand(9, hidden, dtype=dtype, seed=2)
+    w = 1 + 0.1 * _rand(hidden, seed=3)
+    rows = torch.tensor([8, 0, 3, 3], dtype=torch.int32, device="cuda")
+    keep = res.clone()
+    out = torch.empty(4, hidden, dtype=dtype, device="cuda")
+    ops.gather_add_rmsnorm(res, delta, rows, w, 1e-5, out)
+    want = plain_llama.rms_norm((keep.double() + delta.double())[rows.long()], w.double(), 1e-5)
+    assert torch.equal(res, keep)
+    assert (out.double() - want).abs().max() <= _tol(dtype, want.abs().max().item())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu(ops, dtype):
+    gu = _rand(11, 200, dtype=dtype, scale=3.0)
+    out = torch.empty(11, 100, dtype=dtype, device="cuda")
+    ops.swiglu(gu, out)
+    g, u = gu[:, :100].double(), gu[:, 100:].double()
+    want = g / (1 + torch.exp(-g)) * u
+    assert (out.double() - want).abs().max() <= _tol(dtype, want.abs().max().item())
+
+
+@pytest.mark.parametrize("in_dtype, out_dtype", [(torch.float32, torch.float32),
+                                                 (torch.bfloat16, torch.float32),
+                                                 (torch.bfloat16, torch.bfloat16)])
+@pytest.mark.parametrize("M, N, K", [(1, 301, 72), (37, 301, 70), (130, 64, 2049), (64, 129, 16)])
+def test_linear(ops, in_dtype, out_dtype, M, N, K):
+    x, w = _rand(M, K, dtype=in_dtype, seed=1), _rand(N, K, dtype=in_dtype, seed=2)
+    y = ops.linear(x, w, out_dtype=out_dtype)
+    want = x.double() @ w.double().T
+    assert y.dtype == out_dtype and y.shape == (M, N)
+    tol = 3e-7 * K if out_dtype == torch.float32 else 1e-2 * want.abs().max().item()
+    assert (y.double() - want).abs().max() <= tol
+
+
+def test_linear_float32_is_true_32_bit(ops):
+    # (1 + 2^-20) * 1 + 1 * (-1) = 2^-20 exactly in 32-bit; a reduced-precision matrix mode
+    # (10-bit mantissa operands) rounds the first factor to 1 and returns 0
+    K = 256
+    x = torch.zeros(1, K, device="cuda")
+    w = torch.zeros(1, K, device="cuda")
+    x[0, 0], w[0, 0] = 1 + 2.0 ** -20, 1.0
+    x[0, 1], w[0, 1] = 1.0, -1.0
+    assert ops.linear(x, w).item() == 2.0 ** -20
+
+
+# --------------------------------------------------------------- rope + cache
+class _Ctx:
+    pass
+
+
+def _make_ctx(q_lens, kv_lens, table_rows=None):
+    from llm_singularity_b200.engine.batch import ContextBuilder
+    b = ContextBuilder("cuda", 4096, 64)
+    R = len(q_lens)
+    toks = [[0] * n for n in q_lens]
+    starts = [kv - q for kv, q in zip(kv_lens, q_lens)]
+    ctx, _ = b.build(toks, starts, table_rows or list(range(R)), [[] for _ in range(R)])
+    ctx._keep = b
+    return ctx
+
+
+def _make_cache(R, max_kv, nkv, hd, page_size, dtype, seed=0, window=None, slots=None):
+    from llm_singularity_b200.cache.manager import KVCacheView
+    pages_per = -(-max_kv // page_size)
+    slots = slots or R
+    n_pages = slots * pages_per + 3
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(n_pages, generator=g)[:slots * pages_per].view(slots, pages_per)
+    k = torch.zeros(n_pages, nkv, page_size, hd, dtype=dtype, device="cuda")
+    v = torch.zeros_like(k)
+    return KVCacheView(k, v, perm.to(torch.int32).cuda(), page_size, window, 0)
+
+
+def _fill(cache, row, K, V):
+    """Write dense K, V [len, nkv, hd] of one request into its pages."""
+    n = K.shape[0]
+    pos = torch.arange(n)
+    pages = cache.block_table[row].cpu()[pos // cache.page_size].long()
+    cache.k_pages[pages, :, pos % cache.page_size, :] = K.to(cache.k_pages.dtype).cuda()
+    cache.v_pages[pages, :, pos % cache.page_size, :] = V.to(cache.v_pages.dtype).cuda()
+
+
+def _dense(cache, row, n):
+    pos = torch.arange(n)
+    pages = cache.block_table[row].cpu()[pos // cache.page_size].long()
+    return cache.k_pages[pages, :, pos % cache.page_size, :], cache.v_pages[pages, :, pos % cache.page_size, :]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh, nkv, hd, rot, page", [(5, 5, 80, 40, 4), (4, 1, 32, 32, 8), (6, 2, 128, 128, 16)])
+def test_rope_kv_store(ops, dtype, nh, nkv, hd, rot, page):
+    from llm_singularity_b200.parts.rotary import rotary_inv_freq
+    q_lens, kv_lens = [3, 1, 9], [3, 30, 20]          # a fresh prompt, a decode token, a later portion
+    ctx = _make_ctx(q_lens, kv_lens, table_rows=[2, 0, 1])
+    cache = _make_cache(3, 32, nkv, hd, page, dtype)
+    T = sum(q_lens)
+    qkv = _rand(T, (nh + 2 * nkv) * hd, dtype=dtype, seed=5)
+    orig = qkv.clone()
+    inv = rotary_inv_freq(rot, 10000.0).float().cuda()
+    ops.rope_kv_store(qkv, nh, nkv, hd, ctx, cache, inv, rot)
+    pos = ctx.positions.cpu().tolist()
+    assert pos == [0, 1, 2, 29] + list(range(11, 20))
+    o = orig.double().cpu()
+    q0 = o[:, :nh * hd].view(T, nh, hd)
+    k0 = o[:, nh * hd:(nh + nkv) * hd].view(T, nkv, hd)
+    v0 = o[:, (nh + nkv) * hd:].view(T, nkv, hd)
+
+    def rope(x):
+        y = x.clone()
+        y[..., :rot] = plain_llama.apply_rope(x[..., :rot], pos, inv.double().cpu())
+        return y
+    tol = _tol(dtype, 4.0)
+    got_q = qkv[:, :nh * hd].double().cpu().view(T, nh, hd)
+    assert (got_q - rope(q0)).abs().max() <= tol
+    assert torch.equal(qkv[:, (nh + nkv) * hd:], orig[:, (nh + nkv) * hd:])       # values untouched
+    want_k = rope(k0)
+    t = 0
+    for r, (ql, kl) in enumerate(zip(q_lens, kv_lens)):
+        Kc, Vc = _dense(cache, [2, 0, 1][r], kl)
+        sl = slice(kl - ql, kl)
+        assert (Kc[sl].double().cpu() - want_k[t:t + ql]).abs().max() <= tol
+        assert torch.equal(Vc[sl].cpu(), v0[t:t + ql].to(dtype))
+        assert Kc[:kl - ql].abs().max() == 0 if kl > ql else True             # nothing else written
+        t += ql
+    # store=False rotates but leaves the pages alone
+    before = cache.k_pages.clone()
+    qkv2 = orig.clone()
+    ops.rope_kv_store(qkv2, nh, nkv, hd, ctx, cache, inv, rot, store=False)
+    assert torch.equal(cache.k_pages, before) and torch.equal(qkv2[:, :nh * hd], qkv[:, :nh * hd])
+
+
+def test_rope_kv_store_reports_a_page_that_is_not_held(ops):
+    ctx = _make_ctx([2], [2])
+    cache = _make_cache(1, 16, 1, 16, 16, torch.float32)
+    cache.block_table[0, 0] = -1
+    qkv = _rand(2, 3 * 16)
+    ops.rope_kv_store(qkv, 1, 1, 16, ctx, cache, None, 0)
+    with pytest.raises(ops.KernelError, match="page"):
+        ops.check_status()
+    assert cache.k_pages.abs().max() == 0
+
+
+# ------------------------------------------------------------------- attention
+def _ref_attention(q, K, V, scale, window):
+    """q [n, nh, hd] are the last n positions of a sequence whose keys/values are K, V [len, nkv, hd]."""
+    n, nh, hd = q.shape
+    L, nkv = K.shape[0], K.shape[1]
+    out = torch.zeros(n, nh, hd, dtype=torch.float64)
+    for i in range(n):
+        p = L - n + i
+        lo = max(0, p - window + 1) if window else 0
+        for h in range(nh):
+            g = h // (nh // nkv)
+            s = (K[lo:p + 1, g] @ q[i, h]) * scale
+            out[i, h] = torch.softmax(s, 0) @ V[lo:p + 1, g]
+    return out
+
+
+def _run_attention(ops, dtype, nh, nkv, hd, page, q_lens, kv_lens, window=0, seed=0, qk_boost=None):
+    R = len(q_lens)
+    rows = list(reversed(range(R)))
+    ctx = _make_ctx(q_lens, kv_lens, table_rows=rows)
+    cache = _make_cache(R, max(kv_lens), nkv, hd, page, dtype, seed=seed)
+    T = sum(q_lens)
+    qkv = _rand(T, (nh + 2 * nkv) * hd, dtype=dtype, seed=seed + 1)
+    Ks, Vs = [], []
+    for r in range(R):
+        K = _rand(kv_lens[r], nkv, hd, dtype=dtype, seed=seed + 10 + r).cpu()
+        V = _rand(kv_lens[r], nkv, hd, dtype=dtype, seed=seed + 20 + r).cpu()
+        Ks.append(K); Vs.append(V)
+    if qk_boost:
+        qk_boost(qkv, Ks, ctx)
+    for r in range(R):
+        _fill(cache, rows[r], Ks[r], Vs[r])
+    out = torch.empty(T, nh * hd, dtype=dtype, device="cuda")
+    scale = 1.0 / math.sqrt(hd)
+    ops.paged_attention(qkv, nh, nkv, hd, ctx, cache, scale, window, out)
+    t = 0
+    worst = 0.0
+    for r in range(R):
+        q = qkv[t:t + q_lens[r], :nh * hd].double().cpu().view(q_lens[r], nh, hd)
+        want = _ref_attention(q, Ks[r].double(), Vs[r].double(), scale, window)
+        got = out[t:t + q_lens[r]].double().cpu().view(q_lens[r], nh, hd)
+        worst = max(worst, (got - want).abs().max().item())
+        t += q_lens[r]
+    return worst
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nh, nkv, hd, page", [(6, 3, 48, 16), (8, 1, 16, 8), (5, 5, 128, 4),
+                                               (4, 2, 256, 32), (3, 1, 80, 16)])
+def test_attention_mixed_batch(ops, dtype, nh, nkv, hd, page):
+    # a whole prompt, a decode token on a long context, a portion in the middle, two tokens
+    worst = _run_attention(ops, dtype, nh, nkv, hd, page, [37, 1, 12, 2, 1], [37, 300, 45, 64, 1])
+    assert worst <= _tol(dtype, 3.0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("kv_len", [15, 16, 17, 31, 32, 33, 64, 65])
+def test_attention_at_page_edges(ops, dtype, kv_len):
+    # lengths that end just before, on and just after a page's edge; decode and 2-token portions
+    assert _run_attention(ops, dtype, 4, 2, 32, 16, [1, 2], [kv_len, kv_len]) <= _tol(dtype, 3.0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_attention_finds_one_far_key_among_hundreds(ops, dtype):
+    # the query of the last row points at key 3 of 700 (times 6): softmax puts nearly all mass
+    # there, so skipping, misplacing or mis-paging that one key changes the output by O(1)
+    def boost(qkv, Ks, ctx):
+        nh, hd = 4, 64
+        for h in range(nh):
+            qkv[-1, h * hd:(h + 1) * hd] = (Ks[0][3, h // 2] * 6).to(qkv.dtype)
+    assert _run_attention(ops, dtype, 4, 2, 64, 16, [1], [700], qk_boost=boost) <= _tol(dtype, 3.0)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("window", [1, 5, 16, 17])
+@pytest.mark.parametrize("offset", [0, 1])
+def test_attention_window_edge(ops, dtype, window, offset):
+    # the stand-out key sits just outside (offset 0) or just inside (offset 1) the window of the
+    # last query: taking it in or leaving it out by mistake changes the output by O(1)
+    kv_len = 50
+
+    def boost(qkv, Ks, ctx):
+        j = kv_len - 1 - window + offset
+        qkv[-1, :32] = (Ks[0][j, 0] * 6).to(qkv.dtype)
+    worst = _run_attention(ops, dtype, 1, 1, 32, 8, [3], [kv_len], window=window, qk_boost=boost)
+    assert worst <= _tol(dtype, 3.0)
+
+
+def test_attention_refuses_sizes_it_does_not_take(ops):
+    ctx = _make_ctx([1], [1])
+    for hd in (24, 272):
+        cache = _make_cache(1, 16, 1, hd, 16, torch.float32)
+        with pytest.raises(ops.KernelError, match="head_dim"):
+            ops.paged_attention(_rand(1, 3 * hd), 1, 1, hd, ctx, cache, 1.0, 0,
+                                torch.empty(1, hd, device="cuda"))
+    cache = _make_cache(1, 16, 2, 16, 16, torch.float32)
+    with pytest.raises(ops.KernelError, match="kv heads"):
+        ops.paged_attention(_rand(1, 7 * 16), 3, 2, 16, ctx, cache, 1.0, 0,
+                            torch.empty(1, 48, device="cuda"))
+
+
+# -------------------------------------------------------------------- sampling
+def _u(i):
+    from llm_singularity_b200.sampling import uniform
+    return uniform(1234, i)
+
+
+@pytest.mark.parametrize("vocab", [301, 5000])
+def test_sampling_matches_the_plain_sampler(ops, vocab):
+    g = torch.Generator().manual_seed(0)
+    R = 24
+    logits = (torch.randn(R, vocab, generator=g) * 3).cuda()
+    combos = [(0.0, 0, 1.0, 1.0), (1.0, 0, 1.0, 1.0), (0.7, 5, 1.0, 1.0), (1.3, 0, 0.8, 1.0),
+              (0.9, 40, 0.6, 1.0), (1.0, 0, 1.0, 1.7), (0.0, 0, 1.0, 50.0), (0.8, 3, 0.9, 1.3)]
+    params, topk, prev, prev_start = [], [], [], [0]
+    for r in range(R):
+        t, k, p, pen = combos[r % len(combos)]
+        params.append([t, p, pen, _u(r)])
+        topk.append(k)
+        mine = torch.randint(0, vocab, (6,), generator=g).tolist() + [int(logits[r].argmax())] * 2
+        prev += mine
+        prev_start.append(len(prev))
+    out = torch.empty(R, dtype=torch.int32, device="cuda")
+    ops.sample(logits, torch.tensor(params, device="cuda"), torch.tensor(topk, dtype=torch.int32, device="cuda"),
+               torch.tensor(prev_start, dtype=torch.int32, device="cuda"),
+               torch.tensor(prev, dtype=torch.int32, device="cuda"), out)
+    got = out.cpu().tolist()
+    host = logits.cpu()
+    for r in range(R):
+        t, k, p, pen = combos[r % len(combos)]
+        mine = prev[prev_start[r]:prev_start[r + 1]]
+        # the plain sampler in float32 arithmetic mirrors the kernel's rounding of x / T
+        row = host[r].tolist()
+        want = plain_llama.sample_plain(row, t, k, p, pen, mine, params[r][3])
+        if got[r] != want:
+            # only acceptable when u falls within rounding of a boundary of the CDF
+            lo = plain_llama.sample_plain(row, t, k, p, pen, mine, max(params[r][3] - 1e-5, 1e-9))
+            hi = plain_llama.sample_plain(row, t, k, p, pen, mine, min(params[r][3] + 1e-5, 1 - 1e-9))
+            assert got[r] in (lo, hi), f"row {r}: got {got[r]}, plain {want}"
+
+
+def test_greedy_takes_the_first_maximum(ops):
+    logits = torch.zeros(3, 70000, device="cuda")
+    logits[0, [69999, 40000, 123]] = 5.0
+    logits[1, 69999] = 1.0
+    out = torch.empty(3, dtype=torch.int32, device="cuda")
+    params = torch.tensor([[0.0, 1.0, 1.0, 0.5]] * 3, device="cuda")
+    ops.sample(logits, params, torch.zeros(3, dtype=torch.int32, device="cuda"), None, None, out)
+    assert out.cpu().tolist() == [123, 69999, 0]
+
+
+def test_sampling_follows_the_distribution(ops):
+    # 4000 draws from softmax([2, 1, 0, -1] / 1): frequencies within 3 sigma
+    R = 4000
+    logits = torch.tensor([[2.0, 1.0, 0.0, -1.0] + [-30.0] * 60], device="cuda").repeat(R, 1)
+    params = torch.tensor([[1.0, 1.0, 1.0, _u(i)] for i in range(R)], device="cuda")
+    out = torch.empty(R, dtype=torch.int32, device="cuda")
+    ops.sample(logits, params, torch.zeros(R, dtype=torch.int32, device="cuda"), None, None, out)
+    counts = np.bincount(out.cpu().numpy(), minlength=4)[:4] / R
+    p = torch.softmax(torch.tensor([2.0, 1.0, 0.0, -1.0]), 0).numpy()
+    assert np.all(np.abs(counts - p) < 3 * np.sqrt(p * (1 - p) / R) + 1e-3)

@@ -1,0 +1,148 @@
+"""The plain implementation, and the engine's host logic against it (no GPU).
+
+The second half drives the real ModelRunner / Engine (cache manager, block tables, step
+metadata, scheduler) with dense-tensor stand-ins for the kernels (tests/standin_ops.py), so
+that a fault of the cache or the batch shows here, where no GPU exists.
+"""
+import math
+
+import pytest
+import torch
+
+import cuttings
+import plain_llama
+import replay_util
+import standin_ops
+import tiny_models
+from llm_singularity_b200.engine import ModelRunner
+from llm_singularity_b200.engine.engine import Engine
+from llm_singularity_b200.parts.rotary import rotary_inv_freq
+from llm_singularity_b200.config.specs import Llama3RopeScaling
+
+
+# ------------------------------------------------------------------ plain parts
+def test_rms_norm_by_hand():
+    # tests/test_kernels.cpp:33-95: 2x4 rows against sqrt(mean) by hand
+    x = torch.tensor([[1.0, 2.0, 3.0, 4.0], [0.5, -0.5, 0.5, -0.5]], dtype=torch.float64)
+    w = torch.tensor([1.0, 2.0, 0.5, 1.0], dtype=torch.float64)
+    y = plain_llama.rms_norm(x, w, 1e-5)
+    r0 = math.sqrt((1 + 4 + 9 + 16) / 4 + 1e-5)
+    assert torch.allclose(y[0], torch.tensor([1 / r0, 4 / r0, 1.5 / r0, 4 / r0], dtype=torch.float64))
+    assert torch.allclose(y[1].abs(), torch.tensor([1, 2, .5, 1], dtype=torch.float64) * 0.5 / math.sqrt(0.25 + 1e-5))
+
+
+def test_rope_pairs_split_halves_and_position_zero_is_identity():
+    # kernels/src/rope.cu:20-21 rotates (i, i + hd/2); CLAUDE.md:87: position 0 hides a wrong pairing
+    x = torch.arange(1.0, 9.0, dtype=torch.float64).view(1, 2, 4).repeat(2, 1, 1)
+    inv = plain_llama.rope_inv_freq(4, 10000.0)
+    assert torch.allclose(inv, torch.tensor([1.0, 0.01], dtype=torch.float64))
+    y = plain_llama.apply_rope(x, [0, 1], inv)
+    assert torch.equal(y[0], x[0])
+    c, s = math.cos(1.0), math.sin(1.0)
+    assert abs(y[1, 0, 0] - (1 * c - 3 * s)) < 1e-6 and abs(y[1, 0, 2] - (1 * s + 3 * c)) < 1e-6
+    c2, s2 = math.cos(0.01), math.sin(0.01)
+    assert abs(y[1, 0, 1] - (2 * c2 - 4 * s2)) < 1e-6 and abs(y[1, 0, 3] - (2 * s2 + 4 * c2)) < 1e-6
+
+
+def test_llama3_scaling_two_restatements_agree():
+    sc = dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
+              original_max_position_embeddings=64)
+    for hd, theta in ((32, 500000.0), (64, 500000.0), (16, 10000.0)):
+        plain = plain_llama.rope_inv_freq(hd, theta, sc)
+        ours = rotary_inv_freq(hd, theta, Llama3RopeScaling(32.0, 1.0, 4.0, 64))
+        assert torch.allclose(plain, ours, rtol=1e-12, atol=0)
+        base = plain_llama.rope_inv_freq(hd, theta)
+        assert torch.equal(plain[0], base[0])                        # shortest wavelength kept
+        assert torch.allclose(plain[-1], base[-1] / 32.0)            # longest stretched by factor
+        assert ((plain <= base) & (plain >= base / 32.0 * (1 - 1e-12))).all()
+
+
+def test_attention_is_causal_grouped_and_windowed():
+    torch.manual_seed(0)
+    q, k, v = torch.randn(6, 4, 8, dtype=torch.float64), torch.randn(6, 2, 8, dtype=torch.float64), \
+        torch.randn(6, 2, 8, dtype=torch.float64)
+    full = plain_llama.causal_attention(q, k, v, 0.3)
+    assert torch.allclose(full[0, 1], v[0, 0]) and torch.allclose(full[0, 3], v[0, 1])   # one key
+    k2, v2 = k.clone(), v.clone()
+    k2[4:], v2[4:] = 9.0, 9.0
+    assert torch.allclose(plain_llama.causal_attention(q, k2, v2, 0.3)[:4], full[:4])     # no future
+    w1 = plain_llama.causal_attention(q, k, v, 0.3, window=1)
+    assert torch.allclose(w1[:, 0], v[:, 0])                                              # only itself
+
+
+def test_plain_sampler_follows_the_reference_cases():
+    # tests/test_sampling.cpp:6-47
+    logits = [1.0, 5.0, 2.0, 5.0, -1.0]
+    assert plain_llama.sample_plain(logits, temperature=0.0) == 1                  # first maximum
+    assert plain_llama.sample_plain([0.1, 0.2, 10.0, 0.3], temperature=0.001, u=0.7) == 2
+    seen = {plain_llama.sample_plain([1.0, 2.0, 3.0, 4.0], top_k=2, u=u / 20 + 0.01) for u in range(20)}
+    assert seen == {2, 3}
+    assert plain_llama.sample_plain([5.0, 1.0, 0.5], temperature=0.0, repetition_penalty=100.0,
+                                    prev_tokens=[0]) != 0
+    # top-p keeps the smallest set whose mass exceeds p
+    seen = {plain_llama.sample_plain([2.0, 1.0, 0.0, -1.0], top_p=0.6, u=u / 50 + 0.001) for u in range(50)}
+    assert seen == {0}                                                             # p0 = 0.64 > 0.6
+    seen = {plain_llama.sample_plain([2.0, 1.0, 0.0, -1.0], top_p=0.7, u=u / 50 + 0.001) for u in range(50)}
+    assert seen == {0, 1}
+
+
+def test_plain_decode_equals_plain_prefix(model_dirs):
+    cfg, w = plain_llama.load_model_dir(model_dirs["tiny_a"])
+    toks = tiny_models.random_tokens(256, 12, 3)
+    full = plain_llama.forward_logits(cfg, w, toks)
+    assert torch.allclose(plain_llama.forward_logits(cfg, w, toks[:7]), full[:7], atol=1e-12)
+
+
+# ------------------------------------------------- host logic with stand-in kernels
+def _requests(name, lengths, seed=0):
+    vocab = tiny_models.CONFIGS[name]["vocab_size"]
+    return {f"r{i}": tiny_models.random_tokens(vocab, n, seed + i) for i, n in enumerate(lengths)}
+
+
+@pytest.fixture(scope="module")
+def plain_refs(model_dirs):
+    out = {}
+    for name, lengths in (("tiny_a", (5, 17, 33, 70)), ("tiny_b", (1, 9, 40, 70, 50, 23))):
+        cfg, w = plain_llama.load_model_dir(model_dirs[name])
+        seqs = _requests(name, lengths)
+        out[name] = (seqs, {rid: plain_llama.forward_logits(cfg, w, t) for rid, t in seqs.items()})
+    return out
+
+
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+@pytest.mark.parametrize("cut", ["whole", "tail_decode", "portions", "mixed"])
+def test_host_logic_matches_plain_under_every_cutting(model_dirs, plain_refs, tmp_path, name, cut):
+    seqs, refs = plain_refs[name]
+    steps, max_tokens = getattr(cuttings, cut)(seqs)
+    ps = tiny_models.PAGE_SIZE[name]
+    runner = ModelRunner(model_dirs[name], dtype="float32", device="cpu", page_size=ps,
+                         num_pages=max_tokens // ps, max_requests=4, max_model_len=max_tokens,
+                         ops=standin_ops)
+    replay_util.replay_in_process(runner, steps, str(tmp_path))
+    rows = replay_util.collect(steps, str(tmp_path), tiny_models.CONFIGS[name]["vocab_size"])
+    replay_util.compare(rows, refs, 2e-5, f"{name}/{cut}")
+    runner.cache.check_invariants()
+    assert runner.cache.free_pages() == max_tokens // ps          # everything was given back
+
+
+def test_mixed_cutting_really_reuses_pages_and_mixes(plain_refs):
+    seqs, _ = plain_refs["tiny_b"]
+    steps, max_tokens = cuttings.mixed(seqs)
+    assert max_tokens < sum(-(-len(t) // 64) * 64 for t in seqs.values())      # pool < total
+    assert any(len(s["entries"]) >= 3 for s in steps)
+    assert any(len({len(e["tokens"]) for e in s["entries"]}) > 1 and
+               min(len(e["tokens"]) for e in s["entries"]) == 1 for s in steps)
+
+
+def test_engine_greedy_matches_plain_even_with_few_pages_and_preemption(model_dirs):
+    cfg, w = plain_llama.load_model_dir(model_dirs["tiny_a"])
+    prompts = [tiny_models.random_tokens(256, n, 40 + n) for n in (5, 17, 33)]
+    ref = [plain_llama.greedy_generate(cfg, w, p, 8) for p in prompts]
+    for pages, chunk in ((64, None), (5, 7)):
+        eng = Engine(model_dirs["tiny_a"], dtype="float32", device="cpu", kv_block_size=16,
+                     num_kv_blocks=pages, max_batch_size=4, max_tokens_per_batch=24,
+                     prefill_chunk=chunk, ops=standin_ops, prefix_cache=False)
+        assert eng.generate(prompts, max_new_tokens=8, ignore_eos=True) == ref
+        eng.runner.cache.check_invariants()
+        if pages == 5:
+            assert eng.stats()["preemptions"] > 0
