@@ -69,8 +69,18 @@ def check_status() -> None:
             raise KernelError(f"{n}: {_STATUS_TEXT.get(code.value, f'status {code.value}')}")
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many kernel launches this process has made through this module."""
+    return _launches
+
+
 def _call(libname: str, fn: str, *args) -> None:
+    global _launches
     lib = _lib(libname)
+    _launches += 1
     rc = getattr(lib, fn)(*args)
     if rc != 0:
         raise KernelError(f"{fn} failed: {lib.lsb_error_string(rc).decode()} (code {rc})")
