@@ -75,7 +75,7 @@ class ModelRunner:
         self.model = _build_model(self.spec, self.rt, arch)
         if ops is None:
             # compile (first call) and load what this model needs; raises if it cannot
-            self.rt.ops.prepare(self.model.required_kernels() + ["sampling", "cache_table"],
+            self.rt.ops.prepare(self.model.required_kernels() + ["cache_table"],
                                 verbose=verbose)
 
         expected = self.model.expected_tensors()

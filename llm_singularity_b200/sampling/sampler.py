@@ -20,6 +20,9 @@ from .rng import uniform
 class Sampler:
     def __init__(self, rt):
         self.rt = rt
+        prepare = getattr(rt.ops, "prepare", None)
+        if prepare is not None:
+            prepare(["sampling"])
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams],
                draw_index: Sequence[int],
