@@ -1,0 +1,522 @@
+// Tensor-core attention over the paged cache for bfloat16: a split-KV kernel for single
+// decode tokens and a tiled causal kernel for prompt portions, head sizes 64 and 128.
+//
+// Both walk a request's keys in tiles of 64 through its block table, stage K and V tiles in
+// shared memory with 16-byte asynchronous copies (two stages, XOR-swizzled so that ldmatrix
+// reads are free of bank conflicts), form scores with mma.sync m16n8k16 (bf16 in, 32-bit
+// accumulate), keep the running maximum / sum / output of the online softmax in 32-bit
+// registers, round the probabilities to bfloat16 only as the left operand of the P.V product,
+// and divide by the sum at the end.
+//
+//  * decode: one thread block per (split, kv head, request).  The nh/nkv query heads that share
+//    the kv head are the rows of one 16-row MMA tile, so every key and value is read once for
+//    the whole group; the four warps take 16 keys each of every tile and merge through shared
+//    memory; with more than one split, partial (max, sum, output) go to scratch and a small
+//    merge kernel finishes.  The split count depends only on the batch, and each split finds
+//    its share of tiles from the request's length on the device, so a captured launch stays
+//    valid as sequences grow.
+//  * prefill: one thread block per (64-query tile, head, request); warp w owns rows 16w..16w+15.
+//    Query row i of a request with q_len new tokens and kv_len cached tokens sits at position
+//    p = kv_len - q_len + i and sees keys [max(0, p - window + 1), p].
+//
+// These replace the reference's paged_attention_kernel (kernels/src/attention.cu:27-172), which
+// serves both cases with 32 threads per (head, row) and scalar fp32 loops.  The generic kernel in
+// attention.cu remains the 32-bit path and the fallback for other head sizes.
+#include "common.cuh"
+
+#include <float.h>
+
+LSB_DEFINE_STATUS()
+
+typedef __nv_bfloat16 bf16;
+
+constexpr int kTile = 64;        // keys per tile
+constexpr int kThreads = 128;
+constexpr int kStages = 2;
+constexpr float kLog2e = 1.4426950408889634f;
+
+// ------------------------------------------------------------------ PTX helpers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return (uint32_t)__cvta_generic_to_shared(p);
+}
+__device__ __forceinline__ void cp_async16(void* dst, const void* src, bool valid) {
+    const int n = valid ? 16 : 0;       // 0 source bytes: the 16 destination bytes are zero-filled
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(dst)), "l"(src), "r"(n));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;\n" ::"n"(N));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], const void* p) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(smem_u32(p)));
+}
+// D(16x8, f32) += A(16x16, bf16) * B(16x8, bf16)
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// A tile is rows of HD bf16 = HD/8 chunks of 16 bytes; chunk c of row r lives at chunk c ^ (r & 7).
+template <int HD> __device__ __forceinline__ bf16* tile_ptr(bf16* base, int row, int chunk) {
+    return base + (row * (HD / 8) + (chunk ^ (row & 7))) * 8;
+}
+
+// Stage one 64-key tile of K and V of kv head g into shared memory (zero rows outside [lo, hi]).
+template <int HD>
+__device__ __forceinline__ void load_kv_tile(bf16* sK, bf16* sV, const bf16* __restrict__ k_pages,
+                                             const bf16* __restrict__ v_pages, const int* __restrict__ bt,
+                                             int tile, int lo, int hi, int g, int nkv, int page_size,
+                                             int num_pages) {
+    constexpr int CPR = HD / 8;
+    for (int idx = threadIdx.x; idx < kTile * CPR; idx += kThreads) {
+        const int kk = idx / CPR, c = idx - kk * CPR;
+        const int key = tile * kTile + kk;
+        bool valid = key >= lo && key <= hi;
+        long long off = 0;
+        if (valid) {
+            const int page = bt[key / page_size];
+            if (page < 0 || page >= num_pages) {
+                lsb_set_status(LSB_BAD_PAGE);
+                valid = false;
+            } else {
+                off = (((long long)page * nkv + g) * page_size + (key % page_size)) * HD + c * 8;
+            }
+        }
+        cp_async16(tile_ptr<HD>(sK, kk, c), k_pages + off, valid);
+        cp_async16(tile_ptr<HD>(sV, kk, c), v_pages + off, valid);
+    }
+}
+
+// ------------------------------------------------------------------ decode
+template <int HD>
+__global__ void __launch_bounds__(kThreads)
+decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
+                        const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
+                        const int* __restrict__ q_start, const int* __restrict__ kv_len_arr,
+                        const int* __restrict__ table_rows, const int* __restrict__ block_table,
+                        int table_stride, bf16* __restrict__ out, float* __restrict__ part_o,
+                        float* __restrict__ part_ml, int nh, int nkv, int page_size, int num_pages,
+                        float scale, int window, int splits) {
+    constexpr int CPR = HD / 8, KS = HD / 16;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    bf16* sQ = reinterpret_cast<bf16*>(smem_raw);            // [16][HD]
+    bf16* sK = sQ + 16 * HD;                                 // [stages][64][HD]
+    bf16* sV = sK + kStages * kTile * HD;
+
+    const int split = blockIdx.x, g = blockIdx.y, r = blockIdx.z;
+    const int qs = q_start[r];
+    if (q_start[r + 1] - qs != 1) return;                    // prompt portions go to the other kernel
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int G = nh / nkv;
+    const int kv_len = kv_len_arr[r];
+    const int p = kv_len - 1;
+    const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    const int* bt = block_table + (size_t)table_rows[r] * table_stride;
+
+    const int first_tile = lo / kTile;
+    const int n_tiles = p / kTile + 1 - first_tile;
+    const int per = (n_tiles + splits - 1) / splits;
+    const int t0 = first_tile + split * per;
+    const int t1 = min(t0 + per, first_tile + n_tiles);
+
+    // queries of the group: rows 0..G-1 of a 16-row tile, the rest zero
+    for (int idx = threadIdx.x; idx < 16 * CPR; idx += kThreads) {
+        const int row = idx / CPR, c = idx - row * CPR;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row < G)
+            v = *reinterpret_cast<const uint4*>(qkv + (size_t)qs * qkv_stride + (size_t)(g * G + row) * HD + c * 8);
+        *reinterpret_cast<uint4*>(tile_ptr<HD>(sQ, row, c)) = v;
+    }
+    if (t0 < t1) load_kv_tile<HD>(sK, sV, k_pages, v_pages, bt, t0, lo, p, g, nkv, page_size, num_pages);
+    cp_async_commit();
+    __syncthreads();
+
+    uint32_t qf[KS][4];
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks)
+        ldmatrix_x4(qf[ks], tile_ptr<HD>(sQ, ((lane >> 3) & 1) * 8 + (lane & 7), 2 * ks + (lane >> 4)));
+
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    const float sc = scale * kLog2e;
+
+    for (int t = t0; t < t1; ++t) {
+        const int stage = (t - t0) & 1;
+        if (t + 1 < t1)
+            load_kv_tile<HD>(sK + (stage ^ 1) * kTile * HD, sV + (stage ^ 1) * kTile * HD, k_pages, v_pages,
+                             bt, t + 1, lo, p, g, nkv, page_size, num_pages);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        bf16* tK = sK + stage * kTile * HD;
+        bf16* tV = sV + stage * kTile * HD;
+
+        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks) {
+            uint32_t b[4];
+            ldmatrix_x4(b, tile_ptr<HD>(tK, warp * 16 + (lane >> 4) * 8 + (lane & 7), 2 * ks + ((lane >> 3) & 1)));
+            mma_bf16(s[0], qf[ks], b[0], b[1]);
+            mma_bf16(s[1], qf[ks], b[2], b[3]);
+        }
+        // mask keys outside [lo, p]; scale into the log2 domain
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const int key = t * kTile + warp * 16 + nt * 8 + 2 * (lane & 3) + (e & 1);
+                const float v = (key >= lo && key <= p) ? s[nt][e] * sc : -INFINITY;
+                s[nt][e] = v;
+                mx[e >> 1] = fmaxf(mx[e >> 1], v);
+            }
+        float corr[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+            const float m_new = fmaxf(m[h], mx[h]);
+            corr[h] = (m[h] == -INFINITY) ? 0.f : exp2f(m[h] - m_new);
+            m[h] = m_new;
+            l[h] *= corr[h];
+        }
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float pv = (s[nt][e] == -INFINITY) ? 0.f : exp2f(s[nt][e] - m[e >> 1]);
+                s[nt][e] = pv;
+                l[e >> 1] += pv;
+            }
+#pragma unroll
+        for (int i = 0; i < HD / 8; ++i) {
+            o[i][0] *= corr[0]; o[i][1] *= corr[0];
+            o[i][2] *= corr[1]; o[i][3] *= corr[1];
+        }
+        uint32_t pa[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]),
+                          pack_bf16(s[1][0], s[1][1]), pack_bf16(s[1][2], s[1][3])};
+#pragma unroll
+        for (int dt = 0; dt < HD / 16; ++dt) {
+            uint32_t b[4];
+            ldmatrix_x4_trans(b, tile_ptr<HD>(tV, warp * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), 2 * dt + (lane >> 4)));
+            mma_bf16(o[2 * dt], pa, b[0], b[1]);
+            mma_bf16(o[2 * dt + 1], pa, b[2], b[3]);
+        }
+        __syncthreads();                                       // the stage is overwritten next round
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+    }
+
+    // merge the four warps (each saw different keys) through shared memory
+    float* sO = reinterpret_cast<float*>(sK);                  // [4][16][HD]
+    float* sM = sO + 4 * 16 * HD;                              // [4][16]
+    float* sL = sM + 4 * 16;
+    __syncthreads();
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) {
+        const int d = i * 8 + 2 * (lane & 3);
+        float* dst = sO + ((warp * 16 + (lane >> 2)) * HD + d);
+        dst[0] = o[i][0]; dst[1] = o[i][1];
+        dst[8 * HD] = o[i][2]; dst[8 * HD + 1] = o[i][3];
+    }
+    if ((lane & 3) == 0) {
+        sM[warp * 16 + (lane >> 2)] = m[0]; sM[warp * 16 + (lane >> 2) + 8] = m[1];
+        sL[warp * 16 + (lane >> 2)] = l[0]; sL[warp * 16 + (lane >> 2) + 8] = l[1];
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * HD; idx += kThreads) {
+        const int h = idx / HD, d = idx - h * HD;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) M = fmaxf(M, sM[w * 16 + h]);
+        float L = 0.f, O = 0.f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = sM[w * 16 + h];
+            const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+            L += sL[w * 16 + h] * f;
+            O += sO[(w * 16 + h) * HD + d] * f;
+        }
+        const int head = g * G + h;
+        if (splits == 1) {
+            out[(size_t)qs * nh * HD + (size_t)head * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        } else {
+            const size_t slot = ((size_t)r * nh + head) * splits + split;
+            part_o[slot * HD + d] = O;
+            if (d == 0) { part_ml[slot * 2] = M; part_ml[slot * 2 + 1] = L; }
+        }
+    }
+}
+
+// out[t, head, :] = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M)
+template <int HD>
+__global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                    const int* __restrict__ q_start, bf16* __restrict__ out, int nh,
+                                    int splits) {
+    const int head = blockIdx.x, r = blockIdx.y;
+    const int qs = q_start[r];
+    if (q_start[r + 1] - qs != 1) return;
+    const size_t base = ((size_t)r * nh + head) * splits;
+    float M = -INFINITY;
+    for (int s = 0; s < splits; ++s) M = fmaxf(M, part_ml[(base + s) * 2]);
+    for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+        float L = 0.f, O = 0.f;
+        for (int s = 0; s < splits; ++s) {
+            const float ms = part_ml[(base + s) * 2];
+            const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
+            L += part_ml[(base + s) * 2 + 1] * f;
+            O += part_o[(base + s) * HD + d] * f;
+        }
+        out[(size_t)qs * nh * HD + (size_t)head * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+    }
+}
+
+// ------------------------------------------------------------------ prefill
+template <int HD>
+__global__ void __launch_bounds__(kThreads)
+prefill_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
+                         const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
+                         const int* __restrict__ q_start, const int* __restrict__ kv_len_arr,
+                         const int* __restrict__ table_rows, const int* __restrict__ block_table,
+                         int table_stride, bf16* __restrict__ out, int nh, int nkv, int page_size,
+                         int num_pages, float scale, int window, int skip_single) {
+    constexpr int CPR = HD / 8, KS = HD / 16;
+    extern __shared__ __align__(128) unsigned char smem_raw[];
+    bf16* sQ = reinterpret_cast<bf16*>(smem_raw);            // [64][HD]
+    bf16* sK = sQ + kTile * HD;
+    bf16* sV = sK + kStages * kTile * HD;
+
+    const int r = blockIdx.z, h = blockIdx.y;
+    const int qs = q_start[r];
+    const int q_len = q_start[r + 1] - qs;
+    const int i0 = blockIdx.x * kTile;
+    if (i0 >= q_len || (skip_single && q_len == 1)) return;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = h / (nh / nkv);
+    const int kv_len = kv_len_arr[r];
+    const int p0 = kv_len - q_len + i0;                       // position of the tile's first row
+    const int rows = min(kTile, q_len - i0);
+    const int p_last = p0 + rows - 1;
+    const int lo_cta = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
+    const int* bt = block_table + (size_t)table_rows[r] * table_stride;
+    const int t0 = lo_cta / kTile, t1 = p_last / kTile + 1;
+
+    for (int idx = threadIdx.x; idx < kTile * CPR; idx += kThreads) {
+        const int row = idx / CPR, c = idx - row * CPR;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (row < rows)
+            v = *reinterpret_cast<const uint4*>(qkv + (size_t)(qs + i0 + row) * qkv_stride + (size_t)h * HD + c * 8);
+        *reinterpret_cast<uint4*>(tile_ptr<HD>(sQ, row, c)) = v;
+    }
+    load_kv_tile<HD>(sK, sV, k_pages, v_pages, bt, t0, lo_cta, p_last, g, nkv, page_size, num_pages);
+    cp_async_commit();
+    __syncthreads();
+
+    uint32_t qf[KS][4];
+#pragma unroll
+    for (int ks = 0; ks < KS; ++ks)
+        ldmatrix_x4(qf[ks], tile_ptr<HD>(sQ, warp * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), 2 * ks + (lane >> 4)));
+
+    float o[HD / 8][4];
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    const float sc = scale * kLog2e;
+    // this thread's two rows and their positions
+    const int row_a = warp * 16 + (lane >> 2), row_b = row_a + 8;
+    const int pos[2] = {p0 + row_a, p0 + row_b};
+    const bool live[2] = {row_a < rows, row_b < rows};
+    const int warp_hi = p0 + min(warp * 16 + 15, rows - 1);    // last position any row of the warp sees
+    const int warp_lo = (window > 0) ? max(0, p0 + warp * 16 - window + 1) : 0;
+
+    for (int t = t0; t < t1; ++t) {
+        const int stage = (t - t0) & 1;
+        if (t + 1 < t1)
+            load_kv_tile<HD>(sK + (stage ^ 1) * kTile * HD, sV + (stage ^ 1) * kTile * HD, k_pages, v_pages,
+                             bt, t + 1, lo_cta, p_last, g, nkv, page_size, num_pages);
+        cp_async_commit();
+        cp_async_wait<1>();
+        __syncthreads();
+        bf16* tK = sK + stage * kTile * HD;
+        bf16* tV = sV + stage * kTile * HD;
+        const int key0 = t * kTile;
+        // a warp whose rows see none of this tile's keys only keeps the barriers
+        if (warp * 16 < rows && key0 <= warp_hi && key0 + kTile - 1 >= warp_lo) {
+            float s[8][4];
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+            for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+                for (int np = 0; np < 4; ++np) {
+                    uint32_t b[4];
+                    ldmatrix_x4(b, tile_ptr<HD>(tK, np * 16 + (lane >> 4) * 8 + (lane & 7), 2 * ks + ((lane >> 3) & 1)));
+                    mma_bf16(s[2 * np], qf[ks], b[0], b[1]);
+                    mma_bf16(s[2 * np + 1], qf[ks], b[2], b[3]);
+                }
+            float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = key0 + nt * 8 + 2 * (lane & 3) + (e & 1);
+                    const int hh = e >> 1;
+                    const bool ok = live[hh] && key <= pos[hh] && (window <= 0 || key > pos[hh] - window);
+                    const float v = ok ? s[nt][e] * sc : -INFINITY;
+                    s[nt][e] = v;
+                    mx[hh] = fmaxf(mx[hh], v);
+                }
+            float corr[2];
+#pragma unroll
+            for (int hh = 0; hh < 2; ++hh) {
+                mx[hh] = fmaxf(mx[hh], __shfl_xor_sync(0xffffffffu, mx[hh], 1));
+                mx[hh] = fmaxf(mx[hh], __shfl_xor_sync(0xffffffffu, mx[hh], 2));
+                const float m_new = fmaxf(m[hh], mx[hh]);
+                corr[hh] = (m[hh] == -INFINITY) ? 0.f : exp2f(m[hh] - m_new);
+                m[hh] = m_new;
+                l[hh] *= corr[hh];
+            }
+#pragma unroll
+            for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float pv = (s[nt][e] == -INFINITY) ? 0.f : exp2f(s[nt][e] - m[e >> 1]);
+                    s[nt][e] = pv;
+                    l[e >> 1] += pv;
+                }
+#pragma unroll
+            for (int i = 0; i < HD / 8; ++i) {
+                o[i][0] *= corr[0]; o[i][1] *= corr[0];
+                o[i][2] *= corr[1]; o[i][3] *= corr[1];
+            }
+#pragma unroll
+            for (int kt = 0; kt < 4; ++kt) {
+                uint32_t pa[4] = {pack_bf16(s[2 * kt][0], s[2 * kt][1]), pack_bf16(s[2 * kt][2], s[2 * kt][3]),
+                                  pack_bf16(s[2 * kt + 1][0], s[2 * kt + 1][1]),
+                                  pack_bf16(s[2 * kt + 1][2], s[2 * kt + 1][3])};
+#pragma unroll
+                for (int dt = 0; dt < HD / 16; ++dt) {
+                    uint32_t b[4];
+                    ldmatrix_x4_trans(b, tile_ptr<HD>(tV, kt * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), 2 * dt + (lane >> 4)));
+                    mma_bf16(o[2 * dt], pa, b[0], b[1]);
+                    mma_bf16(o[2 * dt + 1], pa, b[2], b[3]);
+                }
+            }
+        }
+        __syncthreads();
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int hh = 0; hh < 2; ++hh) {
+        l[hh] += __shfl_xor_sync(0xffffffffu, l[hh], 1);
+        l[hh] += __shfl_xor_sync(0xffffffffu, l[hh], 2);
+    }
+    const float inv[2] = {l[0] > 0.f ? 1.f / l[0] : 0.f, l[1] > 0.f ? 1.f / l[1] : 0.f};
+#pragma unroll
+    for (int i = 0; i < HD / 8; ++i) {
+        const int d = i * 8 + 2 * (lane & 3);
+        if (live[0]) {
+            bf16* dst = out + (size_t)(qs + i0 + row_a) * nh * HD + (size_t)h * HD + d;
+            *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(o[i][0] * inv[0], o[i][1] * inv[0]);
+        }
+        if (live[1]) {
+            bf16* dst = out + (size_t)(qs + i0 + row_b) * nh * HD + (size_t)h * HD + d;
+            *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(o[i][2] * inv[1], o[i][3] * inv[1]);
+        }
+    }
+}
+
+// ------------------------------------------------------------------ host side
+template <int HD> constexpr size_t decode_smem() { return (16 * HD + 2 * kStages * kTile * HD) * sizeof(bf16); }
+template <int HD> constexpr size_t prefill_smem() { return (kTile * HD + 2 * kStages * kTile * HD) * sizeof(bf16); }
+
+template <int HD> static int configure_once() {
+    static int done = -1;
+    if (done >= 0) return done;
+    cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<HD>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem<HD>());
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(prefill_attention_kernel<HD>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_smem<HD>());
+    done = (int)e;
+    return done;
+}
+
+// floats of scratch the decode kernel needs for `splits` > 1: outputs, then (max, sum) pairs
+LSB_API long long lsb_decode_scratch_floats(int n_requests, int nh, int hd, int splits) {
+    return splits <= 1 ? 0 : (long long)n_requests * nh * splits * (hd + 2);
+}
+
+// Single decode tokens (requests with q_len == 1; others are skipped).  bf16, hd 64 or 128,
+// nh / nkv <= 16.  `scratch` holds lsb_decode_scratch_floats floats when splits > 1.
+LSB_API int lsb_decode_attention(const void* qkv, int qkv_stride, const void* k_pages, const void* v_pages,
+                                 const int* q_start, const int* kv_len, const int* table_rows,
+                                 const int* block_table, int table_stride, void* out, float* scratch,
+                                 int n_requests, int nh, int nkv, int hd, int page_size, int num_pages,
+                                 float scale, int window, int splits, cudaStream_t stream) {
+    if (n_requests <= 0) return 0;
+    if (nkv <= 0 || nh % nkv || nh / nkv > 16 || splits < 1 || n_requests > 65535 || nkv > 65535)
+        return (int)cudaErrorInvalidValue;
+    if (splits > 1 && !scratch) return (int)cudaErrorInvalidValue;
+    float* part_o = scratch;
+    float* part_ml = scratch ? scratch + (size_t)n_requests * nh * splits * hd : nullptr;
+    dim3 grid(splits, nkv, n_requests);
+#define LAUNCH_DECODE(HD)                                                                          \
+    do {                                                                                           \
+        int rc = configure_once<HD>();                                                             \
+        if (rc) return rc;                                                                         \
+        decode_attention_kernel<HD><<<grid, kThreads, decode_smem<HD>(), stream>>>(                \
+            (const bf16*)qkv, qkv_stride, (const bf16*)k_pages, (const bf16*)v_pages, q_start,    \
+            kv_len, table_rows, block_table, table_stride, (bf16*)out, part_o, part_ml, nh, nkv,  \
+            page_size, num_pages, scale, window, splits);                                          \
+        if (splits > 1)                                                                            \
+            decode_merge_kernel<HD><<<dim3(nh, n_requests), 64, 0, stream>>>(                      \
+                part_o, part_ml, q_start, (bf16*)out, nh, splits);                                 \
+    } while (0)
+    if (hd == 64) LAUNCH_DECODE(64);
+    else if (hd == 128) LAUNCH_DECODE(128);
+    else return (int)cudaErrorInvalidValue;
+#undef LAUNCH_DECODE
+    return LSB_LAUNCH_CHECK();
+}
+
+// Prompt portions (and, unless skip_single, single tokens too).  bf16, hd 64 or 128.
+LSB_API int lsb_prefill_attention(const void* qkv, int qkv_stride, const void* k_pages, const void* v_pages,
+                                  const int* q_start, const int* kv_len, const int* table_rows,
+                                  const int* block_table, int table_stride, void* out, int n_requests,
+                                  int max_q_len, int nh, int nkv, int hd, int page_size, int num_pages,
+                                  float scale, int window, int skip_single, cudaStream_t stream) {
+    if (n_requests <= 0 || max_q_len <= 0) return 0;
+    if (nkv <= 0 || nh % nkv || n_requests > 65535 || nh > 65535) return (int)cudaErrorInvalidValue;
+    dim3 grid((max_q_len + kTile - 1) / kTile, nh, n_requests);
+#define LAUNCH_PREFILL(HD)                                                                         \
+    do {                                                                                           \
+        int rc = configure_once<HD>();                                                             \
+        if (rc) return rc;                                                                         \
+        prefill_attention_kernel<HD><<<grid, kThreads, prefill_smem<HD>(), stream>>>(              \
+            (const bf16*)qkv, qkv_stride, (const bf16*)k_pages, (const bf16*)v_pages, q_start,    \
+            kv_len, table_rows, block_table, table_stride, (bf16*)out, nh, nkv, page_size,        \
+            num_pages, scale, window, skip_single);                                                \
+    } while (0)
+    if (hd == 64) LAUNCH_PREFILL(64);
+    else if (hd == 128) LAUNCH_PREFILL(128);
+    else return (int)cudaErrorInvalidValue;
+#undef LAUNCH_PREFILL
+    return LSB_LAUNCH_CHECK();
+}

@@ -246,9 +246,29 @@ def rope_kv_store(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache,
           _i(1 if store else 0), _stream(qkv))
 
 
+NUM_SMS = 148                   # B200: 2 dies x 74
+_TC_HEAD_DIMS = (64, 128)
+_scratch: Dict[tuple, torch.Tensor] = {}
+
+
+def decode_splits(n_decode: int, nkv: int) -> int:
+    """How many ways each request's keys are split among thread blocks in the decode kernel:
+    enough blocks to fill the GPU twice; a function of the batch alone, so that a captured
+    launch stays valid as sequences grow."""
+    return max(1, min(32, (2 * NUM_SMS) // max(1, n_decode * nkv)))
+
+
+def tensor_core_attention_ok(dtype, hd: int, nh: int, nkv: int) -> bool:
+    return dtype == torch.bfloat16 and hd in _TC_HEAD_DIMS and nh // nkv <= 16
+
+
 def paged_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache, scale: float,
                     window: int, out: torch.Tensor) -> None:
-    """Causal attention of this step's query rows over their requests' cached keys and values."""
+    """Causal attention of this step's query rows over their requests' cached keys and values.
+
+    bfloat16 with head size 64 or 128 runs on the tensor cores: single decode tokens in the
+    split-KV kernel, prompt portions in the tiled kernel.  Everything else (32-bit, other head
+    sizes) runs the generic kernel."""
     _req(qkv, "qkv", dim=2)
     _req(out, "out", qkv.dtype, 2)
     T = qkv.shape[0]
@@ -262,11 +282,34 @@ def paged_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache, s
     if ctx.n_requests > 65535 or nh > 65535:
         raise KernelError("attention: at most 65535 requests and heads per step")
     _check_cache(cache, nkv, hd, qkv.dtype)
-    _call("attention", "lsb_paged_attention_generic", _p(qkv), _i(qkv.shape[1]), _p(cache.k_pages),
-          _p(cache.v_pages), _p(ctx.q_start), _p(ctx.kv_len), _p(ctx.table_rows),
-          _p(cache.block_table), _i(cache.block_table.shape[1]), _p(out), _i(_dt(qkv)),
-          _i(ctx.n_requests), _i(ctx.max_q_len), _i(nh), _i(nkv), _i(hd), _i(cache.page_size),
-          _i(cache.k_pages.shape[0]), _f(scale), _i(window), _stream(out))
+    common = (_p(qkv), _i(qkv.shape[1]), _p(cache.k_pages), _p(cache.v_pages), _p(ctx.q_start),
+              _p(ctx.kv_len), _p(ctx.table_rows), _p(cache.block_table),
+              _i(cache.block_table.shape[1]), _p(out))
+    tail = (_i(nh), _i(nkv), _i(hd), _i(cache.page_size), _i(cache.k_pages.shape[0]), _f(scale),
+            _i(window))
+    if not tensor_core_attention_ok(qkv.dtype, hd, nh, nkv):
+        _call("attention", "lsb_paged_attention_generic", *common, _i(_dt(qkv)),
+              _i(ctx.n_requests), _i(ctx.max_q_len), *tail, _stream(out))
+        return
+    R = ctx.n_requests
+    n_decode = int((ctx.h_q_len == 1).sum())
+    if n_decode:
+        splits = decode_splits(n_decode, nkv)
+        if not getattr(ctx, "fixed_launch", False):
+            splits = min(splits, -(-ctx.max_kv_len // 64))
+        scratch = None
+        if splits > 1:
+            key = (qkv.device, R, nh, hd, splits)
+            scratch = _scratch.get(key)
+            if scratch is None:
+                scratch = torch.empty(R * nh * splits * (hd + 2), dtype=torch.float32,
+                                      device=qkv.device)
+                _scratch[key] = scratch
+        _call("attention_tc", "lsb_decode_attention", *common, _p(scratch), _i(R), *tail,
+              _i(splits), _stream(out))
+    if n_decode < R:
+        _call("attention_tc", "lsb_prefill_attention", *common, _i(R), _i(ctx.max_q_len), *tail,
+              _i(1 if n_decode else 0), _stream(out))
 
 
 def sample(logits: torch.Tensor, params: torch.Tensor, top_k: torch.Tensor,

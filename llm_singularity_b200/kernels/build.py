@@ -34,6 +34,7 @@ SOURCES: Dict[str, str] = {
     "cache_table": "cache_table.cu",
     "rope_cache": "rope_cache.cu",
     "attention": "attention.cu",
+    "attention_tc": "attention_tc.cu",
     "gemm": "gemm.cu",
     "sampling": "sampling.cu",
 }

@@ -22,7 +22,7 @@ def _tol(dtype, scale=1.0):
 def ops():
     from llm_singularity_b200 import kernels
     kernels.prepare(["embedding", "norm", "activation", "cache_table", "rope_cache", "attention",
-                     "gemm", "sampling"])
+                     "attention_tc", "gemm", "sampling"])
     yield kernels
     kernels.check_status()
 
@@ -282,18 +282,31 @@ def _run_attention(ops, dtype, nh, nkv, hd, page, q_lens, kv_lens, window=0, see
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("nh, nkv, hd, page", [(6, 3, 48, 16), (8, 1, 16, 8), (5, 5, 128, 4),
-                                               (4, 2, 256, 32), (3, 1, 80, 16)])
+                                               (4, 2, 256, 32), (3, 1, 80, 16), (8, 2, 64, 16),
+                                               (16, 1, 64, 8), (6, 2, 128, 32), (34, 2, 64, 16)])
 def test_attention_mixed_batch(ops, dtype, nh, nkv, hd, page):
     # a whole prompt, a decode token on a long context, a portion in the middle, two tokens
+    # (bfloat16 with head size 64/128 takes the tensor-core kernels, unless a group has > 16 heads)
     worst = _run_attention(ops, dtype, nh, nkv, hd, page, [37, 1, 12, 2, 1], [37, 300, 45, 64, 1])
     assert worst <= _tol(dtype, 3.0)
 
 
+@pytest.mark.parametrize("hd", [64, 128])
+@pytest.mark.parametrize("q_lens, kv_lens", [([1], [5000]), ([1, 1, 1], [1, 64, 65]), ([200], [200]),
+                                             ([130, 1], [700, 129]), ([64, 65, 63], [64, 65, 1000])])
+def test_tensor_core_attention_shapes(ops, hd, q_lens, kv_lens):
+    # decode with many splits, lengths on tile edges (64), prompts over several 64-row tiles,
+    # a portion deep inside a long context
+    worst = _run_attention(ops, torch.bfloat16, 8, 2, hd, 16, q_lens, kv_lens, seed=3)
+    assert worst <= _tol(torch.bfloat16, 3.0)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("kv_len", [15, 16, 17, 31, 32, 33, 64, 65])
-def test_attention_at_page_edges(ops, dtype, kv_len):
+@pytest.mark.parametrize("hd", [32, 64])
+def test_attention_at_page_edges(ops, dtype, kv_len, hd):
     # lengths that end just before, on and just after a page's edge; decode and 2-token portions
-    assert _run_attention(ops, dtype, 4, 2, 32, 16, [1, 2], [kv_len, kv_len]) <= _tol(dtype, 3.0)
+    assert _run_attention(ops, dtype, 4, 2, hd, 16, [1, 2], [kv_len, kv_len]) <= _tol(dtype, 3.0)
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -308,17 +321,18 @@ def test_attention_finds_one_far_key_among_hundreds(ops, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("window", [1, 5, 16, 17])
+@pytest.mark.parametrize("window", [1, 5, 16, 17, 70])
 @pytest.mark.parametrize("offset", [0, 1])
-def test_attention_window_edge(ops, dtype, window, offset):
+@pytest.mark.parametrize("hd, q_len", [(32, 3), (64, 3), (64, 1)])
+def test_attention_window_edge(ops, dtype, window, offset, hd, q_len):
     # the stand-out key sits just outside (offset 0) or just inside (offset 1) the window of the
     # last query: taking it in or leaving it out by mistake changes the output by O(1)
-    kv_len = 50
+    kv_len = 150
 
     def boost(qkv, Ks, ctx):
         j = kv_len - 1 - window + offset
-        qkv[-1, :32] = (Ks[0][j, 0] * 6).to(qkv.dtype)
-    worst = _run_attention(ops, dtype, 1, 1, 32, 8, [3], [kv_len], window=window, qk_boost=boost)
+        qkv[-1, :hd] = (Ks[0][j, 0] * 6).to(qkv.dtype)
+    worst = _run_attention(ops, dtype, 1, 1, hd, 8, [q_len], [kv_len], window=window, qk_boost=boost)
     assert worst <= _tol(dtype, 3.0)
 
 

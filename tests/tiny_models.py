@@ -3,7 +3,8 @@
 tiny_a / tiny_b are the two small configurations the engine is specified on
 (tied vs untied head, no rope scaling vs llama3 scaling, eps 1e-5 vs 1e-6, two vs
 one kv head, page 16 vs 8); tiny_c has sizes that are no power of two anywhere
-(hidden 72, six heads of 48 in three groups, 100 wide feed-forward, 301 tokens).
+(hidden 72, six heads of 48 in three groups, 100 wide feed-forward, 301 tokens); tiny_d has
+heads of 64, the size the bfloat16 tensor-core attention kernels take.
 Weights are random; query and key projections are scaled up so that attention is
 peaked: a wrong, missing or stale key then changes the logits visibly instead of
 drowning in a near-uniform average.
@@ -28,9 +29,14 @@ CONFIGS = {
                    num_attention_heads=6, num_key_value_heads=3, head_dim=48,
                    intermediate_size=100, vocab_size=301, rope_theta=25000.0, rope_scaling=None,
                    rms_norm_eps=3e-6, tie_word_embeddings=False),
+    # head size 64: the size the tensor-core attention kernels take in bfloat16
+    "tiny_d": dict(architectures=["LlamaForCausalLM"], num_hidden_layers=2, hidden_size=96,
+                   num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                   intermediate_size=144, vocab_size=200, rope_theta=10000.0, rope_scaling=None,
+                   rms_norm_eps=1e-5, tie_word_embeddings=True),
 }
-PAGE_SIZE = {"tiny_a": 16, "tiny_b": 8, "tiny_c": 16}
-SEEDS = {"tiny_a": 11, "tiny_b": 22, "tiny_c": 33}
+PAGE_SIZE = {"tiny_a": 16, "tiny_b": 8, "tiny_c": 16, "tiny_d": 16}
+SEEDS = {"tiny_a": 11, "tiny_b": 22, "tiny_c": 33, "tiny_d": 44}
 
 
 def make_model_dir(path, name, sharpen=4.0, dtype=torch.bfloat16):
