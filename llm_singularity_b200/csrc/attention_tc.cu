@@ -520,3 +520,73 @@ LSB_API int lsb_prefill_attention(const void* qkv, int qkv_stride, const void* k
 #undef LAUNCH_PREFILL
     return LSB_LAUNCH_CHECK();
 }
+
+// ------------------------------------------------------------------ no-allocation entry point
+// See attention_tc_noalloc.h for who needs this and the rules that come with it.
+#include "attention_tc_noalloc.h"
+
+constexpr long long kNoAllocFloats = 1LL << 20;                // 4 MiB per device
+static __device__ __align__(256) float lsb_noalloc_scratch[kNoAllocFloats];
+
+// In host code `lsb_noalloc_scratch` is only a handle for the runtime, not an address a
+// kernel could use: the device address is looked up once per device and kept here.
+constexpr int kNoAllocMaxDevices = 64;
+static float* g_noalloc_dev_ptr[kNoAllocMaxDevices] = {};
+
+LSB_API long long lsb_decode_attention_noalloc_max_floats(void) { return kNoAllocFloats; }
+
+LSB_API const char* lsb_decode_attention_noalloc_error(int code) {
+    if (code == LSB_NOALLOC_TOO_LARGE)
+        return "decode attention (no-alloc): n_requests * nh * splits * (hd + 2) exceeds the "
+               "built-in scratch array; use fewer splits or the regular entry point";
+    if (code == LSB_NOALLOC_BAD_DEVICE)
+        return "decode attention (no-alloc): current device index is outside the library's table";
+    return cudaGetErrorString((cudaError_t)code);
+}
+
+LSB_API int lsb_decode_attention_noalloc(const void* qkv, int qkv_stride, const void* k_pages,
+                                         const void* v_pages, const int* q_start, const int* kv_len,
+                                         const int* table_rows, const int* block_table,
+                                         int table_stride, void* out, int n_requests, int nh, int nkv,
+                                         int hd, int page_size, int num_pages, float scale, int window,
+                                         int splits, cudaStream_t stream) {
+    if (n_requests <= 0) return 0;
+    if (nkv <= 0 || nh % nkv || nh / nkv > 16 || splits < 1 || n_requests > 65535 || nkv > 65535 ||
+        (hd != 64 && hd != 128))
+        return (int)cudaErrorInvalidValue;
+    float* scratch = nullptr;
+    if (splits > 1) {
+        if (lsb_decode_scratch_floats(n_requests, nh, hd, splits) > kNoAllocFloats)
+            return LSB_NOALLOC_TOO_LARGE;
+        int dev = -1;
+        cudaError_t e = cudaGetDevice(&dev);
+        if (e != cudaSuccess) return (int)e;
+        if (dev < 0 || dev >= kNoAllocMaxDevices) return LSB_NOALLOC_BAD_DEVICE;
+        if (!g_noalloc_dev_ptr[dev]) {                          // first call on this device
+            float* p = nullptr;
+            e = cudaGetSymbolAddress((void**)&p, lsb_noalloc_scratch);
+            if (e != cudaSuccess) return (int)e;
+            g_noalloc_dev_ptr[dev] = p;
+        }
+        scratch = g_noalloc_dev_ptr[dev];
+    }
+    float* part_o = scratch;
+    float* part_ml = scratch ? scratch + (size_t)n_requests * nh * splits * hd : nullptr;
+    dim3 grid(splits, nkv, n_requests);
+#define LAUNCH_DECODE_NOALLOC(HD)                                                                  \
+    do {                                                                                           \
+        int rc = configure_once<HD>();                                                             \
+        if (rc) return rc;                                                                         \
+        decode_attention_kernel<HD><<<grid, kThreads, decode_smem<HD>(), stream>>>(                \
+            (const bf16*)qkv, qkv_stride, (const bf16*)k_pages, (const bf16*)v_pages, q_start,    \
+            kv_len, table_rows, block_table, table_stride, (bf16*)out, part_o, part_ml, nh, nkv,  \
+            page_size, num_pages, scale, window, splits);                                          \
+        if (splits > 1)                                                                            \
+            decode_merge_kernel<HD><<<dim3(nh, n_requests), 64, 0, stream>>>(                      \
+                part_o, part_ml, q_start, (bf16*)out, nh, splits);                                 \
+    } while (0)
+    if (hd == 64) LAUNCH_DECODE_NOALLOC(64);
+    else LAUNCH_DECODE_NOALLOC(128);
+#undef LAUNCH_DECODE_NOALLOC
+    return LSB_LAUNCH_CHECK();
+}

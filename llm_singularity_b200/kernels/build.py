@@ -38,7 +38,7 @@ SOURCES: Dict[str, str] = {
     "gemm": "gemm.cu",
     "sampling": "sampling.cu",
 }
-HEADERS = ["common.cuh"]
+HEADERS = ["common.cuh", "attention_tc_noalloc.h"]
 
 
 class BuildError(RuntimeError):
