@@ -21,3 +21,25 @@ LSB_API int lsb_scatter_i32(int* dst, const int* idx, const int* val, int n, lon
     scatter_i32_kernel<<<(n + 255) / 256, 256, 0, stream>>>(dst, idx, val, n, dst_size);
     return LSB_LAUNCH_CHECK();
 }
+
+// The same with the count on the device: packed = [n, idx[cap], val[cap]].  A captured graph can
+// hold this launch and still apply a different number of changes at every replay.
+__global__ void scatter_i32_counted_kernel(int* __restrict__ dst, const int* __restrict__ packed,
+                                           int cap, long long dst_size) {
+    int n = packed[0];
+    if (n > cap) { if (threadIdx.x == 0) lsb_set_status(LSB_BAD_ROW); n = cap; }
+    const int* idx = packed + 1;
+    const int* val = packed + 1 + cap;
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+        const int j = idx[i];
+        if (j < 0 || j >= dst_size) { lsb_set_status(LSB_BAD_ROW); continue; }
+        dst[j] = val[i];
+    }
+}
+
+LSB_API int lsb_scatter_i32_counted(int* dst, const int* packed, int cap, long long dst_size,
+                                    cudaStream_t stream) {
+    if (cap <= 0) return 0;
+    scatter_i32_counted_kernel<<<1, 256, 0, stream>>>(dst, packed, cap, dst_size);
+    return LSB_LAUNCH_CHECK();
+}

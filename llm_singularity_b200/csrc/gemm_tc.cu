@@ -1,0 +1,434 @@
+// bfloat16 matrix product on the 5th-generation tensor cores:  D[i, j] = sum_k P[i, k] * Q[j, k].
+//
+// Both operands are row-major with K contiguous ("K-major"), which is how activations [M, K] and
+// checkpoint weights [N, K] already lie in memory (the reference hands the same pair to
+// cublasSgemm, kernels/src/cublas_provider.cpp:36-51).  P supplies the 128 rows of a tile (the MMA
+// M side, one accumulator row per TMEM lane), Q the BN columns (16..256).  The host picks which
+// of activations and weights plays which role:
+//   * many tokens (prefill): P = activations, Q = weights, output row-major [M, N];
+//   * few tokens (decode): P = weights, Q = activations, so each thread block streams a 128-row
+//     slab of the weight matrix exactly once and the batch rides on the narrow N side; the
+//     output is written transposed back into [M, N]; K may be split over several blocks
+//     (partials in 32-bit, summed by a second kernel in a fixed order).
+//
+// One thread block = one output tile (x one K split).  Warp 0 (one lane) issues TMA loads of
+// [128 x 64] and [BN x 64] bf16 boxes with the 128-byte swizzle into a ring of shared-memory
+// stages; warp 1 (one lane) issues tcgen05.mma (kind::f16, 32-bit accumulate in TMEM) and hands
+// stages back with tcgen05.commit; warps 2-5 read the accumulator with tcgen05.ld and store it.
+// Every wait on an mbarrier is bounded: when it runs out, the block records LSB_WAIT_TIMEOUT,
+// all roles leave their loops, outstanding copies are waited for (bounded again), TMEM is freed
+// and the block returns.  No load in this file uses cluster multicast.
+#include "common.cuh"
+
+#include <cuda.h>
+
+LSB_DEFINE_STATUS()
+
+typedef __nv_bfloat16 bf16;
+
+constexpr int kBM = 128;             // rows of P per tile (TMEM lanes)
+constexpr int kBK = 64;              // K per stage: 64 bf16 = one 128-byte swizzle row
+constexpr int kUmmaK = 16;           // K of one tcgen05.mma for 16-bit inputs
+constexpr int kGemmThreads = 192;    // warp 0: TMA, warp 1: MMA + TMEM, warps 2-5: epilogue
+constexpr uint32_t kSpinLimit = 1u << 22;
+
+// ------------------------------------------------------------------ PTX wrappers
+__device__ __forceinline__ uint32_t smem_addr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_addr(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false if the limit ran out or another role already gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 255u) == 255u) {
+            if (*abort_flag) return false;
+            __nanosleep(128);
+        }
+    }
+    *abort_flag = 1;
+    lsb_set_status(LSB_WAIT_TIMEOUT);
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(smem_addr(dst)), "l"(map), "r"(smem_addr(bar)), "r"(c0), "r"(c1) : "memory");
+}
+__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_addr(dst_smem)), "r"(ncols));
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::);
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols));
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
+// arrives on the mbarrier once all tcgen05.mma issued so far by this thread have finished
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                 : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile written by TMA with the 128-byte swizzle:
+// rows of 128 bytes, groups of 8 rows 1024 bytes apart (stride byte offset), tile base aligned to
+// 1024 bytes.  Fields: start address >> 4 [0,14), leading byte offset >> 4 [16,30) (unused for
+// swizzled K-major, set to 1), stride byte offset >> 4 [32,46), version 1 at [46,48), layout
+// type SWIZZLE_128B = 2 at [61,64).
+__device__ __forceinline__ uint64_t make_smem_desc(const void* tile) {
+    uint64_t d = (uint64_t)((smem_addr(tile) >> 4) & 0x3FFFu);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+// Instruction descriptor of kind::f16: D format F32 (1) at [4,6), A and B format BF16 (1) at
+// [7,10) and [10,13), both K-major (0 at bits 15, 16), N >> 3 at [17,23), M >> 4 at [24,29).
+__host__ __device__ constexpr uint32_t make_idesc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(kBM >> 4) << 24);
+}
+
+struct GemmParams {
+    int rows_p, rows_q, K;        // D is [rows_p, rows_q]
+    long long ldc_i, ldc_j;       // element strides of the output along i and j
+    int kb_per_split;             // 64-wide K blocks each split handles
+    int num_kb;                   // ceil(K / 64)
+    int out_f32;                  // output element type when there is one split
+    void* out;                    // bf16 or float [.. ldc ..] (splits == 1)
+    float* partial;               // [splits][out elements] (splits > 1)
+    long long partial_stride;     // elements between splits
+};
+
+template <int BN, int STAGES>
+struct SmemLayout {
+    static constexpr int kPBytes = kBM * kBK * 2;
+    static constexpr int kQBytes = BN * kBK * 2;
+    static constexpr int kStageBytes = kPBytes + kQBytes;
+    static constexpr int kBars = 2 * STAGES + 1;
+    static constexpr size_t kTotal = 1024 + (size_t)STAGES * kStageBytes + kBars * 8 + 16;
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
+               const GemmParams prm) {
+    using L = SmemLayout<BN, STAGES>;
+    constexpr uint32_t kTmemCols = BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256;
+    extern __shared__ unsigned char smem_raw[];
+    // stage buffers need 1024-byte alignment (swizzle atom); the dynamic window is only 16-aligned
+    unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* stages = base;
+    uint64_t* full = reinterpret_cast<uint64_t*>(base + (size_t)STAGES * L::kStageBytes);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int i0 = blockIdx.x * kBM, j0 = blockIdx.y * BN;
+    const int split = blockIdx.z;
+    const int kb0 = split * prm.kb_per_split;
+    const int kb1 = min(prm.num_kb, kb0 + prm.kb_per_split);
+    const int nkb = max(0, kb1 - kb0);
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        mbar_init(acc_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_p) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+            int issued = 0;
+            for (int kb = 0; kb < nkb; ++kb) {
+                const int s = kb % STAGES;
+                if (kb >= STAGES && !mbar_wait(&empty[s], ((kb / STAGES) - 1) & 1, &abort_flag)) break;
+                mbar_expect_tx(&full[s], L::kStageBytes);
+                unsigned char* st = stages + (size_t)s * L::kStageBytes;
+                tma_load_2d(st, &map_p, &full[s], (kb0 + kb) * kBK, i0);
+                tma_load_2d(st + L::kPBytes, &map_q, &full[s], (kb0 + kb) * kBK, j0);
+                issued = kb + 1;
+            }
+            // copies still in flight must land before the block may exit
+            for (int kb = max(0, issued - STAGES); kb < issued; ++kb) {
+                int dummy = 0;
+                mbar_wait(&full[kb % STAGES], (kb / STAGES) & 1, &dummy);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(BN);
+            bool ok = true;
+            for (int kb = 0; kb < nkb && ok; ++kb) {
+                const int s = kb % STAGES;
+                ok = mbar_wait(&full[s], (kb / STAGES) & 1, &abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                unsigned char* st = stages + (size_t)s * L::kStageBytes;
+                const uint64_t dp = make_smem_desc(st), dq = make_smem_desc(st + L::kPBytes);
+#pragma unroll
+                for (int k = 0; k < kBK / kUmmaK; ++k)    // 32 bytes further along K: +2 in 16-byte units
+                    umma_bf16(tmem_base, dp + 2 * k, dq + 2 * k, idesc, (kb | k) ? 1u : 0u);
+                umma_commit(&empty[s]);
+            }
+            umma_commit(acc_full);                         // arrives at once if nothing is pending
+        }
+    } else {
+        // epilogue: warp w may touch TMEM lanes 32 * (w % 4) .. + 31
+        const int q = warp & 3;
+        const int i = i0 + q * 32 + lane;
+        bool ok = true;
+        if (nkb > 0) {
+            ok = mbar_wait(acc_full, 0, &abort_flag);
+            tc_fence_after();
+        }
+        if (ok && !abort_flag) {
+            const bool row_ok = i < prm.rows_p;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                if (nkb > 0) {
+                    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+                    if (BN - c0 >= 32) tmem_ld_32x32(taddr, r);
+                    else { tmem_ld_32x16(taddr, r); }
+                    tmem_ld_wait();
+                } else {
+#pragma unroll
+                    for (int x = 0; x < 32; ++x) r[x] = 0u;
+                }
+                if (!row_ok) continue;
+                const int ncols = min(32, min(BN, prm.rows_q - j0) - c0);
+                if (ncols <= 0) continue;
+                const long long o = (long long)i * prm.ldc_i + (long long)(j0 + c0) * prm.ldc_j;
+                if (prm.partial) {
+                    float* dst = prm.partial + (long long)split * prm.partial_stride + o;
+                    for (int x = 0; x < ncols; ++x) dst[x * prm.ldc_j] = __uint_as_float(r[x]);
+                } else if (prm.out_f32) {
+                    float* dst = reinterpret_cast<float*>(prm.out) + o;
+                    if (prm.ldc_j == 1 && ncols == 32 && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+                        for (int x = 0; x < 32; x += 4)
+                            *reinterpret_cast<uint4*>(dst + x) = make_uint4(r[x], r[x + 1], r[x + 2], r[x + 3]);
+                    } else {
+                        for (int x = 0; x < ncols; ++x) dst[x * prm.ldc_j] = __uint_as_float(r[x]);
+                    }
+                } else {
+                    bf16* dst = reinterpret_cast<bf16*>(prm.out) + o;
+                    if (prm.ldc_j == 1 && ncols == 32 && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+                        for (int x = 0; x < 32; x += 8) {
+                            uint4 v;
+                            __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r[x]), __uint_as_float(r[x + 1]));
+                            __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r[x + 2]), __uint_as_float(r[x + 3]));
+                            __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[x + 4]), __uint_as_float(r[x + 5]));
+                            __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(r[x + 6]), __uint_as_float(r[x + 7]));
+                            v.x = *reinterpret_cast<uint32_t*>(&h0); v.y = *reinterpret_cast<uint32_t*>(&h1);
+                            v.z = *reinterpret_cast<uint32_t*>(&h2); v.w = *reinterpret_cast<uint32_t*>(&h3);
+                            *reinterpret_cast<uint4*>(dst + x) = v;
+                        }
+                    } else {
+                        for (int x = 0; x < ncols; ++x) dst[x * prm.ldc_j] = __float2bfloat16_rn(__uint_as_float(r[x]));
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
+// out[e] = sum over splits of partial[s][e], in split order (deterministic)
+template <typename TOut>
+__global__ void splitk_reduce_kernel(const float* __restrict__ partial, long long stride, int splits,
+                                     TOut* __restrict__ out, long long n) {
+    long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= n) return;
+    float acc = 0.f;
+    for (int s = 0; s < splits; ++s) acc += partial[(long long)s * stride + e];
+    out[e] = lsb_from_float<TOut>(acc);
+}
+
+// ------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// [rows, K] bf16 row-major, boxes of [box_rows x 64], 128-byte swizzle, zero fill outside
+static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return (int)cudaErrorNotSupported;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    cuuint32_t box[2] = {(cuuint32_t)kBK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+template <int BN, int STAGES>
+static int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmParams& prm, dim3 grid,
+                  cudaStream_t stream) {
+    static int configured = -1;
+    constexpr size_t smem = SmemLayout<BN, STAGES>::kTotal;
+    if (configured < 0)
+        configured = (int)cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (configured) return configured;
+    gemm_tc_kernel<BN, STAGES><<<grid, kGemmThreads, smem, stream>>>(mp, mq, prm);
+    return LSB_LAUNCH_CHECK();
+}
+
+// Can this kernel take the product?  (TMA needs 16-byte aligned bases and row strides.)
+LSB_API int lsb_gemm_tc_supported(const void* x, const void* w, int M, int N, int K) {
+    return M > 0 && N > 0 && K > 0 && K % 8 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0;
+}
+
+// How many K splits the decode orientation would use, and the floats of scratch that needs.
+LSB_API int lsb_gemm_tc_plan(int M, int N, int K, int* swap, int* bn, int* splits) {
+    const int num_kb = (K + kBK - 1) / kBK;
+    if (M <= 128) {
+        *swap = 1;
+        *bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+        const int tiles = (N + kBM - 1) / kBM;
+        int s = 1;
+        if (tiles < 120) {                       // too few slabs to fill 148 SMs: split K
+            s = (148 + tiles - 1) / tiles;
+            s = s < 1 ? 1 : s;
+            if (s > num_kb / 4) s = num_kb / 4 > 0 ? num_kb / 4 : 1;   // at least 4 K blocks each
+        }
+        *splits = s;
+    } else {
+        *swap = 0;
+        // the widest tile that still fills the machine reasonably
+        const int mt = (M + kBM - 1) / kBM;
+        int best = 64;
+        double best_eff = -1.0;
+        const int cands[3] = {256, 128, 64};
+        for (int c = 0; c < 3; ++c) {
+            const int t = mt * ((N + cands[c] - 1) / cands[c]);
+            const int waves = (t + 147) / 148;
+            double eff = (double)t / (waves * 148.0);
+            if (cands[c] == 64) eff *= 0.8;      // narrower tiles reuse P less
+            else if (cands[c] == 128) eff *= 0.93;
+            if (eff > best_eff + 1e-9) { best_eff = eff; best = cands[c]; }
+        }
+        *bn = best;
+        *splits = 1;
+    }
+    return 0;
+}
+
+// out[M, N] = x[M, K] * w[N, K]^T, bf16 inputs, bf16 or float output.  `scratch` must hold
+// splits * M * N floats when the plan uses more than one split.
+LSB_API int lsb_gemm_tc(const void* x, const void* w, void* out, int out_f32, int M, int N, int K,
+                        float* scratch, cudaStream_t stream) {
+    if (!lsb_gemm_tc_supported(x, w, M, N, K)) return (int)cudaErrorInvalidValue;
+    int swap, bn, splits;
+    lsb_gemm_tc_plan(M, N, K, &swap, &bn, &splits);
+    if (splits > 1 && !scratch) return (int)cudaErrorInvalidValue;
+    GemmParams prm;
+    prm.K = K;
+    prm.num_kb = (K + kBK - 1) / kBK;
+    prm.kb_per_split = (prm.num_kb + splits - 1) / splits;
+    prm.out_f32 = out_f32;
+    prm.out = out;
+    prm.partial = splits > 1 ? scratch : nullptr;
+    prm.partial_stride = (long long)M * N;
+    CUtensorMap mp, mq;
+    int rc;
+    dim3 grid;
+    if (swap) {
+        prm.rows_p = N; prm.rows_q = M; prm.ldc_i = 1; prm.ldc_j = N;
+        if ((rc = make_map(&mp, w, N, K, kBM))) return rc;
+        if ((rc = make_map(&mq, x, M, K, bn))) return rc;
+        grid = dim3((N + kBM - 1) / kBM, 1, splits);
+    } else {
+        prm.rows_p = M; prm.rows_q = N; prm.ldc_i = N; prm.ldc_j = 1;
+        if ((rc = make_map(&mp, x, M, K, kBM))) return rc;
+        if ((rc = make_map(&mq, w, N, K, bn))) return rc;
+        grid = dim3((M + kBM - 1) / kBM, (N + bn - 1) / bn, 1);
+    }
+    switch (bn) {
+        case 16: rc = launch<16, 8>(mp, mq, prm, grid, stream); break;
+        case 32: rc = launch<32, 8>(mp, mq, prm, grid, stream); break;
+        case 64: rc = launch<64, 6>(mp, mq, prm, grid, stream); break;
+        case 128: rc = launch<128, 6>(mp, mq, prm, grid, stream); break;
+        case 256: rc = launch<256, 4>(mp, mq, prm, grid, stream); break;
+        default: return (int)cudaErrorInvalidValue;
+    }
+    if (rc) return rc;
+    if (splits > 1) {
+        const long long n = (long long)M * N;
+        const int blocks = (int)((n + 255) / 256);
+        if (out_f32)
+            splitk_reduce_kernel<float><<<blocks, 256, 0, stream>>>(scratch, prm.partial_stride, splits, (float*)out, n);
+        else
+            splitk_reduce_kernel<bf16><<<blocks, 256, 0, stream>>>(scratch, prm.partial_stride, splits, (bf16*)out, n);
+        rc = LSB_LAUNCH_CHECK();
+    }
+    return rc;
+}

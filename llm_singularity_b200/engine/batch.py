@@ -80,10 +80,13 @@ class ContextBuilder:
         self._events = [None] * self.RING
 
     def build(self, tokens: List[Sequence[int]], starts: List[int], rows: List[int],
-              wants: List[Sequence[int]], extra: Optional[List[np.ndarray]] = None):
+              wants: List[Sequence[int]], extra: Optional[List[np.ndarray]] = None,
+              static: Optional[torch.Tensor] = None):
         """``tokens[r]`` are request r's new tokens, ``starts[r]`` how many it already
         holds, ``rows[r]`` its block-table row, ``wants[r]`` places among its tokens.
-        ``extra`` are further int32 arrays to ride along; returns (ctx, extra on device)."""
+        ``extra`` are further int32 arrays to ride along; returns (ctx, extra on device).
+        ``static``: a persistent device buffer to fill instead of the ring's (so that the
+        arrays keep their addresses from step to step, as a captured graph needs)."""
         R = len(tokens)
         q_len = np.fromiter((len(t) for t in tokens), dtype=np.int32, count=R)
         if R == 0 or (q_len <= 0).any():
@@ -131,7 +134,9 @@ class ContextBuilder:
         s_want = put(np.asarray(want_rows, dtype=np.int32))
         s_extra = [put(e) for e in extra]
 
-        dev = self._dev[i]
+        dev = self._dev[i] if static is None else static
+        if dev.numel() < o:
+            raise ValueError(f"static metadata buffer holds {dev.numel()} ints, step needs {o}")
         dev[:o].copy_(self._host[i][:o], non_blocking=True)
         if self._cuda:
             ev = torch.cuda.Event()

@@ -54,13 +54,26 @@ def expected_tensors_of(spec: ModelSpec) -> Dict[str, Tuple[Tuple[int, ...], str
     return {n: (ps.shape, ps.role, ps.init) for n, (_, _, ps) in shell.expected_tensors().items()}
 
 
+class _DecodeGraph:
+    """What a captured decode step of one batch size keeps: its metadata buffer at a fixed
+    address, the captured graph and the logits tensor the graph writes."""
+
+    def __init__(self, n_requests: int, n_groups: int, device):
+        self.cap = 2 * n_requests + 8                    # block-table cells changed per step
+        n = 3 * n_requests + (n_requests + 1) + 3 * n_requests + n_groups * (1 + 2 * self.cap)
+        self.meta = torch.zeros(n, dtype=torch.int32, device=device)
+        self.graph = None
+        self.logits: Optional[torch.Tensor] = None
+        self.warm = 0
+
+
 class ModelRunner:
     def __init__(self, model_dir: Optional[str] = None, *, config=None,
                  tensors: Optional[Dict[str, torch.Tensor]] = None,
                  dtype="bfloat16", device="cuda:0", page_size: int = 16,
                  num_pages: int = 1024, max_requests: int = 64,
                  max_tokens_per_step: int = 2048, max_model_len: Optional[int] = None,
-                 ops=None, verbose: bool = False):
+                 ops=None, verbose: bool = False, cuda_graphs: bool = True):
         """Either ``model_dir`` (config.json + safetensors) or ``config`` + ``tensors``
         (checkpoint names -> tensors, e.g. from ``random_tensors``)."""
         self.dtype = parse_dtype(dtype)
@@ -96,6 +109,13 @@ class ModelRunner:
         self._ctx = ContextBuilder(self.rt.device, max_tokens_per_step, max_requests)
         self.steps = 0
         self.tokens_run = 0
+        # decode-only steps are captured once per batch size and replayed (no per-kernel launch
+        # cost); only if every part launches the same kernels whatever the host-side values are
+        self._graphs: Dict[int, "_DecodeGraph"] = {}
+        self.cuda_graphs = (cuda_graphs and ops is None and self.rt.device.type == "cuda"
+                            and all(getattr(p, "graph_safe", False)
+                                    for p in self.model._owners().values()))
+        self.graph_replays = 0
 
     @property
     def vocab_size(self) -> int:
@@ -132,13 +152,65 @@ class ModelRunner:
                 raise OutOfPages(
                     f"request {e.request!r} needs {cache.pages_needed(e.request, new_len)} more "
                     f"pages, {cache.free_pages()} are free")
-        ctx = self.prepare_context(entries, starts)
-        logits = self.model.forward(ctx, cache)
+        if self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
+            logits, n_tokens = self._decode_with_graph(entries, starts), len(entries)
+        else:
+            ctx = self.prepare_context(entries, starts)
+            logits, n_tokens = self.model.forward(ctx, cache), ctx.n_tokens
         for e, s in zip(entries, starts):
             cache.commit(e.request, s + len(e.tokens))
         self.steps += 1
-        self.tokens_run += ctx.n_tokens
+        self.tokens_run += n_tokens
         return logits
+
+    # ------------------------------------------------------------ decode graphs
+    def _decode_with_graph(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> torch.Tensor:
+        """A step of single decode tokens, all wanted: replay the graph captured for this batch
+        size.  The step's metadata and the block-table cells that changed are copied into buffers
+        at fixed addresses first; everything else happens inside the graph.  The returned logits
+        live in the graph's own memory and are overwritten by the next step of the same size."""
+        cache, R = self.cache, len(entries)
+        st = self._graphs.get(R)
+        if st is None:
+            st = self._graphs[R] = _DecodeGraph(R, len(cache.groups), self.rt.device)
+        extra: List[np.ndarray] = []
+        for gi in range(len(cache.groups)):
+            last = dict(cache.take_updates(gi))
+            if len(last) > st.cap:                       # rare (many requests closed): plain path
+                keys = list(last)
+                spill = {k: last.pop(k) for k in keys[st.cap:]}
+                idx = torch.tensor(list(spill), dtype=torch.int32, device=self.rt.device)
+                val = torch.tensor(list(spill.values()), dtype=torch.int32, device=self.rt.device)
+                self.rt.ops.scatter_i32(cache.groups[gi].dev_table, idx, val)
+            packed = np.zeros(1 + 2 * st.cap, dtype=np.int32)
+            packed[0] = len(last)
+            packed[1:1 + len(last)] = np.fromiter(last.keys(), dtype=np.int32, count=len(last))
+            packed[1 + st.cap:1 + st.cap + len(last)] = np.fromiter(last.values(), dtype=np.int32,
+                                                                    count=len(last))
+            extra.append(packed)
+        ctx, dev_extra = self._ctx.build(
+            [e.tokens for e in entries], list(starts), [cache.slot(e.request) for e in entries],
+            [e.want for e in entries], extra, static=st.meta)
+        ctx.fixed_launch = True
+
+        def run():
+            for gi, g in enumerate(cache.groups):
+                self.rt.ops.scatter_i32_counted(g.dev_table, dev_extra[gi], st.cap)
+            return self.model.forward(ctx, cache)
+
+        if st.graph is None:
+            if st.warm < 1:                              # once eagerly: loads libraries, sizes scratch
+                st.warm += 1
+                return run()
+            torch.cuda.synchronize(self.rt.device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                st.logits = run()
+            st.graph = graph
+            # the capture did not execute anything: the replay below runs this step
+        st.graph.replay()
+        self.graph_replays += 1
+        return st.logits
 
     def check_kernels(self) -> None:
         """Raise if a kernel recorded a fault (a page not held, a token outside the table).

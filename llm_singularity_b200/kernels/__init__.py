@@ -70,6 +70,7 @@ def check_status() -> None:
 
 
 _launches = 0
+_scratch: Dict[tuple, torch.Tensor] = {}      # scratch buffers by use and size, kept for reuse
 
 
 def launch_count() -> int:
@@ -132,6 +133,16 @@ def scatter_i32(dst: torch.Tensor, idx: torch.Tensor, val: torch.Tensor) -> None
           _ll(dst.numel()), _stream(dst))
 
 
+def scatter_i32_counted(dst: torch.Tensor, packed: torch.Tensor, cap: int) -> None:
+    """dst.flat[idx[i]] = val[i] for i < n, with packed = [n, idx[cap], val[cap]] on the device."""
+    _req(dst, "dst", torch.int32)
+    _req(packed, "packed", torch.int32, 1)
+    if packed.numel() != 1 + 2 * cap:
+        raise KernelError("scatter_i32_counted: packed must hold 1 + 2 * cap ints")
+    _call("cache_table", "lsb_scatter_i32_counted", _p(dst), _p(packed), _i(cap), _ll(dst.numel()),
+          _stream(dst))
+
+
 def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
     """out[t, :] = float(table[ids[t], :])."""
     _req(table, "table", dim=2)
@@ -183,7 +194,8 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     """x [M, K] times w [N, K] transposed -> [M, N]; 32-bit accumulation.
 
     float32 operands run on the CUDA cores in true 32-bit.  bfloat16 operands run on the
-    tensor cores.
+    tensor cores (tcgen05, accumulators in TMEM) when K is a multiple of 8, else on the CUDA
+    cores as well.
     """
     _req(x, "x", dim=2)
     _req(w, "w", x.dtype, 2)
@@ -194,12 +206,30 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     out_dtype = out_dtype or x.dtype
     if out_dtype not in (x.dtype, torch.float32):
         raise KernelError(f"linear: output must be {x.dtype} or float32")
-    if x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16:
-        return torch.matmul(x, w.t())
     out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+    if x.dtype == torch.bfloat16 and tensor_core_gemm_ok(x, w):
+        lib = _lib("gemm_tc")
+        swap, bn, splits = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
+        lib.lsb_gemm_tc_plan(_i(M), _i(N), _i(K), ctypes.byref(swap), ctypes.byref(bn),
+                             ctypes.byref(splits))
+        scratch = None
+        if splits.value > 1:
+            key = ("gemm", x.device, M * N * splits.value)
+            scratch = _scratch.get(key)
+            if scratch is None:
+                scratch = _scratch[key] = torch.empty(M * N * splits.value, dtype=torch.float32,
+                                                      device=x.device)
+        _call("gemm_tc", "lsb_gemm_tc", _p(x), _p(w), _p(out), _i(1 if out_dtype == torch.float32 else 0),
+              _i(M), _i(N), _i(K), _p(scratch), _stream(out))
+        return out
     _call("gemm", "lsb_gemm_nt", _p(x), _p(w), _p(out), _i(_dt(x)), _i(_dt(out)), _i(M), _i(N), _i(K),
           _ll(K), _ll(K), _ll(N), _stream(out))
     return out
+
+
+def tensor_core_gemm_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """TMA needs 16-byte aligned bases and row strides: K a multiple of 8 for bfloat16."""
+    return (x.shape[1] % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
@@ -248,7 +278,6 @@ def rope_kv_store(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache,
 
 NUM_SMS = 148                   # B200: 2 dies x 74
 _TC_HEAD_DIMS = (64, 128)
-_scratch: Dict[tuple, torch.Tensor] = {}
 
 
 def decode_splits(n_decode: int, nkv: int) -> int:

@@ -36,6 +36,7 @@ SOURCES: Dict[str, str] = {
     "attention": "attention.cu",
     "attention_tc": "attention_tc.cu",
     "gemm": "gemm.cu",
+    "gemm_tc": "gemm_tc.cu",
     "sampling": "sampling.cu",
 }
 HEADERS = ["common.cuh", "attention_tc_noalloc.h"]

@@ -100,6 +100,8 @@ class DecoderModel:
             for k in getattr(part, "kernels", ()):
                 if k not in names:
                     names.append(k)
+        if self.rt.dtype == torch.bfloat16 and "gemm" in names:
+            names.append("gemm_tc")            # bfloat16 products run on the tensor cores
         return names
 
     # ------------------------------------------------------------------ forward

@@ -20,6 +20,7 @@ from .base import POSITIONS, PagedKVSpec, ParamSpec, Part, register_mixer
 
 @register_mixer("attention")
 class PagedAttention(Part):
+    graph_safe = True
     kernels = ("gemm", "rope_cache", "attention")
 
     def __init__(self, spec, rt):

@@ -95,7 +95,14 @@ class Runtime:
 
 
 class Part:
-    """Base class: parameters in, ``forward`` out."""
+    """Base class: parameters in, ``forward`` out.
+
+    ``graph_safe``: the part's ``forward`` launches the same kernels with the same arguments
+    whatever the step's host-side values are (it reads lengths, positions and rows only on the
+    device), so a decode step through it can be captured once in a CUDA graph and replayed.
+    """
+
+    graph_safe = False
 
     def __init__(self, spec, rt: Runtime):
         self.spec = spec

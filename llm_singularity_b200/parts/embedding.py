@@ -21,6 +21,7 @@ from .base import NORMS, ParamSpec, Part
 
 
 class Embedding(Part):
+    graph_safe = True
     kernels = ("embedding",)
 
     @classmethod
@@ -37,6 +38,7 @@ class Embedding(Part):
 
 
 class LMHead(Part):
+    graph_safe = True
     kernels = ("gemm", "norm")
 
     def __init__(self, spec, rt):

@@ -17,6 +17,7 @@ from .base import ParamSpec, Part, register_norm
 
 @register_norm("rmsnorm")
 class RMSNorm(Part):
+    graph_safe = True
     kernels = ("norm",)
 
     @classmethod

@@ -41,6 +41,7 @@ def rotary_inv_freq(rotary_dim: int, theta: float, scaling=None) -> torch.Tensor
 
 @register_position("rotary")
 class RotaryEncoding(Part):
+    graph_safe = True
     kernels = ("rope_cache",)
 
     def __init__(self, spec, rt):
@@ -57,6 +58,7 @@ class RotaryEncoding(Part):
 
 @register_position("none")
 class NoPosition(Part):
+    graph_safe = True
     def rotary_table(self):
         return None
 
