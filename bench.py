@@ -232,10 +232,15 @@ def run_ours(args):
     value = args.batch / ms * 1e3
 
     # ---- end to end through Engine.step: host tokens in, host tokens out, every step
-    prompts = [torch.randint(0, V, (ctx_len - (args.steps + args.warmup) - 1,), generator=g).tolist()
+    # requests finish their prompts one after another, so the first ones decode a few tokens
+    # while the last still prefill: leave room for that, and let none finish inside the timed
+    # region (the batch must stay at --batch requests throughout)
+    slack = 4 * args.batch + 8
+    prompts = [torch.randint(0, V, (ctx_len - (args.steps + args.warmup) - slack,), generator=g).tolist()
                for _ in range(args.batch)]
     for p in prompts:
-        eng.add_request(p, max_new_tokens=args.steps + args.warmup, temperature=0.0, ignore_eos=True)
+        eng.add_request(p, max_new_tokens=args.steps + args.warmup + slack, temperature=0.0,
+                        ignore_eos=True)
     while any(not r.generated for r in eng._requests.values()):
         eng.step()                                   # prefill until every request decodes
     for _ in range(args.warmup - 1):
@@ -248,6 +253,7 @@ def run_ours(args):
     torch.cuda.synchronize()
     e2e_s = time.perf_counter() - t0
     e2e_value = n_e2e / e2e_s
+    assert n_e2e == args.steps * args.batch, "the batch changed inside the timed region"
     while eng.has_work():
         eng.step()
     h2d = 4 * (3 * args.batch + (args.batch + 1) + 2 * args.batch + args.batch) + 4 * 5 * args.batch

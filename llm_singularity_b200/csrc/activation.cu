@@ -1,8 +1,9 @@
-// SwiGLU on a fused gate/up product: out[t, i] = silu(gu[t, i]) * gu[t, I + i],
-// silu(g) = g / (1 + exp(-g)), evaluated in 32-bit.
+// SwiGLU on a fused gate/up product whose columns alternate gate_i, up_i:
+// out[t, i] = silu(gu[t, 2i]) * gu[t, 2i + 1], silu(g) = g / (1 + exp(-g)), evaluated in 32-bit.
 //
 // Replaces silu_mul_kernel of the reference (kernels/src/activations.cu:11-21), which
-// reads two separate fp32 buffers.
+// reads two separate fp32 buffers.  The bfloat16 tensor-core product applies the same formula
+// in its epilogue; this kernel serves the 32-bit path and shapes that product does not take.
 #include "common.cuh"
 
 LSB_DEFINE_STATUS()
@@ -13,11 +14,9 @@ __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out
     long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (; idx < total; idx += stride) {
-        const long long t = idx / inter;
-        const int i = (int)(idx - t * inter);
-        const T* row = gate_up + t * 2 * (long long)inter;
-        const float g = lsb_to_float(row[i]);
-        const float u = lsb_to_float(row[inter + i]);
+        // out is [tokens, inter] and gate_up [tokens, 2 * inter]: element idx reads 2 idx, 2 idx + 1
+        const float g = lsb_to_float(gate_up[2 * idx]);
+        const float u = lsb_to_float(gate_up[2 * idx + 1]);
         out[idx] = lsb_from_float<T>(g / (1.f + expf(-g)) * u);
     }
 }

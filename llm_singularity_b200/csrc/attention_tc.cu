@@ -10,9 +10,10 @@
 //
 //  * decode: one thread block per (split, kv head, request).  The nh/nkv query heads that share
 //    the kv head are the rows of one 16-row MMA tile, so every key and value is read once for
-//    the whole group; the four warps take 16 keys each of every tile and merge through shared
-//    memory; with more than one split, partial (max, sum, output) go to scratch and a small
-//    merge kernel finishes.  The split count depends only on the batch, and each split finds
+//    the whole group; each of the four warps pipelines its own 16-key chunks (four in flight,
+//    no block barrier in the loop) and the warps merge through shared memory at the end; with
+//    more than one split, partial (max, sum, output) go to scratch and a small merge kernel
+//    finishes.  The split count depends only on the batch, and each split finds
 //    its share of tiles from the request's length on the device, so a captured launch stays
 //    valid as sequences grow.
 //  * prefill: one thread block per (64-query tile, head, request); warp w owns rows 16w..16w+15.
@@ -98,6 +99,18 @@ __device__ __forceinline__ void load_kv_tile(bf16* sK, bf16* sV, const bf16* __r
 }
 
 // ------------------------------------------------------------------ decode
+constexpr int kChunk = 16;           // keys a warp handles per step
+constexpr int kDecStages = 4;        // chunks in flight per warp
+constexpr int kBtCache = 1024;       // block-table entries kept in shared memory per block
+
+__device__ __forceinline__ int div_page(int key, int page_size, int page_shift) {
+    return page_shift >= 0 ? key >> page_shift : key / page_size;
+}
+
+// Each warp runs its own pipeline over every fourth 16-key chunk of the block's key range:
+// asynchronous 16-byte copies of the chunk's K and V rows into the warp's ring of stages, no
+// block-wide barrier inside the loop.  The block's slice of the block table is read into shared
+// memory first, so that copies are issued without waiting on a table lookup.
 template <int HD>
 __global__ void __launch_bounds__(kThreads)
 decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
@@ -108,10 +121,11 @@ decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
                         float* __restrict__ part_ml, int nh, int nkv, int page_size, int num_pages,
                         float scale, int window, int splits) {
     constexpr int CPR = HD / 8, KS = HD / 16;
+    constexpr int kStageElems = 2 * kChunk * HD;             // K rows then V rows
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);            // [16][HD]
-    bf16* sK = sQ + 16 * HD;                                 // [stages][64][HD]
-    bf16* sV = sK + kStages * kTile * HD;
+    bf16* sKV = sQ + 16 * HD;                                // [4 warps][stages][K|V][16][HD]
+    int* sBT = reinterpret_cast<int*>(sKV + 4 * kDecStages * kStageElems);
 
     const int split = blockIdx.x, g = blockIdx.y, r = blockIdx.z;
     const int qs = q_start[r];
@@ -122,12 +136,21 @@ decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
     const int p = kv_len - 1;
     const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
     const int* bt = block_table + (size_t)table_rows[r] * table_stride;
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
 
-    const int first_tile = lo / kTile;
-    const int n_tiles = p / kTile + 1 - first_tile;
-    const int per = (n_tiles + splits - 1) / splits;
-    const int t0 = first_tile + split * per;
-    const int t1 = min(t0 + per, first_tile + n_tiles);
+    const int first_chunk = lo / kChunk;
+    const int n_chunks = p / kChunk + 1 - first_chunk;
+    const int per = (n_chunks + splits - 1) / splits;
+    const int c0 = first_chunk + split * per;
+    const int c1 = min(c0 + per, first_chunk + n_chunks);
+
+    // this block's slice of the block table
+    const int page0 = div_page(c0 * kChunk, page_size, page_shift);
+    const int n_pages_here = c1 > c0 ? div_page(c1 * kChunk - 1, page_size, page_shift) - page0 + 1 : 0;
+    const bool cached = n_pages_here <= kBtCache;
+    if (cached)
+        for (int idx = threadIdx.x; idx < n_pages_here; idx += kThreads)
+            sBT[idx] = (page0 + idx < table_stride) ? bt[page0 + idx] : -1;
 
     // queries of the group: rows 0..G-1 of a 16-row tile, the rest zero
     for (int idx = threadIdx.x; idx < 16 * CPR; idx += kThreads) {
@@ -137,8 +160,6 @@ decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
             v = *reinterpret_cast<const uint4*>(qkv + (size_t)qs * qkv_stride + (size_t)(g * G + row) * HD + c * 8);
         *reinterpret_cast<uint4*>(tile_ptr<HD>(sQ, row, c)) = v;
     }
-    if (t0 < t1) load_kv_tile<HD>(sK, sV, k_pages, v_pages, bt, t0, lo, p, g, nkv, page_size, num_pages);
-    cp_async_commit();
     __syncthreads();
 
     uint32_t qf[KS][4];
@@ -152,22 +173,54 @@ decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     const float sc = scale * kLog2e;
 
-    for (int t = t0; t < t1; ++t) {
-        const int stage = (t - t0) & 1;
-        if (t + 1 < t1)
-            load_kv_tile<HD>(sK + (stage ^ 1) * kTile * HD, sV + (stage ^ 1) * kTile * HD, k_pages, v_pages,
-                             bt, t + 1, lo, p, g, nkv, page_size, num_pages);
+    bf16* ring = sKV + (size_t)warp * kDecStages * kStageElems;
+    const int n_mine = (c1 - c0 - warp + 3) / 4;             // chunks c0 + warp, c0 + warp + 4, ...
+
+    auto issue = [&](int i) {
+        if (i < n_mine) {
+            const int chunk = c0 + warp + 4 * i;
+            bf16* dK = ring + (size_t)(i % kDecStages) * kStageElems;
+            bf16* dV = dK + kChunk * HD;
+#pragma unroll
+            for (int idx = lane; idx < kChunk * CPR; idx += 32) {
+                const int kk = idx / CPR, c = idx - kk * CPR;
+                const int key = chunk * kChunk + kk;
+                bool valid = key >= lo && key <= p;
+                long long off = 0;
+                if (valid) {
+                    const int pi = div_page(key, page_size, page_shift);
+                    const int page = cached ? sBT[pi - page0] : (pi < table_stride ? bt[pi] : -1);
+                    if (page < 0 || page >= num_pages) {
+                        lsb_set_status(LSB_BAD_PAGE);
+                        valid = false;
+                    } else {
+                        const int within = key - pi * page_size;
+                        off = (((long long)page * nkv + g) * page_size + within) * HD + c * 8;
+                    }
+                }
+                cp_async16(tile_ptr<HD>(dK, kk, c), k_pages + off, valid);
+                cp_async16(tile_ptr<HD>(dV, kk, c), v_pages + off, valid);
+            }
+        }
         cp_async_commit();
-        cp_async_wait<1>();
-        __syncthreads();
-        bf16* tK = sK + stage * kTile * HD;
-        bf16* tV = sV + stage * kTile * HD;
+    };
+
+#pragma unroll
+    for (int i = 0; i < kDecStages - 1; ++i) issue(i);
+
+    for (int i = 0; i < n_mine; ++i) {
+        issue(i + kDecStages - 1);
+        cp_async_wait<kDecStages - 1>();
+        __syncwarp();
+        const int chunk = c0 + warp + 4 * i;
+        bf16* tK = ring + (size_t)(i % kDecStages) * kStageElems;
+        bf16* tV = tK + kChunk * HD;
 
         float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
         for (int ks = 0; ks < KS; ++ks) {
             uint32_t b[4];
-            ldmatrix_x4(b, tile_ptr<HD>(tK, warp * 16 + (lane >> 4) * 8 + (lane & 7), 2 * ks + ((lane >> 3) & 1)));
+            ldmatrix_x4(b, tile_ptr<HD>(tK, (lane >> 4) * 8 + (lane & 7), 2 * ks + ((lane >> 3) & 1)));
             mma_bf16(s[0], qf[ks], b[0], b[1]);
             mma_bf16(s[1], qf[ks], b[2], b[3]);
         }
@@ -177,7 +230,7 @@ decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const int key = t * kTile + warp * 16 + nt * 8 + 2 * (lane & 3) + (e & 1);
+                const int key = chunk * kChunk + nt * 8 + 2 * (lane & 3) + (e & 1);
                 const float v = (key >= lo && key <= p) ? s[nt][e] * sc : -INFINITY;
                 s[nt][e] = v;
                 mx[e >> 1] = fmaxf(mx[e >> 1], v);
@@ -201,20 +254,20 @@ decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
                 l[e >> 1] += pv;
             }
 #pragma unroll
-        for (int i = 0; i < HD / 8; ++i) {
-            o[i][0] *= corr[0]; o[i][1] *= corr[0];
-            o[i][2] *= corr[1]; o[i][3] *= corr[1];
+        for (int i2 = 0; i2 < HD / 8; ++i2) {
+            o[i2][0] *= corr[0]; o[i2][1] *= corr[0];
+            o[i2][2] *= corr[1]; o[i2][3] *= corr[1];
         }
         uint32_t pa[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]),
                           pack_bf16(s[1][0], s[1][1]), pack_bf16(s[1][2], s[1][3])};
 #pragma unroll
         for (int dt = 0; dt < HD / 16; ++dt) {
             uint32_t b[4];
-            ldmatrix_x4_trans(b, tile_ptr<HD>(tV, warp * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), 2 * dt + (lane >> 4)));
+            ldmatrix_x4_trans(b, tile_ptr<HD>(tV, ((lane >> 3) & 1) * 8 + (lane & 7), 2 * dt + (lane >> 4)));
             mma_bf16(o[2 * dt], pa, b[0], b[1]);
             mma_bf16(o[2 * dt + 1], pa, b[2], b[3]);
         }
-        __syncthreads();                                       // the stage is overwritten next round
+        __syncwarp();                                          // the stage is overwritten next round
     }
     cp_async_wait<0>();
 #pragma unroll
@@ -224,7 +277,7 @@ decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
     }
 
     // merge the four warps (each saw different keys) through shared memory
-    float* sO = reinterpret_cast<float*>(sK);                  // [4][16][HD]
+    float* sO = reinterpret_cast<float*>(sKV);                 // [4][16][HD]
     float* sM = sO + 4 * 16 * HD;                              // [4][16]
     float* sL = sM + 4 * 16;
     __syncthreads();
@@ -443,7 +496,9 @@ prefill_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
 }
 
 // ------------------------------------------------------------------ host side
-template <int HD> constexpr size_t decode_smem() { return (16 * HD + 2 * kStages * kTile * HD) * sizeof(bf16); }
+template <int HD> constexpr size_t decode_smem() {
+    return (16 * HD + 4 * kDecStages * 2 * kChunk * HD) * sizeof(bf16) + kBtCache * sizeof(int);
+}
 template <int HD> constexpr size_t prefill_smem() { return (kTile * HD + 2 * kStages * kTile * HD) * sizeof(bf16); }
 
 template <int HD> static int configure_once() {

@@ -8,8 +8,9 @@
 //   * many tokens (prefill): P = activations, Q = weights, output row-major [M, N];
 //   * few tokens (decode): P = weights, Q = activations, so each thread block streams a 128-row
 //     slab of the weight matrix exactly once and the batch rides on the narrow N side; the
-//     output is written transposed back into [M, N]; K may be split over several blocks
-//     (partials in 32-bit, summed by a second kernel in a fixed order).
+//     output is written transposed back into [M, N]; K may be split over the blocks of a
+//     thread-block cluster, which sum their 32-bit partial tiles through distributed shared
+//     memory in rank order (no scratch in global memory, no second kernel, same bits every run).
 //
 // One thread block = one output tile (x one K split).  Warp 0 (one lane) issues TMA loads of
 // [128 x 64] and [BN x 64] bf16 boxes with the 128-byte swizzle into a ring of shared-memory
@@ -103,6 +104,24 @@ __device__ __forceinline__ void tmem_ld_32x16(uint32_t taddr, uint32_t (&r)[32])
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// thread-block cluster: rank, barrier over all threads of all blocks, peer shared memory
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float4 ld_peer_f4(const void* own_smem, uint32_t rank) {
+    uint32_t peer;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer) : "r"(smem_addr(own_smem)), "r"(rank));
+    float4 v;
+    asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];"
+                 : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(peer) : "memory");
+    return v;
+}
+
 // Shared-memory matrix descriptor of a K-major tile written by TMA with the 128-byte swizzle:
 // rows of 128 bytes, groups of 8 rows 1024 bytes apart (stride byte offset), tile base aligned to
 // 1024 bytes.  Fields: start address >> 4 [0,14), leading byte offset >> 4 [16,30) (unused for
@@ -127,11 +146,110 @@ struct GemmParams {
     long long ldc_i, ldc_j;       // element strides of the output along i and j
     int kb_per_split;             // 64-wide K blocks each split handles
     int num_kb;                   // ceil(K / 64)
-    int out_f32;                  // output element type when there is one split
-    void* out;                    // bf16 or float [.. ldc ..] (splits == 1)
-    float* partial;               // [splits][out elements] (splits > 1)
-    long long partial_stride;     // elements between splits
+    int splits;                   // > 1: the blocks of one tile form a cluster along z
+    int out_f32;                  // output element type
+    int swiglu;                   // 0: plain; 1: weight rows alternate gate/up along j; 2: along i.
+                                  // The output then has half as many columns: silu(gate) * up.
+    void* out;                    // bf16 or float
 };
+
+template <int BN>
+__device__ __forceinline__ void load_acc(uint32_t tmem_base, int q, int c0, bool have, uint32_t (&r)[32]) {
+    if (have) {
+        const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
+        if (BN - c0 >= 32) tmem_ld_32x32(taddr, r);
+        else tmem_ld_32x16(taddr, r);
+        tmem_ld_wait();
+    } else {
+#pragma unroll
+        for (int x = 0; x < 32; ++x) r[x] = 0u;
+    }
+}
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + expf(-g)) * u; }
+
+template <typename T> __device__ __forceinline__ void put(void* base, long long off, float v);
+template <> __device__ __forceinline__ void put<float>(void* base, long long off, float v) {
+    reinterpret_cast<float*>(base)[off] = v;
+}
+template <> __device__ __forceinline__ void put<bf16>(void* base, long long off, float v) {
+    reinterpret_cast<bf16*>(base)[off] = __float2bfloat16_rn(v);
+}
+
+// Store n (<= 32) accumulator values of row i, columns j .. j + n - 1.  The whole warp calls this
+// together (the gate/up exchange of swiglu mode 2 is a warp shuffle).
+template <int BN>
+__device__ __forceinline__ void store_chunk(const GemmParams& prm, uint32_t (&r)[32], int i, int j, int n, int lane) {
+    const bool row_ok = i < prm.rows_p;
+    const int ncols = min(n, prm.rows_q - j);              // may be <= 0
+    if (prm.swiglu == 2) {
+        // rows alternate gate, up: even lanes hold gates, their odd neighbours the matching ups
+        for (int x = 0; x < n; ++x) {
+            const float v = __uint_as_float(r[x]);
+            const float other = __shfl_xor_sync(0xffffffffu, v, 1);
+            if (!(lane & 1) && row_ok && x < ncols) {
+                const long long o = (long long)(i >> 1) * prm.ldc_i + (long long)(j + x) * prm.ldc_j;
+                if (prm.out_f32) put<float>(prm.out, o, silu_mul(v, other));
+                else put<bf16>(prm.out, o, silu_mul(v, other));
+            }
+        }
+        return;
+    }
+    if (!row_ok || ncols <= 0) return;
+    if (prm.swiglu == 1) {
+        // columns alternate gate, up (j is even: tiles start on even columns)
+        const long long o = (long long)i * prm.ldc_i + (long long)(j >> 1) * prm.ldc_j;
+        bf16* dst = reinterpret_cast<bf16*>(prm.out) + o;
+        if (!prm.out_f32 && prm.ldc_j == 1 && ncols == 32 && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+            for (int x = 0; x < 32; x += 16) {
+                uint32_t w[4];
+#pragma unroll
+                for (int y = 0; y < 4; ++y) {
+                    const float a = silu_mul(__uint_as_float(r[x + 4 * y]), __uint_as_float(r[x + 4 * y + 1]));
+                    const float b = silu_mul(__uint_as_float(r[x + 4 * y + 2]), __uint_as_float(r[x + 4 * y + 3]));
+                    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+                    w[y] = *reinterpret_cast<uint32_t*>(&h);
+                }
+                *reinterpret_cast<uint4*>(dst + x / 2) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        } else {
+            for (int x = 0; x + 1 < ncols; x += 2) {
+                const float v = silu_mul(__uint_as_float(r[x]), __uint_as_float(r[x + 1]));
+                if (prm.out_f32) put<float>(prm.out, o + (x >> 1) * prm.ldc_j, v);
+                else put<bf16>(prm.out, o + (x >> 1) * prm.ldc_j, v);
+            }
+        }
+        return;
+    }
+    const long long o = (long long)i * prm.ldc_i + (long long)j * prm.ldc_j;
+    if (prm.out_f32) {
+        float* dst = reinterpret_cast<float*>(prm.out) + o;
+        if (prm.ldc_j == 1 && ncols == 32 && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+            for (int x = 0; x < 32; x += 4)
+                *reinterpret_cast<uint4*>(dst + x) = make_uint4(r[x], r[x + 1], r[x + 2], r[x + 3]);
+        } else {
+            for (int x = 0; x < ncols; ++x) dst[x * prm.ldc_j] = __uint_as_float(r[x]);
+        }
+    } else {
+        bf16* dst = reinterpret_cast<bf16*>(prm.out) + o;
+        if (prm.ldc_j == 1 && ncols == 32 && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+            for (int x = 0; x < 32; x += 8) {
+                uint32_t w[4];
+#pragma unroll
+                for (int y = 0; y < 4; ++y) {
+                    __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[x + 2 * y]), __uint_as_float(r[x + 2 * y + 1]));
+                    w[y] = *reinterpret_cast<uint32_t*>(&h);
+                }
+                *reinterpret_cast<uint4*>(dst + x) = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        } else {
+            for (int x = 0; x < ncols; ++x) dst[x * prm.ldc_j] = __float2bfloat16_rn(__uint_as_float(r[x]));
+        }
+    }
+}
 
 template <int BN, int STAGES>
 struct SmemLayout {
@@ -219,62 +337,64 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     } else {
         // epilogue: warp w may touch TMEM lanes 32 * (w % 4) .. + 31
         const int q = warp & 3;
-        const int i = i0 + q * 32 + lane;
+        const int il = q * 32 + lane;                      // row within the tile
         bool ok = true;
         if (nkb > 0) {
             ok = mbar_wait(acc_full, 0, &abort_flag);
             tc_fence_after();
         }
-        if (ok && !abort_flag) {
-            const bool row_ok = i < prm.rows_p;
+        ok = ok && !abort_flag;
+        if (prm.splits == 1) {
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t r[32];
-                if (nkb > 0) {
-                    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0;
-                    if (BN - c0 >= 32) tmem_ld_32x32(taddr, r);
-                    else { tmem_ld_32x16(taddr, r); }
-                    tmem_ld_wait();
-                } else {
-#pragma unroll
-                    for (int x = 0; x < 32; ++x) r[x] = 0u;
+                load_acc<BN>(tmem_base, q, c0, nkb > 0, r);
+                if (ok) store_chunk<BN>(prm, r, i0 + il, j0 + c0, BN - c0 >= 32 ? 32 : 16, lane);
+            }
+        } else if (ok) {
+            // this block's 32-bit partial tile goes to its own shared memory (the stage buffers
+            // are free: every MMA that read them has completed); the cluster sums them below
+            float* part = reinterpret_cast<float*>(stages) + (size_t)il * BN;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t r[32];
+                load_acc<BN>(tmem_base, q, c0, nkb > 0, r);
+                const int n = BN - c0 >= 32 ? 32 : 16;
+                for (int x = 0; x < n; x += 4)
+                    *reinterpret_cast<uint4*>(part + c0 + x) = make_uint4(r[x], r[x + 1], r[x + 2], r[x + 3]);
+            }
+        }
+    }
+    if (prm.splits > 1) {
+        // The blocks of a tile (one per K split) are one cluster.  After the barrier every block
+        // sums a share of the tile over all blocks' shared memory, in rank order, and stores it.
+        __syncwarp();               // lanes that took a role branch rejoin their warp first
+        cluster_barrier();
+        if (warp >= 2 && !abort_flag) {
+            const uint32_t rank = cluster_rank();
+            const float* part = reinterpret_cast<const float*>(stages);
+            const int t = (warp - 2) * 32 + lane;
+            for (int g4 = (int)rank * 128 + t; g4 < kBM * BN / 4; g4 += prm.splits * 128) {
+                const int e = g4 * 4;
+                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+                for (int peer = 0; peer < prm.splits; ++peer) {
+                    const float4 v = ld_peer_f4(part + e, (uint32_t)peer);
+                    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
                 }
-                if (!row_ok) continue;
-                const int ncols = min(32, min(BN, prm.rows_q - j0) - c0);
-                if (ncols <= 0) continue;
-                const long long o = (long long)i * prm.ldc_i + (long long)(j0 + c0) * prm.ldc_j;
-                if (prm.partial) {
-                    float* dst = prm.partial + (long long)split * prm.partial_stride + o;
-                    for (int x = 0; x < ncols; ++x) dst[x * prm.ldc_j] = __uint_as_float(r[x]);
-                } else if (prm.out_f32) {
-                    float* dst = reinterpret_cast<float*>(prm.out) + o;
-                    if (prm.ldc_j == 1 && ncols == 32 && (((uintptr_t)dst) & 15) == 0) {
-#pragma unroll
-                        for (int x = 0; x < 32; x += 4)
-                            *reinterpret_cast<uint4*>(dst + x) = make_uint4(r[x], r[x + 1], r[x + 2], r[x + 3]);
-                    } else {
-                        for (int x = 0; x < ncols; ++x) dst[x * prm.ldc_j] = __uint_as_float(r[x]);
-                    }
-                } else {
-                    bf16* dst = reinterpret_cast<bf16*>(prm.out) + o;
-                    if (prm.ldc_j == 1 && ncols == 32 && (((uintptr_t)dst) & 15) == 0) {
-#pragma unroll
-                        for (int x = 0; x < 32; x += 8) {
-                            uint4 v;
-                            __nv_bfloat162 h0 = __floats2bfloat162_rn(__uint_as_float(r[x]), __uint_as_float(r[x + 1]));
-                            __nv_bfloat162 h1 = __floats2bfloat162_rn(__uint_as_float(r[x + 2]), __uint_as_float(r[x + 3]));
-                            __nv_bfloat162 h2 = __floats2bfloat162_rn(__uint_as_float(r[x + 4]), __uint_as_float(r[x + 5]));
-                            __nv_bfloat162 h3 = __floats2bfloat162_rn(__uint_as_float(r[x + 6]), __uint_as_float(r[x + 7]));
-                            v.x = *reinterpret_cast<uint32_t*>(&h0); v.y = *reinterpret_cast<uint32_t*>(&h1);
-                            v.z = *reinterpret_cast<uint32_t*>(&h2); v.w = *reinterpret_cast<uint32_t*>(&h3);
-                            *reinterpret_cast<uint4*>(dst + x) = v;
-                        }
-                    } else {
-                        for (int x = 0; x < ncols; ++x) dst[x * prm.ldc_j] = __float2bfloat16_rn(__uint_as_float(r[x]));
+                const int i = i0 + e / BN, j = j0 + e % BN;
+                if (i < prm.rows_p) {
+                    const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
+                    for (int x = 0; x < 4; ++x) {
+                        if (j + x >= prm.rows_q) break;
+                        const long long o = (long long)i * prm.ldc_i + (long long)(j + x) * prm.ldc_j;
+                        if (prm.out_f32) put<float>(prm.out, o, vals[x]);
+                        else put<bf16>(prm.out, o, vals[x]);
                     }
                 }
             }
         }
+        __syncwarp();
+        cluster_barrier();          // nobody leaves while a peer may still read its shared memory
     }
     tc_fence_before();
     __syncthreads();
@@ -282,17 +402,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         tc_fence_after();
         tmem_dealloc(tmem_base, kTmemCols);
     }
-}
-
-// out[e] = sum over splits of partial[s][e], in split order (deterministic)
-template <typename TOut>
-__global__ void splitk_reduce_kernel(const float* __restrict__ partial, long long stride, int splits,
-                                     TOut* __restrict__ out, long long n) {
-    long long e = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (e >= n) return;
-    float acc = 0.f;
-    for (int s = 0; s < splits; ++s) acc += partial[(long long)s * stride + e];
-    out[e] = lsb_from_float<TOut>(acc);
 }
 
 // ------------------------------------------------------------------ host side
@@ -338,8 +447,23 @@ static int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmParams
         configured = (int)cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (configured) return configured;
-    gemm_tc_kernel<BN, STAGES><<<grid, kGemmThreads, smem, stream>>>(mp, mq, prm);
-    return LSB_LAUNCH_CHECK();
+    if (prm.splits == 1) {
+        gemm_tc_kernel<BN, STAGES><<<grid, kGemmThreads, smem, stream>>>(mp, mq, prm);
+        return LSB_LAUNCH_CHECK();
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 1;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = prm.splits;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    return (int)cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES>, mp, mq, prm);
 }
 
 // Can this kernel take the product?  (TMA needs 16-byte aligned bases and row strides.)
@@ -347,18 +471,26 @@ LSB_API int lsb_gemm_tc_supported(const void* x, const void* w, int M, int N, in
     return M > 0 && N > 0 && K > 0 && K % 8 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0;
 }
 
-// How many K splits the decode orientation would use, and the floats of scratch that needs.
-LSB_API int lsb_gemm_tc_plan(int M, int N, int K, int* swap, int* bn, int* splits) {
+// The plan for a product: orientation (swap = weights on the 128-row side), tile width and K
+// splits.  With more than one split the blocks of a tile form a thread-block cluster and sum their
+// partial tiles through distributed shared memory, so there is no scratch in global memory; the
+// portable cluster size limits the splits to 8.
+LSB_API int lsb_gemm_tc_plan(int M, int N, int K, int swiglu, int* swap, int* bn, int* splits) {
     const int num_kb = (K + kBK - 1) / kBK;
     if (M <= 128) {
         *swap = 1;
         *bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
         const int tiles = (N + kBM - 1) / kBM;
         int s = 1;
-        if (tiles < 120) {                       // too few slabs to fill 148 SMs: split K
+        if (tiles < 120 && !swiglu) {            // too few slabs to fill 148 SMs: split K
             s = (148 + tiles - 1) / tiles;
-            s = s < 1 ? 1 : s;
+            if (s > 8) s = 8;
             if (s > num_kb / 4) s = num_kb / 4 > 0 ? num_kb / 4 : 1;   // at least 4 K blocks each
+            if (s < 1) s = 1;
+        }
+        if (s > 1) {                              // no empty splits
+            const int per = (num_kb + s - 1) / s;
+            s = (num_kb + per - 1) / per;
         }
         *splits = s;
     } else {
@@ -382,32 +514,35 @@ LSB_API int lsb_gemm_tc_plan(int M, int N, int K, int* swap, int* bn, int* split
     return 0;
 }
 
-// out[M, N] = x[M, K] * w[N, K]^T, bf16 inputs, bf16 or float output.  `scratch` must hold
-// splits * M * N floats when the plan uses more than one split.
+// out[M, N] = x[M, K] * w[N, K]^T, bf16 inputs, bf16 or float output.
+// swiglu != 0: w has 2 * N_out rows alternating gate_i, up_i; out is [M, N / 2] with
+// out[m, i] = silu(d[m, 2i]) * d[m, 2i + 1].
 LSB_API int lsb_gemm_tc(const void* x, const void* w, void* out, int out_f32, int M, int N, int K,
-                        float* scratch, cudaStream_t stream) {
+                        int swiglu, cudaStream_t stream) {
     if (!lsb_gemm_tc_supported(x, w, M, N, K)) return (int)cudaErrorInvalidValue;
+    if (swiglu && (N % 2)) return (int)cudaErrorInvalidValue;
     int swap, bn, splits;
-    lsb_gemm_tc_plan(M, N, K, &swap, &bn, &splits);
-    if (splits > 1 && !scratch) return (int)cudaErrorInvalidValue;
+    lsb_gemm_tc_plan(M, N, K, swiglu, &swap, &bn, &splits);
+    const int n_out = swiglu ? N / 2 : N;
     GemmParams prm;
     prm.K = K;
     prm.num_kb = (K + kBK - 1) / kBK;
     prm.kb_per_split = (prm.num_kb + splits - 1) / splits;
+    prm.splits = splits;
     prm.out_f32 = out_f32;
     prm.out = out;
-    prm.partial = splits > 1 ? scratch : nullptr;
-    prm.partial_stride = (long long)M * N;
     CUtensorMap mp, mq;
     int rc;
     dim3 grid;
     if (swap) {
-        prm.rows_p = N; prm.rows_q = M; prm.ldc_i = 1; prm.ldc_j = N;
+        prm.rows_p = N; prm.rows_q = M; prm.ldc_i = 1; prm.ldc_j = n_out;
+        prm.swiglu = swiglu ? 2 : 0;
         if ((rc = make_map(&mp, w, N, K, kBM))) return rc;
         if ((rc = make_map(&mq, x, M, K, bn))) return rc;
         grid = dim3((N + kBM - 1) / kBM, 1, splits);
     } else {
-        prm.rows_p = M; prm.rows_q = N; prm.ldc_i = N; prm.ldc_j = 1;
+        prm.rows_p = M; prm.rows_q = N; prm.ldc_i = n_out; prm.ldc_j = 1;
+        prm.swiglu = swiglu ? 1 : 0;
         if ((rc = make_map(&mp, x, M, K, kBM))) return rc;
         if ((rc = make_map(&mq, w, N, K, bn))) return rc;
         grid = dim3((M + kBM - 1) / kBM, (N + bn - 1) / bn, 1);
@@ -419,16 +554,6 @@ LSB_API int lsb_gemm_tc(const void* x, const void* w, void* out, int out_f32, in
         case 128: rc = launch<128, 6>(mp, mq, prm, grid, stream); break;
         case 256: rc = launch<256, 4>(mp, mq, prm, grid, stream); break;
         default: return (int)cudaErrorInvalidValue;
-    }
-    if (rc) return rc;
-    if (splits > 1) {
-        const long long n = (long long)M * N;
-        const int blocks = (int)((n + 255) / 256);
-        if (out_f32)
-            splitk_reduce_kernel<float><<<blocks, 256, 0, stream>>>(scratch, prm.partial_stride, splits, (float*)out, n);
-        else
-            splitk_reduce_kernel<bf16><<<blocks, 256, 0, stream>>>(scratch, prm.partial_stride, splits, (bf16*)out, n);
-        rc = LSB_LAUNCH_CHECK();
     }
     return rc;
 }

@@ -190,12 +190,17 @@ def gather_add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], ro
           _i(_dt(out)), _i(rows.shape[0]), _i(T), _i(H), _f(eps), _stream(out))
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+           gated: bool = False) -> torch.Tensor:
     """x [M, K] times w [N, K] transposed -> [M, N]; 32-bit accumulation.
 
     float32 operands run on the CUDA cores in true 32-bit.  bfloat16 operands run on the
     tensor cores (tcgen05, accumulators in TMEM) when K is a multiple of 8, else on the CUDA
     cores as well.
+
+    ``gated``: the rows of ``w`` alternate gate_i, up_i and the result is [M, N / 2] with
+    ``out[m, i] = silu(d[m, 2i]) * d[m, 2i + 1]`` (applied in the product's epilogue on the
+    tensor-core path, by the activation kernel otherwise).
     """
     _req(x, "x", dim=2)
     _req(w, "w", x.dtype, 2)
@@ -203,27 +208,23 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     N = w.shape[0]
     if w.shape[1] != K:
         raise KernelError(f"linear: x is {tuple(x.shape)}, w is {tuple(w.shape)}")
+    if gated and N % 2:
+        raise KernelError("linear: a gated product needs an even number of weight rows")
     out_dtype = out_dtype or x.dtype
     if out_dtype not in (x.dtype, torch.float32):
         raise KernelError(f"linear: output must be {x.dtype} or float32")
-    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
     if x.dtype == torch.bfloat16 and tensor_core_gemm_ok(x, w):
-        lib = _lib("gemm_tc")
-        swap, bn, splits = ctypes.c_int(), ctypes.c_int(), ctypes.c_int()
-        lib.lsb_gemm_tc_plan(_i(M), _i(N), _i(K), ctypes.byref(swap), ctypes.byref(bn),
-                             ctypes.byref(splits))
-        scratch = None
-        if splits.value > 1:
-            key = ("gemm", x.device, M * N * splits.value)
-            scratch = _scratch.get(key)
-            if scratch is None:
-                scratch = _scratch[key] = torch.empty(M * N * splits.value, dtype=torch.float32,
-                                                      device=x.device)
+        out = torch.empty((M, N // 2 if gated else N), dtype=out_dtype, device=x.device)
         _call("gemm_tc", "lsb_gemm_tc", _p(x), _p(w), _p(out), _i(1 if out_dtype == torch.float32 else 0),
-              _i(M), _i(N), _i(K), _p(scratch), _stream(out))
+              _i(M), _i(N), _i(K), _i(1 if gated else 0), _stream(out))
         return out
+    out = torch.empty((M, N), dtype=out_dtype, device=x.device)
     _call("gemm", "lsb_gemm_nt", _p(x), _p(w), _p(out), _i(_dt(x)), _i(_dt(out)), _i(M), _i(N), _i(K),
           _ll(K), _ll(K), _ll(N), _stream(out))
+    if gated:
+        act = torch.empty((M, N // 2), dtype=out_dtype, device=x.device)
+        swiglu(out, act)
+        return act
     return out
 
 
@@ -233,7 +234,7 @@ def tensor_core_gemm_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
 
 
 def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, i] = silu(gate_up[t, i]) * gate_up[t, I + i]."""
+    """out[t, i] = silu(gate_up[t, 2i]) * gate_up[t, 2i + 1] (gate and up alternate)."""
     _req(gate_up, "gate_up", dim=2)
     _req(out, "out", gate_up.dtype, 2)
     T, I = out.shape
@@ -282,9 +283,9 @@ _TC_HEAD_DIMS = (64, 128)
 
 def decode_splits(n_decode: int, nkv: int) -> int:
     """How many ways each request's keys are split among thread blocks in the decode kernel:
-    enough blocks to fill the GPU twice; a function of the batch alone, so that a captured
-    launch stays valid as sequences grow."""
-    return max(1, min(32, (2 * NUM_SMS) // max(1, n_decode * nkv)))
+    enough blocks for three per SM; a function of the batch alone, so that a captured launch
+    stays valid as sequences grow."""
+    return max(1, min(32, (3 * NUM_SMS) // max(1, n_decode * nkv)))
 
 
 def tensor_core_attention_ok(dtype, hd: int, nh: int, nkv: int) -> bool:
@@ -325,7 +326,7 @@ def paged_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache, s
     if n_decode:
         splits = decode_splits(n_decode, nkv)
         if not getattr(ctx, "fixed_launch", False):
-            splits = min(splits, -(-ctx.max_kv_len // 64))
+            splits = min(splits, -(-ctx.max_kv_len // 128))
         scratch = None
         if splits > 1:
             key = (qkv.device, R, nh, hd, splits)

@@ -2,9 +2,10 @@
 
 Reference: two products, ``silu(g) * u`` with ``silu(g) = g / (1 + exp(-g))``,
 then the down product (models/llama/llama_model.cpp:634-649;
-kernels/src/activations.cu:11-21).  Here gate and up are one product against the
-row-wise concatenation ``[Wgate; Wup]`` and the activation kernel reads both
-halves of each output row; the activation is evaluated in 32-bit.
+kernels/src/activations.cu:11-21).  Here gate and up are one product against a
+matrix whose rows alternate ``Wgate[i], Wup[i]``, so that a gate and its up value
+come out side by side and the activation is applied in the product's epilogue
+(evaluated in 32-bit); the gate/up values themselves never go to memory.
 """
 from __future__ import annotations
 
@@ -32,12 +33,12 @@ class GatedMLP(Part):
                 "down_proj": ParamSpec((H, I))}
 
     def load(self, tensors):
-        self.w_gate_up = torch.cat([tensors["gate_proj"], tensors["up_proj"]], dim=0).contiguous()
+        # rows 2i, 2i + 1 = gate_i, up_i
+        self.w_gate_up = torch.stack([tensors["gate_proj"], tensors["up_proj"]], dim=1).reshape(
+            2 * self.spec.intermediate_size, self.spec.hidden_size).contiguous()
         self.w_down = tensors["down_proj"].contiguous()
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         ops = self.rt.ops
-        gate_up = ops.linear(x, self.w_gate_up)                 # [T, 2I]
-        act = self.rt.empty(x.shape[0], self.spec.intermediate_size)
-        ops.swiglu(gate_up, act)
+        act = ops.linear(x, self.w_gate_up, gated=True)         # [T, I]
         return ops.linear(act, self.w_down)

@@ -41,14 +41,16 @@ def gather_add_rmsnorm(residual, delta, rows, weight, eps, out):
     out.copy_(_rms(x, weight, eps).to(out.dtype))
 
 
-def linear(x, w, out_dtype=None):
+def linear(x, w, out_dtype=None, gated=False):
     y = x.float() @ w.float().T
+    if gated:
+        g, u = y[:, 0::2], y[:, 1::2]
+        y = g / (1 + torch.exp(-g)) * u
     return y.to(out_dtype or x.dtype)
 
 
 def swiglu(gate_up, out):
-    I = out.shape[1]
-    g, u = gate_up[:, :I].float(), gate_up[:, I:].float()
+    g, u = gate_up[:, 0::2].float(), gate_up[:, 1::2].float()
     out.copy_((g / (1 + torch.exp(-g)) * u).to(out.dtype))
 
 

@@ -22,7 +22,7 @@ def _tol(dtype, scale=1.0):
 def ops():
     from llm_singularity_b200 import kernels
     kernels.prepare(["embedding", "norm", "activation", "cache_table", "rope_cache", "attention",
-                     "attention_tc", "gemm", "sampling"])
+                     "attention_tc", "gemm", "gemm_tc", "sampling"])
     yield kernels
     kernels.check_status()
 
@@ -108,7 +108,7 @@ def test_swiglu(ops, dtype):
     gu = _rand(11, 200, dtype=dtype, scale=3.0)
     out = torch.empty(11, 100, dtype=dtype, device="cuda")
     ops.swiglu(gu, out)
-    g, u = gu[:, :100].double(), gu[:, 100:].double()
+    g, u = gu[:, 0::2].double(), gu[:, 1::2].double()       # gate and up alternate
     want = g / (1 + torch.exp(-g)) * u
     assert (out.double() - want).abs().max() <= _tol(dtype, want.abs().max().item())
 
@@ -124,6 +124,35 @@ def test_linear(ops, in_dtype, out_dtype, M, N, K):
     assert y.dtype == out_dtype and y.shape == (M, N)
     tol = 3e-7 * K if out_dtype == torch.float32 else 1e-2 * want.abs().max().item()
     assert (y.double() - want).abs().max() <= tol
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("M, N, K", [(1, 256, 64), (8, 16384, 2048), (40, 200, 72), (300, 1000, 136),
+                                     (2048, 512, 256), (5, 64, 2048)])
+def test_gated_linear(ops, dtype, M, N, K):
+    # out[m, i] = silu(x . w[2i]) * (x . w[2i + 1]); small N with large K makes the decode
+    # orientation split K, so the activation has to wait for the sum of all splits
+    x, w = _rand(M, K, dtype=dtype, seed=1, scale=0.5), _rand(N, K, dtype=dtype, seed=2, scale=0.2)
+    y = ops.linear(x, w, gated=True)
+    d = x.double() @ w.double().T
+    g, u = d[:, 0::2], d[:, 1::2]
+    want = g / (1 + torch.exp(-g)) * u
+    assert y.shape == (M, N // 2) and y.dtype == dtype
+    tol = 3e-6 * K if dtype == torch.float32 else 1.5e-2 * (want.abs().max().item() + 1)
+    assert (y.double() - want).abs().max() <= tol
+
+
+@pytest.mark.parametrize("M, N, K", [(8, 3072, 2048), (8, 2048, 8192), (64, 2048, 2048), (3, 128, 4096)])
+def test_split_k_products_are_repeatable(ops, M, N, K):
+    # the decode orientation splits K over several blocks; the block arriving last sums the partial
+    # tiles in split order, so the bits do not depend on arrival order, and the tile counters are
+    # handed back zeroed for the next launch
+    x, w = _rand(M, K, dtype=torch.bfloat16, seed=3), _rand(N, K, dtype=torch.bfloat16, seed=4)
+    first = ops.linear(x, w, out_dtype=torch.float32)
+    want = x.double() @ w.double().T
+    assert (first.double() - want).abs().max() <= 3e-7 * K * 8
+    for _ in range(5):
+        assert torch.equal(ops.linear(x, w, out_dtype=torch.float32), first)
 
 
 def test_linear_float32_is_true_32_bit(ops):
