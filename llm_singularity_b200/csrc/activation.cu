@@ -11,6 +11,8 @@ LSB_DEFINE_STATUS()
 template <typename T>
 __global__ void swiglu_kernel(const T* __restrict__ gate_up, T* __restrict__ out,
                               int inter, long long total) {
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
     long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long stride = (long long)gridDim.x * blockDim.x;
     for (; idx < total; idx += stride) {
@@ -28,7 +30,7 @@ LSB_API int lsb_swiglu(const void* gate_up, void* out, int dtype, int tokens, in
     const int threads = 256;
     long long blocks = (total + threads - 1) / threads;
     if (blocks > 148 * 32) blocks = 148 * 32;
-    LSB_DISPATCH_DTYPE(dtype, (swiglu_kernel<T><<<(int)blocks, threads, 0, stream>>>(
-        (const T*)gate_up, (T*)out, inter, total)));
-    return LSB_LAUNCH_CHECK();
+    LSB_DISPATCH_DTYPE(dtype, return lsb_launch(swiglu_kernel<T>, dim3((int)blocks), dim3(threads), 0, stream, 1,
+                                                (const T*)gate_up, (T*)out, inter, total));
+    return 0;
 }

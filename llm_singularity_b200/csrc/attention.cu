@@ -63,6 +63,8 @@ paged_attention_generic_kernel(
     T* __restrict__ out,                                    // [tokens, nh*hd]
     int nh, int nkv, int hd, int page_size, int num_pages, float scale, int window) {
     __shared__ float q_sh[kAttnWarps][kMaxHeadDim];
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int r = blockIdx.z, h = blockIdx.y;
     const int qs = q_start[r];
@@ -139,9 +141,10 @@ LSB_API int lsb_paged_attention_generic(
     if (hd % 16 || hd <= 0 || hd > kMaxHeadDim || nkv <= 0 || nh % nkv) return (int)cudaErrorInvalidValue;
     if (n_requests > 65535 || nh > 65535) return (int)cudaErrorInvalidValue;
     dim3 grid((max_q_len + kAttnWarps - 1) / kAttnWarps, nh, n_requests);
-    LSB_DISPATCH_DTYPE(dtype, (paged_attention_generic_kernel<T><<<grid, kAttnWarps * 32, 0, stream>>>(
+    LSB_DISPATCH_DTYPE(dtype, return lsb_launch(
+        paged_attention_generic_kernel<T>, grid, dim3(kAttnWarps * 32), 0, stream, 1,
         (const T*)qkv, qkv_stride, (const T*)k_pages, (const T*)v_pages, q_start, kv_len,
         table_rows, block_table, table_stride, (T*)out, nh, nkv, hd, page_size, num_pages,
-        scale, window)));
-    return LSB_LAUNCH_CHECK();
+        scale, window));
+    return 0;
 }

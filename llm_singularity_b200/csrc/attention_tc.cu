@@ -126,6 +126,8 @@ decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);            // [16][HD]
     bf16* sKV = sQ + 16 * HD;                                // [4 warps][stages][K|V][16][HD]
     int* sBT = reinterpret_cast<int*>(sKV + 4 * kDecStages * kStageElems);
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
 
     const int split = blockIdx.x, g = blockIdx.y, r = blockIdx.z;
     const int qs = q_start[r];
@@ -322,6 +324,8 @@ template <int HD>
 __global__ void decode_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                     const int* __restrict__ q_start, bf16* __restrict__ out, int nh,
                                     int splits) {
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
     const int head = blockIdx.x, r = blockIdx.y;
     const int qs = q_start[r];
     if (q_start[r + 1] - qs != 1) return;
@@ -354,6 +358,8 @@ prefill_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);            // [64][HD]
     bf16* sK = sQ + kTile * HD;
     bf16* sV = sK + kStages * kTile * HD;
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
 
     const int r = blockIdx.z, h = blockIdx.y;
     const int qs = q_start[r];
@@ -536,19 +542,21 @@ LSB_API int lsb_decode_attention(const void* qkv, int qkv_stride, const void* k_
     do {                                                                                           \
         int rc = configure_once<HD>();                                                             \
         if (rc) return rc;                                                                         \
-        decode_attention_kernel<HD><<<grid, kThreads, decode_smem<HD>(), stream>>>(                \
+        rc = lsb_launch(decode_attention_kernel<HD>, grid, dim3(kThreads), decode_smem<HD>(), stream, 1, \
             (const bf16*)qkv, qkv_stride, (const bf16*)k_pages, (const bf16*)v_pages, q_start,    \
             kv_len, table_rows, block_table, table_stride, (bf16*)out, part_o, part_ml, nh, nkv,  \
             page_size, num_pages, scale, window, splits);                                          \
+        if (rc) return rc;                                                                         \
         if (splits > 1)                                                                            \
-            decode_merge_kernel<HD><<<dim3(nh, n_requests), 64, 0, stream>>>(                      \
-                part_o, part_ml, q_start, (bf16*)out, nh, splits);                                 \
+            rc = lsb_launch(decode_merge_kernel<HD>, dim3(nh, n_requests), dim3(64), 0, stream, 1, \
+                (const float*)part_o, (const float*)part_ml, q_start, (bf16*)out, nh, splits);     \
+        if (rc) return rc;                                                                         \
     } while (0)
     if (hd == 64) LAUNCH_DECODE(64);
     else if (hd == 128) LAUNCH_DECODE(128);
     else return (int)cudaErrorInvalidValue;
 #undef LAUNCH_DECODE
-    return LSB_LAUNCH_CHECK();
+    return 0;
 }
 
 // Prompt portions (and, unless skip_single, single tokens too).  bf16, hd 64 or 128.
@@ -564,16 +572,17 @@ LSB_API int lsb_prefill_attention(const void* qkv, int qkv_stride, const void* k
     do {                                                                                           \
         int rc = configure_once<HD>();                                                             \
         if (rc) return rc;                                                                         \
-        prefill_attention_kernel<HD><<<grid, kThreads, prefill_smem<HD>(), stream>>>(              \
+        rc = lsb_launch(prefill_attention_kernel<HD>, grid, dim3(kThreads), prefill_smem<HD>(), stream, 1, \
             (const bf16*)qkv, qkv_stride, (const bf16*)k_pages, (const bf16*)v_pages, q_start,    \
             kv_len, table_rows, block_table, table_stride, (bf16*)out, nh, nkv, page_size,        \
             num_pages, scale, window, skip_single);                                                \
+        if (rc) return rc;                                                                         \
     } while (0)
     if (hd == 64) LAUNCH_PREFILL(64);
     else if (hd == 128) LAUNCH_PREFILL(128);
     else return (int)cudaErrorInvalidValue;
 #undef LAUNCH_PREFILL
-    return LSB_LAUNCH_CHECK();
+    return 0;
 }
 
 // ------------------------------------------------------------------ no-allocation entry point
@@ -632,16 +641,18 @@ LSB_API int lsb_decode_attention_noalloc(const void* qkv, int qkv_stride, const 
     do {                                                                                           \
         int rc = configure_once<HD>();                                                             \
         if (rc) return rc;                                                                         \
-        decode_attention_kernel<HD><<<grid, kThreads, decode_smem<HD>(), stream>>>(                \
+        rc = lsb_launch(decode_attention_kernel<HD>, grid, dim3(kThreads), decode_smem<HD>(), stream, 1, \
             (const bf16*)qkv, qkv_stride, (const bf16*)k_pages, (const bf16*)v_pages, q_start,    \
             kv_len, table_rows, block_table, table_stride, (bf16*)out, part_o, part_ml, nh, nkv,  \
             page_size, num_pages, scale, window, splits);                                          \
+        if (rc) return rc;                                                                         \
         if (splits > 1)                                                                            \
-            decode_merge_kernel<HD><<<dim3(nh, n_requests), 64, 0, stream>>>(                      \
-                part_o, part_ml, q_start, (bf16*)out, nh, splits);                                 \
+            rc = lsb_launch(decode_merge_kernel<HD>, dim3(nh, n_requests), dim3(64), 0, stream, 1, \
+                (const float*)part_o, (const float*)part_ml, q_start, (bf16*)out, nh, splits);     \
+        if (rc) return rc;                                                                         \
     } while (0)
     if (hd == 64) LAUNCH_DECODE_NOALLOC(64);
     else LAUNCH_DECODE_NOALLOC(128);
 #undef LAUNCH_DECODE_NOALLOC
-    return LSB_LAUNCH_CHECK();
+    return 0;
 }

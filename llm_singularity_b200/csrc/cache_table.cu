@@ -8,6 +8,8 @@ LSB_DEFINE_STATUS()
 
 __global__ void scatter_i32_kernel(int* __restrict__ dst, const int* __restrict__ idx,
                                    const int* __restrict__ val, int n, long long dst_size) {
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const int j = idx[i];
@@ -18,14 +20,16 @@ __global__ void scatter_i32_kernel(int* __restrict__ dst, const int* __restrict_
 LSB_API int lsb_scatter_i32(int* dst, const int* idx, const int* val, int n, long long dst_size,
                             cudaStream_t stream) {
     if (n <= 0) return 0;
-    scatter_i32_kernel<<<(n + 255) / 256, 256, 0, stream>>>(dst, idx, val, n, dst_size);
-    return LSB_LAUNCH_CHECK();
+    return lsb_launch(scatter_i32_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, 1, dst, idx, val, n,
+                      dst_size);
 }
 
 // The same with the count on the device: packed = [n, idx[cap], val[cap]].  A captured graph can
 // hold this launch and still apply a different number of changes at every replay.
 __global__ void scatter_i32_counted_kernel(int* __restrict__ dst, const int* __restrict__ packed,
                                            int cap, long long dst_size) {
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
     int n = packed[0];
     if (n > cap) { if (threadIdx.x == 0) lsb_set_status(LSB_BAD_ROW); n = cap; }
     const int* idx = packed + 1;
@@ -40,6 +44,5 @@ __global__ void scatter_i32_counted_kernel(int* __restrict__ dst, const int* __r
 LSB_API int lsb_scatter_i32_counted(int* dst, const int* packed, int cap, long long dst_size,
                                     cudaStream_t stream) {
     if (cap <= 0) return 0;
-    scatter_i32_counted_kernel<<<1, 256, 0, stream>>>(dst, packed, cap, dst_size);
-    return LSB_LAUNCH_CHECK();
+    return lsb_launch(scatter_i32_counted_kernel, dim3(1), dim3(256), 0, stream, 1, dst, packed, cap, dst_size);
 }

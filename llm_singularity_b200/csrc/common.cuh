@@ -82,6 +82,57 @@ __device__ __forceinline__ float lsb_block_sum(float v, float* scratch) {
 
 #define LSB_LAUNCH_CHECK() ((int)cudaGetLastError())
 
+// Programmatic dependent launch.  Every kernel of these libraries is launched with the
+// "programmatic stream serialization" attribute: it may become resident while the kernel before
+// it in the stream is still running, set itself up, and must call lsb_pdl_wait() before it reads
+// or writes anything an earlier kernel of the stream touches (the wait returns once that kernel
+// has completed and its writes are visible).  lsb_pdl_launch_dependents() at a kernel's start lets
+// the next kernel of the stream do the same.  What this hides is launch latency, block
+// scheduling, per-block set-up and, in the matrix products, the first loads of weights.
+__device__ __forceinline__ void lsb_pdl_launch_dependents() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void lsb_pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+#include <stdlib.h>
+static inline bool lsb_pdl_enabled() {
+    static int on = -1;
+    if (on < 0) {
+        const char* e = getenv("LSB_PDL");
+        on = (e && e[0] == '0') ? 0 : 1;
+    }
+    return on != 0;
+}
+
+// kernel<<<grid, block, smem, stream>>>(args...) with the launch attributes above; cluster_z > 1
+// makes the blocks along z one thread-block cluster.
+template <typename... KArgs, typename... Args>
+static inline int lsb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                             cudaStream_t stream, int cluster_z, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (lsb_pdl_enabled()) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster_z > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = 1;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = cluster_z;
+        ++n;
+    }
+    cfg.attrs = attr;
+    cfg.numAttrs = n;
+    return (int)cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...);
+}
+
 // Calls `body` with `T` bound to the element type named by `dtype`.
 #define LSB_DISPATCH_DTYPE(dtype, ...)                                               \
     do {                                                                             \

@@ -10,6 +10,8 @@ LSB_DEFINE_STATUS()
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                                  float* __restrict__ out, int hidden, int vocab) {
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
     const int t = blockIdx.x;
     const int id = ids[t];
     float* o = out + (size_t)t * hidden;
@@ -26,7 +28,7 @@ LSB_API int lsb_embedding(const void* table, int dtype, const int* ids, float* o
                           int tokens, int hidden, int vocab, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     int threads = hidden < 256 ? ((hidden + 31) / 32) * 32 : 256;
-    LSB_DISPATCH_DTYPE(dtype, (embedding_kernel<T><<<tokens, threads, 0, stream>>>(
-        (const T*)table, ids, out, hidden, vocab)));
-    return LSB_LAUNCH_CHECK();
+    LSB_DISPATCH_DTYPE(dtype, return lsb_launch(embedding_kernel<T>, dim3(tokens), dim3(threads), 0, stream, 1,
+                                                (const T*)table, ids, out, hidden, vocab));
+    return 0;
 }

@@ -42,6 +42,8 @@ gemm_nt_kernel(const TIn* __restrict__ A, const TIn* __restrict__ W, TOut* __res
                int M, int N, int K, long long lda, long long ldw, long long ldc, bool vec_ok) {
     __shared__ __align__(16) float As[BK][BM + 4];
     __shared__ __align__(16) float Ws[BK][BN + 4];
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
     const int tid = threadIdx.x;
     const int ty = tid / (BN / TN), tx = tid % (BN / TN);
     const long long m0 = (long long)blockIdx.y * BM, n0 = (long long)blockIdx.x * BN;
@@ -95,19 +97,17 @@ LSB_API int lsb_gemm_nt(const void* A, const void* W, void* C, int in_dtype, int
     const int esize = in_dtype == LSB_F32 ? 4 : 2;
     const bool vec_ok = ((uintptr_t)A % (4 * esize) == 0) && ((uintptr_t)W % (4 * esize) == 0) &&
                         lda % 4 == 0 && ldw % 4 == 0;
-    if (in_dtype == LSB_F32 && out_dtype == LSB_F32) {
-        gemm_nt_kernel<float, float><<<grid, kGemmThreads, 0, stream>>>(
-            (const float*)A, (const float*)W, (float*)C, M, N, K, lda, ldw, ldc, vec_ok);
-    } else if (in_dtype == LSB_BF16 && out_dtype == LSB_BF16) {
-        gemm_nt_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, kGemmThreads, 0, stream>>>(
-            (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, (__nv_bfloat16*)C, M, N, K, lda, ldw,
-            ldc, vec_ok);
-    } else if (in_dtype == LSB_BF16 && out_dtype == LSB_F32) {
-        gemm_nt_kernel<__nv_bfloat16, float><<<grid, kGemmThreads, 0, stream>>>(
-            (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, (float*)C, M, N, K, lda, ldw, ldc,
-            vec_ok);
-    } else {
-        return (int)cudaErrorInvalidValue;
-    }
-    return LSB_LAUNCH_CHECK();
+    const dim3 block(kGemmThreads);
+    if (in_dtype == LSB_F32 && out_dtype == LSB_F32)
+        return lsb_launch(gemm_nt_kernel<float, float>, grid, block, 0, stream, 1, (const float*)A,
+                          (const float*)W, (float*)C, M, N, K, lda, ldw, ldc, vec_ok);
+    if (in_dtype == LSB_BF16 && out_dtype == LSB_BF16)
+        return lsb_launch(gemm_nt_kernel<__nv_bfloat16, __nv_bfloat16>, grid, block, 0, stream, 1,
+                          (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, (__nv_bfloat16*)C, M, N, K,
+                          lda, ldw, ldc, vec_ok);
+    if (in_dtype == LSB_BF16 && out_dtype == LSB_F32)
+        return lsb_launch(gemm_nt_kernel<__nv_bfloat16, float>, grid, block, 0, stream, 1,
+                          (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, (float*)C, M, N, K, lda, ldw,
+                          ldc, vec_ok);
+    return (int)cudaErrorInvalidValue;
 }

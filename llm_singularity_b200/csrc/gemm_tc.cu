@@ -150,6 +150,7 @@ struct GemmParams {
     int out_f32;                  // output element type
     int swiglu;                   // 0: plain; 1: weight rows alternate gate/up along j; 2: along i.
                                   // The output then has half as many columns: silu(gate) * up.
+    int static_operand;           // 1: P holds weights, 2: Q does (loaded before the PDL wait)
     void* out;                    // bf16 or float
 };
 
@@ -261,7 +262,7 @@ struct SmemLayout {
 };
 
 template <int BN, int STAGES>
-__global__ void __launch_bounds__(kGemmThreads, 1)
+__global__ void __launch_bounds__(kGemmThreads)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                const GemmParams prm) {
     using L = SmemLayout<BN, STAGES>;
@@ -295,15 +296,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    lsb_pdl_launch_dependents();
+    if (threadIdx.x != 0) lsb_pdl_wait();      // thread 0 (the TMA producer) waits after its prefetch
 
     if (warp == 0) {
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_p) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
-            int issued = 0;
-            for (int kb = 0; kb < nkb; ++kb) {
+            // Weights are not written by anything in the stream: their first STAGES boxes are
+            // requested before the wait on the previous kernel, the activations after it.
+            const int pre = min(nkb, STAGES);
+            for (int kb = 0; kb < pre; ++kb) {
+                unsigned char* st = stages + (size_t)kb * L::kStageBytes;
+                mbar_expect_tx(&full[kb], L::kStageBytes);
+                if (prm.static_operand == 1) tma_load_2d(st, &map_p, &full[kb], (kb0 + kb) * kBK, i0);
+                else tma_load_2d(st + L::kPBytes, &map_q, &full[kb], (kb0 + kb) * kBK, j0);
+            }
+            lsb_pdl_wait();
+            for (int kb = 0; kb < pre; ++kb) {
+                unsigned char* st = stages + (size_t)kb * L::kStageBytes;
+                if (prm.static_operand == 1) tma_load_2d(st + L::kPBytes, &map_q, &full[kb], (kb0 + kb) * kBK, j0);
+                else tma_load_2d(st, &map_p, &full[kb], (kb0 + kb) * kBK, i0);
+            }
+            int issued = pre;
+            for (int kb = pre; kb < nkb; ++kb) {
                 const int s = kb % STAGES;
-                if (kb >= STAGES && !mbar_wait(&empty[s], ((kb / STAGES) - 1) & 1, &abort_flag)) break;
+                if (!mbar_wait(&empty[s], ((kb / STAGES) - 1) & 1, &abort_flag)) break;
                 mbar_expect_tx(&full[s], L::kStageBytes);
                 unsigned char* st = stages + (size_t)s * L::kStageBytes;
                 tma_load_2d(st, &map_p, &full[s], (kb0 + kb) * kBK, i0);
@@ -447,23 +465,7 @@ static int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmParams
         configured = (int)cudaFuncSetAttribute(gemm_tc_kernel<BN, STAGES>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (configured) return configured;
-    if (prm.splits == 1) {
-        gemm_tc_kernel<BN, STAGES><<<grid, kGemmThreads, smem, stream>>>(mp, mq, prm);
-        return LSB_LAUNCH_CHECK();
-    }
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = grid;
-    cfg.blockDim = dim3(kGemmThreads);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = 1;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = prm.splits;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    return (int)cudaLaunchKernelEx(&cfg, gemm_tc_kernel<BN, STAGES>, mp, mq, prm);
+    return lsb_launch(gemm_tc_kernel<BN, STAGES>, grid, dim3(kGemmThreads), smem, stream, prm.splits, mp, mq, prm);
 }
 
 // Can this kernel take the product?  (TMA needs 16-byte aligned bases and row strides.)
@@ -537,23 +539,38 @@ LSB_API int lsb_gemm_tc(const void* x, const void* w, void* out, int out_f32, in
     if (swap) {
         prm.rows_p = N; prm.rows_q = M; prm.ldc_i = 1; prm.ldc_j = n_out;
         prm.swiglu = swiglu ? 2 : 0;
+        prm.static_operand = 1;
         if ((rc = make_map(&mp, w, N, K, kBM))) return rc;
         if ((rc = make_map(&mq, x, M, K, bn))) return rc;
         grid = dim3((N + kBM - 1) / kBM, 1, splits);
     } else {
         prm.rows_p = M; prm.rows_q = N; prm.ldc_i = n_out; prm.ldc_j = 1;
         prm.swiglu = swiglu ? 1 : 0;
+        prm.static_operand = 2;
         if ((rc = make_map(&mp, x, M, K, kBM))) return rc;
         if ((rc = make_map(&mq, w, N, K, bn))) return rc;
         grid = dim3((M + kBM - 1) / kBM, (N + bn - 1) / bn, 1);
     }
-    switch (bn) {
-        case 16: rc = launch<16, 8>(mp, mq, prm, grid, stream); break;
-        case 32: rc = launch<32, 8>(mp, mq, prm, grid, stream); break;
-        case 64: rc = launch<64, 6>(mp, mq, prm, grid, stream); break;
-        case 128: rc = launch<128, 6>(mp, mq, prm, grid, stream); break;
-        case 256: rc = launch<256, 4>(mp, mq, prm, grid, stream); break;
-        default: return (int)cudaErrorInvalidValue;
+    // Blocks of a split product are co-scheduled as clusters: four stages keep their shared memory
+    // small enough for two or three blocks per SM, so that every cluster finds room at once.
+    // Unsplit products run one block per SM and want the deeper ring to keep HBM busy.
+    if (splits > 1) {
+        switch (bn) {
+            case 16: rc = launch<16, 4>(mp, mq, prm, grid, stream); break;
+            case 32: rc = launch<32, 4>(mp, mq, prm, grid, stream); break;
+            case 64: rc = launch<64, 4>(mp, mq, prm, grid, stream); break;
+            case 128: rc = launch<128, 4>(mp, mq, prm, grid, stream); break;
+            default: return (int)cudaErrorInvalidValue;
+        }
+    } else {
+        switch (bn) {
+            case 16: rc = launch<16, 8>(mp, mq, prm, grid, stream); break;
+            case 32: rc = launch<32, 8>(mp, mq, prm, grid, stream); break;
+            case 64: rc = launch<64, 6>(mp, mq, prm, grid, stream); break;
+            case 128: rc = launch<128, 6>(mp, mq, prm, grid, stream); break;
+            case 256: rc = launch<256, 4>(mp, mq, prm, grid, stream); break;
+            default: return (int)cudaErrorInvalidValue;
+        }
     }
     return rc;
 }

@@ -21,6 +21,8 @@ add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                    const int* __restrict__ rows, const float* __restrict__ weight,
                    T* __restrict__ out, int hidden, int n_rows_total, float eps) {
     __shared__ float scratch[33];
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
     const int r_out = blockIdx.x;
     int r_in = r_out;
     if (GATHER) {
@@ -82,9 +84,10 @@ add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
 LSB_API int lsb_add_rmsnorm(float* residual, const void* delta, const float* weight, void* out,
                             int dtype, int rows, int hidden, float eps, cudaStream_t stream) {
     if (rows <= 0) return 0;
-    LSB_DISPATCH_DTYPE(dtype, (add_rmsnorm_kernel<T, false><<<rows, kNormThreads, 0, stream>>>(
-        residual, (const T*)delta, nullptr, weight, (T*)out, hidden, rows, eps)));
-    return LSB_LAUNCH_CHECK();
+    LSB_DISPATCH_DTYPE(dtype, return lsb_launch(
+        add_rmsnorm_kernel<T, false>, dim3(rows), dim3(kNormThreads), 0, stream, 1,
+        residual, (const T*)delta, (const int*)nullptr, weight, (T*)out, hidden, rows, eps));
+    return 0;
 }
 
 // out[i,:] = norm(residual[rows[i],:] + delta[rows[i],:]); residual is not modified.
@@ -92,7 +95,8 @@ LSB_API int lsb_gather_add_rmsnorm(const float* residual, const void* delta, con
                                    const float* weight, void* out, int dtype, int n_out,
                                    int n_rows_total, int hidden, float eps, cudaStream_t stream) {
     if (n_out <= 0) return 0;
-    LSB_DISPATCH_DTYPE(dtype, (add_rmsnorm_kernel<T, true><<<n_out, kNormThreads, 0, stream>>>(
-        (float*)residual, (const T*)delta, rows, weight, (T*)out, hidden, n_rows_total, eps)));
-    return LSB_LAUNCH_CHECK();
+    LSB_DISPATCH_DTYPE(dtype, return lsb_launch(
+        add_rmsnorm_kernel<T, true>, dim3(n_out), dim3(kNormThreads), 0, stream, 1,
+        (float*)residual, (const T*)delta, rows, weight, (T*)out, hidden, n_rows_total, eps));
+    return 0;
 }

@@ -22,6 +22,8 @@ __global__ void rope_kv_store_kernel(
     const float* __restrict__ inv_freq, int rotary_dim,
     T* __restrict__ k_pages, T* __restrict__ v_pages,
     int nh, int nkv, int hd, int page_size, int num_pages, int store) {
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
     const int t = blockIdx.x;
     const int pos = positions[t];
     const int half_hd = hd >> 1;
@@ -91,8 +93,9 @@ LSB_API int lsb_rope_kv_store(void* qkv, int dtype, int tokens, int nh, int nkv,
         return (int)cudaErrorInvalidValue;
     int work = (nh + nkv) * (hd / 2);
     int threads = work >= 256 ? 256 : ((work + 31) / 32) * 32;
-    LSB_DISPATCH_DTYPE(dtype, (rope_kv_store_kernel<T><<<tokens, threads, 0, stream>>>(
+    LSB_DISPATCH_DTYPE(dtype, return lsb_launch(
+        rope_kv_store_kernel<T>, dim3(tokens), dim3(threads), 0, stream, 1,
         (T*)qkv, positions, token_req, table_rows, block_table, table_stride, inv_freq, rotary_dim,
-        (T*)k_pages, (T*)v_pages, nh, nkv, hd, page_size, num_pages, store)));
-    return LSB_LAUNCH_CHECK();
+        (T*)k_pages, (T*)v_pages, nh, nkv, hd, page_size, num_pages, store));
+    return 0;
 }

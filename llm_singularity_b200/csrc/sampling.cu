@@ -92,6 +92,8 @@ sample_kernel(const float* __restrict__ logits, float* __restrict__ work, int vo
               int* __restrict__ out) {
     __shared__ BlockScratch sc;
     __shared__ float chunk_sum[kSampleThreads];
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
     const int row = blockIdx.x, tid = threadIdx.x;
     const float temperature = params[row * 4 + 0], top_p = params[row * 4 + 1];
     const float penalty = params[row * 4 + 2], u = params[row * 4 + 3];
@@ -205,7 +207,6 @@ LSB_API int lsb_sample(const float* logits, float* work, int rows, int vocab, co
                        cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) return (int)cudaErrorInvalidValue;
-    sample_kernel<<<rows, kSampleThreads, 0, stream>>>(logits, work, vocab, params, top_k, prev_start,
-                                                      prev_tokens, out);
-    return LSB_LAUNCH_CHECK();
+    return lsb_launch(sample_kernel, dim3(rows), dim3(kSampleThreads), 0, stream, 1, logits, work, vocab,
+                      params, top_k, prev_start, prev_tokens, out);
 }
