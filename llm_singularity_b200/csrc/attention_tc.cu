@@ -16,7 +16,8 @@
 //    finishes.  The split count depends only on the batch, and each split finds
 //    its share of tiles from the request's length on the device, so a captured launch stays
 //    valid as sequences grow.
-//  * prefill: one thread block per (64-query tile, head, request); warp w owns rows 16w..16w+15.
+//  * prefill: one thread block per (128-query tile, head, request); warp w of 8 owns rows
+//    16w..16w+15; K/V tiles of 64 keys in a three-stage ring; tiles below the diagonal skip the mask.
 //    Query row i of a request with q_len new tokens and kv_len cached tokens sits at position
 //    p = kv_len - q_len + i and sees keys [max(0, p - window + 1), p].
 //
@@ -33,7 +34,6 @@ typedef __nv_bfloat16 bf16;
 
 constexpr int kTile = 64;        // keys per tile
 constexpr int kThreads = 128;
-constexpr int kStages = 2;
 constexpr float kLog2e = 1.4426950408889634f;
 
 // ------------------------------------------------------------------ PTX helpers
@@ -62,6 +62,13 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+// 2^x on the special-function unit (one MUFU.EX2; fast_exp2() adds range handling around it that the
+// softmax does not need: arguments here are <= 0 and -inf gives 0)
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -70,32 +77,6 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
 // A tile is rows of HD bf16 = HD/8 chunks of 16 bytes; chunk c of row r lives at chunk c ^ (r & 7).
 template <int HD> __device__ __forceinline__ bf16* tile_ptr(bf16* base, int row, int chunk) {
     return base + (row * (HD / 8) + (chunk ^ (row & 7))) * 8;
-}
-
-// Stage one 64-key tile of K and V of kv head g into shared memory (zero rows outside [lo, hi]).
-template <int HD>
-__device__ __forceinline__ void load_kv_tile(bf16* sK, bf16* sV, const bf16* __restrict__ k_pages,
-                                             const bf16* __restrict__ v_pages, const int* __restrict__ bt,
-                                             int tile, int lo, int hi, int g, int nkv, int page_size,
-                                             int num_pages) {
-    constexpr int CPR = HD / 8;
-    for (int idx = threadIdx.x; idx < kTile * CPR; idx += kThreads) {
-        const int kk = idx / CPR, c = idx - kk * CPR;
-        const int key = tile * kTile + kk;
-        bool valid = key >= lo && key <= hi;
-        long long off = 0;
-        if (valid) {
-            const int page = bt[key / page_size];
-            if (page < 0 || page >= num_pages) {
-                lsb_set_status(LSB_BAD_PAGE);
-                valid = false;
-            } else {
-                off = (((long long)page * nkv + g) * page_size + (key % page_size)) * HD + c * 8;
-            }
-        }
-        cp_async16(tile_ptr<HD>(sK, kk, c), k_pages + off, valid);
-        cp_async16(tile_ptr<HD>(sV, kk, c), v_pages + off, valid);
-    }
 }
 
 // ------------------------------------------------------------------ decode
@@ -243,7 +224,7 @@ decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
             mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
             mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
             const float m_new = fmaxf(m[h], mx[h]);
-            corr[h] = (m[h] == -INFINITY) ? 0.f : exp2f(m[h] - m_new);
+            corr[h] = (m[h] == -INFINITY) ? 0.f : fast_exp2(m[h] - m_new);
             m[h] = m_new;
             l[h] *= corr[h];
         }
@@ -251,7 +232,7 @@ decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const float pv = (s[nt][e] == -INFINITY) ? 0.f : exp2f(s[nt][e] - m[e >> 1]);
+                const float pv = (s[nt][e] == -INFINITY) ? 0.f : fast_exp2(s[nt][e] - m[e >> 1]);
                 s[nt][e] = pv;
                 l[e >> 1] += pv;
             }
@@ -304,7 +285,7 @@ decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
             const float mw = sM[w * 16 + h];
-            const float f = (mw == -INFINITY) ? 0.f : exp2f(mw - M);
+            const float f = (mw == -INFINITY) ? 0.f : fast_exp2(mw - M);
             L += sL[w * 16 + h] * f;
             O += sO[(w * 16 + h) * HD + d] * f;
         }
@@ -336,7 +317,7 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_o, const floa
         float L = 0.f, O = 0.f;
         for (int s = 0; s < splits; ++s) {
             const float ms = part_ml[(base + s) * 2];
-            const float f = (ms == -INFINITY) ? 0.f : exp2f(ms - M);
+            const float f = (ms == -INFINITY) ? 0.f : fast_exp2(ms - M);
             L += part_ml[(base + s) * 2 + 1] * f;
             O += part_o[(base + s) * HD + d] * f;
         }
@@ -345,8 +326,42 @@ __global__ void decode_merge_kernel(const float* __restrict__ part_o, const floa
 }
 
 // ------------------------------------------------------------------ prefill
+constexpr int kPfRows = 128;         // query rows per block (8 warps x 16)
+constexpr int kPfThreads = 256;
+constexpr int kPfStages = 3;
+
+// Stage one 64-key tile of K and V for the prefill kernel: 256 threads, the block's slice of the
+// block table already in shared memory.
 template <int HD>
-__global__ void __launch_bounds__(kThreads)
+__device__ __forceinline__ void pf_load_tile(bf16* sK, bf16* sV, const bf16* __restrict__ k_pages,
+                                             const bf16* __restrict__ v_pages, const int* __restrict__ bt,
+                                             const int* sBT, bool cached, int page0, int table_stride,
+                                             int tile, int lo, int hi, int g, int nkv, int page_size,
+                                             int page_shift, int num_pages) {
+    constexpr int CPR = HD / 8;
+#pragma unroll
+    for (int idx = threadIdx.x; idx < kTile * CPR; idx += kPfThreads) {
+        const int kk = idx / CPR, c = idx - kk * CPR;
+        const int key = tile * kTile + kk;
+        bool valid = key >= lo && key <= hi;
+        long long off = 0;
+        if (valid) {
+            const int pi = div_page(key, page_size, page_shift);
+            const int page = cached ? sBT[pi - page0] : (pi < table_stride ? bt[pi] : -1);
+            if (page < 0 || page >= num_pages) {
+                lsb_set_status(LSB_BAD_PAGE);
+                valid = false;
+            } else {
+                off = (((long long)page * nkv + g) * page_size + (key - pi * page_size)) * HD + c * 8;
+            }
+        }
+        cp_async16(tile_ptr<HD>(sK, kk, c), k_pages + off, valid);
+        cp_async16(tile_ptr<HD>(sV, kk, c), v_pages + off, valid);
+    }
+}
+
+template <int HD>
+__global__ void __launch_bounds__(kPfThreads)
 prefill_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
                          const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                          const int* __restrict__ q_start, const int* __restrict__ kv_len_arr,
@@ -355,37 +370,56 @@ prefill_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
                          int num_pages, float scale, int window, int skip_single) {
     constexpr int CPR = HD / 8, KS = HD / 16;
     extern __shared__ __align__(128) unsigned char smem_raw[];
-    bf16* sQ = reinterpret_cast<bf16*>(smem_raw);            // [64][HD]
-    bf16* sK = sQ + kTile * HD;
-    bf16* sV = sK + kStages * kTile * HD;
+    bf16* sQ = reinterpret_cast<bf16*>(smem_raw);            // [128][HD]
+    bf16* sK = sQ + kPfRows * HD;                            // [stages][64][HD]
+    bf16* sV = sK + kPfStages * kTile * HD;
+    int* sBT = reinterpret_cast<int*>(sV + kPfStages * kTile * HD);
     lsb_pdl_launch_dependents();
     lsb_pdl_wait();
 
     const int r = blockIdx.z, h = blockIdx.y;
     const int qs = q_start[r];
     const int q_len = q_start[r + 1] - qs;
-    const int i0 = blockIdx.x * kTile;
-    if (i0 >= q_len || (skip_single && q_len == 1)) return;
+    // heavy tiles (late rows see the most keys) are scheduled first
+    const int n_qt = (q_len + kPfRows - 1) / kPfRows;
+    if ((int)blockIdx.x >= n_qt || (skip_single && q_len == 1)) return;
+    const int i0 = (n_qt - 1 - (int)blockIdx.x) * kPfRows;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = h / (nh / nkv);
     const int kv_len = kv_len_arr[r];
     const int p0 = kv_len - q_len + i0;                       // position of the tile's first row
-    const int rows = min(kTile, q_len - i0);
+    const int rows = min(kPfRows, q_len - i0);
     const int p_last = p0 + rows - 1;
     const int lo_cta = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
     const int* bt = block_table + (size_t)table_rows[r] * table_stride;
+    const int page_shift = (page_size & (page_size - 1)) == 0 ? __ffs(page_size) - 1 : -1;
     const int t0 = lo_cta / kTile, t1 = p_last / kTile + 1;
 
-    for (int idx = threadIdx.x; idx < kTile * CPR; idx += kThreads) {
+    const int page0 = div_page(t0 * kTile, page_size, page_shift);
+    const int n_pages_here = div_page(p_last, page_size, page_shift) - page0 + 1;
+    const bool cached = n_pages_here <= kBtCache;
+    if (cached)
+        for (int idx = threadIdx.x; idx < n_pages_here; idx += kPfThreads)
+            sBT[idx] = (page0 + idx < table_stride) ? bt[page0 + idx] : -1;
+    for (int idx = threadIdx.x; idx < kPfRows * CPR; idx += kPfThreads) {
         const int row = idx / CPR, c = idx - row * CPR;
         uint4 v = make_uint4(0, 0, 0, 0);
         if (row < rows)
             v = *reinterpret_cast<const uint4*>(qkv + (size_t)(qs + i0 + row) * qkv_stride + (size_t)h * HD + c * 8);
         *reinterpret_cast<uint4*>(tile_ptr<HD>(sQ, row, c)) = v;
     }
-    load_kv_tile<HD>(sK, sV, k_pages, v_pages, bt, t0, lo_cta, p_last, g, nkv, page_size, num_pages);
-    cp_async_commit();
     __syncthreads();
+
+    auto issue = [&](int t) {
+        if (t < t1) {
+            const int st = (t - t0) % kPfStages;
+            pf_load_tile<HD>(sK + st * kTile * HD, sV + st * kTile * HD, k_pages, v_pages, bt, sBT, cached, page0,
+                             table_stride, t, lo_cta, p_last, g, nkv, page_size, page_shift, num_pages);
+        }
+        cp_async_commit();
+    };
+#pragma unroll
+    for (int i = 0; i < kPfStages - 1; ++i) issue(t0 + i);
 
     uint32_t qf[KS][4];
 #pragma unroll
@@ -401,22 +435,21 @@ prefill_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
     const int row_a = warp * 16 + (lane >> 2), row_b = row_a + 8;
     const int pos[2] = {p0 + row_a, p0 + row_b};
     const bool live[2] = {row_a < rows, row_b < rows};
+    const int warp_first = p0 + warp * 16;                     // position of the warp's first row
     const int warp_hi = p0 + min(warp * 16 + 15, rows - 1);    // last position any row of the warp sees
-    const int warp_lo = (window > 0) ? max(0, p0 + warp * 16 - window + 1) : 0;
+    const int warp_lo = (window > 0) ? max(0, warp_first - window + 1) : 0;
+    const bool warp_live = warp * 16 < rows;
 
     for (int t = t0; t < t1; ++t) {
-        const int stage = (t - t0) & 1;
-        if (t + 1 < t1)
-            load_kv_tile<HD>(sK + (stage ^ 1) * kTile * HD, sV + (stage ^ 1) * kTile * HD, k_pages, v_pages,
-                             bt, t + 1, lo_cta, p_last, g, nkv, page_size, num_pages);
-        cp_async_commit();
-        cp_async_wait<1>();
-        __syncthreads();
+        cp_async_wait<kPfStages - 2>();
+        __syncthreads();                                       // tile t has landed; tile t-1 is free
+        issue(t + kPfStages - 1);
+        const int stage = (t - t0) % kPfStages;
         bf16* tK = sK + stage * kTile * HD;
         bf16* tV = sV + stage * kTile * HD;
         const int key0 = t * kTile;
         // a warp whose rows see none of this tile's keys only keeps the barriers
-        if (warp * 16 < rows && key0 <= warp_hi && key0 + kTile - 1 >= warp_lo) {
+        if (warp_live && key0 <= warp_hi && key0 + kTile - 1 >= warp_lo) {
             float s[8][4];
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
@@ -429,33 +462,49 @@ prefill_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
                     mma_bf16(s[2 * np], qf[ks], b[0], b[1]);
                     mma_bf16(s[2 * np + 1], qf[ks], b[2], b[3]);
                 }
+            // tiles wholly inside every row's range need no mask: all keys <= the warp's first
+            // position, all keys inside the window of its last, all 16 rows present
+            const bool full = key0 + kTile - 1 <= warp_first && warp * 16 + 15 < rows &&
+                              (window <= 0 || key0 > warp_hi - window);
             float mx[2] = {-INFINITY, -INFINITY};
+            if (full) {
 #pragma unroll
-            for (int nt = 0; nt < 8; ++nt)
+                for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    const int key = key0 + nt * 8 + 2 * (lane & 3) + (e & 1);
-                    const int hh = e >> 1;
-                    const bool ok = live[hh] && key <= pos[hh] && (window <= 0 || key > pos[hh] - window);
-                    const float v = ok ? s[nt][e] * sc : -INFINITY;
-                    s[nt][e] = v;
-                    mx[hh] = fmaxf(mx[hh], v);
-                }
+                    for (int e = 0; e < 4; ++e) {
+                        s[nt][e] *= sc;
+                        mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
+                    }
+            } else {
+#pragma unroll
+                for (int nt = 0; nt < 8; ++nt)
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        const int key = key0 + nt * 8 + 2 * (lane & 3) + (e & 1);
+                        const int hh = e >> 1;
+                        const bool ok = live[hh] && key <= pos[hh] && (window <= 0 || key > pos[hh] - window);
+                        const float v = ok ? s[nt][e] * sc : -INFINITY;
+                        s[nt][e] = v;
+                        mx[hh] = fmaxf(mx[hh], v);
+                    }
+            }
             float corr[2];
 #pragma unroll
             for (int hh = 0; hh < 2; ++hh) {
                 mx[hh] = fmaxf(mx[hh], __shfl_xor_sync(0xffffffffu, mx[hh], 1));
                 mx[hh] = fmaxf(mx[hh], __shfl_xor_sync(0xffffffffu, mx[hh], 2));
                 const float m_new = fmaxf(m[hh], mx[hh]);
-                corr[hh] = (m[hh] == -INFINITY) ? 0.f : exp2f(m[hh] - m_new);
+                corr[hh] = (m[hh] == -INFINITY) ? 0.f : fast_exp2(m[hh] - m_new);
                 m[hh] = m_new;
                 l[hh] *= corr[hh];
             }
+            // a row with no key yet keeps m = -inf; fast_exp2(-inf - (-inf)) must not be formed
+            const float mref[2] = {m[0] == -INFINITY ? 0.f : m[0], m[1] == -INFINITY ? 0.f : m[1]};
 #pragma unroll
             for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const float pv = (s[nt][e] == -INFINITY) ? 0.f : exp2f(s[nt][e] - m[e >> 1]);
+                    const float pv = fast_exp2(s[nt][e] - mref[e >> 1]);      // fast_exp2(-inf) = 0
                     s[nt][e] = pv;
                     l[e >> 1] += pv;
                 }
@@ -478,7 +527,6 @@ prefill_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
                 }
             }
         }
-        __syncthreads();
     }
     cp_async_wait<0>();
 #pragma unroll
@@ -505,7 +553,9 @@ prefill_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
 template <int HD> constexpr size_t decode_smem() {
     return (16 * HD + 4 * kDecStages * 2 * kChunk * HD) * sizeof(bf16) + kBtCache * sizeof(int);
 }
-template <int HD> constexpr size_t prefill_smem() { return (kTile * HD + 2 * kStages * kTile * HD) * sizeof(bf16); }
+template <int HD> constexpr size_t prefill_smem() {
+    return (kPfRows * HD + 2 * kPfStages * kTile * HD) * sizeof(bf16) + kBtCache * sizeof(int);
+}
 
 template <int HD> static int configure_once() {
     static int done = -1;
@@ -567,12 +617,12 @@ LSB_API int lsb_prefill_attention(const void* qkv, int qkv_stride, const void* k
                                   float scale, int window, int skip_single, cudaStream_t stream) {
     if (n_requests <= 0 || max_q_len <= 0) return 0;
     if (nkv <= 0 || nh % nkv || n_requests > 65535 || nh > 65535) return (int)cudaErrorInvalidValue;
-    dim3 grid((max_q_len + kTile - 1) / kTile, nh, n_requests);
+    dim3 grid((max_q_len + kPfRows - 1) / kPfRows, nh, n_requests);
 #define LAUNCH_PREFILL(HD)                                                                         \
     do {                                                                                           \
         int rc = configure_once<HD>();                                                             \
         if (rc) return rc;                                                                         \
-        rc = lsb_launch(prefill_attention_kernel<HD>, grid, dim3(kThreads), prefill_smem<HD>(), stream, 1, \
+        rc = lsb_launch(prefill_attention_kernel<HD>, grid, dim3(kPfThreads), prefill_smem<HD>(), stream, 1, \
             (const bf16*)qkv, qkv_stride, (const bf16*)k_pages, (const bf16*)v_pages, q_start,    \
             kv_len, table_rows, block_table, table_stride, (bf16*)out, nh, nkv, page_size,        \
             num_pages, scale, window, skip_single);                                                \
