@@ -167,7 +167,13 @@ __device__ __forceinline__ void load_acc(uint32_t tmem_base, int q, int c0, bool
     }
 }
 
-__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.f + expf(-g)) * u; }
+// silu(g) * u with the special-function unit: ex2 and an approximate division (each good to about
+// 1e-7 relative, far inside the rounding of the bfloat16 result).  The division must be the
+// approximate one: for very negative gates 1 + e^-g is huge or infinite and an IEEE reciprocal
+// drops into its slow denormal path, which cost 15 us per tile on random data.
+__device__ __forceinline__ float silu_mul(float g, float u) {
+    return __fdividef(g, 1.f + __expf(-g)) * u;
+}
 
 template <typename T> __device__ __forceinline__ void put(void* base, long long off, float v);
 template <> __device__ __forceinline__ void put<float>(void* base, long long off, float v) {
@@ -249,6 +255,66 @@ __device__ __forceinline__ void store_chunk(const GemmParams& prm, uint32_t (&r)
         } else {
             for (int x = 0; x < ncols; ++x) dst[x * prm.ldc_j] = __float2bfloat16_rn(__uint_as_float(r[x]));
         }
+    }
+}
+
+// Epilogue of a full-width bfloat16 tile in the row-major orientation: every thread converts
+// its accumulator row (one TMEM lane), applies the gate if asked, and parks it in shared memory
+// (the pipeline's stage buffers are idle by now) in 16-byte chunks XOR-swizzled by row; the warp
+// then writes whole rows back with one 16-byte chunk per lane, so global stores are contiguous
+// 256- or 512-byte runs instead of 32 scattered 16-byte pieces per instruction.
+template <int BN, bool GATED>
+__device__ __forceinline__ void epilogue_staged(const GemmParams& prm, unsigned char* stage_base, uint32_t tmem_base,
+                                                int q, int lane, int i0, int j0) {
+    constexpr int OUT_COLS = GATED ? BN / 2 : BN;
+    constexpr int CPROW = OUT_COLS / 8;                       // 16-byte chunks per output row
+    static_assert(CPROW >= 8, "the swizzle needs at least eight chunks per row");
+    uint4* mine = reinterpret_cast<uint4*>(stage_base) + (size_t)q * 32 * CPROW;
+#pragma unroll
+    for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)c0, r);
+        tmem_ld_wait();
+        if (GATED) {
+#pragma unroll
+            for (int k = 0; k < 2; ++k) {
+                uint32_t w[4];
+#pragma unroll
+                for (int y = 0; y < 4; ++y) {
+                    const int x = 16 * k + 4 * y;
+                    const float a = silu_mul(__uint_as_float(r[x]), __uint_as_float(r[x + 1]));
+                    const float b = silu_mul(__uint_as_float(r[x + 2]), __uint_as_float(r[x + 3]));
+                    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+                    w[y] = *reinterpret_cast<uint32_t*>(&h);
+                }
+                const int cc = (c0 / 32) * 2 + k;
+                mine[lane * CPROW + (cc ^ (lane & 7))] = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        } else {
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                uint32_t w[4];
+#pragma unroll
+                for (int y = 0; y < 4; ++y) {
+                    __nv_bfloat162 h = __floats2bfloat162_rn(__uint_as_float(r[8 * k + 2 * y]),
+                                                             __uint_as_float(r[8 * k + 2 * y + 1]));
+                    w[y] = *reinterpret_cast<uint32_t*>(&h);
+                }
+                const int cc = (c0 / 32) * 4 + k;
+                mine[lane * CPROW + (cc ^ (lane & 7))] = make_uint4(w[0], w[1], w[2], w[3]);
+            }
+        }
+    }
+    __syncwarp();
+    bf16* out = reinterpret_cast<bf16*>(prm.out);
+    const int jo = GATED ? j0 / 2 : j0;
+#pragma unroll
+    for (int it = 0; it < CPROW; ++it) {                       // 32 rows x CPROW chunks / 32 lanes
+        const int idx = it * 32 + lane;
+        const int row = idx / CPROW, c = idx % CPROW;
+        const int i = i0 + q * 32 + row;
+        if (i < prm.rows_p)
+            *reinterpret_cast<uint4*>(out + (long long)i * prm.ldc_i + jo + c * 8) = mine[row * CPROW + (c ^ (row & 7))];
     }
 }
 
@@ -362,7 +428,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
             tc_fence_after();
         }
         ok = ok && !abort_flag;
-        if (prm.splits == 1) {
+        // the common case of prompts: row-major bfloat16 output, the tile wholly inside the matrix
+        const int n_out = prm.swiglu == 1 ? prm.rows_q / 2 : prm.rows_q;
+        const bool staged = prm.splits == 1 && !prm.out_f32 && prm.ldc_j == 1 && prm.swiglu != 2 && nkb > 0 &&
+                            j0 + BN <= prm.rows_q && (n_out % 8) == 0 && (((uintptr_t)prm.out) & 15) == 0 &&
+                            (prm.swiglu == 0 ? BN >= 64 : BN >= 128);
+        if (staged) {
+            if (ok) {
+                if constexpr (BN >= 128) {
+                    if (prm.swiglu == 1) epilogue_staged<BN, true>(prm, stages, tmem_base, q, lane, i0, j0);
+                    else epilogue_staged<BN, false>(prm, stages, tmem_base, q, lane, i0, j0);
+                } else if constexpr (BN >= 64) {
+                    epilogue_staged<BN, false>(prm, stages, tmem_base, q, lane, i0, j0);
+                }
+            }
+        } else if (prm.splits == 1) {
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t r[32];
