@@ -177,10 +177,15 @@ def run_ours(args):
         return out
 
     def time_decode(batch, steps, warmup):
-        start = ctx_len - (steps + warmup)
+        start = ctx_len - (steps + warmup + 2)
         ids = fill(batch, start)
         feed = torch.randint(0, V, (batch,), generator=g).tolist()
-        decode_steps(ids, warmup, feed)
+        runner.cuda_graphs, keep = False, runner.cuda_graphs
+        n0 = kernels.launch_count()
+        decode_steps(ids, 1, feed)                  # one step launched kernel by kernel: counted
+        per_step = kernels.launch_count() - n0
+        runner.cuda_graphs = keep
+        decode_steps(ids, max(warmup - 1, 2), feed)
         torch.cuda.synchronize()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         launches0 = kernels.launch_count()
@@ -189,7 +194,8 @@ def run_ours(args):
         e1.record()
         torch.cuda.synchronize()
         ms = e0.elapsed_time(e1) / steps
-        launches = kernels.launch_count() - launches0
+        # replayed graphs launch the same kernels as the counted step did, without the wrappers
+        launches = per_step * steps if runner.graph_replays else kernels.launch_count() - launches0
         kernels.check_status()
         for rid in ids:
             runner.close(rid)

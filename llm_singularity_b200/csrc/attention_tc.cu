@@ -81,7 +81,7 @@ template <int HD> __device__ __forceinline__ bf16* tile_ptr(bf16* base, int row,
 
 // ------------------------------------------------------------------ decode
 constexpr int kChunk = 16;           // keys a warp handles per step
-constexpr int kDecStages = 4;        // chunks in flight per warp
+constexpr int kDecStages = 3;        // chunks in flight per warp (four blocks fit per SM)
 constexpr int kBtCache = 1024;       // block-table entries kept in shared memory per block
 
 __device__ __forceinline__ int div_page(int key, int page_size, int page_shift) {
@@ -377,13 +377,14 @@ prefill_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
     lsb_pdl_launch_dependents();
     lsb_pdl_wait();
 
-    const int r = blockIdx.z, h = blockIdx.y;
+    // grid: x = head (fastest), y = query tile, z = request, so that across all heads the heavy
+    // tiles (late rows see the most keys) are handed out first and the light ones fill the tail
+    const int r = blockIdx.z, h = blockIdx.x;
     const int qs = q_start[r];
     const int q_len = q_start[r + 1] - qs;
-    // heavy tiles (late rows see the most keys) are scheduled first
     const int n_qt = (q_len + kPfRows - 1) / kPfRows;
-    if ((int)blockIdx.x >= n_qt || (skip_single && q_len == 1)) return;
-    const int i0 = (n_qt - 1 - (int)blockIdx.x) * kPfRows;
+    if ((int)blockIdx.y >= n_qt || (skip_single && q_len == 1)) return;
+    const int i0 = (n_qt - 1 - (int)blockIdx.y) * kPfRows;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = h / (nh / nkv);
     const int kv_len = kv_len_arr[r];
@@ -616,8 +617,9 @@ LSB_API int lsb_prefill_attention(const void* qkv, int qkv_stride, const void* k
                                   int max_q_len, int nh, int nkv, int hd, int page_size, int num_pages,
                                   float scale, int window, int skip_single, cudaStream_t stream) {
     if (n_requests <= 0 || max_q_len <= 0) return 0;
-    if (nkv <= 0 || nh % nkv || n_requests > 65535 || nh > 65535) return (int)cudaErrorInvalidValue;
-    dim3 grid((max_q_len + kPfRows - 1) / kPfRows, nh, n_requests);
+    if (nkv <= 0 || nh % nkv || n_requests > 65535 || (max_q_len + kPfRows - 1) / kPfRows > 65535)
+        return (int)cudaErrorInvalidValue;
+    dim3 grid(nh, (max_q_len + kPfRows - 1) / kPfRows, n_requests);
 #define LAUNCH_PREFILL(HD)                                                                         \
     do {                                                                                           \
         int rc = configure_once<HD>();                                                             \
