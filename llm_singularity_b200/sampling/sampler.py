@@ -20,6 +20,7 @@ from .rng import uniform
 class Sampler:
     def __init__(self, rt):
         self.rt = rt
+        self._greedy = {}               # batch size -> device arrays for all-greedy batches
         prepare = getattr(rt.ops, "prepare", None)
         if prepare is not None:
             prepare(["sampling"])
@@ -33,6 +34,17 @@ class Sampler:
         R = logits.shape[0]
         if len(params) != R or len(draw_index) != R:
             raise ValueError("one SamplingParams and one draw index per row of logits")
+        dev = self.rt.device
+        if all(p.greedy and p.repetition_penalty == 1.0 for p in params):
+            # nothing varies from step to step: keep the per-row arrays on the device
+            cached = self._greedy.get(R)
+            if cached is None:
+                fl = torch.tensor([[0.0, 1.0, 1.0, 0.5]] * R, dtype=torch.float32, device=dev)
+                cached = self._greedy[R] = (fl, torch.zeros(R, dtype=torch.int32, device=dev),
+                                            torch.empty(R, dtype=torch.int32, device=dev))
+            d_fl, d_tk, out = cached
+            self.rt.ops.sample(logits, d_fl, d_tk, None, None, out)
+            return out
         fl = np.empty((R, 4), dtype=np.float32)
         tk = np.empty(R, dtype=np.int32)
         penal = False
@@ -41,7 +53,6 @@ class Sampler:
                      0.5 if p.greedy else uniform(p.seed, n))
             tk[r] = p.top_k
             penal |= p.repetition_penalty != 1.0
-        dev = self.rt.device
         d_fl = torch.from_numpy(fl).to(dev, non_blocking=True)
         d_tk = torch.from_numpy(tk).to(dev, non_blocking=True)
         d_start = d_prev = None
