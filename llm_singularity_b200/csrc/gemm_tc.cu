@@ -316,6 +316,7 @@ __device__ __forceinline__ void epilogue_staged(const GemmParams& prm, unsigned 
         if (i < prm.rows_p)
             *reinterpret_cast<uint4*>(out + (long long)i * prm.ldc_i + jo + c * 8) = mine[row * CPROW + (c ^ (row & 7))];
     }
+    __syncwarp();                                              // the buffer may be refilled right away
 }
 
 template <int BN, int STAGES>
@@ -502,6 +503,160 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     }
 }
 
+// ------------------------------------------------------------------ persistent kernel (prompts)
+// One block per SM walks a list of output tiles (row-major orientation, 128 x BN, one K range).
+// The accumulator is double-buffered in TMEM (2 x BN columns): while the epilogue warps drain
+// tile i from one buffer into global memory, the MMA warp already fills the other with tile i+1,
+// and the TMA warp runs ahead through the ring of stages without regard to tile boundaries.  This
+// removes the per-tile set-up (barriers, TMEM allocation, first loads) and hides the epilogue.
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_addr(bar)) : "memory");
+}
+
+constexpr int kEpiCols = 128;                                 // columns drained per pass
+constexpr int kEpiBytes = 4 * 32 * kEpiCols * 2;             // 4 warps x 32 rows x 128 bf16
+
+template <int BN, int STAGES>
+struct PersistentLayout {
+    static constexpr int kPBytes = kBM * kBK * 2;
+    static constexpr int kQBytes = BN * kBK * 2;
+    static constexpr int kStageBytes = kPBytes + kQBytes;
+    static constexpr int kBars = 2 * STAGES + 4;
+    static constexpr size_t kTotal = 1024 + (size_t)STAGES * kStageBytes + kEpiBytes + kBars * 8 + 16;
+};
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kGemmThreads)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
+                          const GemmParams prm, int tiles_m, int tiles_n) {
+    using L = PersistentLayout<BN, STAGES>;
+    static_assert(BN == 128 || BN == 256, "two accumulators of BN columns must fit 512 TMEM columns");
+    constexpr uint32_t kTmemCols = 2 * BN;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* stages = base;
+    unsigned char* epi = base + (size_t)STAGES * L::kStageBytes;
+    uint64_t* full = reinterpret_cast<uint64_t*>(epi + kEpiBytes);
+    uint64_t* empty = full + STAGES;
+    uint64_t* acc_full = empty + STAGES;                      // [2]
+    uint64_t* acc_empty = acc_full + 2;                       // [2]
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    __shared__ int abort_flag;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_tiles = tiles_m * tiles_n;
+    const int nkb = prm.num_kb;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+        for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 128); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+
+    // tile t -> (row block, column block); neighbouring blocks share the weight columns
+    if (warp == 0) {
+        if (lane == 0) {
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_p) : "memory");
+            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+            long long it = 0;                                  // K blocks issued so far, over all tiles
+            bool ok = true;
+            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
+                const int i0 = (t % tiles_m) * kBM, j0 = (t / tiles_m) * BN;
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = (int)(it % STAGES);
+                    if (it >= STAGES && !mbar_wait(&empty[s], (uint32_t)((it / STAGES) - 1) & 1, &abort_flag)) { ok = false; break; }
+                    mbar_expect_tx(&full[s], L::kStageBytes);
+                    unsigned char* st = stages + (size_t)s * L::kStageBytes;
+                    tma_load_2d(st, &map_p, &full[s], kb * kBK, i0);
+                    tma_load_2d(st + L::kPBytes, &map_q, &full[s], kb * kBK, j0);
+                }
+            }
+            // copies still in flight must land before the block may exit
+            for (long long k = it > STAGES ? it - STAGES : 0; k < it; ++k) {
+                int dummy = 0;
+                mbar_wait(&full[k % STAGES], (uint32_t)(k / STAGES) & 1, &dummy);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = make_idesc(BN);
+            long long it = 0;
+            int local = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++local) {
+                const int a = local & 1;
+                // the epilogue must have drained this accumulator (passes at once the first time)
+                ok = mbar_wait(&acc_empty[a], (uint32_t)((local >> 1) & 1) ^ 1u, &abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                const uint32_t tmem_d = tmem_base + (uint32_t)(a * BN);
+                for (int kb = 0; kb < nkb; ++kb, ++it) {
+                    const int s = (int)(it % STAGES);
+                    ok = mbar_wait(&full[s], (uint32_t)(it / STAGES) & 1, &abort_flag);
+                    if (!ok) break;
+                    tc_fence_after();
+                    unsigned char* st = stages + (size_t)s * L::kStageBytes;
+                    const uint64_t dp = make_smem_desc(st), dq = make_smem_desc(st + L::kPBytes);
+#pragma unroll
+                    for (int k = 0; k < kBK / kUmmaK; ++k)
+                        umma_bf16(tmem_d, dp + 2 * k, dq + 2 * k, idesc, (kb | k) ? 1u : 0u);
+                    umma_commit(&empty[s]);
+                }
+                umma_commit(&acc_full[a]);
+            }
+        }
+    } else {
+        const int q = warp & 3;
+        const int il = q * 32 + lane;
+        const int n_out = prm.swiglu == 1 ? prm.rows_q / 2 : prm.rows_q;
+        const bool aligned = !prm.out_f32 && (n_out % 8) == 0 && (((uintptr_t)prm.out) & 15) == 0;
+        int local = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x, ++local) {
+            const int a = local & 1;
+            const int i0 = (t % tiles_m) * kBM, j0 = (t / tiles_m) * BN;
+            ok = mbar_wait(&acc_full[a], (uint32_t)(local >> 1) & 1, &abort_flag);
+            tc_fence_after();
+            ok = ok && !abort_flag;
+            if (!ok) break;
+            const uint32_t tmem_acc = tmem_base + (uint32_t)(a * BN);
+            if (aligned && j0 + BN <= prm.rows_q) {
+#pragma unroll
+                for (int h = 0; h < BN / kEpiCols; ++h) {
+                    if (prm.swiglu == 1)
+                        epilogue_staged<kEpiCols, true>(prm, epi, tmem_acc + h * kEpiCols, q, lane, i0, j0 + h * kEpiCols);
+                    else
+                        epilogue_staged<kEpiCols, false>(prm, epi, tmem_acc + h * kEpiCols, q, lane, i0, j0 + h * kEpiCols);
+                }
+            } else {
+#pragma unroll 1
+                for (int c0 = 0; c0 < BN; c0 += 32) {
+                    uint32_t r[32];
+                    load_acc<BN>(tmem_acc, q, c0, true, r);
+                    store_chunk<BN>(prm, r, i0 + il, j0 + c0, 32, lane);
+                }
+            }
+            tc_fence_before();
+            mbar_arrive(&acc_empty[a]);                        // 128 arrivals hand the buffer back
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kTmemCols);
+    }
+}
+
 // ------------------------------------------------------------------ host side
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
@@ -548,6 +703,26 @@ static int launch(const CUtensorMap& mp, const CUtensorMap& mq, const GemmParams
     return lsb_launch(gemm_tc_kernel<BN, STAGES>, grid, dim3(kGemmThreads), smem, stream, prm.splits, mp, mq, prm);
 }
 
+template <int BN, int STAGES>
+static int launch_persistent(const CUtensorMap& mp, const CUtensorMap& mq, const GemmParams& prm, int tiles_m,
+                             int tiles_n, cudaStream_t stream) {
+    static int configured = -1;
+    static int sms = 0;
+    constexpr size_t smem = PersistentLayout<BN, STAGES>::kTotal;
+    if (configured < 0) {
+        configured = (int)cudaFuncSetAttribute(gemm_tc_persistent_kernel<BN, STAGES>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    }
+    if (configured) return configured;
+    const int tiles = tiles_m * tiles_n;
+    const int blocks = tiles < sms ? tiles : sms;
+    return lsb_launch(gemm_tc_persistent_kernel<BN, STAGES>, dim3(blocks), dim3(kGemmThreads), smem, stream, 1,
+                      mp, mq, prm, tiles_m, tiles_n);
+}
+
 // Can this kernel take the product?  (TMA needs 16-byte aligned bases and row strides.)
 LSB_API int lsb_gemm_tc_supported(const void* x, const void* w, int M, int N, int K) {
     return M > 0 && N > 0 && K > 0 && K % 8 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0;
@@ -590,6 +765,9 @@ LSB_API int lsb_gemm_tc_plan(int M, int N, int K, int swiglu, int* swap, int* bn
             else if (cands[c] == 128) eff *= 0.93;
             if (eff > best_eff + 1e-9) { best_eff = eff; best = cands[c]; }
         }
+        // persistent blocks walk the tile list, so whole waves no longer matter: take the widest
+        // tile unless that leaves SMs without any
+        if (mt * ((N + 255) / 256) >= 120 || N >= 2048) best = 256;
         *bn = best;
         *splits = 1;
     }
@@ -634,6 +812,12 @@ LSB_API int lsb_gemm_tc(const void* x, const void* w, void* out, int out_f32, in
     // Blocks of a split product are co-scheduled as clusters: four stages keep their shared memory
     // small enough for two or three blocks per SM, so that every cluster finds room at once.
     // Unsplit products run one block per SM and want the deeper ring to keep HBM busy.
+    if (!swap && !out_f32 && bn >= 128) {
+        // prompts: persistent blocks, double-buffered accumulator
+        const int tm = (M + kBM - 1) / kBM, tn = (N + bn - 1) / bn;
+        return bn == 256 ? launch_persistent<256, 4>(mp, mq, prm, tm, tn, stream)
+                         : launch_persistent<128, 6>(mp, mq, prm, tm, tn, stream);
+    }
     if (splits > 1) {
         switch (bn) {
             case 16: rc = launch<16, 4>(mp, mq, prm, grid, stream); break;
