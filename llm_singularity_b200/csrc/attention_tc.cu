@@ -24,6 +24,7 @@
 // These replace the reference's paged_attention_kernel (kernels/src/attention.cu:27-172), which
 // serves both cases with 32 threads per (head, row) and scalar fp32 loops.  The generic kernel in
 // attention.cu remains the 32-bit path and the fallback for other head sizes.
+#define LSB_CLUSTER_ALONG_X            // decode splits are blockIdx.x
 #include "common.cuh"
 
 #include <float.h>
@@ -74,14 +75,37 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// thread-block cluster helpers: rank, barrier over all threads of all blocks, a float from a peer
+__device__ __forceinline__ uint32_t cluster_rank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ void cluster_barrier() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ float ld_peer_f32(const float* own_smem, uint32_t rank) {
+    uint32_t peer;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(peer) : "r"(smem_u32(own_smem)), "r"(rank));
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(peer) : "memory");
+    return v;
+}
+
 // A tile is rows of HD bf16 = HD/8 chunks of 16 bytes; chunk c of row r lives at chunk c ^ (r & 7).
 template <int HD> __device__ __forceinline__ bf16* tile_ptr(bf16* base, int row, int chunk) {
     return base + (row * (HD / 8) + (chunk ^ (row & 7))) * 8;
 }
 
 // ------------------------------------------------------------------ decode
-constexpr int kChunk = 16;           // keys a warp handles per step
-constexpr int kDecStages = 3;        // chunks in flight per warp (four blocks fit per SM)
+#ifndef LSB_DEC_CHUNK
+#define LSB_DEC_CHUNK 16
+#endif
+#ifndef LSB_DEC_STAGES
+#define LSB_DEC_STAGES 2
+#endif
+constexpr int kChunk = LSB_DEC_CHUNK;           // keys a warp handles per step
+constexpr int kDecStages = LSB_DEC_STAGES;        // chunks in flight per warp
 constexpr int kBtCache = 1024;       // block-table entries kept in shared memory per block
 
 __device__ __forceinline__ int div_page(int key, int page_size, int page_shift) {
@@ -92,15 +116,18 @@ __device__ __forceinline__ int div_page(int key, int page_size, int page_shift) 
 // asynchronous 16-byte copies of the chunk's K and V rows into the warp's ring of stages, no
 // block-wide barrier inside the loop.  The block's slice of the block table is read into shared
 // memory first, so that copies are issued without waiting on a table lookup.
+#ifndef LSB_DEC_MINBLOCKS
+#define LSB_DEC_MINBLOCKS 4
+#endif
 template <int HD>
-__global__ void __launch_bounds__(kThreads)
+__global__ void __launch_bounds__(kThreads, LSB_DEC_MINBLOCKS)
 decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
                         const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
                         const int* __restrict__ q_start, const int* __restrict__ kv_len_arr,
                         const int* __restrict__ table_rows, const int* __restrict__ block_table,
                         int table_stride, bf16* __restrict__ out, float* __restrict__ part_o,
                         float* __restrict__ part_ml, int nh, int nkv, int page_size, int num_pages,
-                        float scale, int window, int splits) {
+                        float scale, int window, int splits, int cluster_merge) {
     constexpr int CPR = HD / 8, KS = HD / 16;
     constexpr int kStageElems = 2 * kChunk * HD;             // K rows then V rows
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -199,18 +226,23 @@ decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
         bf16* tK = ring + (size_t)(i % kDecStages) * kStageElems;
         bf16* tV = tK + kChunk * HD;
 
-        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        constexpr int NT = kChunk / 8;                         // 8-key score tiles per chunk
+        float s[NT][4];
 #pragma unroll
-        for (int ks = 0; ks < KS; ++ks) {
-            uint32_t b[4];
-            ldmatrix_x4(b, tile_ptr<HD>(tK, (lane >> 4) * 8 + (lane & 7), 2 * ks + ((lane >> 3) & 1)));
-            mma_bf16(s[0], qf[ks], b[0], b[1]);
-            mma_bf16(s[1], qf[ks], b[2], b[3]);
-        }
+        for (int nt = 0; nt < NT; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
+#pragma unroll
+        for (int ks = 0; ks < KS; ++ks)
+#pragma unroll
+            for (int np = 0; np < NT / 2; ++np) {
+                uint32_t b[4];
+                ldmatrix_x4(b, tile_ptr<HD>(tK, np * 16 + (lane >> 4) * 8 + (lane & 7), 2 * ks + ((lane >> 3) & 1)));
+                mma_bf16(s[2 * np], qf[ks], b[0], b[1]);
+                mma_bf16(s[2 * np + 1], qf[ks], b[2], b[3]);
+            }
         // mask keys outside [lo, p]; scale into the log2 domain
         float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
+        for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
                 const int key = chunk * kChunk + nt * 8 + 2 * (lane & 3) + (e & 1);
@@ -218,7 +250,7 @@ decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
                 s[nt][e] = v;
                 mx[e >> 1] = fmaxf(mx[e >> 1], v);
             }
-        float corr[2];
+        float corr[2], mref[2];
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
             mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
@@ -227,12 +259,13 @@ decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
             corr[h] = (m[h] == -INFINITY) ? 0.f : fast_exp2(m[h] - m_new);
             m[h] = m_new;
             l[h] *= corr[h];
+            mref[h] = m_new == -INFINITY ? 0.f : m_new;        // ex2(-inf - 0) = 0 without a branch
         }
 #pragma unroll
-        for (int nt = 0; nt < 2; ++nt)
+        for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const float pv = (s[nt][e] == -INFINITY) ? 0.f : fast_exp2(s[nt][e] - m[e >> 1]);
+                const float pv = fast_exp2(s[nt][e] - mref[e >> 1]);
                 s[nt][e] = pv;
                 l[e >> 1] += pv;
             }
@@ -241,14 +274,18 @@ decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
             o[i2][0] *= corr[0]; o[i2][1] *= corr[0];
             o[i2][2] *= corr[1]; o[i2][3] *= corr[1];
         }
-        uint32_t pa[4] = {pack_bf16(s[0][0], s[0][1]), pack_bf16(s[0][2], s[0][3]),
-                          pack_bf16(s[1][0], s[1][1]), pack_bf16(s[1][2], s[1][3])};
 #pragma unroll
-        for (int dt = 0; dt < HD / 16; ++dt) {
-            uint32_t b[4];
-            ldmatrix_x4_trans(b, tile_ptr<HD>(tV, ((lane >> 3) & 1) * 8 + (lane & 7), 2 * dt + (lane >> 4)));
-            mma_bf16(o[2 * dt], pa, b[0], b[1]);
-            mma_bf16(o[2 * dt + 1], pa, b[2], b[3]);
+        for (int kt = 0; kt < NT / 2; ++kt) {
+            uint32_t pa[4] = {pack_bf16(s[2 * kt][0], s[2 * kt][1]), pack_bf16(s[2 * kt][2], s[2 * kt][3]),
+                              pack_bf16(s[2 * kt + 1][0], s[2 * kt + 1][1]),
+                              pack_bf16(s[2 * kt + 1][2], s[2 * kt + 1][3])};
+#pragma unroll
+            for (int dt = 0; dt < HD / 16; ++dt) {
+                uint32_t b[4];
+                ldmatrix_x4_trans(b, tile_ptr<HD>(tV, kt * 16 + ((lane >> 3) & 1) * 8 + (lane & 7), 2 * dt + (lane >> 4)));
+                mma_bf16(o[2 * dt], pa, b[0], b[1]);
+                mma_bf16(o[2 * dt + 1], pa, b[2], b[3]);
+            }
         }
         __syncwarp();                                          // the stage is overwritten next round
     }
@@ -263,6 +300,8 @@ decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
     float* sO = reinterpret_cast<float*>(sKV);                 // [4][16][HD]
     float* sM = sO + 4 * 16 * HD;                              // [4][16]
     float* sL = sM + 4 * 16;
+    float* sFin = sL + 4 * 16;                                 // [G][HD] this block's merged output
+    float* sFinML = sFin + 16 * HD;                            // [G][2] its (max, sum)
     __syncthreads();
 #pragma unroll
     for (int i = 0; i < HD / 8; ++i) {
@@ -292,11 +331,35 @@ decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
         const int head = g * G + h;
         if (splits == 1) {
             out[(size_t)qs * nh * HD + (size_t)head * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        } else if (cluster_merge) {
+            sFin[idx] = O;
+            if (d == 0) { sFinML[2 * h] = M; sFinML[2 * h + 1] = L; }
         } else {
             const size_t slot = ((size_t)r * nh + head) * splits + split;
             part_o[slot * HD + d] = O;
             if (d == 0) { part_ml[slot * 2] = M; part_ml[slot * 2 + 1] = L; }
         }
+    }
+    if (splits > 1 && cluster_merge) {
+        // The splits of one (request, kv head) are one cluster: every block takes a share of the
+        // group's outputs and sums all blocks' partial results, read from their shared memory in
+        // rank order, so nothing goes through global memory and no second kernel is needed.
+        cluster_barrier();
+        const uint32_t rank = cluster_rank();
+        for (int idx = (int)rank * kThreads + threadIdx.x; idx < G * HD; idx += splits * kThreads) {
+            const int h = idx / HD, d = idx - h * HD;
+            float M = -INFINITY;
+            for (int s2 = 0; s2 < splits; ++s2) M = fmaxf(M, ld_peer_f32(sFinML + 2 * h, (uint32_t)s2));
+            float L = 0.f, O = 0.f;
+            for (int s2 = 0; s2 < splits; ++s2) {
+                const float ms = ld_peer_f32(sFinML + 2 * h, (uint32_t)s2);
+                const float f = (ms == -INFINITY) ? 0.f : fast_exp2(ms - M);
+                L += ld_peer_f32(sFinML + 2 * h + 1, (uint32_t)s2) * f;
+                O += ld_peer_f32(sFin + idx, (uint32_t)s2) * f;
+            }
+            out[(size_t)qs * nh * HD + (size_t)(g * G + h) * HD + d] = __float2bfloat16_rn(L > 0.f ? O / L : 0.f);
+        }
+        cluster_barrier();          // nobody leaves while a peer may still read its shared memory
     }
 }
 
@@ -585,20 +648,22 @@ LSB_API int lsb_decode_attention(const void* qkv, int qkv_stride, const void* k_
     if (n_requests <= 0) return 0;
     if (nkv <= 0 || nh % nkv || nh / nkv > 16 || splits < 1 || n_requests > 65535 || nkv > 65535)
         return (int)cudaErrorInvalidValue;
-    if (splits > 1 && !scratch) return (int)cudaErrorInvalidValue;
+    if (splits > 8 && !scratch) return (int)cudaErrorInvalidValue;
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)n_requests * nh * splits * hd : nullptr;
     dim3 grid(splits, nkv, n_requests);
+    const bool in_cluster = splits > 1 && splits <= 8;      // x is the cluster dimension
 #define LAUNCH_DECODE(HD)                                                                          \
     do {                                                                                           \
         int rc = configure_once<HD>();                                                             \
         if (rc) return rc;                                                                         \
-        rc = lsb_launch(decode_attention_kernel<HD>, grid, dim3(kThreads), decode_smem<HD>(), stream, 1, \
+        rc = lsb_launch(decode_attention_kernel<HD>, grid, dim3(kThreads), decode_smem<HD>(), stream, \
+            in_cluster ? splits : 1,                                                               \
             (const bf16*)qkv, qkv_stride, (const bf16*)k_pages, (const bf16*)v_pages, q_start,    \
             kv_len, table_rows, block_table, table_stride, (bf16*)out, part_o, part_ml, nh, nkv,  \
-            page_size, num_pages, scale, window, splits);                                          \
+            page_size, num_pages, scale, window, splits, in_cluster ? 1 : 0);                      \
         if (rc) return rc;                                                                         \
-        if (splits > 1)                                                                            \
+        if (splits > 1 && !in_cluster)                                                             \
             rc = lsb_launch(decode_merge_kernel<HD>, dim3(nh, n_requests), dim3(64), 0, stream, 1, \
                 (const float*)part_o, (const float*)part_ml, q_start, (bf16*)out, nh, splits);     \
         if (rc) return rc;                                                                         \
@@ -689,16 +754,18 @@ LSB_API int lsb_decode_attention_noalloc(const void* qkv, int qkv_stride, const 
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)n_requests * nh * splits * hd : nullptr;
     dim3 grid(splits, nkv, n_requests);
+    const bool in_cluster = splits > 1 && splits <= 8;      // x is the cluster dimension
 #define LAUNCH_DECODE_NOALLOC(HD)                                                                  \
     do {                                                                                           \
         int rc = configure_once<HD>();                                                             \
         if (rc) return rc;                                                                         \
-        rc = lsb_launch(decode_attention_kernel<HD>, grid, dim3(kThreads), decode_smem<HD>(), stream, 1, \
+        rc = lsb_launch(decode_attention_kernel<HD>, grid, dim3(kThreads), decode_smem<HD>(), stream, \
+            in_cluster ? splits : 1,                                                               \
             (const bf16*)qkv, qkv_stride, (const bf16*)k_pages, (const bf16*)v_pages, q_start,    \
             kv_len, table_rows, block_table, table_stride, (bf16*)out, part_o, part_ml, nh, nkv,  \
-            page_size, num_pages, scale, window, splits);                                          \
+            page_size, num_pages, scale, window, splits, in_cluster ? 1 : 0);                      \
         if (rc) return rc;                                                                         \
-        if (splits > 1)                                                                            \
+        if (splits > 1 && !in_cluster)                                                             \
             rc = lsb_launch(decode_merge_kernel<HD>, dim3(nh, n_requests), dim3(64), 0, stream, 1, \
                 (const float*)part_o, (const float*)part_ml, q_start, (bf16*)out, nh, splits);     \
         if (rc) return rc;                                                                         \

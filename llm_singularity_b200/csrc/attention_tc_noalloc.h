@@ -15,7 +15,8 @@
 //   * Inputs and the output are still the caller's buffers.
 //   * n_requests * nh * splits * (hd + 2) must not exceed the maximum when
 //     splits > 1; larger problems are refused with LSB_NOALLOC_TOO_LARGE and
-//     nothing is launched.  With splits == 1 no scratch is used at all.
+//     nothing is launched.  With splits == 1 no scratch is used at all, and up
+//     to 8 splits are merged inside a thread-block cluster without touching it.
 //   * The first call on each device looks up the array's device address (with
 //     that device current).  Make that first call before starting any stream
 //     capture, and from one thread.

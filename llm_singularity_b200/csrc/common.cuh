@@ -104,8 +104,9 @@ static inline bool lsb_pdl_enabled() {
     return on != 0;
 }
 
-// kernel<<<grid, block, smem, stream>>>(args...) with the launch attributes above; cluster_z > 1
-// makes the blocks along z one thread-block cluster.
+// kernel<<<grid, block, smem, stream>>>(args...) with the launch attributes above; cluster > 1
+// makes that many consecutive blocks one thread-block cluster: along z by default, along x when
+// LSB_CLUSTER_ALONG_X is defined before this header is included.
 template <typename... KArgs, typename... Args>
 static inline int lsb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
                              cudaStream_t stream, int cluster_z, Args... args) {
@@ -123,9 +124,15 @@ static inline int lsb_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, si
     }
     if (cluster_z > 1) {
         attr[n].id = cudaLaunchAttributeClusterDimension;
+#ifdef LSB_CLUSTER_ALONG_X
+        attr[n].val.clusterDim.x = cluster_z;
+        attr[n].val.clusterDim.y = 1;
+        attr[n].val.clusterDim.z = 1;
+#else
         attr[n].val.clusterDim.x = 1;
         attr[n].val.clusterDim.y = 1;
         attr[n].val.clusterDim.z = cluster_z;
+#endif
         ++n;
     }
     cfg.attrs = attr;

@@ -328,7 +328,7 @@ def paged_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache, s
         if not getattr(ctx, "fixed_launch", False):
             splits = min(splits, -(-ctx.max_kv_len // 128))
         scratch = None
-        if splits > 1:
+        if splits > 8:                  # up to 8 splits merge inside a thread-block cluster
             key = (qkv.device, R, nh, hd, splits)
             scratch = _scratch.get(key)
             if scratch is None:

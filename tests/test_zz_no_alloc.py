@@ -71,13 +71,14 @@ def _both(lib, p, splits):
 def test_no_alloc_entry_point_matches_the_regular_one_twice_in_a_row():
     lib = _lib()
     assert lib.lsb_decode_attention_noalloc_max_floats() == 1 << 20
-    # first call: 5 requests, 8 splits; second call: other sizes on top of what the first left
+    # first call: 5 requests, 12 splits (more than a cluster holds, so the partial results go
+    # through the scratch array); second call: other sizes on top of what the first left
     p1 = _problem(5, 8, 2, 64, 16, [700, 64, 1, 333, 65], seed=1)
-    want, got = _both(lib, p1, splits=8)
+    want, got = _both(lib, p1, splits=12)
     assert want.abs().max() > 0.1
     assert (want.float() - got.float()).abs().max().item() <= 1e-2 * 3.0
     p2 = _problem(3, 16, 1, 128, 8, [129, 900, 40], seed=2)
-    want, got = _both(lib, p2, splits=3)
+    want, got = _both(lib, p2, splits=20)
     assert (want.float() - got.float()).abs().max().item() <= 1e-2 * 3.0
     assert torch.equal(want, got)           # same kernels, same order of sums: the same bits
 
