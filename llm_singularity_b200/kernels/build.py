@@ -98,6 +98,17 @@ def library_path(name: str) -> str:
     return os.path.join(build_dir(), f"lsb_{name}.{_digest(name)}.so")
 
 
+def _prune(name: str, keep: str) -> None:
+    """Drop builds of ``name`` made from older sources (the hash in the file name differs)."""
+    d = os.path.dirname(keep)
+    for f in os.listdir(d):
+        if f.startswith(f"lsb_{name}.") and f.endswith(".so") and os.path.join(d, f) != keep:
+            try:
+                os.unlink(os.path.join(d, f))
+            except OSError:
+                pass
+
+
 def ensure_built(names: Iterable[str], verbose: bool = False) -> Dict[str, str]:
     """Compile the named libraries if their current build is absent; returns name -> path."""
     names = list(dict.fromkeys(names))
@@ -134,6 +145,7 @@ def ensure_built(names: Iterable[str], verbose: bool = False) -> Dict[str, str]:
                     os.unlink(tmp)
             else:
                 os.replace(tmp, paths[n])          # atomic: a concurrent process sees all or nothing
+                _prune(n, paths[n])
                 if verbose:
                     print(f"[llm_singularity_b200]   {n} done after {time.time() - t0:.0f} s",
                           file=out, flush=True)
