@@ -204,8 +204,16 @@ class ModelRunner:
                 return run()
             torch.cuda.synchronize(self.rt.device)
             graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph):
-                st.logits = run()
+            try:
+                with torch.cuda.graph(graph):
+                    st.logits = run()
+            except RuntimeError as e:
+                # a driver that cannot capture these launches: decode kernel by kernel from now on
+                import warnings
+                warnings.warn(f"CUDA graph capture failed ({e}); decode steps run without graphs")
+                self.cuda_graphs = False
+                torch.cuda.synchronize(self.rt.device)
+                return run()
             st.graph = graph
             # the capture did not execute anything: the replay below runs this step
         st.graph.replay()
