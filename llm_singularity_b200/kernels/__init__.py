@@ -278,6 +278,7 @@ def rope_kv_store(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache,
 
 
 NUM_SMS = 148                   # B200: 2 dies x 74
+USE_TCGEN05_ATTENTION = True    # prompt portions of 128 tokens and more
 _TC_HEAD_DIMS = (64, 128)
 
 
@@ -338,8 +339,16 @@ def paged_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache, s
         _call("attention_tc", "lsb_decode_attention", *common, _p(scratch), _i(R), *tail,
               _i(splits), _stream(out))
     if n_decode < R:
-        _call("attention_tc", "lsb_prefill_attention", *common, _i(R), _i(ctx.max_q_len), *tail,
-              _i(1 if n_decode else 0), _stream(out))
+        # prompt portions: tcgen05 kernel for long ones (128-row tiles), mma.sync kernel otherwise
+        if (USE_TCGEN05_ATTENTION and ctx.max_q_len >= 128
+                and cache.page_size in (8, 16, 32, 64) and qkv.shape[1] % 8 == 0):
+            _call("attention_tc5", "lsb_prefill_attention_tc5", _p(qkv), _i(qkv.shape[1]), _i(T),
+                  _p(cache.k_pages), _p(cache.v_pages), _p(ctx.q_start), _p(ctx.kv_len),
+                  _p(ctx.table_rows), _p(cache.block_table), _i(cache.block_table.shape[1]), _p(out),
+                  _i(R), _i(ctx.max_q_len), *tail, _i(1 if n_decode else 0), _stream(out))
+        else:
+            _call("attention_tc", "lsb_prefill_attention", *common, _i(R), _i(ctx.max_q_len), *tail,
+                  _i(1 if n_decode else 0), _stream(out))
 
 
 def sample(logits: torch.Tensor, params: torch.Tensor, top_k: torch.Tensor,

@@ -35,6 +35,7 @@ SOURCES: Dict[str, str] = {
     "rope_cache": "rope_cache.cu",
     "attention": "attention.cu",
     "attention_tc": "attention_tc.cu",
+    "attention_tc5": "attention_tc5.cu",
     "gemm": "gemm.cu",
     "gemm_tc": "gemm_tc.cu",
     "sampling": "sampling.cu",

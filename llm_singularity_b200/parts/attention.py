@@ -33,7 +33,7 @@ class PagedAttention(Part):
             raise ValueError(f"window must be at least 1, got {s.window}")
         self.position = POSITIONS.build(s.position, rt)
         if rt.dtype == torch.bfloat16 and s.head_dim in (64, 128):
-            self.kernels = self.kernels + ("attention_tc",)
+            self.kernels = self.kernels + ("attention_tc", "attention_tc5")
         self.q_size = s.num_heads * s.head_dim
         self.kv_size = s.num_kv_heads * s.head_dim
 
