@@ -209,11 +209,11 @@ def greedy_generate(cfg, w, prompt, n_new):
 
 
 # ------------------------------------------------------------------------ sampling
-def sample_plain(logits, temperature=1.0, top_k=0, top_p=1.0, repetition_penalty=1.0,
-                 prev_tokens=(), u=0.5):
-    """The reference sampler (core/src/sampling.cpp:11-118) with the uniform draw ``u``
-    given: repetition penalty -> greedy if T == 0 -> /T -> top-k -> top-p -> softmax ->
-    first i with u <= cumsum."""
+def sample_distribution_plain(logits, temperature=1.0, top_k=0, top_p=1.0, repetition_penalty=1.0,
+                              prev_tokens=()):
+    """The distribution the reference sampler draws from (core/src/sampling.cpp:11-103):
+    repetition penalty -> /T -> top-k -> top-p -> softmax.  With T == 0 it is one at the first
+    maximum of the penalised logits (sampling.cpp:35-38)."""
     work = [float(x) for x in logits]
     V = len(work)
     if repetition_penalty != 1.0:
@@ -221,7 +221,8 @@ def sample_plain(logits, temperature=1.0, top_k=0, top_p=1.0, repetition_penalty
             if 0 <= t < V:
                 work[t] = work[t] / repetition_penalty if work[t] > 0 else work[t] * repetition_penalty
     if temperature == 0.0:
-        return max(range(V), key=lambda i: (work[i], -i))
+        best = max(range(V), key=lambda i: (work[i], -i))
+        return [1.0 if i == best else 0.0 for i in range(V)]
     work = [x / temperature for x in work]
     if 0 < top_k < V:
         order = sorted(range(V), key=lambda i: (-work[i], i))
@@ -243,9 +244,21 @@ def sample_plain(logits, temperature=1.0, top_k=0, top_p=1.0, repetition_penalty
     m = max(work)
     probs = [math.exp(x - m) for x in work]
     s = sum(probs)
+    return [p / s for p in probs]
+
+
+def sample_plain(logits, temperature=1.0, top_k=0, top_p=1.0, repetition_penalty=1.0,
+                 prev_tokens=(), u=0.5):
+    """The reference sampler (core/src/sampling.cpp:11-118) with the uniform draw ``u``
+    given: the first i with u <= cumsum of the distribution above (sampling.cpp:105-117)."""
+    probs = sample_distribution_plain(logits, temperature, top_k, top_p, repetition_penalty,
+                                      prev_tokens)
+    V = len(probs)
+    if temperature == 0.0:
+        return probs.index(1.0)
     c = 0.0
     for i in range(V):
-        c += probs[i] / s
+        c += probs[i]
         if u <= c:
             return i
     return max(i for i in range(V) if probs[i] > 0)
