@@ -52,10 +52,77 @@ def build_parser() -> argparse.ArgumentParser:
     ap.add_argument("--repetition-penalty", type=float, default=1.0)
     ap.add_argument("--ignore-eos", action="store_true")
     ap.add_argument("--stats", action="store_true", help="print engine counters at the end")
+    ap.add_argument("--bench", choices=["decode", "prefill", "serve"], default=None,
+                    help="time instead of printing tokens: 'decode' fills --num-requests contexts of "
+                         "--prompt-len and times --max-new-tokens decode steps; 'prefill' times one "
+                         "prompt of --prompt-len; 'serve' runs --num-requests prompts of mixed length "
+                         "(up to --prompt-len) through continuous batching")
     ap.add_argument("--device", default="cuda:0")
     for flag in ("--host", "--port", "--hf-token"):
         ap.add_argument(flag, default=None, help="accepted for compatibility; not used")
     return ap
+
+
+def _sync_time(device) -> float:
+    torch.cuda.synchronize(device)
+    return time.perf_counter()
+
+
+def run_bench(eng, args) -> dict:
+    """Wall-clock timings through the public entry point (host tokens in, host tokens out),
+    synchronised on both sides.  Prompts are seeded uniform-random token ids."""
+    dev = eng.runner.rt.device
+    g = torch.Generator().manual_seed(args.seed)
+    V = eng.runner.vocab_size
+
+    def prompt(n):
+        return torch.randint(0, V, (n,), generator=g).tolist()
+
+    out = {"bench": args.bench, "dtype": args.dtype, "prompt_len": args.prompt_len,
+           "num_requests": args.num_requests}
+    if args.bench == "prefill":
+        times = []
+        for i in range(4):                       # the first run warms up and is dropped
+            eng.add_request(prompt(args.prompt_len), 1, ignore_eos=True, seed=i)
+            t0 = _sync_time(dev)
+            while eng.has_work():
+                eng.step()
+            times.append(_sync_time(dev) - t0)
+        best = min(times[1:])
+        out.update(seconds=round(best, 6), prompt_tokens_per_s=round(args.prompt_len / best, 1))
+    elif args.bench == "decode":
+        n_new = max(2, args.max_new_tokens)
+        for i in range(args.num_requests):
+            eng.add_request(prompt(args.prompt_len), n_new + 8, ignore_eos=True, seed=i)
+        while any(not eng.request(r).generated for r in range(args.num_requests)):
+            eng.step()                           # prompts in; every request now decodes
+        for _ in range(4):
+            eng.step()
+        t0 = _sync_time(dev)
+        made = 0
+        for _ in range(n_new - 4):
+            made += len(eng.step())
+        dt = _sync_time(dev) - t0
+        out.update(seconds=round(dt, 6), decode_steps=n_new - 4,
+                   generated_tokens_per_s=round(made / dt, 1))
+        while eng.has_work():
+            eng.step()
+    else:
+        lens = torch.randint(max(1, args.prompt_len // 16), args.prompt_len + 1,
+                             (args.num_requests,), generator=g).tolist()
+        for i, n in enumerate(lens):
+            eng.add_request(prompt(n), args.max_new_tokens, temperature=args.temperature,
+                            ignore_eos=args.ignore_eos, seed=args.seed + i)
+        t0 = _sync_time(dev)
+        made = 0
+        while eng.has_work():
+            made += sum(1 for _, tok, _ in eng.step() if tok >= 0)
+        dt = _sync_time(dev) - t0
+        out.update(seconds=round(dt, 6), prompt_tokens=sum(lens), generated_tokens=made,
+                   generated_tokens_per_s=round(made / dt, 1),
+                   total_tokens_per_s=round((made + sum(lens)) / dt, 1))
+    out["stats"] = eng.stats()
+    return out
 
 
 def main(argv=None) -> int:
@@ -70,6 +137,9 @@ def main(argv=None) -> int:
                  num_kv_blocks=args.num_kv_blocks, max_batch_size=args.max_batch_size,
                  max_tokens_per_batch=args.max_tokens_per_batch, prefill_chunk=args.prefill_chunk,
                  prefix_cache=not args.no_prefix_cache, verbose=True)
+    if args.bench:
+        print(json.dumps(run_bench(eng, args)))
+        return 0
     if args.prompt_ids:
         prompts = _read_prompts(args.prompt_ids)
     else:

@@ -119,7 +119,7 @@ __device__ __forceinline__ int div_page(int key, int page_size, int page_shift) 
 #ifndef LSB_DEC_MINBLOCKS
 #define LSB_DEC_MINBLOCKS 4
 #endif
-template <int HD>
+template <int HD, bool LOW8>
 __global__ void __launch_bounds__(kThreads, LSB_DEC_MINBLOCKS)
 decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
                         const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
@@ -191,6 +191,26 @@ decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
             const int chunk = c0 + warp + 4 * i;
             bf16* dK = ring + (size_t)(i % kDecStages) * kStageElems;
             bf16* dV = dK + kChunk * HD;
+            if (page_shift >= 0 && page_size >= kChunk) {
+                // the chunk lies inside one page: one table entry, then a contiguous run of rows
+                const int key0 = chunk * kChunk;
+                const int pi = key0 >> page_shift;
+                const int page = cached ? sBT[pi - page0] : (pi < table_stride ? bt[pi] : -1);
+                const bool page_ok = page >= 0 && page < num_pages;
+                if (!page_ok) lsb_set_status(LSB_BAD_PAGE);
+                const long long base = page_ok
+                    ? (((long long)page * nkv + g) * page_size + (key0 - (pi << page_shift))) * HD : 0;
+                const bf16* srcK = k_pages + base;
+                const bf16* srcV = v_pages + base;
+#pragma unroll
+                for (int idx = lane; idx < kChunk * CPR; idx += 32) {
+                    const int kk = idx / CPR, c = idx - kk * CPR;
+                    const bool valid = page_ok && key0 + kk >= lo && key0 + kk <= p;
+                    const int off = valid ? idx * 8 : 0;
+                    cp_async16(tile_ptr<HD>(dK, kk, c), srcK + off, valid);
+                    cp_async16(tile_ptr<HD>(dV, kk, c), srcV + off, valid);
+                }
+            } else
 #pragma unroll
             for (int idx = lane; idx < kChunk * CPR; idx += 32) {
                 const int kk = idx / CPR, c = idx - kk * CPR;
@@ -239,46 +259,73 @@ decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
                 mma_bf16(s[2 * np], qf[ks], b[0], b[1]);
                 mma_bf16(s[2 * np + 1], qf[ks], b[2], b[3]);
             }
-        // mask keys outside [lo, p]; scale into the log2 domain
+        // Rows 8..15 of the tile hold no query when the group has at most 8 heads: NR is the number
+        // of row halves with work, and everything scalar below skips the other one.
+        constexpr int NR = LOW8 ? 1 : 2;
+        constexpr int NE = 2 * NR;
         float mx[2] = {-INFINITY, -INFINITY};
+        const int key0 = chunk * kChunk;
+        if (key0 >= lo && key0 + kChunk - 1 <= p) {            // whole chunk in range: no mask
 #pragma unroll
-        for (int nt = 0; nt < NT; ++nt)
+            for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int key = chunk * kChunk + nt * 8 + 2 * (lane & 3) + (e & 1);
-                const float v = (key >= lo && key <= p) ? s[nt][e] * sc : -INFINITY;
-                s[nt][e] = v;
-                mx[e >> 1] = fmaxf(mx[e >> 1], v);
-            }
-        float corr[2], mref[2];
+                for (int e = 0; e < NE; ++e) {
+                    s[nt][e] *= sc;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], s[nt][e]);
+                }
+        } else {
+            // mask keys outside [lo, p]; scale into the log2 domain
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
+            for (int nt = 0; nt < NT; ++nt)
+#pragma unroll
+                for (int e = 0; e < NE; ++e) {
+                    const int key = key0 + nt * 8 + 2 * (lane & 3) + (e & 1);
+                    const float v = (key >= lo && key <= p) ? s[nt][e] * sc : -INFINITY;
+                    s[nt][e] = v;
+                    mx[e >> 1] = fmaxf(mx[e >> 1], v);
+                }
+        }
+        float mref[2] = {0.f, 0.f};
+        bool moved = false;
+#pragma unroll
+        for (int h = 0; h < NR; ++h) {
             mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
             mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-            const float m_new = fmaxf(m[h], mx[h]);
-            corr[h] = (m[h] == -INFINITY) ? 0.f : fast_exp2(m[h] - m_new);
-            m[h] = m_new;
-            l[h] *= corr[h];
-            mref[h] = m_new == -INFINITY ? 0.f : m_new;        // ex2(-inf - 0) = 0 without a branch
+            moved = moved || mx[h] > m[h];
         }
+        if (__any_sync(0xffffffffu, moved)) {                  // rare once the first chunks are in
+            float corr[2] = {1.f, 1.f};
+#pragma unroll
+            for (int h = 0; h < NR; ++h) {
+                const float m_new = fmaxf(m[h], mx[h]);
+                corr[h] = (m[h] == -INFINITY) ? 0.f : fast_exp2(m[h] - m_new);
+                m[h] = m_new;
+                l[h] *= corr[h];
+            }
+#pragma unroll
+            for (int i2 = 0; i2 < HD / 8; ++i2) {
+                o[i2][0] *= corr[0]; o[i2][1] *= corr[0];
+                if (!LOW8) { o[i2][2] *= corr[1]; o[i2][3] *= corr[1]; }
+            }
+        }
+#pragma unroll
+        for (int h = 0; h < NR; ++h) mref[h] = m[h] == -INFINITY ? 0.f : m[h];   // ex2(-inf - 0) = 0
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
+            for (int e = 0; e < NE; ++e) {
                 const float pv = fast_exp2(s[nt][e] - mref[e >> 1]);
                 s[nt][e] = pv;
                 l[e >> 1] += pv;
             }
 #pragma unroll
-        for (int i2 = 0; i2 < HD / 8; ++i2) {
-            o[i2][0] *= corr[0]; o[i2][1] *= corr[0];
-            o[i2][2] *= corr[1]; o[i2][3] *= corr[1];
-        }
-#pragma unroll
         for (int kt = 0; kt < NT / 2; ++kt) {
-            uint32_t pa[4] = {pack_bf16(s[2 * kt][0], s[2 * kt][1]), pack_bf16(s[2 * kt][2], s[2 * kt][3]),
-                              pack_bf16(s[2 * kt + 1][0], s[2 * kt + 1][1]),
-                              pack_bf16(s[2 * kt + 1][2], s[2 * kt + 1][3])};
+            uint32_t pa[4] = {pack_bf16(s[2 * kt][0], s[2 * kt][1]), 0u,
+                              pack_bf16(s[2 * kt + 1][0], s[2 * kt + 1][1]), 0u};
+            if (!LOW8) {
+                pa[1] = pack_bf16(s[2 * kt][2], s[2 * kt][3]);
+                pa[3] = pack_bf16(s[2 * kt + 1][2], s[2 * kt + 1][3]);
+            }
 #pragma unroll
             for (int dt = 0; dt < HD / 16; ++dt) {
                 uint32_t b[4];
@@ -624,8 +671,11 @@ template <int HD> constexpr size_t prefill_smem() {
 template <int HD> static int configure_once() {
     static int done = -1;
     if (done >= 0) return done;
-    cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<HD>,
+    cudaError_t e = cudaFuncSetAttribute(decode_attention_kernel<HD, true>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem<HD>());
+    if (e == cudaSuccess)
+        e = cudaFuncSetAttribute(decode_attention_kernel<HD, false>,
+                                 cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem<HD>());
     if (e == cudaSuccess)
         e = cudaFuncSetAttribute(prefill_attention_kernel<HD>,
                                  cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_smem<HD>());
@@ -657,7 +707,9 @@ LSB_API int lsb_decode_attention(const void* qkv, int qkv_stride, const void* k_
     do {                                                                                           \
         int rc = configure_once<HD>();                                                             \
         if (rc) return rc;                                                                         \
-        rc = lsb_launch(decode_attention_kernel<HD>, grid, dim3(kThreads), decode_smem<HD>(), stream, \
+        rc = lsb_launch(nh / nkv <= 8 ? decode_attention_kernel<HD, true>                          \
+                                      : decode_attention_kernel<HD, false>,                        \
+            grid, dim3(kThreads), decode_smem<HD>(), stream,                                       \
             in_cluster ? splits : 1,                                                               \
             (const bf16*)qkv, qkv_stride, (const bf16*)k_pages, (const bf16*)v_pages, q_start,    \
             kv_len, table_rows, block_table, table_stride, (bf16*)out, part_o, part_ml, nh, nkv,  \
@@ -759,7 +811,9 @@ LSB_API int lsb_decode_attention_noalloc(const void* qkv, int qkv_stride, const 
     do {                                                                                           \
         int rc = configure_once<HD>();                                                             \
         if (rc) return rc;                                                                         \
-        rc = lsb_launch(decode_attention_kernel<HD>, grid, dim3(kThreads), decode_smem<HD>(), stream, \
+        rc = lsb_launch(nh / nkv <= 8 ? decode_attention_kernel<HD, true>                          \
+                                      : decode_attention_kernel<HD, false>,                        \
+            grid, dim3(kThreads), decode_smem<HD>(), stream,                                       \
             in_cluster ? splits : 1,                                                               \
             (const bf16*)qkv, qkv_stride, (const bf16*)k_pages, (const bf16*)v_pages, q_start,    \
             kv_len, table_rows, block_table, table_stride, (bf16*)out, part_o, part_ml, nh, nkv,  \

@@ -129,3 +129,19 @@ def test_command_line(model_dirs, tmp_path):
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
     assert res.returncode == 0, res.stderr
     assert [len(json.loads(l)["tokens"]) for l in res.stdout.splitlines()] == [4, 4, 4]
+
+
+@pytest.mark.parametrize("mode", ["decode", "prefill", "serve"])
+def test_command_line_bench_modes(model_dirs, mode):
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "llm-serve-llama"), "--model-dir", model_dirs["tiny_b"],
+           "--bench", mode, "--prompt-len", "40", "--num-requests", "5", "--max-new-tokens", "12",
+           "--ignore-eos", "--kv-block-size", "8", "--num-kv-blocks", "24", "--max-batch-size", "4"]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stderr
+    line = json.loads(res.stdout.splitlines()[-1])
+    assert line["bench"] == mode and line["seconds"] > 0
+    if mode == "serve":
+        assert line["generated_tokens"] == 5 * 12
+        assert line["stats"]["pages_free"] + line["stats"]["prefix_nodes"] >= 0
+    if mode == "decode":
+        assert line["generated_tokens_per_s"] > 0
