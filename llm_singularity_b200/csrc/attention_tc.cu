@@ -75,6 +75,19 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Rotates eight split-half pairs: lo holds x[i..i+7], hi holds x[i+half..], cs/sn their cosines
+// and sines.
+__device__ __forceinline__ void rotate8(uint4& lo, uint4& hi, const float* cs, const float* sn) {
+    bf16* a = reinterpret_cast<bf16*>(&lo);
+    bf16* b = reinterpret_cast<bf16*>(&hi);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        const float x0 = __bfloat162float(a[e]), x1 = __bfloat162float(b[e]);
+        a[e] = __float2bfloat16_rn(x0 * cs[e] - x1 * sn[e]);
+        b[e] = __float2bfloat16_rn(x0 * sn[e] + x1 * cs[e]);
+    }
+}
+
 // thread-block cluster helpers: rank, barrier over all threads of all blocks, a float from a peer
 __device__ __forceinline__ uint32_t cluster_rank() {
     uint32_t r;
@@ -122,18 +135,20 @@ __device__ __forceinline__ int div_page(int key, int page_size, int page_shift) 
 template <int HD, bool LOW8>
 __global__ void __launch_bounds__(kThreads, LSB_DEC_MINBLOCKS)
 decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
-                        const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
+                        bf16* k_pages, bf16* v_pages,
                         const int* __restrict__ q_start, const int* __restrict__ kv_len_arr,
                         const int* __restrict__ table_rows, const int* __restrict__ block_table,
                         int table_stride, bf16* __restrict__ out, float* __restrict__ part_o,
                         float* __restrict__ part_ml, int nh, int nkv, int page_size, int num_pages,
-                        float scale, int window, int splits, int cluster_merge) {
+                        float scale, int window, int splits, int cluster_merge,
+                        const float* __restrict__ inv_freq, int store_kv) {
     constexpr int CPR = HD / 8, KS = HD / 16;
     constexpr int kStageElems = 2 * kChunk * HD;             // K rows then V rows
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* sQ = reinterpret_cast<bf16*>(smem_raw);            // [16][HD]
     bf16* sKV = sQ + 16 * HD;                                // [4 warps][stages][K|V][16][HD]
     int* sBT = reinterpret_cast<int*>(sKV + 4 * kDecStages * kStageElems);
+    float* sCS = reinterpret_cast<float*>(sBT + kBtCache);   // [cos HD/2][sin HD/2] of the position
     lsb_pdl_launch_dependents();
     lsb_pdl_wait();
 
@@ -162,15 +177,62 @@ decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
         for (int idx = threadIdx.x; idx < n_pages_here; idx += kThreads)
             sBT[idx] = (page0 + idx < table_stride) ? bt[page0 + idx] : -1;
 
-    // queries of the group: rows 0..G-1 of a 16-row tile, the rest zero
-    for (int idx = threadIdx.x; idx < 16 * CPR; idx += kThreads) {
-        const int row = idx / CPR, c = idx - row * CPR;
-        uint4 v = make_uint4(0, 0, 0, 0);
-        if (row < G)
-            v = *reinterpret_cast<const uint4*>(qkv + (size_t)qs * qkv_stride + (size_t)(g * G + row) * HD + c * 8);
-        *reinterpret_cast<uint4*>(tile_ptr<HD>(sQ, row, c)) = v;
+    const bf16* tok = qkv + (size_t)qs * qkv_stride;          // this token's row of the projection
+    if (inv_freq) {
+        // The projection comes unrotated: the rotation of the queries and of the new key happens
+        // here (split-half pairs (i, i + HD/2), angle p * inv_freq[i] in 32-bit, as the separate
+        // rotary kernel forms it), and the block whose key range holds position p writes the new
+        // key and value into their page before anybody's copies start.
+        constexpr int HC = CPR / 2;                             // 16-byte chunks per half row
+        for (int i = threadIdx.x; i < HD / 2; i += kThreads)
+            sincosf((float)p * inv_freq[i], &sCS[HD / 2 + i], &sCS[i]);
+        __syncthreads();
+        for (int idx = threadIdx.x; idx < 16 * HC; idx += kThreads) {
+            const int row = idx / HC, c = idx - row * HC;
+            uint4 vlo = make_uint4(0, 0, 0, 0), vhi = make_uint4(0, 0, 0, 0);
+            if (row < G) {
+                const bf16* src = tok + (size_t)(g * G + row) * HD;
+                vlo = *reinterpret_cast<const uint4*>(src + c * 8);
+                vhi = *reinterpret_cast<const uint4*>(src + HD / 2 + c * 8);
+                rotate8(vlo, vhi, sCS + c * 8, sCS + HD / 2 + c * 8);
+            }
+            *reinterpret_cast<uint4*>(tile_ptr<HD>(sQ, row, c)) = vlo;
+            *reinterpret_cast<uint4*>(tile_ptr<HD>(sQ, row, c + HC)) = vhi;
+        }
+        const int pc = p / kChunk;
+        if (store_kv && pc >= c0 && pc < c1) {
+            const int pi = div_page(p, page_size, page_shift);
+            const int page = pi < table_stride ? bt[pi] : -1;
+            if (page < 0 || page >= num_pages) {
+                if (threadIdx.x == 0) lsb_set_status(LSB_BAD_PAGE);
+            } else {
+                const long long dst = (((long long)page * nkv + g) * page_size + (p - pi * page_size)) * HD;
+                if (threadIdx.x < HC) {
+                    const int c = threadIdx.x;
+                    const bf16* src = tok + (size_t)(nh + g) * HD;
+                    uint4 vlo = *reinterpret_cast<const uint4*>(src + c * 8);
+                    uint4 vhi = *reinterpret_cast<const uint4*>(src + HD / 2 + c * 8);
+                    rotate8(vlo, vhi, sCS + c * 8, sCS + HD / 2 + c * 8);
+                    *reinterpret_cast<uint4*>(k_pages + dst + c * 8) = vlo;
+                    *reinterpret_cast<uint4*>(k_pages + dst + HD / 2 + c * 8) = vhi;
+                } else if (threadIdx.x >= 32 && threadIdx.x < 32 + CPR) {
+                    const int c = threadIdx.x - 32;
+                    *reinterpret_cast<uint4*>(v_pages + dst + c * 8) =
+                        *reinterpret_cast<const uint4*>(tok + (size_t)(nh + nkv + g) * HD + c * 8);
+                }
+            }
+        }
+    } else {
+        // queries of the group: rows 0..G-1 of a 16-row tile, the rest zero
+        for (int idx = threadIdx.x; idx < 16 * CPR; idx += kThreads) {
+            const int row = idx / CPR, c = idx - row * CPR;
+            uint4 v = make_uint4(0, 0, 0, 0);
+            if (row < G)
+                v = *reinterpret_cast<const uint4*>(tok + (size_t)(g * G + row) * HD + c * 8);
+            *reinterpret_cast<uint4*>(tile_ptr<HD>(sQ, row, c)) = v;
+        }
     }
-    __syncthreads();
+    __syncthreads();            // also orders the new key and value before the copies below
 
     uint32_t qf[KS][4];
 #pragma unroll
@@ -662,7 +724,8 @@ prefill_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
 
 // ------------------------------------------------------------------ host side
 template <int HD> constexpr size_t decode_smem() {
-    return (16 * HD + 4 * kDecStages * 2 * kChunk * HD) * sizeof(bf16) + kBtCache * sizeof(int);
+    return (16 * HD + 4 * kDecStages * 2 * kChunk * HD) * sizeof(bf16) + kBtCache * sizeof(int) +
+           HD * sizeof(float);
 }
 template <int HD> constexpr size_t prefill_smem() {
     return (kPfRows * HD + 2 * kPfStages * kTile * HD) * sizeof(bf16) + kBtCache * sizeof(int);
@@ -690,11 +753,12 @@ LSB_API long long lsb_decode_scratch_floats(int n_requests, int nh, int hd, int 
 
 // Single decode tokens (requests with q_len == 1; others are skipped).  bf16, hd 64 or 128,
 // nh / nkv <= 16.  `scratch` holds lsb_decode_scratch_floats floats when splits > 1.
-LSB_API int lsb_decode_attention(const void* qkv, int qkv_stride, const void* k_pages, const void* v_pages,
-                                 const int* q_start, const int* kv_len, const int* table_rows,
-                                 const int* block_table, int table_stride, void* out, float* scratch,
-                                 int n_requests, int nh, int nkv, int hd, int page_size, int num_pages,
-                                 float scale, int window, int splits, cudaStream_t stream) {
+static int decode_launch(const void* qkv, int qkv_stride, void* k_pages, void* v_pages,
+                         const int* q_start, const int* kv_len, const int* table_rows,
+                         const int* block_table, int table_stride, void* out, float* scratch,
+                         int n_requests, int nh, int nkv, int hd, int page_size, int num_pages,
+                         float scale, int window, int splits, const float* inv_freq, int store_kv,
+                         cudaStream_t stream) {
     if (n_requests <= 0) return 0;
     if (nkv <= 0 || nh % nkv || nh / nkv > 16 || splits < 1 || n_requests > 65535 || nkv > 65535)
         return (int)cudaErrorInvalidValue;
@@ -711,9 +775,9 @@ LSB_API int lsb_decode_attention(const void* qkv, int qkv_stride, const void* k_
                                       : decode_attention_kernel<HD, false>,                        \
             grid, dim3(kThreads), decode_smem<HD>(), stream,                                       \
             in_cluster ? splits : 1,                                                               \
-            (const bf16*)qkv, qkv_stride, (const bf16*)k_pages, (const bf16*)v_pages, q_start,    \
+            (const bf16*)qkv, qkv_stride, (bf16*)k_pages, (bf16*)v_pages, q_start,                \
             kv_len, table_rows, block_table, table_stride, (bf16*)out, part_o, part_ml, nh, nkv,  \
-            page_size, num_pages, scale, window, splits, in_cluster ? 1 : 0);                      \
+            page_size, num_pages, scale, window, splits, in_cluster ? 1 : 0, inv_freq, store_kv);  \
         if (rc) return rc;                                                                         \
         if (splits > 1 && !in_cluster)                                                             \
             rc = lsb_launch(decode_merge_kernel<HD>, dim3(nh, n_requests), dim3(64), 0, stream, 1, \
@@ -725,6 +789,32 @@ LSB_API int lsb_decode_attention(const void* qkv, int qkv_stride, const void* k_
     else return (int)cudaErrorInvalidValue;
 #undef LAUNCH_DECODE
     return 0;
+}
+
+LSB_API int lsb_decode_attention(const void* qkv, int qkv_stride, const void* k_pages, const void* v_pages,
+                                 const int* q_start, const int* kv_len, const int* table_rows,
+                                 const int* block_table, int table_stride, void* out, float* scratch,
+                                 int n_requests, int nh, int nkv, int hd, int page_size, int num_pages,
+                                 float scale, int window, int splits, cudaStream_t stream) {
+    return decode_launch(qkv, qkv_stride, const_cast<void*>(k_pages), const_cast<void*>(v_pages), q_start,
+                         kv_len, table_rows, block_table, table_stride, out, scratch, n_requests, nh, nkv,
+                         hd, page_size, num_pages, scale, window, splits, nullptr, 0, stream);
+}
+
+// The same over a projection that has not been rotated yet: the kernel rotates the queries and the
+// new key by `inv_freq` (hd / 2 entries: the whole head is rotary) at position kv_len - 1 and,
+// if `store_kv`, writes the new key and value into their page.  Replaces the separate rotary kernel
+// for single decode tokens.
+LSB_API int lsb_decode_attention_rope(const void* qkv, int qkv_stride, void* k_pages, void* v_pages,
+                                      const int* q_start, const int* kv_len, const int* table_rows,
+                                      const int* block_table, int table_stride, void* out, float* scratch,
+                                      int n_requests, int nh, int nkv, int hd, int page_size,
+                                      int num_pages, float scale, int window, int splits,
+                                      const float* inv_freq, int store_kv, cudaStream_t stream) {
+    if (!inv_freq) return (int)cudaErrorInvalidValue;
+    return decode_launch(qkv, qkv_stride, k_pages, v_pages, q_start, kv_len, table_rows, block_table,
+                         table_stride, out, scratch, n_requests, nh, nkv, hd, page_size, num_pages,
+                         scale, window, splits, inv_freq, store_kv, stream);
 }
 
 // Prompt portions (and, unless skip_single, single tokens too).  bf16, hd 64 or 128.
@@ -815,9 +905,11 @@ LSB_API int lsb_decode_attention_noalloc(const void* qkv, int qkv_stride, const 
                                       : decode_attention_kernel<HD, false>,                        \
             grid, dim3(kThreads), decode_smem<HD>(), stream,                                       \
             in_cluster ? splits : 1,                                                               \
-            (const bf16*)qkv, qkv_stride, (const bf16*)k_pages, (const bf16*)v_pages, q_start,    \
+            (const bf16*)qkv, qkv_stride, (bf16*)const_cast<void*>(k_pages),                      \
+            (bf16*)const_cast<void*>(v_pages), q_start,                                            \
             kv_len, table_rows, block_table, table_stride, (bf16*)out, part_o, part_ml, nh, nkv,  \
-            page_size, num_pages, scale, window, splits, in_cluster ? 1 : 0);                      \
+            page_size, num_pages, scale, window, splits, in_cluster ? 1 : 0,                       \
+            (const float*)nullptr, 0);                                                             \
         if (rc) return rc;                                                                         \
         if (splits > 1 && !in_cluster)                                                             \
             rc = lsb_launch(decode_merge_kernel<HD>, dim3(nh, n_requests), dim3(64), 0, stream, 1, \

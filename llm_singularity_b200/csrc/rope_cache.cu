@@ -21,10 +21,15 @@ __global__ void rope_kv_store_kernel(
     const int* __restrict__ table_rows, const int* __restrict__ block_table, int table_stride,
     const float* __restrict__ inv_freq, int rotary_dim,
     T* __restrict__ k_pages, T* __restrict__ v_pages,
-    int nh, int nkv, int hd, int page_size, int num_pages, int store) {
+    int nh, int nkv, int hd, int page_size, int num_pages, int store,
+    const int* __restrict__ skip_q_start) {
     lsb_pdl_launch_dependents();
     lsb_pdl_wait();
     const int t = blockIdx.x;
+    if (skip_q_start) {           // single decode tokens are rotated and stored by their attention kernel
+        const int r = token_req[t];
+        if (skip_q_start[r + 1] - skip_q_start[r] == 1) return;
+    }
     const int pos = positions[t];
     const int half_hd = hd >> 1;
     const int half_rot = rotary_dim >> 1;
@@ -90,12 +95,17 @@ __global__ void rope_kv_store_vec_kernel(
     const int* __restrict__ table_rows, const int* __restrict__ block_table, int table_stride,
     const float* __restrict__ inv_freq, int rotary_dim,
     T* __restrict__ k_pages, T* __restrict__ v_pages,
-    int nh, int nkv, int hd, int page_size, int num_pages, int store) {
+    int nh, int nkv, int hd, int page_size, int num_pages, int store,
+    const int* __restrict__ skip_q_start) {
     constexpr int VEC = 16 / sizeof(T);
     __shared__ float cs[2][128];
     lsb_pdl_launch_dependents();
     lsb_pdl_wait();
     const int t = blockIdx.x;
+    if (skip_q_start) {
+        const int r = token_req[t];
+        if (skip_q_start[r + 1] - skip_q_start[r] == 1) return;
+    }
     const int pos = positions[t];
     const int half_rot = rotary_dim >> 1;
     T* row = qkv + (size_t)t * (nh + 2 * nkv) * hd;
@@ -154,13 +164,15 @@ __global__ void rope_kv_store_vec_kernel(
     }
 }
 
-// inv_freq may be null with rotary_dim == 0 (no rotation, only the cache write).
+// inv_freq may be null with rotary_dim == 0 (no rotation, only the cache write).  With
+// `skip_q_start` (the step's q_start array) tokens of requests that bring a single token are left
+// alone: the decode attention kernel rotates and stores those itself.
 LSB_API int lsb_rope_kv_store(void* qkv, int dtype, int tokens, int nh, int nkv, int hd,
                               const int* positions, const int* token_req, const int* table_rows,
                               const int* block_table, int table_stride,
                               const float* inv_freq, int rotary_dim,
                               void* k_pages, void* v_pages, int page_size, int num_pages,
-                              int store, cudaStream_t stream) {
+                              int store, const int* skip_q_start, cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (hd % 2 || rotary_dim % 2 || rotary_dim > hd || (rotary_dim > 0 && !inv_freq))
         return (int)cudaErrorInvalidValue;
@@ -174,11 +186,11 @@ LSB_API int lsb_rope_kv_store(void* qkv, int dtype, int tokens, int nh, int nkv,
         LSB_DISPATCH_DTYPE(dtype, return lsb_launch(
             rope_kv_store_vec_kernel<T>, dim3(tokens), dim3(th), 0, stream, 1,
             (T*)qkv, positions, token_req, table_rows, block_table, table_stride, inv_freq, rotary_dim,
-            (T*)k_pages, (T*)v_pages, nh, nkv, hd, page_size, num_pages, store));
+            (T*)k_pages, (T*)v_pages, nh, nkv, hd, page_size, num_pages, store, skip_q_start));
     }
     LSB_DISPATCH_DTYPE(dtype, return lsb_launch(
         rope_kv_store_kernel<T>, dim3(tokens), dim3(threads), 0, stream, 1,
         (T*)qkv, positions, token_req, table_rows, block_table, table_stride, inv_freq, rotary_dim,
-        (T*)k_pages, (T*)v_pages, nh, nkv, hd, page_size, num_pages, store));
+        (T*)k_pages, (T*)v_pages, nh, nkv, hd, page_size, num_pages, store, skip_q_start));
     return 0;
 }

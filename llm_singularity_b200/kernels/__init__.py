@@ -253,9 +253,11 @@ def _check_cache(cache, nkv: int, hd: int, dtype) -> None:
 
 
 def rope_kv_store(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache,
-                  inv_freq: Optional[torch.Tensor], rotary_dim: int, store: bool = True) -> None:
+                  inv_freq: Optional[torch.Tensor], rotary_dim: int, store: bool = True,
+                  skip_single: bool = False) -> None:
     """Rotate queries and keys of the fused projection in place and write keys and values
-    of this step's tokens into their cache pages."""
+    of this step's tokens into their cache pages.  ``skip_single`` leaves the tokens of requests
+    that bring one token alone (their attention kernel does the same work itself)."""
     _req(qkv, "qkv", dim=2)
     T = qkv.shape[0]
     if qkv.shape[1] != (nh + 2 * nkv) * hd:
@@ -274,11 +276,12 @@ def rope_kv_store(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache,
           _p(ctx.positions), _p(ctx.token_req), _p(ctx.table_rows), _p(cache.block_table),
           _i(cache.block_table.shape[1]), _p(inv_freq if rotary_dim else None), _i(rotary_dim),
           _p(cache.k_pages), _p(cache.v_pages), _i(cache.page_size), _i(cache.k_pages.shape[0]),
-          _i(1 if store else 0), _stream(qkv))
+          _i(1 if store else 0), _p(ctx.q_start if skip_single else None), _stream(qkv))
 
 
 NUM_SMS = 148                   # B200: 2 dies x 74
 USE_TCGEN05_ATTENTION = True    # prompt portions of 128 tokens and more
+FUSE_DECODE_ROPE = True         # single tokens: rotation and cache write inside the decode kernel
 _TC_HEAD_DIMS = (64, 128)
 
 
@@ -293,13 +296,37 @@ def tensor_core_attention_ok(dtype, hd: int, nh: int, nkv: int) -> bool:
     return dtype == torch.bfloat16 and hd in _TC_HEAD_DIMS and nh // nkv <= 16
 
 
+def rope_store_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache,
+                         inv_freq: Optional[torch.Tensor], rotary_dim: int, store: bool,
+                         scale: float, window: int, out: torch.Tensor) -> None:
+    """``rope_kv_store`` followed by ``paged_attention``, as one operation.  Where the decode
+    kernel can do the rotation and the cache write of single tokens itself (tensor-core path,
+    the whole head rotary), the separate kernel runs only for the tokens of prompt portions, or
+    not at all."""
+    fuse = (FUSE_DECODE_ROPE and rotary_dim == hd and inv_freq is not None
+            and tensor_core_attention_ok(qkv.dtype, hd, nh, nkv))
+    n_decode = int((ctx.h_q_len == 1).sum()) if fuse else 0
+    if not n_decode:
+        rope_kv_store(qkv, nh, nkv, hd, ctx, cache, inv_freq, rotary_dim, store)
+        paged_attention(qkv, nh, nkv, hd, ctx, cache, scale, window, out)
+        return
+    if n_decode < ctx.n_requests:
+        rope_kv_store(qkv, nh, nkv, hd, ctx, cache, inv_freq, rotary_dim, store, skip_single=True)
+    else:
+        _req(inv_freq, "inv_freq", torch.float32, 1)
+        if inv_freq.shape[0] != hd // 2 or qkv.shape[1] != (nh + 2 * nkv) * hd:
+            raise KernelError("rope: inv_freq or qkv do not fit the head size")
+    paged_attention(qkv, nh, nkv, hd, ctx, cache, scale, window, out, decode_rope=(inv_freq, store))
+
+
 def paged_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache, scale: float,
-                    window: int, out: torch.Tensor) -> None:
+                    window: int, out: torch.Tensor, decode_rope=None) -> None:
     """Causal attention of this step's query rows over their requests' cached keys and values.
 
     bfloat16 with head size 64 or 128 runs on the tensor cores: single decode tokens in the
     split-KV kernel, prompt portions in the tiled kernel.  Everything else (32-bit, other head
-    sizes) runs the generic kernel."""
+    sizes) runs the generic kernel.  ``decode_rope = (inv_freq, store)`` says that single tokens
+    come unrotated and not yet in the cache (see ``rope_store_attention``)."""
     _req(qkv, "qkv", dim=2)
     _req(out, "out", qkv.dtype, 2)
     T = qkv.shape[0]
@@ -319,6 +346,8 @@ def paged_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache, s
     tail = (_i(nh), _i(nkv), _i(hd), _i(cache.page_size), _i(cache.k_pages.shape[0]), _f(scale),
             _i(window))
     if not tensor_core_attention_ok(qkv.dtype, hd, nh, nkv):
+        if decode_rope is not None:
+            raise KernelError("attention: only the tensor-core decode kernel rotates by itself")
         _call("attention", "lsb_paged_attention_generic", *common, _i(_dt(qkv)),
               _i(ctx.n_requests), _i(ctx.max_q_len), *tail, _stream(out))
         return
@@ -336,8 +365,12 @@ def paged_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache, s
                 scratch = torch.empty(R * nh * splits * (hd + 2), dtype=torch.float32,
                                       device=qkv.device)
                 _scratch[key] = scratch
-        _call("attention_tc", "lsb_decode_attention", *common, _p(scratch), _i(R), *tail,
-              _i(splits), _stream(out))
+        if decode_rope is None:
+            _call("attention_tc", "lsb_decode_attention", *common, _p(scratch), _i(R), *tail,
+                  _i(splits), _stream(out))
+        else:
+            _call("attention_tc", "lsb_decode_attention_rope", *common, _p(scratch), _i(R), *tail,
+                  _i(splits), _p(decode_rope[0]), _i(1 if decode_rope[1] else 0), _stream(out))
     if n_decode < R:
         # prompt portions: tcgen05 kernel for long ones (128-row tiles), mma.sync kernel otherwise
         if (USE_TCGEN05_ATTENTION and ctx.max_q_len >= 128

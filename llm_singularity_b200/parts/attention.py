@@ -59,14 +59,15 @@ class PagedAttention(Part):
         s, ops = self.spec, self.rt.ops
         qkv = ops.linear(x, self.wqkv)
         table = self.position.rotary_table()
+        out = self.rt.empty(x.shape[0], self.q_size)
         if table is None:
             self.position.apply(qkv[:, :self.q_size], qkv[:, self.q_size:self.q_size + self.kv_size], ctx)
-            inv_freq, rotary_dim = None, 0
+            ops.rope_kv_store(qkv, s.num_heads, s.num_kv_heads, s.head_dim, ctx, cache, None, 0,
+                              store=writes_cache)
+            ops.paged_attention(qkv, s.num_heads, s.num_kv_heads, s.head_dim, ctx, cache,
+                                s.scale, s.window or 0, out)
         else:
             inv_freq, rotary_dim = table
-        ops.rope_kv_store(qkv, s.num_heads, s.num_kv_heads, s.head_dim, ctx, cache,
-                          inv_freq, rotary_dim, store=writes_cache)
-        out = self.rt.empty(x.shape[0], self.q_size)
-        ops.paged_attention(qkv, s.num_heads, s.num_kv_heads, s.head_dim, ctx, cache,
-                            s.scale, s.window or 0, out)
+            ops.rope_store_attention(qkv, s.num_heads, s.num_kv_heads, s.head_dim, ctx, cache,
+                                     inv_freq, rotary_dim, writes_cache, s.scale, s.window or 0, out)
         return ops.linear(out, self.wo)

@@ -78,6 +78,11 @@ def rope_kv_store(qkv, nh, nkv, hd, ctx, cache, inv_freq, rotary_dim, store=True
         cache.v_pages[pages, :, off, :] = v
 
 
+def rope_store_attention(qkv, nh, nkv, hd, ctx, cache, inv_freq, rotary_dim, store, scale, window, out):
+    rope_kv_store(qkv, nh, nkv, hd, ctx, cache, inv_freq, rotary_dim, store)
+    paged_attention(qkv, nh, nkv, hd, ctx, cache, scale, window, out)
+
+
 def paged_attention(qkv, nh, nkv, hd, ctx, cache, scale, window, out):
     T = qkv.shape[0]
     q = qkv[:, :nh * hd].view(T, nh, hd).float()

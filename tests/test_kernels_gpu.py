@@ -264,6 +264,49 @@ def test_rope_kv_store_reports_a_page_that_is_not_held(ops):
 
 
 # ------------------------------------------------------------------- attention
+@pytest.mark.parametrize("nh, nkv, hd, page, window", [(8, 2, 64, 16, 0), (32, 8, 64, 16, 0), (6, 2, 128, 32, 0),
+                                                       (16, 1, 64, 8, 0), (4, 4, 64, 4, 0), (8, 2, 64, 16, 40)])
+@pytest.mark.parametrize("q_lens, kv_lens", [([1, 1, 1, 1], [1, 16, 17, 700]), ([1, 9, 1, 130], [33, 20, 4097, 130]),
+                                             ([1], [5000])])
+def test_decode_kernel_rotates_and_stores_like_the_separate_kernel(ops, nh, nkv, hd, page, window,
+                                                                    q_lens, kv_lens):
+    """rope_store_attention (single tokens rotated and stored inside the decode kernel) against
+    rope_kv_store followed by paged_attention on copies of the same inputs: same outputs, same
+    pages; also with store off."""
+    from llm_singularity_b200.parts.rotary import rotary_inv_freq
+    dtype = torch.bfloat16
+    R = len(q_lens)
+    rows = list(reversed(range(R)))
+    ctx = _make_ctx(q_lens, kv_lens, table_rows=rows)
+    T = sum(q_lens)
+    inv = rotary_inv_freq(hd, 500000.0).float().cuda()
+    scale = 1.0 / math.sqrt(hd)
+    qkv0 = _rand(T, (nh + 2 * nkv) * hd, dtype=dtype, seed=3)
+    results = []
+    for fused in (False, True):
+        for store in (True, False):
+            cache = _make_cache(R, max(kv_lens), nkv, hd, page, dtype, seed=1)
+            for r in range(R):
+                _fill(cache, rows[r], _rand(kv_lens[r], nkv, hd, dtype=dtype, seed=10 + r).cpu(),
+                      _rand(kv_lens[r], nkv, hd, dtype=dtype, seed=20 + r).cpu())
+            qkv = qkv0.clone()
+            out = torch.empty(T, nh * hd, dtype=dtype, device="cuda")
+            if fused:
+                ops.rope_store_attention(qkv, nh, nkv, hd, ctx, cache, inv, hd, store, scale, window, out)
+            else:
+                ops.rope_kv_store(qkv, nh, nkv, hd, ctx, cache, inv, hd, store=store)
+                ops.paged_attention(qkv, nh, nkv, hd, ctx, cache, scale, window, out)
+            ops.check_status()
+            results.append((out.float().cpu(), cache.k_pages.float().cpu(), cache.v_pages.cpu()))
+    for a, b in ((0, 2), (1, 3)):
+        out_a, k_a, v_a = results[a]
+        out_b, k_b, v_b = results[b]
+        assert torch.equal(v_a, v_b)
+        # the two kernels may contract the rotation's multiply-adds differently: one bfloat16 step
+        assert (k_a - k_b).abs().max() <= 2.0 ** -7 * k_a.abs().max()
+        assert (out_a - out_b).abs().max() <= _tol(dtype, 3.0)
+
+
 def _ref_attention(q, K, V, scale, window):
     """q [n, nh, hd] are the last n positions of a sequence whose keys/values are K, V [len, nkv, hd]."""
     n, nh, hd = q.shape
