@@ -530,7 +530,8 @@ __global__ void __launch_bounds__(kGemmThreads)
 gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant__ CUtensorMap map_q,
                           const GemmParams prm, int tiles_m, int tiles_n) {
     using L = PersistentLayout<BN, STAGES>;
-    static_assert(BN == 128 || BN == 256, "two accumulators of BN columns must fit 512 TMEM columns");
+    static_assert(BN == 16 || BN == 32 || BN == 64 || BN == 128 || BN == 256,
+                  "two accumulators of BN columns: a power of two of TMEM columns, at most 512");
     constexpr uint32_t kTmemCols = 2 * BN;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -629,7 +630,7 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
             ok = ok && !abort_flag;
             if (!ok) break;
             const uint32_t tmem_acc = tmem_base + (uint32_t)(a * BN);
-            if (aligned && j0 + BN <= prm.rows_q) {
+            if (BN >= kEpiCols && aligned && j0 + BN <= prm.rows_q) {
 #pragma unroll
                 for (int h = 0; h < BN / kEpiCols; ++h) {
                     if (prm.swiglu == 1)
@@ -824,6 +825,17 @@ LSB_API int lsb_gemm_tc(const void* x, const void* w, void* out, int out_f32, in
             case 32: rc = launch<32, 4>(mp, mq, prm, grid, stream); break;
             case 64: rc = launch<64, 4>(mp, mq, prm, grid, stream); break;
             case 128: rc = launch<128, 4>(mp, mq, prm, grid, stream); break;
+            default: return (int)cudaErrorInvalidValue;
+        }
+    } else if (swap && !swiglu && grid.x >= 2 * 148 && !getenv("LSB_GEMM_NO_PERSISTENT_HEAD")) {
+        // Many more weight slabs than SMs (the output head): persistent blocks walk the slabs, the
+        // loads of the next slab run under the epilogue of this one and no SM idles between waves.
+        const int tm = (int)grid.x;
+        switch (bn) {
+            case 16: rc = launch_persistent<16, 8>(mp, mq, prm, tm, 1, stream); break;
+            case 32: rc = launch_persistent<32, 8>(mp, mq, prm, tm, 1, stream); break;
+            case 64: rc = launch_persistent<64, 6>(mp, mq, prm, tm, 1, stream); break;
+            case 128: rc = launch_persistent<128, 5>(mp, mq, prm, tm, 1, stream); break;
             default: return (int)cudaErrorInvalidValue;
         }
     } else {

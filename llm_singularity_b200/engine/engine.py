@@ -26,13 +26,23 @@ from .runner import ModelRunner
 from .scheduler import Request, Scheduler, SchedulerConfig
 
 
+class _Launched:
+    """A step that is queued on the device and not accounted yet."""
+
+    def __init__(self, wanted: List[Request]):
+        self.wanted = wanted                 # requests whose next token the step samples
+        self.dev_tokens: Optional[torch.Tensor] = None
+        self.host_tokens: Optional[torch.Tensor] = None
+        self.event = None
+
+
 class Engine:
     def __init__(self, model_dir: Optional[str] = None, *, random_weights: bool = False,
                  seed: int = 0, dtype="bfloat16", device="cuda:0", kv_block_size: int = 16,
                  num_kv_blocks: int = 1024, max_batch_size: int = 64,
                  max_tokens_per_batch: int = 2048, prefill_chunk: Optional[int] = None,
                  max_model_len: Optional[int] = None, prefix_cache: bool = True,
-                 config=None, ops=None, verbose: bool = False):
+                 config=None, ops=None, verbose: bool = False, run_ahead: bool = True):
         """``model_dir`` holds config.json and, unless ``random_weights``, the safetensors
         files.  Defaults follow the reference's hints: pages of 16 tokens, 1024 pages, 2048
         tokens per batch (models/llama/llama_model.cpp:111-120)."""
@@ -65,6 +75,12 @@ class Engine:
         self.sampler = Sampler(self.runner.rt)
         self._ids = itertools.count()
         self._requests: Dict[Hashable, Request] = {}
+        self.run_ahead = run_ahead
+        self._inflight: Optional[_Launched] = None
+        pin = torch.device(device).type == "cuda" and ops is None
+        self._host_tokens = [torch.empty(max_batch_size, dtype=torch.int32, pin_memory=pin)
+                             for _ in range(2)]
+        self._host_turn = 0
 
     # ------------------------------------------------------------------ intake
     def add_request(self, token_ids: Sequence[int], max_new_tokens: int = 16,
@@ -86,35 +102,72 @@ class Engine:
         return rid
 
     def has_work(self) -> bool:
-        return self.scheduler.has_work()
+        return self.scheduler.has_work() or self._inflight is not None
 
     # -------------------------------------------------------------------- step
     def step(self) -> List[Tuple[Hashable, int, bool]]:
         """Run one scheduled batch; returns (request id, new token, finished) for every request
-        that produced a token, and (id, -1, True) for requests that ended with an error."""
-        sch = self.scheduler
-        items = sch.schedule()
+        that produced a token, and (id, -1, True) for requests that ended with an error.
+
+        With ``run_ahead`` the step after this one is planned and queued on the device before
+        this one's tokens are read back, whenever the scheduler can tell what it will hold
+        (Scheduler.schedule_ahead): it takes its input tokens from the device, where the sampler
+        left them, and the host's work for it happens while the device is busy.  Each call still
+        returns the tokens of exactly one step."""
         out: List[Tuple[Hashable, int, bool]] = []
-        for req in sch.take_finished():            # errors found while scheduling
-            out.append((req.id, -1, True))
-        if not items:
-            return out
-        entries = [StepEntry(it.request.id, it.tokens, [len(it.tokens) - 1] if it.sample else [])
-                   for it in items]
-        logits = self.runner.step(entries)
-        wanted = [it.request for it in items if it.sample]
-        sampled: Dict[Hashable, int] = {}
-        if wanted:
-            toks = self.sampler.sample(
-                logits, [r.sampling for r in wanted], [len(r.generated) for r in wanted],
-                [r.generated for r in wanted])
-            host = toks.to("cpu").tolist()
-            sampled = {r.id: t for r, t in zip(wanted, host)}
-        done = {r.id for r in sch.update(sampled)}
-        sch.take_finished()
-        for r in wanted:
-            out.append((r.id, sampled[r.id], r.id in done))
+        cur = self._inflight
+        if cur is None:
+            items = self.scheduler.schedule()
+            for req in self.scheduler.take_finished():         # errors found while scheduling
+                out.append((req.id, -1, True))
+            if not items:
+                return out
+            cur = self._launch(items, None)
+        nxt = None
+        if self.run_ahead:
+            items = self.scheduler.schedule_ahead()
+            if items is not None:
+                nxt = self._launch(items, cur)
+        self._inflight = nxt
+        out.extend(self._complete(cur))
         return out
+
+    def _launch(self, items, after: Optional["_Launched"]) -> "_Launched":
+        """Queue one planned step on the device: the model step, sampling, and the copy of the
+        new tokens to the host.  ``after``: the step whose sampled tokens are this one's input."""
+        entries = [StepEntry(it.request.id, it.tokens if after is None else [0],
+                             [len(it.tokens) - 1] if it.sample else []) for it in items]
+        logits = self.runner.step(entries, device_tokens=None if after is None else after.dev_tokens)
+        wanted = [it.request for it in items if it.sample]
+        launched = _Launched(wanted)
+        if wanted:
+            ahead = 0 if after is None else 1                  # a token still in flight counts
+            launched.dev_tokens = self.sampler.sample(
+                logits, [r.sampling for r in wanted], [len(r.generated) + ahead for r in wanted],
+                [r.generated for r in wanted])
+            if launched.dev_tokens.is_cuda:
+                host = self._host_tokens[self._host_turn][:len(wanted)]
+                self._host_turn ^= 1
+                host.copy_(launched.dev_tokens, non_blocking=True)
+                launched.event = torch.cuda.Event()
+                launched.event.record()
+                launched.host_tokens = host
+            else:
+                launched.host_tokens = launched.dev_tokens.clone()
+        return launched
+
+    def _complete(self, launched: "_Launched") -> List[Tuple[Hashable, int, bool]]:
+        """Wait for a queued step's tokens and account it."""
+        sampled: Dict[Hashable, int] = {}
+        if launched.wanted:
+            if launched.event is not None:
+                launched.event.synchronize()
+            host = launched.host_tokens.tolist()
+            sampled = {r.id: t for r, t in zip(launched.wanted, host)}
+        live = [r for r in launched.wanted if r.status == "running"]
+        done = {r.id for r in self.scheduler.update(sampled)}
+        self.scheduler.take_finished()
+        return [(r.id, sampled[r.id], r.id in done) for r in live]
 
     # ---------------------------------------------------------------- generate
     def generate(self, prompts: Sequence[Sequence[int]], max_new_tokens: int = 16,

@@ -131,8 +131,18 @@ class ModelRunner:
         self.cache.close(request)
 
     # -------------------------------------------------------------------- step
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry],
+             device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Run the entries' tokens as one batch from the cache; returns the logits at the wanted
+        places, float32 [wanted, vocab] on the device, in the order of the entries.
+
+        ``device_tokens`` (int32, one per entry) says that the tokens of this step are on the
+        device already (the previous step sampled them there and the host has not read them
+        yet): every entry brings one token, whose value in ``entries`` is ignored."""
         cache = self.cache
+        if device_tokens is not None and (any(len(e.tokens) != 1 for e in entries)
+                                          or device_tokens.numel() != len(entries)):
+            raise ValueError("device_tokens needs one token per entry and entries of one token")
         starts = [cache.length(e.request) for e in entries]
         seen = set()
         for e in entries:
@@ -153,9 +163,11 @@ class ModelRunner:
                     f"request {e.request!r} needs {cache.pages_needed(e.request, new_len)} more "
                     f"pages, {cache.free_pages()} are free")
         if self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
-            logits, n_tokens = self._decode_with_graph(entries, starts), len(entries)
+            logits, n_tokens = self._decode_with_graph(entries, starts, device_tokens), len(entries)
         else:
             ctx = self.prepare_context(entries, starts)
+            if device_tokens is not None:
+                ctx.token_ids.copy_(device_tokens)
             logits, n_tokens = self.model.forward(ctx, cache), ctx.n_tokens
         for e, s in zip(entries, starts):
             cache.commit(e.request, s + len(e.tokens))
@@ -164,7 +176,8 @@ class ModelRunner:
         return logits
 
     # ------------------------------------------------------------ decode graphs
-    def _decode_with_graph(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> torch.Tensor:
+    def _decode_with_graph(self, entries: Sequence[StepEntry], starts: Sequence[int],
+                           device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
         """A step of single decode tokens, all wanted: replay the graph captured for this batch
         size.  The step's metadata and the block-table cells that changed are copied into buffers
         at fixed addresses first; everything else happens inside the graph.  The returned logits
@@ -192,6 +205,8 @@ class ModelRunner:
             [e.tokens for e in entries], list(starts), [cache.slot(e.request) for e in entries],
             [e.want for e in entries], extra, static=st.meta)
         ctx.fixed_launch = True
+        if device_tokens is not None:
+            ctx.token_ids.copy_(device_tokens)       # after the metadata copy, before the graph
 
         def run():
             for gi, g in enumerate(cache.groups):

@@ -85,7 +85,10 @@ class Scheduler:
         self.finished: List[Request] = []
         self.stats = {"steps": 0, "preemptions": 0, "prefill_tokens": 0, "decode_tokens": 0,
                       "prefix_hit_tokens": 0, "evicted_pages": 0, "admitted": 0, "errors": 0}
-        self._last: List[ScheduledItem] = []
+        # plans of steps whose results have not come back yet, oldest first: one in the plain
+        # loop (schedule, run, update), two while a step is planned ahead of the previous one's
+        # tokens (schedule_ahead)
+        self._plans: Deque[List[ScheduledItem]] = deque()
 
     # ----------------------------------------------------------------- intake
     def add(self, request: Request) -> None:
@@ -222,8 +225,48 @@ class Scheduler:
                 self._preempt(self.running[-1])
             return self.schedule()
 
-        self._last = items
+        if items:
+            self._plans.append(items)
         self.stats["steps"] += 1 if items else 0
+        return items
+
+    # ---------------------------------------------------------- schedule ahead
+    PENDING = -1        # stands for a token that the step in flight has yet to produce
+
+    def schedule_ahead(self) -> Optional[List[ScheduledItem]]:
+        """Plan the step after the one in flight before that one's tokens are known, so that the
+        device never waits for the host: possible when the step in flight ends the known tokens
+        of every running request (each then has exactly one new token, which the caller feeds
+        from the device), nobody waits for admission, nobody reaches ``max_new_tokens`` or the
+        model's length with the token in flight or samples with a repetition penalty (which
+        needs that token on the host), and the pages for one more token each are free
+        without eviction or preemption.  A request that turns out to have stopped on the token
+        in flight (a stop token) is skipped when the step planned here is accounted.  Returns
+        the plan, items in the order of the step in flight, or None (then plan with
+        :meth:`schedule` after :meth:`update`)."""
+        if len(self._plans) != 1 or self.waiting:
+            return None
+        last = self._plans[0]
+        if len(last) != len(self.running) or not all(it.sample for it in last):
+            return None
+        for it in last:
+            req = it.request
+            if req.status != "running" or len(req.generated) + 1 >= req.max_new_tokens \
+                    or len(req.tokens) + 2 > self.cfg.max_model_len \
+                    or req.sampling.repetition_penalty != 1.0:     # needs the token on the host
+                return None
+        need = sum(self.cache.pages_needed(it.request.id, len(it.request.tokens) + 1) for it in last)
+        if need > self.cache.free_pages():
+            return None
+        items = []
+        for it in last:
+            req = it.request
+            if not self.cache.reserve(req.id, len(req.tokens) + 1):
+                return None                          # cannot happen after the count above
+            items.append(ScheduledItem(req, len(req.tokens), [self.PENDING], True))
+        self._plans.append(items)
+        self.stats["steps"] += 1
+        self.stats["ahead_steps"] = self.stats.get("ahead_steps", 0) + 1
         return items
 
     def _fit_portion(self, req: Request, n: int) -> int:
@@ -246,13 +289,17 @@ class Scheduler:
 
     # ----------------------------------------------------------------- update
     def update(self, sampled: Dict[Hashable, int]) -> List[Request]:
-        """After the step: advance every scheduled request; ``sampled`` maps the ids of
-        requests whose logits were wanted to their new token.  Returns requests that finished."""
+        """After the oldest step still unaccounted: advance every request it scheduled;
+        ``sampled`` maps the ids of requests whose logits were wanted to their new token.
+        Returns requests that finished."""
         done: List[Request] = []
-        for it in self._last:
+        for it in (self._plans.popleft() if self._plans else []):
             req = it.request
+            if req.status != "running":
+                continue         # planned ahead, but it stopped on the token that was in flight
             req.computed += len(it.tokens)
-            self.cache.commit(req.id, req.computed)      # idempotent if the step function did it
+            if self.cache.length(req.id) < req.computed:  # the step function has done it already,
+                self.cache.commit(req.id, req.computed)   # and a step planned ahead may be further
             if it.sample:
                 if len(it.tokens) == 1 and it.start > 0 and req.generated:
                     self.stats["decode_tokens"] += 1
@@ -275,7 +322,6 @@ class Scheduler:
             self.running.remove(req)
             req.status = "finished"
             self.finished.append(req)
-        self._last = []
         return done
 
     def take_finished(self) -> List[Request]:

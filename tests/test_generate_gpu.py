@@ -145,3 +145,28 @@ def test_command_line_bench_modes(model_dirs, mode):
         assert line["stats"]["pages_free"] + line["stats"]["prefix_nodes"] >= 0
     if mode == "decode":
         assert line["generated_tokens_per_s"] > 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("temperature", [0.0, 0.9])
+def test_running_ahead_gives_the_same_tokens_as_the_plain_loop(model_dirs, dtype, temperature):
+    """Steps queued before the previous step's tokens reach the host (the next step reads them on
+    the device, decode graphs included) against one step at a time: identical tokens, also when a
+    stop token is found one step late."""
+    name = "tiny_b"
+    prompts = [tiny_models.random_tokens(512, n, 700 + n) for n in (2, 21, 40)]
+    outs = []
+    for ahead in (False, True):
+        eng = _engine(model_dirs[name], name, dtype, run_ahead=ahead)
+        first = eng.generate(prompts, max_new_tokens=24, temperature=temperature, seed=11, ignore_eos=True)
+        eng.scheduler.cfg.stop_token_ids = (first[2][6],)
+        second = eng.generate(prompts, max_new_tokens=24, temperature=temperature, seed=11)
+        outs.append((first, second))
+        eng.runner.check_kernels()
+        eng.runner.cache.check_invariants()
+        assert eng.stats().get("ahead_steps", 0) == (0 if not ahead else eng.stats()["ahead_steps"])
+        if ahead:
+            assert eng.stats()["ahead_steps"] >= 20
+    assert outs[0] == outs[1]
+    stop = outs[1][0][2][6]
+    assert outs[1][1][2] == outs[1][0][2][:outs[1][0][2].index(stop) + 1]

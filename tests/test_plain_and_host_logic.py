@@ -146,3 +146,27 @@ def test_engine_greedy_matches_plain_even_with_few_pages_and_preemption(model_di
         eng.runner.cache.check_invariants()
         if pages == 5:
             assert eng.stats()["preemptions"] > 0
+
+
+@pytest.mark.parametrize("temperature", [0.0, 0.8])
+def test_engine_running_ahead_yields_the_same_tokens(model_dirs, temperature):
+    """Steps planned before the previous step's tokens are read (the tokens stay on the device
+    side) against the plain loop: same tokens, also across a stop token found one step late."""
+    prompts = [tiny_models.random_tokens(512, n, 90 + n) for n in (3, 12, 30)]
+    outs, stats = [], []
+    for ahead in (False, True):
+        eng = Engine(model_dirs["tiny_b"], dtype="float32", device="cpu", kv_block_size=8,
+                     num_kv_blocks=40, max_batch_size=4, max_tokens_per_batch=64,
+                     ops=standin_ops, run_ahead=ahead)
+        first = eng.generate(prompts, max_new_tokens=12, temperature=temperature, seed=5, ignore_eos=True)
+        eng.scheduler.cfg.stop_token_ids = (first[1][4],)       # request 1 now stops at its fifth token
+        second = eng.generate(prompts, max_new_tokens=12, temperature=temperature, seed=5)
+        outs.append((first, second))
+        stats.append(eng.stats())
+        eng.runner.cache.check_invariants()
+        assert not eng.has_work()
+    assert outs[0] == outs[1]
+    first, second = outs[1]
+    stop = first[1][4]
+    assert second[1] == first[1][:first[1].index(stop) + 1]
+    assert stats[0].get("ahead_steps", 0) == 0 and stats[1]["ahead_steps"] >= 10

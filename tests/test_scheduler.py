@@ -177,3 +177,76 @@ def test_cached_prefixes_are_evicted_before_anyone_is_preempted():
     assert [it.request.id for it in items] == ["b"] and sch.stats["evicted_pages"] == 2
     assert sch.stats["preemptions"] == 0 and done
     cache.check_invariants()
+
+
+# ------------------------------------------------------------- planning ahead
+def test_a_step_is_planned_ahead_only_when_it_is_known_what_it_holds():
+    sch, cache = make()
+    sch.add(req("a", 20, max_new=6, ignore_eos=True)); sch.add(req("b", 5, max_new=6, ignore_eos=True))
+    first = sch.schedule()                                   # both prompts whole, both sample
+    ahead = sch.schedule_ahead()                             # their first decode step, token unknown
+    assert [(it.request.id, it.start, it.tokens, it.sample) for it in ahead] == \
+        [("a", 20, [Scheduler.PENDING], True), ("b", 5, [Scheduler.PENDING], True)]
+    assert cache.pages_of("a") == [0, 1] and len(cache.pages_of("b")) == 1
+    assert sch.schedule_ahead() is None                      # never two steps ahead
+    assert sch.update({"a": 7, "b": 8}) == []                # accounts the first step
+    assert [r.tokens[-1] for r in sch.running] == [7, 8] and [r.computed for r in sch.running] == [20, 5]
+    again = sch.schedule_ahead()                             # the step after the one planned ahead
+    assert [(it.request.id, it.start) for it in again] == [("a", 21), ("b", 6)]
+    sch.update({"a": 9, "b": 9})
+    assert [r.computed for r in sch.running] == [21, 6] and [r.generated for r in sch.running] == [[7, 9], [8, 9]]
+    sch.update({"a": 1, "b": 1})
+    assert [r.computed for r in sch.running] == [22, 7]
+    assert first and sch.stats["ahead_steps"] == 2
+    cache.check_invariants()
+
+
+def test_no_planning_ahead_when_someone_waits_finishes_or_is_still_in_its_prompt():
+    sch, _ = make(slots=1)
+    sch.add(req("a", 8, max_new=3, ignore_eos=True)); sch.add(req("b", 8, ignore_eos=True))
+    sch.schedule()
+    assert sch.schedule_ahead() is None                      # b waits for a slot
+    sch, _ = make(budget=16)
+    sch.add(req("a", 40, max_new=3, ignore_eos=True))
+    sch.schedule()
+    assert sch.schedule_ahead() is None                      # a portion that does not sample
+    sch.update({})
+    sch, _ = make()
+    sch.add(req("a", 8, max_new=2, ignore_eos=True))
+    sch.schedule()
+    assert sch.schedule_ahead() is not None                  # one more token to come after this one
+    sch.update({"a": 5})
+    assert sch.schedule_ahead() is None                      # the token in flight is its last
+    sch.update({"a": 5})
+    assert not sch.has_work()
+    sch, _ = make()
+    sch.add(Request("p", [1, 2, 3], 8, SamplingParams(0.7, repetition_penalty=1.3), True))
+    sch.schedule()
+    assert sch.schedule_ahead() is None                      # the penalty needs the token on the host
+
+
+def test_no_planning_ahead_without_a_free_page():
+    sch, cache = make(pages=2, page=16)
+    sch.add(req("a", 31, max_new=8, ignore_eos=True))
+    sch.schedule()
+    assert sch.schedule_ahead() is not None                  # position 31 still fits page 1
+    sch.update({"a": 5})
+    assert sch.schedule_ahead() is None                      # position 32 needs a third page
+    cache.check_invariants()
+
+
+def test_a_request_that_stops_on_the_token_in_flight_is_skipped_in_the_step_planned_ahead():
+    sch, cache = make()
+    sch.add(req("a", 8, max_new=8)); sch.add(req("b", 8, max_new=8))
+    sch.schedule()
+    assert sch.schedule_ahead() is not None
+    done = sch.update({"a": EOS, "b": 7})                    # a stops; the step ahead already holds it
+    assert [r.id for r in done] == ["a"]
+    with pytest.raises(KeyError):
+        cache.pages_of("a")                                  # everything it held is given back
+    assert sch.schedule_ahead() is None                      # the running set changed
+    done = sch.update({"a": 3, "b": 9})                      # a's token from the step ahead is dropped
+    assert done == [] and sch.running[0].generated == [7, 9]
+    a = next(r for r in sch.take_finished() if r.id == "a")
+    assert a.generated == [EOS]
+    cache.check_invariants()
