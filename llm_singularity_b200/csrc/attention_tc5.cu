@@ -32,8 +32,11 @@ constexpr int kRows = 128;            // queries per block = TMEM lanes
 #define LSB_ATT5_KEYS 64
 #endif
 constexpr int kKeys = LSB_ATT5_KEYS;  // keys per tile (64: three blocks of head 64 fit per SM)
-constexpr int kThreads = 192;
-constexpr int kKvStages = 2;
+constexpr int kThreads = 224;        // warps: TMA, MMA for S, four softmax warps, MMA for P V
+#ifndef LSB_ATT5_STAGES
+#define LSB_ATT5_STAGES 4
+#endif
+constexpr int kKvStages = LSB_ATT5_STAGES;
 constexpr int kBtCache = 512;         // block-table entries of this block's key range kept in smem
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr uint32_t kSpinLimit = 1u << 22;
@@ -171,8 +174,11 @@ struct Smem {
                                      kBtCache * 4 + 16 * 8 + 16;
 };
 
+#ifndef LSB_ATT5_BLOCKS
+#define LSB_ATT5_BLOCKS 2
+#endif
 template <int HD>
-__global__ void __launch_bounds__(kThreads, HD == 64 ? 3 : 1)
+__global__ void __launch_bounds__(kThreads, HD == 64 ? LSB_ATT5_BLOCKS : 1)
 prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                              const __grid_constant__ CUtensorMap map_v, const AttnParams prm) {
     using L = Smem<HD>;
@@ -192,7 +198,8 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
     uint64_t* s_full = kv_empty + kKvStages;                 // MMA -> softmax
     uint64_t* p_full = s_full + 1;                           // softmax -> MMA (128 arrivals)
     uint64_t* o_full = p_full + 1;                           // MMA -> softmax
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
+    uint64_t* s_free = o_full + 1;                           // softmax -> MMA: S is in registers (128 arrivals)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_free + 1);
     __shared__ int abort_flag;
 
     lsb_pdl_launch_dependents();
@@ -225,6 +232,7 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         mbar_init(s_full, 1);
         mbar_init(p_full, 128);
         mbar_init(o_full, 1);
+        mbar_init(s_free, 128);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -291,17 +299,12 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         // ---------------------------------------------------------------- MMA issuer
         if (lane == 0) {
             constexpr uint32_t idesc_qk = make_idesc(kKeys, 0);
-            constexpr uint32_t idesc_pv = make_idesc(HD, 1);
             bool ok = mbar_wait(q_full, 0, &abort_flag);
-            for (int t = 0; t < n_tiles && ok; ++t) {
-                const int s = t % kKvStages;
-                ok = mbar_wait(&kv_full[s], (uint32_t)(t / kKvStages) & 1, &abort_flag);
-                if (!ok) break;
-                // S may be overwritten once the softmax warps have read the previous one (p_full)
-                if (t > 0) { ok = mbar_wait(p_full, (uint32_t)(t - 1) & 1, &abort_flag); if (!ok) break; }
-                tc_fence_after();
-                const unsigned char* tK = sK + s * L::kKVBytes;
-                const unsigned char* tV = sV + s * L::kKVBytes;
+            // S of tile t + 1 is issued as soon as the softmax warps hold S of tile t in registers,
+            // ahead of the P V of tile t: the tensor pipe works on it while they exponentiate, and
+            // they find the next S waiting when they are done.
+            auto issue_s = [&](int t) {
+                const unsigned char* tK = sK + (t % kKvStages) * L::kKVBytes;
 #pragma unroll
                 for (int kb = 0; kb < KB; ++kb) {
                     const uint64_t da = desc_kmajor(sQ + kb * (kRows * 128));
@@ -310,10 +313,34 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                     for (int k = 0; k < 4; ++k) umma_bf16(tmem_s, da + 2 * k, db + 2 * k, idesc_qk, (kb | k) ? 1u : 0u);
                 }
                 umma_commit(s_full);
+            };
+            if (ok && n_tiles > 0) {
+                ok = mbar_wait(&kv_full[0], 0, &abort_flag);
+                if (ok) { tc_fence_after(); issue_s(0); }
+            }
+            for (int t = 0; t + 1 < n_tiles && ok; ++t) {
+                ok = mbar_wait(&kv_full[(t + 1) % kKvStages], (uint32_t)((t + 1) / kKvStages) & 1, &abort_flag);
+                if (!ok) break;
+                ok = mbar_wait(s_free, (uint32_t)t & 1, &abort_flag);
+                if (!ok) break;
+                tc_fence_after();
+                issue_s(t + 1);
+            }
+        }
+    } else if (warp == 6) {
+        // ---------------------------------------------------------------- MMA issuer for O += P V
+        // A thread of its own: issuing one of these small MMAs takes the better part of a hundred
+        // cycles, and behind the S products of the other issuer every tile would wait for both.
+        if (lane == 0) {
+            constexpr uint32_t idesc_pv = make_idesc(HD, 1);
+            bool ok = true;
+            for (int t = 0; t < n_tiles && ok; ++t) {
+                const int s = t % kKvStages;
                 // P of this tile (and O rescaled where a row's reference maximum moved)
                 ok = mbar_wait(p_full, (uint32_t)t & 1, &abort_flag);
                 if (!ok) break;
                 tc_fence_after();
+                const unsigned char* tV = sV + s * L::kKVBytes;
 #pragma unroll
                 for (int j = 0; j < kKeys / 16; ++j) {         // 16 keys per MMA; O accumulates in TMEM
                     const uint64_t da = desc_kmajor(sP + (j / 4) * (kRows * 128)) + 2 * (j % 4);
@@ -321,6 +348,7 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                     umma_bf16(tmem_o, da, db, idesc_pv, (t | j) ? 1u : 0u);
                 }
                 umma_commit(o_full);
+                // K of this stage was read by the S product that this P descends from
                 umma_commit(&kv_empty[s]);
             }
         }
@@ -355,6 +383,8 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             for (int c0 = 0; c0 < kKeys; c0 += 32)
                 tmem_ld_32x32(tmem_s + lane_sel + c0, *reinterpret_cast<uint32_t(*)[32]>(&v[c0]));
             tmem_ld_wait();
+            tc_fence_before();
+            mbar_arrive(s_free);                               // the next S may overwrite this one
             // columns of this tile the row may see: [c_lo, c_hi]
             const int c_hi = full ? kKeys - 1 : (live ? pos - key0 : -1);
             const int c_lo = (full || prm.window <= 0) ? 0 : pos - prm.window + 1 - key0;
@@ -381,11 +411,14 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 l *= corr;
             }
             const float mref = (m == -INFINITY) ? 0.f : m;
-            if (t > 0 && __any_sync(0xffffffffu, moved)) {
-                // O *= corr for this warp's 32 rows; the P V of the previous tile must have landed
+            if (t > 0) {
+                // the P V of the previous tile must have landed before P is overwritten or O scaled
                 ok = mbar_wait(o_full, (uint32_t)(t - 1) & 1, &abort_flag);
                 tc_fence_after();
                 if (!ok || abort_flag) { ok = false; break; }
+            }
+            if (t > 0 && __any_sync(0xffffffffu, moved)) {
+                // O *= corr for this warp's 32 rows
 #pragma unroll 1
                 for (int c0 = 0; c0 < HD; c0 += 32) {
                     uint32_t ov[32];
