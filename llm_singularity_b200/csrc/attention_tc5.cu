@@ -94,6 +94,12 @@ __device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t desc_a, uint
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
 }
+// The same with the A operand in tensor memory (rows on lanes, two bfloat16 per 32-bit column).
+__device__ __forceinline__ void umma_bf16_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t desc_b, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(desc_b), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_addr(bar)) : "memory");
 }
@@ -169,8 +175,7 @@ struct Smem {
     static constexpr int kKB = HD / 64;                     // 64-dim blocks of a head
     static constexpr int kQBytes = kRows * HD * 2;
     static constexpr int kKVBytes = kKeys * HD * 2;         // one of K or V, one stage
-    static constexpr int kPBytes = kRows * kKeys * 2;
-    static constexpr size_t kTotal = 1024 + kQBytes + 2 * kKvStages * kKVBytes + kPBytes +
+    static constexpr size_t kTotal = 1024 + kQBytes + 2 * kKvStages * kKVBytes +
                                      kBtCache * 4 + 16 * 8 + 16;
 };
 
@@ -183,22 +188,23 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                              const __grid_constant__ CUtensorMap map_v, const AttnParams prm) {
     using L = Smem<HD>;
     constexpr int KB = L::kKB;
-    constexpr uint32_t kTmemCols = (kKeys + HD) <= 128 ? 128 : 256;   // S: kKeys columns, O tile: HD columns
+    // tensor memory: S (kKeys columns of 32-bit scores), P twice (kKeys / 2 columns each: two
+    // bfloat16 per column), the O tile (HD columns)
+    constexpr uint32_t kTmemCols = (2 * kKeys + HD) <= 128 ? 128 : (2 * kKeys + HD) <= 256 ? 256 : 512;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* sQ = base;                                // [KB][128 rows][128 B]
     unsigned char* sK = sQ + L::kQBytes;                     // [stages][KB][128 keys][128 B]
     unsigned char* sV = sK + kKvStages * L::kKVBytes;        // [stages][KB][128 keys][128 B]
-    unsigned char* sP = sV + kKvStages * L::kKVBytes;        // [2][128 rows][128 B]
-    int* sBT = reinterpret_cast<int*>(sP + L::kPBytes);
+    int* sBT = reinterpret_cast<int*>(sV + kKvStages * L::kKVBytes);
     uint64_t* bars = reinterpret_cast<uint64_t*>(sBT + kBtCache);
     uint64_t* q_full = bars;                                 // TMA -> MMA
     uint64_t* kv_full = bars + 1;                            // [stages] TMA -> MMA
     uint64_t* kv_empty = kv_full + kKvStages;                // [stages] MMA -> TMA
     uint64_t* s_full = kv_empty + kKvStages;                 // MMA -> softmax
     uint64_t* p_full = s_full + 1;                           // softmax -> MMA (128 arrivals)
-    uint64_t* o_full = p_full + 1;                           // MMA -> softmax
-    uint64_t* s_free = o_full + 1;                           // softmax -> MMA: S is in registers (128 arrivals)
+    uint64_t* o_full = p_full + 1;                           // [2] MMA -> softmax: P V of an even / odd tile landed
+    uint64_t* s_free = o_full + 2;                           // softmax -> MMA: S is in registers (128 arrivals)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_free + 1);
     __shared__ int abort_flag;
 
@@ -231,7 +237,8 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         for (int s = 0; s < kKvStages; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
         mbar_init(s_full, 1);
         mbar_init(p_full, 128);
-        mbar_init(o_full, 1);
+        mbar_init(&o_full[0], 1);
+        mbar_init(&o_full[1], 1);
         mbar_init(s_free, 128);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -247,7 +254,8 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_s = *tmem_slot;                      // S: columns [0, 128)
-    const uint32_t tmem_o = tmem_s + kKeys;                  // O tile: columns [kKeys, kKeys + HD)
+    const uint32_t tmem_p = tmem_s + kKeys;                  // P of even tiles, then of odd tiles
+    const uint32_t tmem_o = tmem_s + 2 * kKeys;              // O tile
     const int n_tiles = t1 - t0;
 
     if (warp == 0) {
@@ -303,14 +311,21 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             // S of tile t + 1 is issued as soon as the softmax warps hold S of tile t in registers,
             // ahead of the P V of tile t: the tensor pipe works on it while they exponentiate, and
             // they find the next S waiting when they are done.
+            // Descriptors are formed once: the issuer shares its scheduler with busy softmax warps
+            // and gets few issue slots, so every instruction saved per tile shortens the wait for S.
+            uint64_t da_q[KB], db_k0[KB];
+#pragma unroll
+            for (int kb = 0; kb < KB; ++kb) {
+                da_q[kb] = desc_kmajor(sQ + kb * (kRows * 128));
+                db_k0[kb] = desc_kmajor(sK + kb * (kKeys * 128));
+            }
             auto issue_s = [&](int t) {
-                const unsigned char* tK = sK + (t % kKvStages) * L::kKVBytes;
+                const uint64_t stage = (uint64_t)((t % kKvStages) * (L::kKVBytes >> 4));    // address field: bytes / 16
 #pragma unroll
                 for (int kb = 0; kb < KB; ++kb) {
-                    const uint64_t da = desc_kmajor(sQ + kb * (kRows * 128));
-                    const uint64_t db = desc_kmajor(tK + kb * (kKeys * 128));
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) umma_bf16(tmem_s, da + 2 * k, db + 2 * k, idesc_qk, (kb | k) ? 1u : 0u);
+                    for (int k = 0; k < 4; ++k)
+                        umma_bf16(tmem_s, da_q[kb] + 2 * k, db_k0[kb] + stage + 2 * k, idesc_qk, (kb | k) ? 1u : 0u);
                 }
                 umma_commit(s_full);
             };
@@ -333,6 +348,7 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         // cycles, and behind the S products of the other issuer every tile would wait for both.
         if (lane == 0) {
             constexpr uint32_t idesc_pv = make_idesc(HD, 1);
+            const uint64_t db_v0 = desc_mnmajor(sV, kKeys * 128);
             bool ok = true;
             for (int t = 0; t < n_tiles && ok; ++t) {
                 const int s = t % kKvStages;
@@ -340,14 +356,12 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 ok = mbar_wait(p_full, (uint32_t)t & 1, &abort_flag);
                 if (!ok) break;
                 tc_fence_after();
-                const unsigned char* tV = sV + s * L::kKVBytes;
+                const uint64_t db = db_v0 + (uint64_t)(s * (L::kKVBytes >> 4));
+                const uint32_t pa = tmem_p + (uint32_t)((t & 1) * (kKeys / 2));
 #pragma unroll
-                for (int j = 0; j < kKeys / 16; ++j) {         // 16 keys per MMA; O accumulates in TMEM
-                    const uint64_t da = desc_kmajor(sP + (j / 4) * (kRows * 128)) + 2 * (j % 4);
-                    const uint64_t db = desc_mnmajor(tV + j * (16 * 128), kKeys * 128);
-                    umma_bf16(tmem_o, da, db, idesc_pv, (t | j) ? 1u : 0u);
-                }
-                umma_commit(o_full);
+                for (int j = 0; j < kKeys / 16; ++j)           // 16 keys per MMA: eight columns of P, 16 rows of V
+                    umma_bf16_ts(tmem_o, pa + j * 8, db + (uint64_t)(j * ((16 * 128) >> 4)), idesc_pv, (t | j) ? 1u : 0u);
+                umma_commit(&o_full[t & 1]);
                 // K of this stage was read by the S product that this P descends from
                 umma_commit(&kv_empty[s]);
             }
@@ -411,14 +425,17 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 l *= corr;
             }
             const float mref = (m == -INFINITY) ? 0.f : m;
-            if (t > 0) {
-                // the P V of the previous tile must have landed before P is overwritten or O scaled
-                ok = mbar_wait(o_full, (uint32_t)(t - 1) & 1, &abort_flag);
+            if (t > 1) {
+                // this tile's P buffer was read by the P V of the tile before the previous one
+                ok = mbar_wait(&o_full[t & 1], (uint32_t)((t >> 1) - 1) & 1, &abort_flag);
                 tc_fence_after();
                 if (!ok || abort_flag) { ok = false; break; }
             }
             if (t > 0 && __any_sync(0xffffffffu, moved)) {
-                // O *= corr for this warp's 32 rows
+                // O *= corr for this warp's 32 rows; the P V of the previous tile must have landed
+                ok = mbar_wait(&o_full[(t - 1) & 1], (uint32_t)((t - 1) >> 1) & 1, &abort_flag);
+                tc_fence_after();
+                if (!ok || abort_flag) { ok = false; break; }
 #pragma unroll 1
                 for (int c0 = 0; c0 < HD; c0 += 32) {
                     uint32_t ov[32];
@@ -430,32 +447,31 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 }
                 tmem_st_wait();
             }
-            // probabilities (masked scores are -inf: 2^-inf = 0), rounded to bfloat16, into the
-            // swizzled K-major P tile: 8 keys = one 16-byte chunk of this row
+            // probabilities (masked scores are -inf: 2^-inf = 0), rounded to bfloat16, two to a
+            // 32-bit column
             float la[4] = {0.f, 0.f, 0.f, 0.f};
+            uint32_t pw[kKeys / 2];
 #pragma unroll
-            for (int c8 = 0; c8 < kKeys / 8; ++c8) {
-                uint32_t w[4];
-#pragma unroll
-                for (int y = 0; y < 4; ++y) {
-                    const float pa = fast_exp2(fmaf(__uint_as_float(v[8 * c8 + 2 * y]), sc, -mref));
-                    const float pb = fast_exp2(fmaf(__uint_as_float(v[8 * c8 + 2 * y + 1]), sc, -mref));
-                    la[y] += pa + pb;
-                    __nv_bfloat162 hb = __floats2bfloat162_rn(pa, pb);
-                    w[y] = *reinterpret_cast<uint32_t*>(&hb);
-                }
-                unsigned char* prow = sP + (c8 / 8) * (kRows * 128) + il * 128;
-                *reinterpret_cast<uint4*>(prow + (((c8 & 7) ^ (il & 7)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+            for (int x = 0; x < kKeys; x += 2) {
+                const float pa = fast_exp2(fmaf(__uint_as_float(v[x]), sc, -mref));
+                const float pb = fast_exp2(fmaf(__uint_as_float(v[x + 1]), sc, -mref));
+                la[(x >> 1) & 3] += pa + pb;
+                __nv_bfloat162 hb = __floats2bfloat162_rn(pa, pb);
+                pw[x >> 1] = *reinterpret_cast<uint32_t*>(&hb);
             }
             l += (la[0] + la[1]) + (la[2] + la[3]);
-            // the MMA (async proxy) must see the P just written with ordinary stores
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            // P stays in tensor memory: the P V product takes it from there as its A operand
+#pragma unroll
+            for (int c0 = 0; c0 < kKeys / 2; c0 += 32)
+                tmem_st_32x32(tmem_p + lane_sel + (uint32_t)((t & 1) * (kKeys / 2) + c0),
+                              *reinterpret_cast<uint32_t(*)[32]>(&pw[c0]));
+            tmem_st_wait();
             tc_fence_before();
             mbar_arrive(p_full);
         }
         // all tiles issued: the last P V closes the accumulator
         if (ok) {
-            ok = mbar_wait(o_full, (uint32_t)(n_tiles - 1) & 1, &abort_flag);
+            ok = mbar_wait(&o_full[(n_tiles - 1) & 1], (uint32_t)((n_tiles - 1) >> 1) & 1, &abort_flag);
             tc_fence_after();
             ok = ok && !abort_flag;
         }
