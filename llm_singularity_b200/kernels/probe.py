@@ -7,7 +7,7 @@
     python -m llm_singularity_b200.kernels.probe rope --tokens 2048
 
 Times are CUDA-event times on the launching stream after warm-up, with a buffer larger than the
-L2 cache written between iterations (``--no-flush`` to keep it warm).  The same command line is
+L2 cache read between iterations (``--no-flush`` to keep it warm).  The same command line is
 what the profiler summaries under ``profiles/`` were captured from.
 """
 from __future__ import annotations
@@ -43,14 +43,17 @@ def _cache(R, max_kv, nkv, hd, page):
 
 
 def _time(fn, iters, warmup, flush):
-    buf = torch.empty(256 << 20, dtype=torch.uint8, device="cuda") if flush else None
+    # L2 is flushed by READING a buffer larger than it: a write would leave L2 full of dirty
+    # lines whose write-back then competes with the timed kernel for HBM (that cost a memory-bound
+    # kernel 20 % here)
+    buf = torch.zeros(512 << 20, dtype=torch.uint8, device="cuda") if flush else None
     for _ in range(warmup):
         fn()
     torch.cuda.synchronize()
     total = 0.0
     for _ in range(iters):
         if buf is not None:
-            buf.zero_()
+            buf.view(torch.int32).sum()          # no sync: the host queues the timed launch behind it
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         fn()
