@@ -1,0 +1,210 @@
+"""Two more toy parts defined here and registered without a change to the framework's files: a
+feed-forward that routes every token to one of several small experts, and a position encoding
+that is not rotary (a learned vector per position, added to queries and keys).  They sit in
+different layers of one model beside the stock attention and gated feed-forward, and the model is
+stepped in portions and single tokens; a plain whole-sequence computation in float64 is the
+reference.  Neither toy is a model of anybody's."""
+import json
+import math
+import os
+from dataclasses import dataclass, field
+
+import pytest
+import torch
+
+import plain_llama
+import tiny_models
+
+pytestmark = pytest.mark.gpu
+
+W, NH, NKV, HD, INNER, VOCAB, EXPERTS, EINNER, MAXPOS = 40, 3, 1, 16, 56, 83, 3, 24, 64
+
+
+def _register():
+    from llm_singularity_b200 import register_architecture
+    from llm_singularity_b200.config.specs import (AttentionSpec, BlockSpec, EmbeddingSpec, GatedMLPSpec,
+                                                   HeadSpec, LayerCall, ModelSpec, PartSpec, RMSNormSpec,
+                                                   RotarySpec)
+    from llm_singularity_b200.parts import ParamSpec, Part, register_feed_forward, register_position
+
+    @dataclass(frozen=True)
+    class RoutedSpec(PartSpec):
+        hidden_size: int = 0
+        inner: int = 0
+        experts: int = 0
+        kind: str = field(init=False, default="toy_routed")
+
+    @register_feed_forward("toy_routed")
+    class RoutedFeedForward(Part):
+        """Each token goes to the expert with the largest router logit (32-bit); the expert is
+        relu(x W1^T) W2^T, weighted by the softmax probability of that logit."""
+
+        @classmethod
+        def params(cls, spec):
+            p = {"router": ParamSpec((spec.experts, spec.hidden_size))}
+            for e in range(spec.experts):
+                p[f"e{e}_in"] = ParamSpec((spec.inner, spec.hidden_size))
+                p[f"e{e}_out"] = ParamSpec((spec.hidden_size, spec.inner))
+            return p
+
+        def load(self, tensors):
+            self.t = tensors
+
+        def forward(self, x, ctx):
+            ops = self.rt.ops
+            logits = ops.linear(x, self.t["router"], out_dtype=torch.float32)
+            prob, choice = torch.softmax(logits, dim=-1).max(dim=-1)
+            out = torch.zeros_like(x)
+            for e in range(self.spec.experts):
+                rows = (choice == e).nonzero().flatten()
+                if rows.numel():
+                    h = torch.relu(ops.linear(x[rows].contiguous(), self.t[f"e{e}_in"]))
+                    y = ops.linear(h, self.t[f"e{e}_out"]).float() * prob[rows, None]
+                    out[rows] = y.to(x.dtype)
+            return out
+
+    @dataclass(frozen=True)
+    class LearnedPositionSpec(PartSpec):
+        head_dim: int = 0
+        max_positions: int = 0
+        kind: str = field(init=False, default="toy_learned")
+
+    @register_position("toy_learned")
+    class LearnedPosition(Part):
+        """q[t, h] += table[pos_t], k[t, h] += table[pos_t]: nothing rotary, so the mixer calls
+        ``apply`` and then only stores keys and values."""
+
+        @classmethod
+        def params(cls, spec):
+            return {"table": ParamSpec((spec.max_positions, spec.head_dim))}
+
+        def load(self, tensors):
+            self.table = tensors["table"]
+
+        def rotary_table(self):
+            return None
+
+        def apply(self, q, k, ctx):
+            add = self.table[ctx.positions.long()]                       # [T, head_dim]
+            hd = self.spec.head_dim
+            for x in (q, k):
+                v = x.view(x.shape[0], -1, hd) if x.is_contiguous() else None
+                if v is not None:
+                    v += add[:, None, :]
+                else:                                                     # a column slice of qkv
+                    x += add.repeat(1, x.shape[1] // hd)
+
+    class ToyConfig:
+        architecture = "ToyRoutedForCausalLM"
+
+        def __init__(self, d):
+            self.d = d
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(d)
+
+        def to_model_spec(self):
+            d = self.d
+            norm = RMSNormSpec(size=d["width"], eps=d["eps"])
+
+            def attention(position):
+                return AttentionSpec(hidden_size=d["width"], num_heads=d["heads"], num_kv_heads=d["kv"],
+                                     head_dim=d["head"], scale=1 / math.sqrt(d["head"]), position=position)
+            b0 = BlockSpec(mixer=attention(LearnedPositionSpec(head_dim=d["head"], max_positions=d["maxpos"])),
+                           ffn=RoutedSpec(hidden_size=d["width"], inner=d["einner"], experts=d["experts"]),
+                           mixer_norm=norm, ffn_norm=norm)
+            b1 = BlockSpec(mixer=attention(RotarySpec(head_dim=d["head"], rotary_dim=d["head"], theta=d["theta"])),
+                           ffn=GatedMLPSpec(hidden_size=d["width"], intermediate_size=d["inner"]),
+                           mixer_norm=norm, ffn_norm=norm)
+            names = [("emb", ("embedding", "weight")), ("out_norm", ("head.norm", "weight"))]
+            for i in (0, 1):
+                names += [(f"b{i}.{k}", (f"blocks.{i}.mixer", k)) for k in ("q_proj", "k_proj", "v_proj", "o_proj")]
+                names += [(f"b{i}.n1", (f"blocks.{i}.mixer_norm", "weight")),
+                          (f"b{i}.n2", (f"blocks.{i}.ffn_norm", "weight"))]
+            names += [("b0.pos", ("blocks.0.mixer.position", "table")), ("b0.router", ("blocks.0.ffn", "router"))]
+            for e in range(d["experts"]):
+                names += [(f"b0.e{e}_in", ("blocks.0.ffn", f"e{e}_in")), (f"b0.e{e}_out", ("blocks.0.ffn", f"e{e}_out"))]
+            names += [(f"b1.{k}", ("blocks.1.ffn", k)) for k in ("gate_proj", "up_proj", "down_proj")]
+            return ModelSpec(
+                architecture=self.architecture,
+                embedding=EmbeddingSpec(vocab_size=d["vocab"], hidden_size=d["width"]),
+                blocks=(b0, b1), order=(LayerCall(0, 0), LayerCall(1, 1)),
+                head=HeadSpec(vocab_size=d["vocab"], hidden_size=d["width"], tied=True, norm=norm),
+                tensor_names=tuple(names))
+
+    register_architecture(ToyConfig.architecture, ToyConfig)
+    return ToyConfig
+
+
+def _plain(cfg, w, toks):
+    n, nh, nkv, hd = len(toks), cfg["heads"], cfg["kv"], cfg["head"]
+    x = w["emb"][torch.tensor(toks)]
+
+    def attend(x, i, positional):
+        h = plain_llama.rms_norm(x, w[f"b{i}.n1"], cfg["eps"])
+        q = (h @ w[f"b{i}.q_proj"].T).view(n, nh, hd)
+        k = (h @ w[f"b{i}.k_proj"].T).view(n, nkv, hd)
+        v = (h @ w[f"b{i}.v_proj"].T).view(n, nkv, hd)
+        q, k = positional(q, k)
+        a = plain_llama.causal_attention(q, k, v, 1 / math.sqrt(hd))
+        return x + a.reshape(n, -1) @ w[f"b{i}.o_proj"].T
+
+    def learned(q, k):
+        add = w["b0.pos"][:n][:, None, :]
+        return q + add, k + add
+
+    def rotary(q, k):
+        inv = plain_llama.rope_inv_freq(hd, cfg["theta"])
+        return plain_llama.apply_rope(q, range(n), inv), plain_llama.apply_rope(k, range(n), inv)
+
+    x = attend(x, 0, learned)
+    h = plain_llama.rms_norm(x, w["b0.n2"], cfg["eps"])
+    prob, choice = torch.softmax(h @ w["b0.router"].T, dim=-1).max(dim=-1)
+    y = torch.stack([torch.relu(h[t] @ w[f"b0.e{int(choice[t])}_in"].T) @ w[f"b0.e{int(choice[t])}_out"].T * prob[t]
+                     for t in range(n)])
+    x = x + y
+    x = attend(x, 1, rotary)
+    h = plain_llama.rms_norm(x, w["b1.n2"], cfg["eps"])
+    x = x + plain_llama.swiglu_mlp(h, w["b1.gate_proj"], w["b1.up_proj"], w["b1.down_proj"])
+    return plain_llama.rms_norm(x, w["out_norm"], cfg["eps"]) @ w["emb"].T, choice
+
+
+def test_toy_routed_feed_forward_and_learned_positions_register_build_and_step(tmp_path):
+    from llm_singularity_b200.engine import ModelRunner, StepEntry
+    from llm_singularity_b200.engine.runner import expected_tensors_of
+    from llm_singularity_b200.weights import random_tensors, write_safetensors
+    ToyConfig = _register()
+    cfg = dict(architectures=["ToyRoutedForCausalLM"], width=W, heads=NH, kv=NKV, head=HD, inner=INNER,
+               vocab=VOCAB, experts=EXPERTS, einner=EINNER, maxpos=MAXPOS, eps=1e-6, theta=10000.0)
+    d = str(tmp_path)
+    json.dump(cfg, open(os.path.join(d, "config.json"), "w"))
+    expected = expected_tensors_of(ToyConfig(cfg).to_model_spec())
+    assert "b0.pos" in expected and "b0.router" in expected and f"b0.e{EXPERTS - 1}_out" in expected
+    tensors = random_tensors(expected, seed=11, dtype=torch.float32, std=0.2, norm_noise=0.1)
+    write_safetensors(os.path.join(d, "model.safetensors"), tensors)
+    w = {k: v.double() for k, v in tensors.items()}
+
+    runner = ModelRunner(d, dtype="float32", page_size=8, num_pages=12, max_requests=2)
+    seqs = {"a": tiny_models.random_tokens(VOCAB, 37, 5), "b": tiny_models.random_tokens(VOCAB, 50, 6)}
+    got = {"a": [], "b": []}
+    pos = {"a": 0, "b": 0}
+    runner.open("a"); runner.open("b")
+    plan = [[("a", 9), ("b", 2)], [("a", 1), ("b", 30)], [("a", 1), ("b", 1)], [("a", 26), ("b", 1)], [("b", 16)]]
+    for step in plan:
+        entries = [StepEntry(r, seqs[r][pos[r]:pos[r] + n], list(range(n))) for r, n in step]
+        out = runner.step(entries)
+        k = 0
+        for r, n in step:
+            got[r].append(out[k:k + n]); k += n; pos[r] += n
+    runner.check_kernels()
+    assert pos == {"a": 37, "b": 50}
+    used = set()
+    for r in "ab":
+        want, choice = _plain(cfg, w, seqs[r])
+        used |= set(choice.tolist())
+        diff = (torch.cat(got[r]).double().cpu() - want).abs().max().item()
+        assert diff <= 2e-4, (r, diff)
+    assert len(used) >= 2                     # the router really sends tokens to different experts
+    runner.close("a"); runner.close("b")
+    runner.cache.check_invariants()
