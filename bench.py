@@ -30,7 +30,7 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-LLAMA_3_2_1B = dict(                      # BASELINE.json configs[2]
+LLAMA_3_2_1B = dict(                      # the sizes of Llama 3.2 1B
     architectures=["LlamaForCausalLM"], num_hidden_layers=16, hidden_size=2048,
     num_attention_heads=32, num_key_value_heads=8, head_dim=64, intermediate_size=8192,
     vocab_size=128256, rope_theta=500000.0,
@@ -312,7 +312,7 @@ def main():
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "the reference is a CMake C++/CUDA project with no Python packaging "
-                          "(pip install of /root/reference fails: no setup.py or pyproject.toml) "
+                          "(pip install of its source tree fails: no setup.py or pyproject.toml) "
                           "and its CMake build fetches dependencies from the network"}))
         return 0
     if args.gpus != 1:
