@@ -827,7 +827,7 @@ LSB_API int lsb_gemm_tc(const void* x, const void* w, void* out, int out_f32, in
             case 128: rc = launch<128, 4>(mp, mq, prm, grid, stream); break;
             default: return (int)cudaErrorInvalidValue;
         }
-    } else if (swap && !swiglu && grid.x >= 2 * 148 && !getenv("LSB_GEMM_NO_PERSISTENT_HEAD")) {
+    } else if (swap && !swiglu && grid.x >= 2 * 148) {
         // Many more weight slabs than SMs (the output head): persistent blocks walk the slabs, the
         // loads of the next slab run under the epilogue of this one and no SM idles between waves.
         const int tm = (int)grid.x;
