@@ -1,4 +1,5 @@
-"""RadixPrefixCache: finished requests leave their full pages behind for later prompts.
+"""RadixPrefixCache: requests leave their full pages behind for later prompts, the prompt's
+pages as soon as the prompt has run, the rest when the request ends.
 
 A tree keyed by page-sized chunks of token ids; a node owns one page per cache
 group (the keys and values of that chunk after the path above it).  A new prompt
@@ -45,6 +46,7 @@ class RadixPrefixCache:
         self._clock = itertools.count(1)
         self.num_nodes = 0
         self.hits = 0                                # pages adopted instead of recomputed
+        self._idle = 0                               # nodes no live request uses (kept up to date)
         cache.external_refs = self._owns
 
     # ---------------------------------------------------------------- lookup
@@ -67,6 +69,8 @@ class RadixPrefixCache:
             return 0
         now = next(self._clock)
         for n in path:
+            if n.users == 0:
+                self._idle -= 1
             n.users += 1
             n.last_used = now
         per_group = [[n.pages[g] for n in path] for g in range(len(self.cache.groups))]
@@ -79,6 +83,8 @@ class RadixPrefixCache:
         now = next(self._clock)
         for n in path:
             n.users -= 1
+            if n.users == 0:
+                self._idle += 1
             n.last_used = now
 
     # ---------------------------------------------------------------- insert
@@ -99,14 +105,48 @@ class RadixPrefixCache:
                 child = _Node(key, mine, node)
                 node.children[key] = child
                 self.num_nodes += 1
+                self._idle += 1
                 kept += 1
             child.last_used = now
             node = child
         return kept
 
+    def share(self, tokens: Sequence[int], request, held: Sequence[_Node]) -> List[_Node]:
+        """Like :meth:`insert`, for a request that goes on running: its full pages become
+        visible to later prompts now (a prompt that arrives while this one still decodes need
+        not recompute what they have in common).  ``held``: the nodes the request already counts
+        as a user of (its adopted prefix).  Returns the further nodes whose pages are the
+        request's own; it is a user of those too until :meth:`release`, so that they are not
+        offered for eviction while evicting them would free nothing."""
+        ps = self.page_size
+        n_full = min(len(tokens), self.cache.length(request)) // ps
+        pages = [self.cache.pages_of(request, g) for g in range(len(self.cache.groups))]
+        mine_of = lambda i: tuple(pages[g][i] for g in range(len(pages)))
+        have = set(map(id, held))
+        node, now, added = self.root, next(self._clock), []
+        for i in range(n_full):
+            key = tuple(tokens[i * ps:(i + 1) * ps])
+            mine = mine_of(i)
+            child = node.children.get(key)
+            if child is None:
+                for g, p in enumerate(mine):
+                    self.cache.groups[g].pool.retain(p)
+                child = _Node(key, mine, node)
+                node.children[key] = child
+                self.num_nodes += 1
+                self._idle += 1
+            child.last_used = now
+            if child.pages == mine and id(child) not in have:
+                if child.users == 0:
+                    self._idle -= 1
+                child.users += 1
+                added.append(child)
+            node = child
+        return added
+
     # -------------------------------------------------------------- eviction
     def evictable_pages(self) -> int:
-        return sum(1 for n in self._nodes() if n.users == 0)
+        return self._idle
 
     def evict(self, pages_wanted: int) -> int:
         """Give back up to ``pages_wanted`` pages per group; returns how many were freed."""
@@ -123,8 +163,18 @@ class RadixPrefixCache:
                     self.cache.groups[g].pool.release(p)
                 del n.parent.children[n.key]
                 self.num_nodes -= 1
+                self._idle -= 1
                 freed += 1
         return freed
+
+    def check_invariants(self) -> None:
+        """The counters agree with the tree (tests call this)."""
+        nodes = list(self._nodes())
+        if len(nodes) != self.num_nodes or sum(1 for n in nodes if n.users == 0) != self._idle:
+            raise AssertionError(f"prefix tree: {len(nodes)} nodes / {self.num_nodes} counted, "
+                                 f"{sum(1 for n in nodes if n.users == 0)} idle / {self._idle} counted")
+        if any(n.users < 0 for n in nodes):
+            raise AssertionError("prefix tree: a node has fewer than zero users")
 
     def _nodes(self):
         stack = list(self.root.children.values())

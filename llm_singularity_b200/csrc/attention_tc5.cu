@@ -202,8 +202,12 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
     uint64_t* kv_full = bars + 1;                            // [stages] TMA -> MMA
     uint64_t* kv_empty = kv_full + kKvStages;                // [stages] MMA -> TMA
     uint64_t* s_full = kv_empty + kKvStages;                 // MMA -> softmax
-    uint64_t* p_full = s_full + 1;                           // softmax -> MMA (128 arrivals)
-    uint64_t* o_full = p_full + 1;                           // [2] MMA -> softmax: P V of an even / odd tile landed
+    // P of even and of odd tiles has a barrier each: a softmax warp may be a whole tile ahead of
+    // another (S of the next tile comes early), and its arrival for tile t + 1 must not count
+    // towards tile t, whose P a slower warp has yet to write.  Two tiles ahead it cannot be: P of
+    // tile t + 2 waits for the P V product of tile t, which waits for every warp's P of tile t.
+    uint64_t* p_full = s_full + 1;                           // [2] softmax -> MMA (128 arrivals)
+    uint64_t* o_full = p_full + 2;                           // [2] MMA -> softmax: P V of an even / odd tile landed
     uint64_t* s_free = o_full + 2;                           // softmax -> MMA: S is in registers (128 arrivals)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_free + 1);
     __shared__ int abort_flag;
@@ -236,7 +240,8 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         mbar_init(q_full, 1);
         for (int s = 0; s < kKvStages; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
         mbar_init(s_full, 1);
-        mbar_init(p_full, 128);
+        mbar_init(&p_full[0], 128);
+        mbar_init(&p_full[1], 128);
         mbar_init(&o_full[0], 1);
         mbar_init(&o_full[1], 1);
         mbar_init(s_free, 128);
@@ -353,7 +358,7 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             for (int t = 0; t < n_tiles && ok; ++t) {
                 const int s = t % kKvStages;
                 // P of this tile (and O rescaled where a row's reference maximum moved)
-                ok = mbar_wait(p_full, (uint32_t)t & 1, &abort_flag);
+                ok = mbar_wait(&p_full[t & 1], (uint32_t)(t >> 1) & 1, &abort_flag);
                 if (!ok) break;
                 tc_fence_after();
                 const uint64_t db = db_v0 + (uint64_t)(s * (L::kKVBytes >> 4));
@@ -467,7 +472,7 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                               *reinterpret_cast<uint32_t(*)[32]>(&pw[c0]));
             tmem_st_wait();
             tc_fence_before();
-            mbar_arrive(p_full);
+            mbar_arrive(&p_full[t & 1]);
         }
         // all tiles issued: the last P V closes the accumulator
         if (ok) {

@@ -305,6 +305,10 @@ class Scheduler:
                     self.stats["decode_tokens"] += 1
                 else:
                     self.stats["prefill_tokens"] += len(it.tokens)
+                    if self.prefix is not None:
+                        # the prompt has run: later prompts may share its full pages from now on
+                        req.prefix_path = req.prefix_path + self.prefix.share(
+                            req.tokens[:req.computed], req.id, req.prefix_path)
                 tok = int(sampled[req.id])
                 req.tokens.append(tok)
                 req.generated.append(tok)

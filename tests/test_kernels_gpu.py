@@ -373,6 +373,41 @@ def test_tensor_core_attention_shapes(ops, hd, q_lens, kv_lens):
     assert worst <= _tol(torch.bfloat16, 3.0)
 
 
+@pytest.mark.parametrize("hd", [64, 128])
+def test_prompt_attention_with_ragged_last_tiles_is_the_same_every_time(ops, hd):
+    """Several prompt portions whose last 128-row tile is partly empty, run many times: every run
+    must match the reference and the first run bit for bit.  (Rows without a query make their
+    softmax warp faster than its neighbours; once it ran a whole tile ahead, its arrival was
+    counted for the tile the others were still writing P for.)"""
+    nh, nkv, page = 8, 2, 16
+    q_lens, kv_lens = [577, 577, 577, 101], [1024, 1024, 1024, 1024]
+    dtype = torch.bfloat16
+    R, T = len(q_lens), sum(q_lens)
+    ctx = _make_ctx(q_lens, kv_lens, table_rows=list(range(R)))
+    cache = _make_cache(R, max(kv_lens), nkv, hd, page, dtype, seed=2)
+    Ks = [_rand(kv_lens[r], nkv, hd, dtype=dtype, seed=30 + r).cpu() for r in range(R)]
+    Vs = [_rand(kv_lens[r], nkv, hd, dtype=dtype, seed=40 + r).cpu() for r in range(R)]
+    for r in range(R):
+        _fill(cache, r, Ks[r], Vs[r])
+    qkv = _rand(T, (nh + 2 * nkv) * hd, dtype=dtype, seed=4)
+    scale = 1.0 / math.sqrt(hd)
+    first = None
+    for it in range(60):
+        out = torch.full((T, nh * hd), float("nan"), dtype=dtype, device="cuda")
+        ops.paged_attention(qkv, nh, nkv, hd, ctx, cache, scale, 0, out)
+        if first is None:
+            first = out.clone()
+            t = 0
+            for r in range(R):
+                q = qkv[t:t + q_lens[r], :nh * hd].double().cpu().view(q_lens[r], nh, hd)
+                want = _ref_attention(q, Ks[r].double(), Vs[r].double(), scale, 0)
+                got = out[t:t + q_lens[r]].double().cpu().view(q_lens[r], nh, hd)
+                assert (got - want).abs().max() <= _tol(dtype, 3.0)
+                t += q_lens[r]
+        else:
+            assert torch.equal(out, first), f"run {it} differs from the first"
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("kv_len", [15, 16, 17, 31, 32, 33, 64, 65])
 @pytest.mark.parametrize("hd", [32, 64])

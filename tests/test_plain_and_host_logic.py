@@ -170,3 +170,26 @@ def test_engine_running_ahead_yields_the_same_tokens(model_dirs, temperature):
     stop = first[1][4]
     assert second[1] == first[1][:first[1].index(stop) + 1]
     assert stats[0].get("ahead_steps", 0) == 0 and stats[1]["ahead_steps"] >= 10
+
+
+def test_engine_shares_prompt_pages_between_live_requests_and_yields_the_same_tokens(model_dirs):
+    """Prompts with a common beginning, admitted a few per step under a small token budget: the
+    later ones adopt pages of the earlier ones while those still decode.  Tokens must be the same
+    as without the prefix cache."""
+    common = tiny_models.random_tokens(512, 24, 7)
+    prompts = []
+    for i in range(8):
+        head = common if i % 2 == 0 else tiny_models.random_tokens(512, 24, 100 + i)
+        prompts.append(head + tiny_models.random_tokens(512, 5 + i, 200 + i))
+    outs, stats = [], []
+    for sharing in (False, True):
+        eng = Engine(model_dirs["tiny_b"], dtype="float32", device="cpu", kv_block_size=8,
+                     num_kv_blocks=64, max_batch_size=8, max_tokens_per_batch=40,
+                     ops=standin_ops, prefix_cache=sharing)
+        outs.append(eng.generate(prompts, max_new_tokens=10, ignore_eos=True))
+        stats.append(eng.stats())
+        eng.runner.cache.check_invariants()
+        if sharing:
+            eng.prefix.check_invariants()
+    assert outs[0] == outs[1]
+    assert stats[1]["prefix_hit_pages"] >= 3 * 3 and stats[0]["prefix_hit_pages"] == 0

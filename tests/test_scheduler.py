@@ -250,3 +250,31 @@ def test_a_request_that_stops_on_the_token_in_flight_is_skipped_in_the_step_plan
     a = next(r for r in sch.take_finished() if r.id == "a")
     assert a.generated == [EOS]
     cache.check_invariants()
+
+
+def test_a_running_requests_prompt_pages_are_shared_with_a_later_prompt():
+    sch, cache = make(pages=12, page=16, prefix=True)
+    a = req("a", 48, max_new=3, ignore_eos=True)
+    sch.add(a)
+    run_step(sch, 7)                                         # a's prompt has run; a goes on decoding
+    assert a.status == "running" and sch.prefix.num_nodes == 3
+    b = Request("b", a.prompt[:32] + list(range(500, 520)), 3, SamplingParams(0.0), True)
+    sch.add(b)
+    items = sch.schedule()
+    by = {it.request.id: it for it in items}
+    assert by["b"].start == 32 and len(by["b"].tokens) == 20 and by["a"].tokens == [7]
+    assert cache.pages_of("b")[:2] == cache.pages_of("a")[:2] and sch.stats["prefix_hit_tokens"] == 32
+    cache.check_invariants(); sch.prefix.check_invariants()
+    sch.update({"a": 8, "b": 9})
+    # a's shared pages are in use twice over: not offered for eviction, and evicting frees nothing
+    assert sch.prefix.evictable_pages() == 0 and sch.prefix.evict(4) == 0
+    run_step(sch, 5)                                         # a reaches max_new_tokens and ends
+    assert a.status == "finished" and b.status == "running"
+    assert cache.pages_of("b")[:2] == [n.pages[0] for n in sch.prefix.match(b.tokens)[:2]]
+    cache.check_invariants()
+    run_step(sch, 5)
+    assert b.status == "finished" and not sch.has_work()
+    cache.check_invariants(); sch.prefix.check_invariants()
+    sch.prefix.evict(100)
+    sch.prefix.check_invariants()
+    assert cache.free_pages() == 12 and sch.prefix.num_nodes == 0
