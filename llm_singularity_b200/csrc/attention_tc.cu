@@ -133,7 +133,7 @@ __device__ __forceinline__ int div_page(int key, int page_size, int page_shift) 
 #define LSB_DEC_MINBLOCKS 4
 #endif
 template <int HD, bool LOW8>
-__global__ void __launch_bounds__(kThreads, LSB_DEC_MINBLOCKS)
+__global__ void __launch_bounds__(kThreads, HD == 64 ? LSB_DEC_MINBLOCKS : 3)
 decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
                         bf16* k_pages, bf16* v_pages,
                         const int* __restrict__ q_start, const int* __restrict__ kv_len_arr,
