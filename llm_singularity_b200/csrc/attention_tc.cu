@@ -746,6 +746,36 @@ template <int HD> static int configure_once() {
     return done;
 }
 
+// The largest cluster the decode kernel may be launched with: 16 (beyond the portable 8) where the
+// device says that such a cluster of these blocks can be resident, else 8.
+template <int HD> static int max_cluster() {
+    static int value = 0;
+    if (value) return value;
+    value = 8;
+    if (configure_once<HD>()) return value;
+    bool ok = true;
+    for (int low8 = 0; low8 < 2 && ok; ++low8) {
+        auto kernel = low8 ? decode_attention_kernel<HD, true> : decode_attention_kernel<HD, false>;
+        ok = cudaFuncSetAttribute(kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+        if (!ok) break;
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(16, 1, 1);
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = decode_smem<HD>();
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 16; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+        int n = 0;
+        ok = cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) == cudaSuccess && n > 0;
+    }
+    (void)cudaGetLastError();
+    if (ok) value = 16;
+    return value;
+}
+
+LSB_API int lsb_decode_max_cluster(int hd) { return hd == 64 ? max_cluster<64>() : hd == 128 ? max_cluster<128>() : 8; }
+
 // floats of scratch the decode kernel needs for `splits` > 1: outputs, then (max, sum) pairs
 LSB_API long long lsb_decode_scratch_floats(int n_requests, int nh, int hd, int splits) {
     return splits <= 1 ? 0 : (long long)n_requests * nh * splits * (hd + 2);
@@ -762,11 +792,12 @@ static int decode_launch(const void* qkv, int qkv_stride, void* k_pages, void* v
     if (n_requests <= 0) return 0;
     if (nkv <= 0 || nh % nkv || nh / nkv > 16 || splits < 1 || n_requests > 65535 || nkv > 65535)
         return (int)cudaErrorInvalidValue;
-    if (splits > 8 && !scratch) return (int)cudaErrorInvalidValue;
+    const int cluster_cap = lsb_decode_max_cluster(hd);
+    if (splits > cluster_cap && !scratch) return (int)cudaErrorInvalidValue;
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)n_requests * nh * splits * hd : nullptr;
     dim3 grid(splits, nkv, n_requests);
-    const bool in_cluster = splits > 1 && splits <= 8;      // x is the cluster dimension
+    const bool in_cluster = splits > 1 && splits <= cluster_cap;      // x is the cluster dimension
 #define LAUNCH_DECODE(HD)                                                                          \
     do {                                                                                           \
         int rc = configure_once<HD>();                                                             \

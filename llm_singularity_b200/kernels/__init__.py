@@ -292,6 +292,16 @@ def decode_splits(n_decode: int, nkv: int) -> int:
     return max(1, min(32, (3 * NUM_SMS) // max(1, n_decode * nkv)))
 
 
+_cluster_caps: Dict[int, int] = {}
+
+
+def _decode_cluster_cap(hd: int) -> int:
+    """The largest thread-block cluster the decode kernel can be launched with here (8 or 16)."""
+    if hd not in _cluster_caps:
+        _cluster_caps[hd] = int(_lib("attention_tc").lsb_decode_max_cluster(_i(hd)))
+    return _cluster_caps[hd]
+
+
 def tensor_core_attention_ok(dtype, hd: int, nh: int, nkv: int) -> bool:
     return dtype == torch.bfloat16 and hd in _TC_HEAD_DIMS and nh // nkv <= 16
 
@@ -357,8 +367,12 @@ def paged_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache, s
         splits = decode_splits(n_decode, nkv)
         if not getattr(ctx, "fixed_launch", False):
             splits = min(splits, -(-ctx.max_kv_len // 128))
+        cluster_cap = _decode_cluster_cap(hd)
+        if cluster_cap >= 16 and splits > 8 and n_decode * nkv <= 16:
+            splits = 16                 # a few requests: one 16-block cluster each, no merge kernel
+                                        # (with more clusters than that the merge kernel was faster)
         scratch = None
-        if splits > 8:                  # up to 8 splits merge inside a thread-block cluster
+        if splits > cluster_cap:        # splits of a cluster merge through distributed shared memory
             key = (qkv.device, R, nh, hd, splits)
             scratch = _scratch.get(key)
             if scratch is None:
