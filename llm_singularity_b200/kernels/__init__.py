@@ -371,6 +371,8 @@ def paged_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache, s
         if cluster_cap >= 16 and splits > 8 and n_decode * nkv <= 16:
             splits = 16                 # a few requests: one 16-block cluster each, no merge kernel
                                         # (with more clusters than that the merge kernel was faster)
+        elif splits > 12:
+            splits = 12                 # finer splits than this only lengthen the merge
         scratch = None
         if splits > cluster_cap:        # splits of a cluster merge through distributed shared memory
             key = (qkv.device, R, nh, hd, splits)
