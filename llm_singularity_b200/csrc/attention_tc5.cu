@@ -250,9 +250,15 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
     }
     if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
     // this block's slice of the block table (pages outside the pool are caught here)
+    // Pages that lie wholly before the first key any row of this block may see (a window has passed
+    // them) may have been given back already: their keys are masked, any page stands in for them.
+    const int page_needed = lo_cta >> prm.page_shift;
     for (int idx = threadIdx.x; idx < min(n_pages_here, kBtCache); idx += kThreads) {
         int page = (page_first + idx < prm.table_stride) ? bt[page_first + idx] : -1;
-        if (page < 0 || page >= prm.num_pages) { lsb_set_status(LSB_BAD_PAGE); page = 0; }
+        if (page < 0 || page >= prm.num_pages) {
+            if (page_first + idx >= page_needed) lsb_set_status(LSB_BAD_PAGE);
+            page = 0;
+        }
         sBT[idx] = page;
     }
     tc_fence_before();
@@ -292,7 +298,10 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 if (idx < kBtCache) page = sBT[idx];
                 else {
                     page = pi < prm.table_stride ? bt[pi] : -1;
-                    if (page < 0 || page >= prm.num_pages) { lsb_set_status(LSB_BAD_PAGE); page = 0; }
+                    if (page < 0 || page >= prm.num_pages) {
+                        if (pi >= page_needed) lsb_set_status(LSB_BAD_PAGE);
+                        page = 0;
+                    }
                 }
                 const int row_off = lane * prm.page_size * 128;    // bytes into a 64-dim block
                 for (int kb = 0; kb < KB; ++kb) {

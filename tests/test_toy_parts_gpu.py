@@ -208,3 +208,111 @@ def test_toy_routed_feed_forward_and_learned_positions_register_build_and_step(t
     assert len(used) >= 2                     # the router really sends tokens to different experts
     runner.close("a"); runner.close("b")
     runner.cache.check_invariants()
+
+
+# ------------------------------------------------------------------ a windowed layer beside a full one
+def _register_window():
+    from llm_singularity_b200 import register_architecture
+    from llm_singularity_b200.config.specs import (AttentionSpec, BlockSpec, EmbeddingSpec, GatedMLPSpec,
+                                                   HeadSpec, LayerCall, ModelSpec, RMSNormSpec, RotarySpec)
+
+    class WindowConfig:
+        architecture = "ToyWindowForCausalLM"
+
+        def __init__(self, d):
+            self.d = d
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(d)
+
+        def to_model_spec(self):
+            d = self.d
+            norm = RMSNormSpec(size=d["width"], eps=d["eps"])
+            rot = RotarySpec(head_dim=d["head"], rotary_dim=d["head"], theta=d["theta"])
+            mlp = GatedMLPSpec(hidden_size=d["width"], intermediate_size=d["inner"])
+
+            def block(window):
+                return BlockSpec(mixer=AttentionSpec(hidden_size=d["width"], num_heads=d["heads"], num_kv_heads=d["kv"],
+                                                     head_dim=d["head"], scale=1 / math.sqrt(d["head"]),
+                                                     window=window, position=rot),
+                                 ffn=mlp, mixer_norm=norm, ffn_norm=norm)
+            names = [("emb", ("embedding", "weight")), ("out_norm", ("head.norm", "weight"))]
+            for i in (0, 1):
+                names += [(f"b{i}.{k}", (f"blocks.{i}.mixer", k)) for k in ("q_proj", "k_proj", "v_proj", "o_proj")]
+                names += [(f"b{i}.{k}", (f"blocks.{i}.ffn", k)) for k in ("gate_proj", "up_proj", "down_proj")]
+                names += [(f"b{i}.n1", (f"blocks.{i}.mixer_norm", "weight")), (f"b{i}.n2", (f"blocks.{i}.ffn_norm", "weight"))]
+            return ModelSpec(architecture=self.architecture,
+                             embedding=EmbeddingSpec(vocab_size=d["vocab"], hidden_size=d["width"]),
+                             blocks=(block(d["window"]), block(None)), order=(LayerCall(0, 0), LayerCall(1, 1)),
+                             head=HeadSpec(vocab_size=d["vocab"], hidden_size=d["width"], tied=True, norm=norm),
+                             tensor_names=tuple(names))
+
+    register_architecture(WindowConfig.architecture, WindowConfig)
+    return WindowConfig
+
+
+def _plain_window(cfg, w, toks):
+    n, nh, nkv, hd = len(toks), cfg["heads"], cfg["kv"], cfg["head"]
+    x = w["emb"][torch.tensor(toks)]
+    inv = plain_llama.rope_inv_freq(hd, cfg["theta"])
+    for i, window in ((0, cfg["window"]), (1, None)):
+        h = plain_llama.rms_norm(x, w[f"b{i}.n1"], cfg["eps"])
+        q = plain_llama.apply_rope((h @ w[f"b{i}.q_proj"].T).view(n, nh, hd), range(n), inv)
+        k = plain_llama.apply_rope((h @ w[f"b{i}.k_proj"].T).view(n, nkv, hd), range(n), inv)
+        v = (h @ w[f"b{i}.v_proj"].T).view(n, nkv, hd)
+        a = plain_llama.causal_attention(q, k, v, 1 / math.sqrt(hd), window)
+        x = x + a.reshape(n, -1) @ w[f"b{i}.o_proj"].T
+        h = plain_llama.rms_norm(x, w[f"b{i}.n2"], cfg["eps"])
+        x = x + plain_llama.swiglu_mlp(h, w[f"b{i}.gate_proj"], w[f"b{i}.up_proj"], w[f"b{i}.down_proj"])
+    return plain_llama.rms_norm(x, w["out_norm"], cfg["eps"]) @ w["emb"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_windowed_layer_beside_a_full_one_keeps_pages_of_its_own(tmp_path, dtype):
+    """Two attention layers, one seeing the last 40 keys only, one seeing all: two cache groups.
+    Heads of 64, so bfloat16 runs the tensor-core kernels with their window arguments.  The
+    windowed group gives pages back as the window passes them; logits match the plain model in
+    portions of 150 tokens (the tcgen05 kernel), small portions and single tokens."""
+    from llm_singularity_b200.engine import ModelRunner, StepEntry
+    from llm_singularity_b200.engine.runner import expected_tensors_of
+    from llm_singularity_b200.weights import random_tensors, write_safetensors
+    WindowConfig = _register_window()
+    cfg = dict(architectures=["ToyWindowForCausalLM"], width=128, heads=4, kv=2, head=64, inner=160, vocab=211,
+               window=40, eps=1e-5, theta=10000.0)
+    d = str(tmp_path)
+    json.dump(cfg, open(os.path.join(d, "config.json"), "w"))
+    tensors = random_tensors(expected_tensors_of(WindowConfig(cfg).to_model_spec()), seed=17,
+                             dtype=torch.bfloat16, std=0.08, norm_noise=0.1)
+    write_safetensors(os.path.join(d, "model.safetensors"), tensors)
+    w = {k: v.double() for k, v in tensors.items()}
+
+    runner = ModelRunner(d, dtype=dtype, page_size=16, num_pages=40, max_requests=2)
+    cache = runner.cache
+    assert sorted(g.window or 0 for g in cache.groups) == [0, 40]
+    windowed = next(g for g in cache.groups if g.window)
+    full = next(g for g in cache.groups if not g.window)
+    seqs = {"a": tiny_models.random_tokens(211, 230, 1), "b": tiny_models.random_tokens(211, 200, 2)}
+    plan = [[("a", 150)], [("a", 30), ("b", 150)], [("a", 1), ("b", 7)], [("a", 1), ("b", 1)], [("a", 48), ("b", 42)]]
+    got, pos = {"a": [], "b": []}, {"a": 0, "b": 0}
+    runner.open("a"); runner.open("b")
+    for step in plan:
+        entries = [StepEntry(r, seqs[r][pos[r]:pos[r] + n], list(range(n))) for r, n in step]
+        out = runner.step(entries)
+        k = 0
+        for r, n in step:
+            got[r].append(out[k:k + n]); k += n; pos[r] += n
+    runner.check_kernels()
+    assert pos == {"a": 230, "b": 200}
+    # 430 tokens are held: 28 pages in the full group, only the windows' pages in the other
+    assert full.pool.num_used == -(-230 // 16) + -(-200 // 16)
+    assert windowed.pool.num_used <= 2 * (-(-40 // 16) + 1)
+    cache.check_invariants()
+    tol = 2e-4 if dtype == "float32" else None
+    for r in "ab":
+        want = _plain_window(cfg, w, seqs[r])
+        have = torch.cat(got[r]).double().cpu()
+        bound = tol if tol is not None else 4e-2 * want.abs().max().item()
+        assert (have - want).abs().max().item() <= bound, r
+    runner.close("a"); runner.close("b")
+    assert windowed.pool.num_used == 0 and full.pool.num_used == 0
