@@ -316,3 +316,104 @@ def test_a_windowed_layer_beside_a_full_one_keeps_pages_of_its_own(tmp_path, dty
         assert (have - want).abs().max().item() <= bound, r
     runner.close("a"); runner.close("b")
     assert windowed.pool.num_used == 0 and full.pool.num_used == 0
+
+
+# ------------------------------------------------------------------ a layer that reads another layer's cache
+def _register_shared():
+    from llm_singularity_b200 import register_architecture
+    from llm_singularity_b200.config.specs import (AttentionSpec, BlockSpec, EmbeddingSpec, GatedMLPSpec,
+                                                   HeadSpec, LayerCall, ModelSpec, RMSNormSpec, RotarySpec)
+
+    class SharedConfig:
+        architecture = "ToySharedCacheForCausalLM"
+
+        def __init__(self, d):
+            self.d = d
+
+        @classmethod
+        def from_dict(cls, d):
+            return cls(d)
+
+        def to_model_spec(self):
+            d = self.d
+            norm = RMSNormSpec(size=d["width"], eps=d["eps"])
+            rot = RotarySpec(head_dim=d["head"], rotary_dim=d["head"], theta=d["theta"])
+            blk = BlockSpec(mixer=AttentionSpec(hidden_size=d["width"], num_heads=d["heads"], num_kv_heads=d["kv"],
+                                                head_dim=d["head"], scale=1 / math.sqrt(d["head"]), position=rot),
+                            ffn=GatedMLPSpec(hidden_size=d["width"], intermediate_size=d["inner"]),
+                            mixer_norm=norm, ffn_norm=norm)
+            names = [("emb", ("embedding", "weight")), ("out_norm", ("head.norm", "weight"))]
+            for i in (0, 1):
+                names += [(f"b{i}.{k}", (f"blocks.{i}.mixer", k)) for k in ("q_proj", "k_proj", "v_proj", "o_proj")]
+                names += [(f"b{i}.{k}", (f"blocks.{i}.ffn", k)) for k in ("gate_proj", "up_proj", "down_proj")]
+                names += [(f"b{i}.n1", (f"blocks.{i}.mixer_norm", "weight")), (f"b{i}.n2", (f"blocks.{i}.ffn_norm", "weight"))]
+            # the second layer writes no keys or values: it attends over what the first one cached;
+            # the third call runs the first block again, on a cache of its own
+            return ModelSpec(architecture=self.architecture,
+                             embedding=EmbeddingSpec(vocab_size=d["vocab"], hidden_size=d["width"]),
+                             blocks=(blk, blk),
+                             order=(LayerCall(0, 0), LayerCall(1, 0, writes_cache=False), LayerCall(0, 1)),
+                             head=HeadSpec(vocab_size=d["vocab"], hidden_size=d["width"], tied=True, norm=norm),
+                             tensor_names=tuple(names))
+
+    register_architecture(SharedConfig.architecture, SharedConfig)
+    return SharedConfig
+
+
+def _plain_shared(cfg, w, toks):
+    n, nh, nkv, hd = len(toks), cfg["heads"], cfg["kv"], cfg["head"]
+    x = w["emb"][torch.tensor(toks)]
+    inv = plain_llama.rope_inv_freq(hd, cfg["theta"])
+    kept = None
+    for i, own_cache in ((0, True), (1, False), (0, True)):
+        h = plain_llama.rms_norm(x, w[f"b{i}.n1"], cfg["eps"])
+        q = plain_llama.apply_rope((h @ w[f"b{i}.q_proj"].T).view(n, nh, hd), range(n), inv)
+        if own_cache:
+            k = plain_llama.apply_rope((h @ w[f"b{i}.k_proj"].T).view(n, nkv, hd), range(n), inv)
+            v = (h @ w[f"b{i}.v_proj"].T).view(n, nkv, hd)
+            if kept is None:
+                kept = (k, v)
+        else:
+            k, v = kept                                     # the first layer's keys and values
+        a = plain_llama.causal_attention(q, k, v, 1 / math.sqrt(hd))
+        x = x + a.reshape(n, -1) @ w[f"b{i}.o_proj"].T
+        h = plain_llama.rms_norm(x, w[f"b{i}.n2"], cfg["eps"])
+        x = x + plain_llama.swiglu_mlp(h, w[f"b{i}.gate_proj"], w[f"b{i}.up_proj"], w[f"b{i}.down_proj"])
+    return plain_llama.rms_norm(x, w["out_norm"], cfg["eps"]) @ w["emb"].T
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_layer_reads_another_layers_cache(tmp_path, dtype):
+    """The run order lets the second layer attend over the keys and values the first one cached
+    (it stores none of its own) and names the first block a second time with a cache of its own."""
+    from llm_singularity_b200.engine import ModelRunner, StepEntry
+    from llm_singularity_b200.engine.runner import expected_tensors_of
+    from llm_singularity_b200.weights import random_tensors, write_safetensors
+    SharedConfig = _register_shared()
+    cfg = dict(architectures=["ToySharedCacheForCausalLM"], width=128, heads=4, kv=2, head=64, inner=96, vocab=157,
+               eps=1e-5, theta=10000.0)
+    d = str(tmp_path)
+    json.dump(cfg, open(os.path.join(d, "config.json"), "w"))
+    tensors = random_tensors(expected_tensors_of(SharedConfig(cfg).to_model_spec()), seed=23,
+                             dtype=torch.bfloat16, std=0.08, norm_noise=0.1)
+    write_safetensors(os.path.join(d, "model.safetensors"), tensors)
+    w = {k: v.double() for k, v in tensors.items()}
+    runner = ModelRunner(d, dtype=dtype, page_size=16, num_pages=24, max_requests=2)
+    assert len(runner.model.cache_specs()) == 2             # two caches for three layer calls
+    seqs = {"a": tiny_models.random_tokens(157, 170, 3), "b": tiny_models.random_tokens(157, 60, 4)}
+    plan = [[("a", 140)], [("a", 1), ("b", 33)], [("a", 1), ("b", 1)], [("a", 28), ("b", 26)]]
+    got, pos = {"a": [], "b": []}, {"a": 0, "b": 0}
+    runner.open("a"); runner.open("b")
+    for step in plan:
+        entries = [StepEntry(r, seqs[r][pos[r]:pos[r] + n], list(range(n))) for r, n in step]
+        out = runner.step(entries)
+        k = 0
+        for r, n in step:
+            got[r].append(out[k:k + n]); k += n; pos[r] += n
+    runner.check_kernels()
+    for r in "ab":
+        want = _plain_shared(cfg, w, seqs[r])
+        have = torch.cat(got[r]).double().cpu()
+        bound = 2e-4 if dtype == "float32" else 4e-2 * want.abs().max().item()
+        assert (have - want).abs().max().item() <= bound, r
+    runner.cache.check_invariants()
