@@ -293,7 +293,10 @@ def test_a_windowed_layer_beside_a_full_one_keeps_pages_of_its_own(tmp_path, dty
     windowed = next(g for g in cache.groups if g.window)
     full = next(g for g in cache.groups if not g.window)
     seqs = {"a": tiny_models.random_tokens(211, 230, 1), "b": tiny_models.random_tokens(211, 200, 2)}
-    plan = [[("a", 150)], [("a", 30), ("b", 150)], [("a", 1), ("b", 7)], [("a", 1), ("b", 1)], [("a", 48), ("b", 42)]]
+    # the run of single tokens at the end goes through the captured decode graph (two block tables
+    # to patch inside it, pages leaving the windowed one as it goes)
+    plan = [[("a", 150)], [("a", 30), ("b", 150)], [("a", 1), ("b", 7)], [("a", 1), ("b", 1)], [("a", 28), ("b", 22)]] \
+        + [[("a", 1), ("b", 1)]] * 20
     got, pos = {"a": [], "b": []}, {"a": 0, "b": 0}
     runner.open("a"); runner.open("b")
     for step in plan:
@@ -301,9 +304,9 @@ def test_a_windowed_layer_beside_a_full_one_keeps_pages_of_its_own(tmp_path, dty
         out = runner.step(entries)
         k = 0
         for r, n in step:
-            got[r].append(out[k:k + n]); k += n; pos[r] += n
+            got[r].append(out[k:k + n].clone()); k += n; pos[r] += n      # graph logits are overwritten
     runner.check_kernels()
-    assert pos == {"a": 230, "b": 200}
+    assert pos == {"a": 230, "b": 200} and runner.graph_replays >= 15
     # 430 tokens are held: 28 pages in the full group, only the windows' pages in the other
     assert full.pool.num_used == -(-230 // 16) + -(-200 // 16)
     assert windowed.pool.num_used <= 2 * (-(-40 // 16) + 1)
@@ -401,7 +404,7 @@ def test_a_layer_reads_another_layers_cache(tmp_path, dtype):
     runner = ModelRunner(d, dtype=dtype, page_size=16, num_pages=24, max_requests=2)
     assert len(runner.model.cache_specs()) == 2             # two caches for three layer calls
     seqs = {"a": tiny_models.random_tokens(157, 170, 3), "b": tiny_models.random_tokens(157, 60, 4)}
-    plan = [[("a", 140)], [("a", 1), ("b", 33)], [("a", 1), ("b", 1)], [("a", 28), ("b", 26)]]
+    plan = [[("a", 140)], [("a", 1), ("b", 33)], [("a", 1), ("b", 1)], [("a", 16), ("b", 14)]] + [[("a", 1), ("b", 1)]] * 12
     got, pos = {"a": [], "b": []}, {"a": 0, "b": 0}
     runner.open("a"); runner.open("b")
     for step in plan:
@@ -409,8 +412,9 @@ def test_a_layer_reads_another_layers_cache(tmp_path, dtype):
         out = runner.step(entries)
         k = 0
         for r, n in step:
-            got[r].append(out[k:k + n]); k += n; pos[r] += n
+            got[r].append(out[k:k + n].clone()); k += n; pos[r] += n
     runner.check_kernels()
+    assert pos == {"a": 170, "b": 60} and runner.graph_replays >= 8
     for r in "ab":
         want = _plain_shared(cfg, w, seqs[r])
         have = torch.cat(got[r]).double().cpu()
