@@ -16,7 +16,7 @@ import tiny_models
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"tiny_a": (5, 17, 33, 70), "tiny_b": (1, 9, 40, 70, 50, 23), "tiny_c": (3, 64, 65, 47, 2),
-           "tiny_d": (130, 64, 7, 65, 200)}
+           "tiny_d": (130, 64, 7, 65, 200), "tiny_e": (150, 3, 129, 66)}
 F32_TOL = 1e-4            # float32 logits against float64 plain logits (observed ~1e-6)
 # bfloat16 is held to the plain implementation with activations rounded to bfloat16 at the same
 # places; what is left is summation order and single-ulp (2^-8) flips, which the sharpened
