@@ -111,10 +111,21 @@ add_rmsnorm_vec4_kernel(float* __restrict__ residual, const T* __restrict__ delt
                         T* __restrict__ out, int hidden, int n_rows_total, float eps) {
     __shared__ float scratch[33];
     lsb_pdl_launch_dependents();
+    const int nvec = hidden >> 2;
+    const bool in_regs = nvec <= kNormThreads * kVecRegs;
+    // the norm's weight does not depend on the kernel before: it is on its way while that one
+    // finishes, instead of costing a second round trip to L2 after the sum of squares
+    float4 wv[kVecRegs];
+    if (in_regs) {
+#pragma unroll
+        for (int j = 0; j < kVecRegs; ++j) {
+            const int v = threadIdx.x + j * kNormThreads;
+            wv[j] = v < nvec ? Vec4<float>::load(weight + 4 * v) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+    }
     lsb_pdl_wait();
     const int r_out = blockIdx.x;
     int r_in = r_out;
-    const int nvec = hidden >> 2;
     if (GATHER) {
         r_in = rows[r_out];
         if (r_in < 0 || r_in >= n_rows_total) {
@@ -128,7 +139,6 @@ add_rmsnorm_vec4_kernel(float* __restrict__ residual, const T* __restrict__ delt
     const T* dl = delta ? delta + (size_t)r_in * hidden : nullptr;
     T* o = out + (size_t)r_out * hidden;
     float4 keep[kVecRegs];
-    const bool in_regs = nvec <= kNormThreads * kVecRegs;
     float ss = 0.f;
     if (in_regs) {
 #pragma unroll
@@ -164,7 +174,7 @@ add_rmsnorm_vec4_kernel(float* __restrict__ residual, const T* __restrict__ delt
         for (int j = 0; j < kVecRegs; ++j) {
             const int v = threadIdx.x + j * kNormThreads;
             if (v < nvec) {
-                const float4 w = Vec4<float>::load(weight + 4 * v);
+                const float4 w = wv[j];
                 const float4 x = keep[j];
                 Vec4<T>::store(o + 4 * v, make_float4(x.x * inv * w.x, x.y * inv * w.y, x.z * inv * w.z, x.w * inv * w.w));
             }
