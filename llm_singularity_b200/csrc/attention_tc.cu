@@ -150,11 +150,15 @@ decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
     int* sBT = reinterpret_cast<int*>(sKV + 4 * kDecStages * kStageElems);
     float* sCS = reinterpret_cast<float*>(sBT + kBtCache);   // [cos HD/2][sin HD/2] of the position
     lsb_pdl_launch_dependents();
-    lsb_pdl_wait();
 
+    // Before the wait on the previous kernel, what does not depend on it: the step's metadata was
+    // copied to the device before the step's first kernel started, so the block's key range and
+    // the sines and cosines of the token's position can be had while the projection is still
+    // being computed.  The block table may still be receiving this step's new pages: it is read
+    // after the wait.
     const int split = blockIdx.x, g = blockIdx.y, r = blockIdx.z;
     const int qs = q_start[r];
-    if (q_start[r + 1] - qs != 1) return;                    // prompt portions go to the other kernel
+    const bool single = q_start[r + 1] - qs == 1;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int G = nh / nkv;
     const int kv_len = kv_len_arr[r];
@@ -173,6 +177,13 @@ decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
     const int page0 = div_page(c0 * kChunk, page_size, page_shift);
     const int n_pages_here = c1 > c0 ? div_page(c1 * kChunk - 1, page_size, page_shift) - page0 + 1 : 0;
     const bool cached = n_pages_here <= kBtCache;
+    if (inv_freq && single)
+        for (int i = threadIdx.x; i < HD / 2; i += kThreads)
+            sincosf((float)p * inv_freq[i], &sCS[HD / 2 + i], &sCS[i]);
+
+    lsb_pdl_wait();
+    if (!single) return;                                     // prompt portions go to the other kernel
+
     if (cached)
         for (int idx = threadIdx.x; idx < n_pages_here; idx += kThreads)
             sBT[idx] = (page0 + idx < table_stride) ? bt[page0 + idx] : -1;
@@ -184,9 +195,7 @@ decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
         // rotary kernel forms it), and the block whose key range holds position p writes the new
         // key and value into their page before anybody's copies start.
         constexpr int HC = CPR / 2;                             // 16-byte chunks per half row
-        for (int i = threadIdx.x; i < HD / 2; i += kThreads)
-            sincosf((float)p * inv_freq[i], &sCS[HD / 2 + i], &sCS[i]);
-        __syncthreads();
+        __syncthreads();                                        // the sines and cosines formed above
         for (int idx = threadIdx.x; idx < 16 * HC; idx += kThreads) {
             const int row = idx / HC, c = idx - row * HC;
             uint4 vlo = make_uint4(0, 0, 0, 0), vhi = make_uint4(0, 0, 0, 0);

@@ -100,14 +100,20 @@ __global__ void rope_kv_store_vec_kernel(
     constexpr int VEC = 16 / sizeof(T);
     __shared__ float cs[2][128];
     lsb_pdl_launch_dependents();
-    lsb_pdl_wait();
+    // positions and the request index of each token are metadata of the step (on the device before
+    // its first kernel starts): the sines and cosines are formed while the projection is computed
     const int t = blockIdx.x;
-    if (skip_q_start) {
-        const int r = token_req[t];
-        if (skip_q_start[r + 1] - skip_q_start[r] == 1) return;
-    }
     const int pos = positions[t];
     const int half_rot = rotary_dim >> 1;
+    bool skip = false;
+    if (skip_q_start) {
+        const int r = token_req[t];
+        skip = skip_q_start[r + 1] - skip_q_start[r] == 1;
+    }
+    if (!skip)
+        for (int i = threadIdx.x; i < half_rot; i += blockDim.x) sincosf((float)pos * inv_freq[i], &cs[1][i], &cs[0][i]);
+    lsb_pdl_wait();
+    if (skip) return;
     T* row = qkv + (size_t)t * (nh + 2 * nkv) * hd;
 
     long long page_base = -1;
@@ -122,7 +128,6 @@ __global__ void rope_kv_store_vec_kernel(
             page_base = ((long long)page * nkv * page_size + (pos % page_size)) * hd;
         }
     }
-    for (int i = threadIdx.x; i < half_rot; i += blockDim.x) sincosf((float)pos * inv_freq[i], &cs[1][i], &cs[0][i]);
     __syncthreads();
 
     const int per = half_rot / VEC;
