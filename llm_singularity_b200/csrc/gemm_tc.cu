@@ -561,22 +561,41 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     lsb_pdl_launch_dependents();
-    lsb_pdl_wait();
+    if (threadIdx.x != 0) lsb_pdl_wait();      // thread 0 (the TMA producer) waits after its first weight boxes
 
     // tile t -> (row block, column block); neighbouring blocks share the weight columns
     if (warp == 0) {
         if (lane == 0) {
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_p) : "memory");
             asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+            // The weights are not written by anything in the stream: the boxes of the first ring
+            // fill are requested before the wait on the previous kernel, the activations after it.
+            const bool weights_p = prm.static_operand == 1;
+            int pre = 0;
+            for (int t = blockIdx.x; t < n_tiles && pre < STAGES; t += gridDim.x) {
+                const int i0 = (t % tiles_m) * kBM, j0 = (t / tiles_m) * BN;
+                for (int kb = 0; kb < nkb && pre < STAGES; ++kb, ++pre) {
+                    unsigned char* st = stages + (size_t)pre * L::kStageBytes;
+                    mbar_expect_tx(&full[pre], L::kStageBytes);
+                    if (weights_p) tma_load_2d(st, &map_p, &full[pre], kb * kBK, i0);
+                    else tma_load_2d(st + L::kPBytes, &map_q, &full[pre], kb * kBK, j0);
+                }
+            }
+            lsb_pdl_wait();
             long long it = 0;                                  // K blocks issued so far, over all tiles
             bool ok = true;
             for (int t = blockIdx.x; t < n_tiles && ok; t += gridDim.x) {
                 const int i0 = (t % tiles_m) * kBM, j0 = (t / tiles_m) * BN;
                 for (int kb = 0; kb < nkb; ++kb, ++it) {
                     const int s = (int)(it % STAGES);
+                    unsigned char* st = stages + (size_t)s * L::kStageBytes;
+                    if (it < pre) {                            // the other half of a box requested above
+                        if (weights_p) tma_load_2d(st + L::kPBytes, &map_q, &full[s], kb * kBK, j0);
+                        else tma_load_2d(st, &map_p, &full[s], kb * kBK, i0);
+                        continue;
+                    }
                     if (it >= STAGES && !mbar_wait(&empty[s], (uint32_t)((it / STAGES) - 1) & 1, &abort_flag)) { ok = false; break; }
                     mbar_expect_tx(&full[s], L::kStageBytes);
-                    unsigned char* st = stages + (size_t)s * L::kStageBytes;
                     tma_load_2d(st, &map_p, &full[s], kb * kBK, i0);
                     tma_load_2d(st + L::kPBytes, &map_q, &full[s], kb * kBK, j0);
                 }
