@@ -213,8 +213,8 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
     __shared__ int abort_flag;
 
     lsb_pdl_launch_dependents();
-    lsb_pdl_wait();
-
+    // What follows up to the wait needs nothing from the kernel before: the step's metadata is on
+    // the device before the step's first kernel starts; barriers and tensor memory are this block's.
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.x, r = blockIdx.z;
     const int qs = prm.q_start[r];
@@ -249,6 +249,7 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
+    lsb_pdl_wait();
     // this block's slice of the block table (pages outside the pool are caught here)
     // Pages that lie wholly before the first key any row of this block may see (a window has passed
     // them) may have been given back already: their keys are masked, any page stands in for them.
