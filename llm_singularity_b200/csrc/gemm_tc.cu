@@ -334,6 +334,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
                const GemmParams prm) {
     using L = SmemLayout<BN, STAGES>;
     constexpr uint32_t kTmemCols = BN <= 32 ? 32 : BN <= 64 ? 64 : BN <= 128 ? 128 : 256;
+    constexpr int kPartSwizzle = BN / 4 >= 8 ? 7 : BN / 4 - 1;     // see the partial tile below
+    static_assert((size_t)kBM * BN * 4 <= (size_t)STAGES * L::kStageBytes, "the partial tile lives in the stage buffers");
     extern __shared__ unsigned char smem_raw[];
     // stage buffers need 1024-byte alignment (swizzle atom); the dynamic window is only 16-aligned
     unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -453,14 +455,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         } else if (ok) {
             // this block's 32-bit partial tile goes to its own shared memory (the stage buffers
             // are free: every MMA that read them has completed); the cluster sums them below
-            float* part = reinterpret_cast<float*>(stages) + (size_t)il * BN;
+            // (groups of four floats are swizzled by the row, so that the 32 rows a warp writes at
+            // once spread over all banks)
+            uint4* part = reinterpret_cast<uint4*>(stages) + (size_t)il * (BN / 4);
 #pragma unroll 1
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t r[32];
                 load_acc<BN>(tmem_base, q, c0, nkb > 0, r);
                 const int n = BN - c0 >= 32 ? 32 : 16;
                 for (int x = 0; x < n; x += 4)
-                    *reinterpret_cast<uint4*>(part + c0 + x) = make_uint4(r[x], r[x + 1], r[x + 2], r[x + 3]);
+                    part[((c0 + x) / 4) ^ (il & kPartSwizzle)] = make_uint4(r[x], r[x + 1], r[x + 2], r[x + 3]);
             }
         }
     }
@@ -471,23 +475,40 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
         cluster_barrier();
         if (warp >= 2 && !abort_flag) {
             const uint32_t rank = cluster_rank();
-            const float* part = reinterpret_cast<const float*>(stages);
+            const uint4* part = reinterpret_cast<const uint4*>(stages);
             const int t = (warp - 2) * 32 + lane;
+            const bool rows_whole = prm.ldc_j == 1 && (prm.ldc_i & 3) == 0 && (((uintptr_t)prm.out) & 15) == 0;
             for (int g4 = (int)rank * 128 + t; g4 < kBM * BN / 4; g4 += prm.splits * 128) {
-                const int e = g4 * 4;
+                const int row = g4 / (BN / 4), c4 = g4 % (BN / 4);
+                const uint4* src = part + (size_t)row * (BN / 4) + (c4 ^ (row & kPartSwizzle));
+                float4 v[8];                                  // all peers' loads in flight at once
+#pragma unroll
+                for (int peer = 0; peer < 8; ++peer)
+                    if (peer < prm.splits) v[peer] = ld_peer_f4(src, (uint32_t)peer);
                 float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (int peer = 0; peer < prm.splits; ++peer) {
-                    const float4 v = ld_peer_f4(part + e, (uint32_t)peer);
-                    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
-                }
-                const int i = i0 + e / BN, j = j0 + e % BN;
+#pragma unroll
+                for (int peer = 0; peer < 8; ++peer)          // summed in rank order
+                    if (peer < prm.splits) { acc.x += v[peer].x; acc.y += v[peer].y; acc.z += v[peer].z; acc.w += v[peer].w; }
+                const int i = i0 + row, j = j0 + c4 * 4;
                 if (i < prm.rows_p) {
-                    const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
-                    for (int x = 0; x < 4; ++x) {
-                        if (j + x >= prm.rows_q) break;
-                        const long long o = (long long)i * prm.ldc_i + (long long)(j + x) * prm.ldc_j;
-                        if (prm.out_f32) put<float>(prm.out, o, vals[x]);
-                        else put<bf16>(prm.out, o, vals[x]);
+                    const long long o0 = (long long)i * prm.ldc_i + (long long)j * prm.ldc_j;
+                    if (rows_whole && j + 3 < prm.rows_q) {
+                        if (prm.out_f32) {
+                            *reinterpret_cast<float4*>(reinterpret_cast<float*>(prm.out) + o0) = acc;
+                        } else {
+                            const __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y);
+                            const __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z, acc.w);
+                            *reinterpret_cast<uint2*>(reinterpret_cast<bf16*>(prm.out) + o0) =
+                                make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+                        }
+                    } else {
+                        const float vals[4] = {acc.x, acc.y, acc.z, acc.w};
+                        for (int x = 0; x < 4; ++x) {
+                            if (j + x >= prm.rows_q) break;
+                            const long long o = o0 + (long long)x * prm.ldc_j;
+                            if (prm.out_f32) put<float>(prm.out, o, vals[x]);
+                            else put<bf16>(prm.out, o, vals[x]);
+                        }
                     }
                 }
             }
@@ -790,6 +811,23 @@ LSB_API int lsb_gemm_tc_plan(int M, int N, int K, int swiglu, int* swap, int* bn
         if (mt * ((N + 255) / 256) >= 120 || N >= 2048) best = 256;
         *bn = best;
         *splits = 1;
+        // A few hundred tokens make too few 128 x 256 tiles for 148 SMs.  Where the walk through K
+        // is long (the down projection), K is split over a cluster, as many ways as fit in one
+        // wave; summing the partial tiles costs about as much as 2048 of K, so shorter walks stay
+        // whole.  (The gated epilogue needs whole sums: gated products stay unsplit too.)
+        const int tiles = mt * ((N + 255) / 256);
+        if (best == 256 && tiles < 120 && !swiglu) {
+            int s = 148 / tiles;
+            if (s > 8) s = 8;
+            if (s > num_kb / 32) s = num_kb / 32;
+            if (s > 1) {
+                const int per = (num_kb + s - 1) / s;
+                *splits = (num_kb + per - 1) / per;
+            }
+        }
+        // Unsplit and at most half the SMs busy: tiles half as wide bring the rest in (each
+        // block's stream of operands, which is what a lone tile waits for, gets shorter).
+        if (*splits == 1 && best == 256 && tiles <= 74 && N > 128) *bn = 128;
     }
     return 0;
 }
@@ -832,6 +870,10 @@ LSB_API int lsb_gemm_tc(const void* x, const void* w, void* out, int out_f32, in
     // Blocks of a split product are co-scheduled as clusters: four stages keep their shared memory
     // small enough for two or three blocks per SM, so that every cluster finds room at once.
     // Unsplit products run one block per SM and want the deeper ring to keep HBM busy.
+    if (!swap && splits > 1) {
+        grid.z = splits;
+        return launch<256, 4>(mp, mq, prm, grid, stream);
+    }
     if (!swap && !out_f32 && bn >= 128) {
         // prompts: persistent blocks, double-buffered accumulator
         const int tm = (M + kBM - 1) / kBM, tn = (N + bn - 1) / bn;
@@ -869,3 +911,4 @@ LSB_API int lsb_gemm_tc(const void* x, const void* w, void* out, int out_f32, in
     }
     return rc;
 }
+

@@ -46,7 +46,7 @@ class SchedulerConfig:
     max_model_len: int = 1 << 30
 
 
-@dataclass
+@dataclass(eq=False)            # a request is itself: compared and looked up by identity
 class Request:
     id: Hashable
     prompt: List[int]
@@ -159,12 +159,12 @@ class Scheduler:
         # 1. decode tokens (requests with exactly one token left to run), oldest first; when
         #    pages run out the youngest running request is preempted (possibly the one asking)
         for req in list(self.running):
-            if req not in self.running or len(req.tokens) - req.computed != 1:
-                continue
-            if cfg.max_tokens_per_batch - sum(len(it.tokens) for it in items) <= 0:
+            if req.status != "running" or len(req.tokens) - req.computed != 1:
+                continue                             # preempted a moment ago, or still in its prompt
+            if len(items) >= cfg.max_tokens_per_batch:
                 break
             placed = False
-            while req in self.running:
+            while req.status == "running":
                 if self._reserve(req, len(req.tokens)):
                     placed = True
                     break
@@ -173,7 +173,7 @@ class Scheduler:
                 self._preempt(victim)
             if placed:
                 items.append(ScheduledItem(req, req.computed, [req.tokens[-1]], True))
-        budget = cfg.max_tokens_per_batch - sum(len(it.tokens) for it in items)
+        budget = cfg.max_tokens_per_batch - len(items)
 
         # 2. next portions of prompts already running (they wait for pages, never preempt)
         for req in self.running:

@@ -112,8 +112,11 @@ def _p(t: Optional[torch.Tensor]):
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 
 
+_raw_stream = torch._C._cuda_getCurrentRawStream      # (device index) -> cudaStream_t as int
+
+
 def _stream(t: torch.Tensor):
-    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+    return ctypes.c_void_p(_raw_stream(t.device.index))
 
 
 _i = ctypes.c_int
