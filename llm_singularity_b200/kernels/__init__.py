@@ -309,6 +309,18 @@ def tensor_core_attention_ok(dtype, hd: int, nh: int, nkv: int) -> bool:
     return dtype == torch.bfloat16 and hd in _TC_HEAD_DIMS and nh // nkv <= 16
 
 
+def _batch_shape(ctx):
+    """(single-token requests, first and one past the last request with more tokens) of a step;
+    worked out once per step and kept on the context."""
+    shape = getattr(ctx, "_batch_shape", None)
+    if shape is None:
+        many = ctx.h_q_len != 1
+        idx = many.nonzero()[0]
+        shape = (int(len(many) - len(idx)),) + ((int(idx[0]), int(idx[-1]) + 1) if len(idx) else (0, 0))
+        ctx._batch_shape = shape
+    return shape
+
+
 def rope_store_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache,
                          inv_freq: Optional[torch.Tensor], rotary_dim: int, store: bool,
                          scale: float, window: int, out: torch.Tensor) -> None:
@@ -318,7 +330,7 @@ def rope_store_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cac
     not at all."""
     fuse = (FUSE_DECODE_ROPE and rotary_dim == hd and inv_freq is not None
             and tensor_core_attention_ok(qkv.dtype, hd, nh, nkv))
-    n_decode = int((ctx.h_q_len == 1).sum()) if fuse else 0
+    n_decode = _batch_shape(ctx)[0] if fuse else 0
     if not n_decode:
         rope_kv_store(qkv, nh, nkv, hd, ctx, cache, inv_freq, rotary_dim, store)
         paged_attention(qkv, nh, nkv, hd, ctx, cache, scale, window, out)
@@ -365,7 +377,7 @@ def paged_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache, s
               _i(ctx.n_requests), _i(ctx.max_q_len), *tail, _stream(out))
         return
     R = ctx.n_requests
-    n_decode = int((ctx.h_q_len == 1).sum())
+    n_decode, first, last = _batch_shape(ctx)
     if n_decode:
         splits = decode_splits(n_decode, nkv)
         if not getattr(ctx, "fixed_launch", False):
@@ -392,15 +404,25 @@ def paged_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache, s
                   _i(splits), _p(decode_rope[0]), _i(1 if decode_rope[1] else 0), _stream(out))
     if n_decode < R:
         # prompt portions: tcgen05 kernel for long ones (128-row tiles), mma.sync kernel otherwise
+        # The grid has a slab of blocks per request, and blocks that find a single token leave at
+        # once, but thousands of them still cost tens of microseconds: the kernels get only the
+        # requests from the first to the last prompt portion (the scheduler puts single tokens
+        # first), by way of offset pointers into the per-request arrays.
+        off = 4 * first
+        per_request = (ctypes.c_void_p(ctx.q_start.data_ptr() + off),
+                       ctypes.c_void_p(ctx.kv_len.data_ptr() + off),
+                       ctypes.c_void_p(ctx.table_rows.data_ptr() + off))
+        skip = _i(1 if n_decode > first + (R - last) else 0)      # single tokens among them
         if (USE_TCGEN05_ATTENTION and ctx.max_q_len >= 128
                 and cache.page_size in (8, 16, 32, 64) and qkv.shape[1] % 8 == 0):
             _call("attention_tc5", "lsb_prefill_attention_tc5", _p(qkv), _i(qkv.shape[1]), _i(T),
-                  _p(cache.k_pages), _p(cache.v_pages), _p(ctx.q_start), _p(ctx.kv_len),
-                  _p(ctx.table_rows), _p(cache.block_table), _i(cache.block_table.shape[1]), _p(out),
-                  _i(R), _i(ctx.max_q_len), *tail, _i(1 if n_decode else 0), _stream(out))
+                  _p(cache.k_pages), _p(cache.v_pages), *per_request, _p(cache.block_table),
+                  _i(cache.block_table.shape[1]), _p(out), _i(last - first), _i(ctx.max_q_len), *tail,
+                  skip, _stream(out))
         else:
-            _call("attention_tc", "lsb_prefill_attention", *common, _i(R), _i(ctx.max_q_len), *tail,
-                  _i(1 if n_decode else 0), _stream(out))
+            _call("attention_tc", "lsb_prefill_attention", _p(qkv), _i(qkv.shape[1]), _p(cache.k_pages),
+                  _p(cache.v_pages), *per_request, _p(cache.block_table), _i(cache.block_table.shape[1]),
+                  _p(out), _i(last - first), _i(ctx.max_q_len), *tail, skip, _stream(out))
 
 
 def sample(logits: torch.Tensor, params: torch.Tensor, top_k: torch.Tensor,
