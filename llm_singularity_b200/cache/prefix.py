@@ -112,15 +112,17 @@ class RadixPrefixCache:
         return kept
 
     def share(self, tokens: Sequence[int], request, held: Sequence[_Node]) -> List[_Node]:
-        """Like :meth:`insert`, for a request that goes on running: its full pages become
-        visible to later prompts now (a prompt that arrives while this one still decodes need
-        not recompute what they have in common).  ``held``: the nodes the request already counts
+        """Like :meth:`insert`, for a request that goes on running: the pages its ``tokens`` fill
+        become visible to later prompts now (a prompt that arrives while this one still decodes
+        need not recompute what they have in common).  ``held``: the nodes the request already counts
         as a user of (its adopted prefix).  Returns the further nodes whose pages are the
         request's own; it is a user of those too until :meth:`release`, so that they are not
         offered for eviction while evicting them would free nothing."""
         ps = self.page_size
-        n_full = min(len(tokens), self.cache.length(request)) // ps
         pages = [self.cache.pages_of(request, g) for g in range(len(self.cache.groups))]
+        # (the step that fills these pages may only be planned yet: whoever reads them is queued
+        # behind it, so the pages count as full as soon as they are the request's)
+        n_full = min([len(tokens) // ps] + [len(p) for p in pages])
         mine_of = lambda i: tuple(pages[g][i] for g in range(len(pages)))
         have = set(map(id, held))
         node, now, added = self.root, next(self._clock), []

@@ -46,3 +46,24 @@ LSB_API int lsb_scatter_i32_counted(int* dst, const int* packed, int cap, long l
     if (cap <= 0) return 0;
     return lsb_launch(scatter_i32_counted_kernel, dim3(1), dim3(256), 0, stream, 1, dst, packed, cap, dst_size);
 }
+
+// dst[dst_idx[i]] = src[src_idx[i]]: the tokens a step sampled on the device become input tokens
+// of the next step, which may hold the requests in another order and other tokens beside them.
+__global__ void move_i32_kernel(int* __restrict__ dst, const int* __restrict__ dst_idx,
+                                const int* __restrict__ src, const int* __restrict__ src_idx, int n,
+                                long long dst_size, long long src_size) {
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int a = dst_idx[i], b = src_idx[i];
+    if (a < 0 || a >= dst_size || b < 0 || b >= src_size) { lsb_set_status(LSB_BAD_ROW); return; }
+    dst[a] = src[b];
+}
+
+LSB_API int lsb_move_i32(int* dst, const int* dst_idx, const int* src, const int* src_idx, int n,
+                         long long dst_size, long long src_size, cudaStream_t stream) {
+    if (n <= 0) return 0;
+    return lsb_launch(move_i32_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, 1, dst, dst_idx, src,
+                      src_idx, n, dst_size, src_size);
+}

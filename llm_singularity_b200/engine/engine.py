@@ -110,10 +110,10 @@ class Engine:
         that produced a token, and (id, -1, True) for requests that ended with an error.
 
         With ``run_ahead`` the step after this one is planned and queued on the device before
-        this one's tokens are read back, whenever the scheduler can tell what it will hold
-        (Scheduler.schedule_ahead): it takes its input tokens from the device, where the sampler
-        left them, and the host's work for it happens while the device is busy.  Each call still
-        returns the tokens of exactly one step."""
+        this one's tokens are read back (Scheduler.schedule_ahead): decoding requests take their
+        input token from the device, where the sampler left it, prompt portions and admissions
+        are known anyway, and the host's work for the step happens while the device is busy.
+        Each call still returns the tokens of exactly one step."""
         out: List[Tuple[Hashable, int, bool]] = []
         cur = self._inflight
         if cur is None:
@@ -126,6 +126,8 @@ class Engine:
         nxt = None
         if self.run_ahead:
             items = self.scheduler.schedule_ahead()
+            for req in self.scheduler.take_finished():
+                out.append((req.id, -1, True))
             if items is not None:
                 nxt = self._launch(items, cur)
         self._inflight = nxt
@@ -134,17 +136,27 @@ class Engine:
 
     def _launch(self, items, after: Optional["_Launched"]) -> "_Launched":
         """Queue one planned step on the device: the model step, sampling, and the copy of the
-        new tokens to the host.  ``after``: the step whose sampled tokens are this one's input."""
-        entries = [StepEntry(it.request.id, it.tokens if after is None else [0],
-                             [len(it.tokens) - 1] if it.sample else []) for it in items]
-        logits = self.runner.step(entries, device_tokens=None if after is None else after.dev_tokens)
+        new tokens to the host.  ``after``: the step in flight, whose sampled tokens are the
+        input of the entries that bring a place-holder."""
+        pending = self.scheduler.PENDING
+        entries, places, which = [], [], []
+        place_of = {r.id: i for i, r in enumerate(after.wanted)} if after is not None else {}
+        for k, it in enumerate(items):
+            tokens = it.tokens
+            if tokens[-1] == pending:                          # a single token, still on the device
+                places.append(place_of[it.request.id])
+                which.append(k)
+                tokens = [0]
+            entries.append(StepEntry(it.request.id, tokens, [len(tokens) - 1] if it.sample else []))
+        feed = (after.dev_tokens, places, which) if which else None
+        logits = self.runner.step(entries, feed=feed)
         wanted = [it.request for it in items if it.sample]
         launched = _Launched(wanted)
         if wanted:
-            ahead = 0 if after is None else 1                  # a token still in flight counts
+            # a request's tokens still in flight count towards its place in the sampling stream
             launched.dev_tokens = self.sampler.sample(
-                logits, [r.sampling for r in wanted], [len(r.generated) + ahead for r in wanted],
-                [r.generated for r in wanted])
+                logits, [r.sampling for r in wanted],
+                [len(r.generated) + r.pending - 1 for r in wanted], [r.generated for r in wanted])
             if launched.dev_tokens.is_cuda:
                 host = self._host_tokens[self._host_turn][:len(wanted)]
                 self._host_turn ^= 1

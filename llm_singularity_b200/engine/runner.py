@@ -60,7 +60,8 @@ class _DecodeGraph:
 
     def __init__(self, n_requests: int, n_groups: int, device):
         self.cap = 2 * n_requests + 8                    # block-table cells changed per step
-        n = 3 * n_requests + (n_requests + 1) + 3 * n_requests + n_groups * (1 + 2 * self.cap)
+        n = 3 * n_requests + (n_requests + 1) + 3 * n_requests + n_groups * (1 + 2 * self.cap) \
+            + 2 * n_requests                             # and which tokens come from the device
         self.meta = torch.zeros(n, dtype=torch.int32, device=device)
         self.graph = None
         self.logits: Optional[torch.Tensor] = None
@@ -131,18 +132,20 @@ class ModelRunner:
         self.cache.close(request)
 
     # -------------------------------------------------------------------- step
-    def step(self, entries: Sequence[StepEntry],
-             device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], feed=None) -> torch.Tensor:
         """Run the entries' tokens as one batch from the cache; returns the logits at the wanted
         places, float32 [wanted, vocab] on the device, in the order of the entries.
 
-        ``device_tokens`` (int32, one per entry) says that the tokens of this step are on the
-        device already (the previous step sampled them there and the host has not read them
-        yet): every entry brings one token, whose value in ``entries`` is ignored."""
+        ``feed = (source, places, which)`` says that some tokens of this step are on the device
+        already (the previous step sampled them there and the host has not read them yet): entry
+        ``which[i]`` brings one token, whose value in ``entries`` is ignored; it is
+        ``source[places[i]]`` (``source``: int32 on the device)."""
         cache = self.cache
-        if device_tokens is not None and (any(len(e.tokens) != 1 for e in entries)
-                                          or device_tokens.numel() != len(entries)):
-            raise ValueError("device_tokens needs one token per entry and entries of one token")
+        if feed is not None:
+            source, places, which = feed
+            if len(places) != len(which) or any(len(entries[k].tokens) != 1 for k in which) \
+                    or any(not 0 <= p < source.numel() for p in places):
+                raise ValueError("feed: one place in the source per entry, and entries of one token")
         starts = [cache.length(e.request) for e in entries]
         seen = set()
         for e in entries:
@@ -162,12 +165,18 @@ class ModelRunner:
                 raise OutOfPages(
                     f"request {e.request!r} needs {cache.pages_needed(e.request, new_len)} more "
                     f"pages, {cache.free_pages()} are free")
+        moves: List[np.ndarray] = []
+        if feed is not None:
+            lens = np.fromiter((len(e.tokens) for e in entries), dtype=np.int32, count=len(entries))
+            first = np.concatenate(([0], np.cumsum(lens[:-1]))).astype(np.int32)   # entry -> its first token
+            moves = [first[np.asarray(which, dtype=np.int64)], np.asarray(places, dtype=np.int32)]
         if self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
-            logits, n_tokens = self._decode_with_graph(entries, starts, device_tokens), len(entries)
+            logits = self._decode_with_graph(entries, starts, moves, None if feed is None else source)
+            n_tokens = len(entries)
         else:
-            ctx = self.prepare_context(entries, starts)
-            if device_tokens is not None:
-                ctx.token_ids.copy_(device_tokens)
+            ctx, dev_moves = self.prepare_context(entries, starts, moves)
+            if feed is not None:
+                self.rt.ops.move_i32(ctx.token_ids, dev_moves[0], source, dev_moves[1])
             logits, n_tokens = self.model.forward(ctx, cache), ctx.n_tokens
         for e, s in zip(entries, starts):
             cache.commit(e.request, s + len(e.tokens))
@@ -177,7 +186,7 @@ class ModelRunner:
 
     # ------------------------------------------------------------ decode graphs
     def _decode_with_graph(self, entries: Sequence[StepEntry], starts: Sequence[int],
-                           device_tokens: Optional[torch.Tensor] = None) -> torch.Tensor:
+                           moves: List[np.ndarray], source: Optional[torch.Tensor]) -> torch.Tensor:
         """A step of single decode tokens, all wanted: replay the graph captured for this batch
         size.  The step's metadata and the block-table cells that changed are copied into buffers
         at fixed addresses first; everything else happens inside the graph.  The returned logits
@@ -203,10 +212,10 @@ class ModelRunner:
             extra.append(packed)
         ctx, dev_extra = self._ctx.build(
             [e.tokens for e in entries], list(starts), [cache.slot(e.request) for e in entries],
-            [e.want for e in entries], extra, static=st.meta)
+            [e.want for e in entries], extra + moves, static=st.meta)
         ctx.fixed_launch = True
-        if device_tokens is not None:
-            ctx.token_ids.copy_(device_tokens)       # after the metadata copy, before the graph
+        if moves:                                    # after the metadata copy, before the graph
+            self.rt.ops.move_i32(ctx.token_ids, dev_extra[-2], source, dev_extra[-1])
 
         def run():
             for gi, g in enumerate(cache.groups):
@@ -242,8 +251,11 @@ class ModelRunner:
         if check is not None:
             check()
 
-    def prepare_context(self, entries: Sequence[StepEntry], starts: Sequence[int]) -> StepContext:
-        """Build the step's device metadata and bring the device block tables up to date."""
+    def prepare_context(self, entries: Sequence[StepEntry], starts: Sequence[int],
+                        more: Sequence[np.ndarray] = ()):
+        """Build the step's device metadata and bring the device block tables up to date.
+        Returns the context and the int32 arrays of ``more`` on the device (they ride along in
+        the metadata's one copy)."""
         cache = self.cache
         extra: List[np.ndarray] = []
         for gi in range(len(cache.groups)):
@@ -254,9 +266,9 @@ class ModelRunner:
             extra.append(np.fromiter(last.values(), dtype=np.int32, count=len(last)))
         ctx, dev_extra = self._ctx.build(
             [e.tokens for e in entries], list(starts),
-            [cache.slot(e.request) for e in entries], [e.want for e in entries], extra)
+            [cache.slot(e.request) for e in entries], [e.want for e in entries], extra + list(more))
         for gi, g in enumerate(cache.groups):
             idx, val = dev_extra[2 * gi], dev_extra[2 * gi + 1]
             if idx.numel():
                 self.rt.ops.scatter_i32(g.dev_table, idx, val)
-        return ctx
+        return ctx, dev_extra[2 * len(cache.groups):]

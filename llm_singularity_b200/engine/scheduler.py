@@ -20,6 +20,13 @@ request that could never fit (its prompt plus one token needs more pages than th
 pool has, or exceeds ``max_model_len``) finishes at once with an error status.
 Nothing here is random, so a run can be replayed.
 
+Accounting has two halves.  Planning a step advances its requests at once: the tokens it runs
+count as computed, and a request whose logits it samples gets a place-holder (``PENDING``) at
+the end of its tokens.  :meth:`Scheduler.update` fills the place-holders in when the sampled
+tokens have come back, and finishes requests.  Between the two the next step can already be
+planned (:meth:`Scheduler.schedule_ahead`): a request with a place-holder decodes on, its input
+token being fed on the device, so the device never waits for the host.
+
 The reference schedules prompts before decode tokens, iterates an unordered map,
 allocates whole prompts at admission, samples after every portion and, when pages
 run out during decoding, silently carries on into page 0
@@ -54,9 +61,10 @@ class Request:
     sampling: SamplingParams = field(default_factory=SamplingParams)
     ignore_eos: bool = False
     # progress
-    tokens: List[int] = field(default_factory=list)      # prompt + generated so far
+    tokens: List[int] = field(default_factory=list)      # prompt + generated so far (+ place-holders)
     generated: List[int] = field(default_factory=list)
-    computed: int = 0                                    # tokens whose keys/values are cached
+    computed: int = 0               # tokens whose keys/values are cached once the planned steps have run
+    pending: int = 0                # place-holders at the end of ``tokens``: sampled, not yet known
     status: str = "waiting"          # waiting | running | finished | error
     error: str = ""
     preemptions: int = 0
@@ -73,6 +81,7 @@ class ScheduledItem:
     start: int                 # == request.computed: position of the first token of the portion
     tokens: List[int]
     sample: bool               # the portion ends the known tokens: logits of its last token wanted
+    decode: bool = False       # one token after a sampled one (the rest is prompt work)
 
 
 class Scheduler:
@@ -150,23 +159,58 @@ class Scheduler:
         return None
 
     # --------------------------------------------------------------- schedule
+    PENDING = -1        # stands for a token that a step in flight has yet to produce
+
     def schedule(self) -> List[ScheduledItem]:
+        """Plan the next step; the step before it has been accounted (:meth:`update`)."""
+        if self._plans:
+            raise RuntimeError("a step is in flight: account it first, or plan with schedule_ahead")
+        return self._plan(ahead=False)
+
+    def schedule_ahead(self) -> Optional[List[ScheduledItem]]:
+        """Plan the step after the one in flight before that one's tokens are known.  A request
+        whose next token is in flight brings ``[PENDING]``; the caller feeds it from the device.
+        Left out of such a step: a request that the token in flight finishes (``max_new_tokens``
+        or the model's length; its pages come back when it is accounted) and anything that
+        needs preemption.  A request that turns out to have stopped on the token in flight (a stop
+        token) is skipped when the step planned here is accounted.  Returns None when there is
+        nothing to run, when two steps would be ahead, or when a request samples with a repetition
+        penalty (which needs the token in flight on the host): plan with :meth:`schedule` after
+        :meth:`update` then."""
+        if len(self._plans) != 1:
+            return None
+        if any(r.pending and r.sampling.repetition_penalty != 1.0 for r in self.running):
+            return None
+        items = self._plan(ahead=True)
+        if items:
+            self.stats["ahead_steps"] = self.stats.get("ahead_steps", 0) + 1
+        return items or None
+
+    def _ends_with_token_in_flight(self, req: Request) -> bool:
+        return len(req.generated) + req.pending >= req.max_new_tokens \
+            or len(req.tokens) + 1 > self.cfg.max_model_len
+
+    def _plan(self, ahead: bool) -> List[ScheduledItem]:
         cfg = self.cfg
         items: List[ScheduledItem] = []
-        budget = cfg.max_tokens_per_batch
         chunk_cap = cfg.max_prefill_chunk or cfg.max_tokens_per_batch
 
         # 1. decode tokens (requests with exactly one token left to run), oldest first; when
-        #    pages run out the youngest running request is preempted (possibly the one asking)
+        #    pages run out the youngest running request is preempted (possibly the one asking),
+        #    or, while a step is in flight, the request waits
         for req in list(self.running):
             if req.status != "running" or len(req.tokens) - req.computed != 1:
                 continue                             # preempted a moment ago, or still in its prompt
+            if req.pending and self._ends_with_token_in_flight(req):
+                continue
             if len(items) >= cfg.max_tokens_per_batch:
                 break
             placed = False
             while req.status == "running":
                 if self._reserve(req, len(req.tokens)):
                     placed = True
+                    break
+                if ahead:
                     break
                 victim = self.running[-1]
                 items = [it for it in items if it.request is not victim]
@@ -215,7 +259,7 @@ class Scheduler:
                 budget -= n
 
         # nothing could move although requests are live: the youngest gives way
-        if not items and self.running:
+        if not items and self.running and not ahead:
             if len(self.running) == 1:
                 req = self.running[0]
                 self._release(req)
@@ -223,50 +267,24 @@ class Scheduler:
                 self._fail(req, "the cache pool cannot hold this request")
             else:
                 self._preempt(self.running[-1])
-            return self.schedule()
+            return self._plan(ahead)
 
+        # the first half of the accounting: the step counts as run
+        for it in items:
+            req = it.request
+            req.computed += len(it.tokens)
+            it.decode = len(it.tokens) == 1 and it.start > 0 and bool(req.generated or req.pending)
+            if it.sample:
+                if self.prefix is not None and not it.decode:
+                    # The prompt is whole with this step: later prompts may share its full pages
+                    # from now on (a step that reads them is queued behind this one).
+                    req.prefix_path = req.prefix_path + self.prefix.share(
+                        req.tokens[:req.computed], req.id, req.prefix_path)
+                req.tokens.append(self.PENDING)
+                req.pending += 1
         if items:
             self._plans.append(items)
-        self.stats["steps"] += 1 if items else 0
-        return items
-
-    # ---------------------------------------------------------- schedule ahead
-    PENDING = -1        # stands for a token that the step in flight has yet to produce
-
-    def schedule_ahead(self) -> Optional[List[ScheduledItem]]:
-        """Plan the step after the one in flight before that one's tokens are known, so that the
-        device never waits for the host: possible when the step in flight ends the known tokens
-        of every running request (each then has exactly one new token, which the caller feeds
-        from the device), nobody waits for admission, nobody reaches ``max_new_tokens`` or the
-        model's length with the token in flight or samples with a repetition penalty (which
-        needs that token on the host), and the pages for one more token each are free
-        without eviction or preemption.  A request that turns out to have stopped on the token
-        in flight (a stop token) is skipped when the step planned here is accounted.  Returns
-        the plan, items in the order of the step in flight, or None (then plan with
-        :meth:`schedule` after :meth:`update`)."""
-        if len(self._plans) != 1 or self.waiting:
-            return None
-        last = self._plans[0]
-        if len(last) != len(self.running) or not all(it.sample for it in last):
-            return None
-        for it in last:
-            req = it.request
-            if req.status != "running" or len(req.generated) + 1 >= req.max_new_tokens \
-                    or len(req.tokens) + 2 > self.cfg.max_model_len \
-                    or req.sampling.repetition_penalty != 1.0:     # needs the token on the host
-                return None
-        need = sum(self.cache.pages_needed(it.request.id, len(it.request.tokens) + 1) for it in last)
-        if need > self.cache.free_pages():
-            return None
-        items = []
-        for it in last:
-            req = it.request
-            if not self.cache.reserve(req.id, len(req.tokens) + 1):
-                return None                          # cannot happen after the count above
-            items.append(ScheduledItem(req, len(req.tokens), [self.PENDING], True))
-        self._plans.append(items)
-        self.stats["steps"] += 1
-        self.stats["ahead_steps"] = self.stats.get("ahead_steps", 0) + 1
+            self.stats["steps"] += 1
         return items
 
     def _fit_portion(self, req: Request, n: int) -> int:
@@ -289,44 +307,45 @@ class Scheduler:
 
     # ----------------------------------------------------------------- update
     def update(self, sampled: Dict[Hashable, int]) -> List[Request]:
-        """After the oldest step still unaccounted: advance every request it scheduled;
-        ``sampled`` maps the ids of requests whose logits were wanted to their new token.
+        """The oldest step still unaccounted has run: ``sampled`` maps the ids of requests whose
+        logits were wanted to their new token, which takes its place among the request's tokens.
         Returns requests that finished."""
-        done: List[Request] = []
+        done: List[Tuple[Request, int]] = []
         for it in (self._plans.popleft() if self._plans else []):
             req = it.request
             if req.status != "running":
                 continue         # planned ahead, but it stopped on the token that was in flight
-            req.computed += len(it.tokens)
-            if self.cache.length(req.id) < req.computed:  # the step function has done it already,
-                self.cache.commit(req.id, req.computed)   # and a step planned ahead may be further
+            end = it.start + len(it.tokens)               # tokens cached now that this step has run
+            if self.cache.length(req.id) < end:           # the step function has done it already,
+                self.cache.commit(req.id, end)            # and a step planned ahead may be further
             if it.sample:
-                if len(it.tokens) == 1 and it.start > 0 and req.generated:
+                if it.decode:
                     self.stats["decode_tokens"] += 1
                 else:
                     self.stats["prefill_tokens"] += len(it.tokens)
-                    if self.prefix is not None:
-                        # the prompt has run: later prompts may share its full pages from now on
-                        req.prefix_path = req.prefix_path + self.prefix.share(
-                            req.tokens[:req.computed], req.id, req.prefix_path)
                 tok = int(sampled[req.id])
-                req.tokens.append(tok)
+                if req.tokens[end] != self.PENDING:
+                    raise RuntimeError(f"request {req.id!r}: no token is outstanding at place {end}")
+                req.tokens[end] = tok
+                req.pending -= 1
                 req.generated.append(tok)
                 stop = (not req.ignore_eos and tok in self.cfg.stop_token_ids) \
                     or len(req.generated) >= req.max_new_tokens \
-                    or len(req.tokens) + 1 > self.cfg.max_model_len
+                    or end + 2 > self.cfg.max_model_len
                 if stop:
-                    done.append(req)
+                    done.append((req, end))
             else:
                 self.stats["prefill_tokens"] += len(it.tokens)
-        for req in done:
+        for req, end in done:
+            del req.tokens[end + 1:]                      # a place-holder of a step planned ahead
+            req.pending, req.computed = 0, end
             if self.prefix is not None:
-                self.prefix.insert(req.tokens[:req.computed], req.id)
+                self.prefix.insert(req.tokens[:end], req.id)
             self._release(req)
             self.running.remove(req)
             req.status = "finished"
             self.finished.append(req)
-        return done
+        return [req for req, _ in done]
 
     def take_finished(self) -> List[Request]:
         out, self.finished = self.finished, []

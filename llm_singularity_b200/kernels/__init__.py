@@ -136,6 +136,16 @@ def scatter_i32(dst: torch.Tensor, idx: torch.Tensor, val: torch.Tensor) -> None
           _ll(dst.numel()), _stream(dst))
 
 
+def move_i32(dst: torch.Tensor, dst_idx: torch.Tensor, src: torch.Tensor, src_idx: torch.Tensor) -> None:
+    """dst[dst_idx[i]] = src[src_idx[i]]."""
+    for name, t in (("dst", dst), ("dst_idx", dst_idx), ("src", src), ("src_idx", src_idx)):
+        _req(t, name, torch.int32, 1)
+    if dst_idx.numel() != src_idx.numel():
+        raise KernelError("move_i32: dst_idx and src_idx differ in length")
+    _call("cache_table", "lsb_move_i32", _p(dst), _p(dst_idx), _p(src), _p(src_idx), _i(dst_idx.numel()),
+          _ll(dst.numel()), _ll(src.numel()), _stream(dst))
+
+
 def scatter_i32_counted(dst: torch.Tensor, packed: torch.Tensor, cap: int) -> None:
     """dst.flat[idx[i]] = val[i] for i < n, with packed = [n, idx[cap], val[cap]] on the device."""
     _req(dst, "dst", torch.int32)

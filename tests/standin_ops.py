@@ -20,6 +20,10 @@ def scatter_i32(dst, idx, val):
     dst.view(-1)[idx.long()] = val
 
 
+def move_i32(dst, dst_idx, src, src_idx):
+    dst[dst_idx.long()] = src[src_idx.long()]
+
+
 def embedding(table, ids, out):
     out.copy_(table[ids.long()].float())
 

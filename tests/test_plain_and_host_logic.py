@@ -138,13 +138,15 @@ def test_engine_greedy_matches_plain_even_with_few_pages_and_preemption(model_di
     cfg, w = plain_llama.load_model_dir(model_dirs["tiny_a"])
     prompts = [tiny_models.random_tokens(256, n, 40 + n) for n in (5, 17, 33)]
     ref = [plain_llama.greedy_generate(cfg, w, p, 8) for p in prompts]
-    for pages, chunk in ((64, None), (5, 7)):
+    for pages, chunk, ahead in ((64, None, True), (5, 7, False), (5, 7, True)):
         eng = Engine(model_dirs["tiny_a"], dtype="float32", device="cpu", kv_block_size=16,
                      num_kv_blocks=pages, max_batch_size=4, max_tokens_per_batch=24,
-                     prefill_chunk=chunk, ops=standin_ops, prefix_cache=False)
+                     prefill_chunk=chunk, ops=standin_ops, prefix_cache=False, run_ahead=ahead)
         assert eng.generate(prompts, max_new_tokens=8, ignore_eos=True) == ref
         eng.runner.cache.check_invariants()
-        if pages == 5:
+        assert eng.runner.cache.free_pages() == pages
+        if pages == 5 and not ahead:
+            # (a step planned ahead never preempts: a request that finds no page waits a step)
             assert eng.stats()["preemptions"] > 0
 
 
@@ -170,6 +172,60 @@ def test_engine_running_ahead_yields_the_same_tokens(model_dirs, temperature):
     stop = first[1][4]
     assert second[1] == first[1][:first[1].index(stop) + 1]
     assert stats[0].get("ahead_steps", 0) == 0 and stats[1]["ahead_steps"] >= 10
+
+
+@pytest.mark.parametrize("seed", [0, 1, 2])
+def test_engine_under_a_random_load_yields_each_requests_own_tokens(model_dirs, seed):
+    """Requests arrive while others run, with prompts that share beginnings, few pages, small
+    budgets, stop tokens and sampled streams: whatever the scheduler makes of it (steps planned
+    ahead, portions, waits for pages, preemption, shared pages), every request ends with the
+    tokens it yields when it runs alone, and every page comes back."""
+    import random
+    rng = random.Random(seed)
+    heads = [tiny_models.random_tokens(512, 16, 300 + i) for i in range(3)]
+    jobs = []
+    for i in range(14):
+        prompt = (rng.choice(heads) if rng.random() < 0.6 else []) + \
+            tiny_models.random_tokens(512, rng.randrange(1, 30), 400 + 17 * seed + i)
+        jobs.append(dict(token_ids=prompt, max_new_tokens=rng.randrange(1, 14),
+                         temperature=rng.choice([0.0, 0.9]), top_k=rng.choice([0, 5]), seed=i,
+                         ignore_eos=rng.random() < 0.5))
+
+    def engine(**kw):
+        return Engine(model_dirs["tiny_b"], dtype="float32", device="cpu", kv_block_size=8,
+                      ops=standin_ops, **kw)
+
+    alone = engine(num_kv_blocks=64, max_batch_size=1, prefix_cache=False, run_ahead=False)
+    stops = tuple(range(3, 512, 6))                              # every sixth token stops a request
+    want = []
+    alone.scheduler.cfg.stop_token_ids = stops
+    for j in jobs:
+        rid = alone.add_request(**j)
+        while alone.has_work():
+            alone.step()
+        want.append(alone.request(rid).generated)
+    assert any(w[-1] in stops and len(w) < j["max_new_tokens"] for w, j in zip(want, jobs))
+
+    for ahead, prefix, pages in ((True, True, 20), (True, False, 14), (False, True, 14)):
+        eng = engine(num_kv_blocks=pages, max_batch_size=5, max_tokens_per_batch=24, prefill_chunk=9,
+                     prefix_cache=prefix, run_ahead=ahead)
+        eng.scheduler.cfg.stop_token_ids = stops
+        ids, todo, order = [], list(jobs), random.Random(seed + 100)
+        while todo or eng.has_work():
+            for _ in range(order.randrange(0, 3)):
+                if todo:
+                    ids.append(eng.add_request(**todo.pop(0)))
+            eng.step()
+        got = [eng.request(r).generated for r in ids]
+        assert got == want, (ahead, prefix, pages)
+        assert all(eng.request(r).status == "finished" and eng.request(r).pending == 0 for r in ids)
+        eng.runner.cache.check_invariants()
+        if prefix:
+            eng.prefix.check_invariants()
+            eng.prefix.evict(10 ** 6)
+        assert eng.runner.cache.free_pages() == pages
+        if ahead:
+            assert eng.stats()["ahead_steps"] > 10
 
 
 def test_engine_shares_prompt_pages_between_live_requests_and_yields_the_same_tokens(model_dirs):

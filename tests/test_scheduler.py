@@ -180,58 +180,95 @@ def test_cached_prefixes_are_evicted_before_anyone_is_preempted():
 
 
 # ------------------------------------------------------------- planning ahead
-def test_a_step_is_planned_ahead_only_when_it_is_known_what_it_holds():
+P = Scheduler.PENDING
+
+
+def plan_of(items):
+    return [(it.request.id, it.start, it.tokens if len(it.tokens) == 1 else len(it.tokens), it.sample)
+            for it in items]
+
+
+def test_the_next_step_is_planned_while_one_is_in_flight():
     sch, cache = make()
     sch.add(req("a", 20, max_new=6, ignore_eos=True)); sch.add(req("b", 5, max_new=6, ignore_eos=True))
     first = sch.schedule()                                   # both prompts whole, both sample
+    # the first half of the accounting: the prompts count as run, place-holders stand for the tokens
+    assert [(r.computed, r.pending, r.tokens[-1]) for r in sch.running] == [(20, 1, P), (5, 1, P)]
     ahead = sch.schedule_ahead()                             # their first decode step, token unknown
-    assert [(it.request.id, it.start, it.tokens, it.sample) for it in ahead] == \
-        [("a", 20, [Scheduler.PENDING], True), ("b", 5, [Scheduler.PENDING], True)]
+    assert plan_of(ahead) == [("a", 20, [P], True), ("b", 5, [P], True)]
     assert cache.pages_of("a") == [0, 1] and len(cache.pages_of("b")) == 1
     assert sch.schedule_ahead() is None                      # never two steps ahead
+    with pytest.raises(RuntimeError):
+        sch.schedule()                                       # plain planning wants every step accounted
     assert sch.update({"a": 7, "b": 8}) == []                # accounts the first step
-    assert [r.tokens[-1] for r in sch.running] == [7, 8] and [r.computed for r in sch.running] == [20, 5]
+    assert [r.tokens[-2:] for r in sch.running] == [[7, P], [8, P]]
+    assert [r.computed for r in sch.running] == [21, 6]
     again = sch.schedule_ahead()                             # the step after the one planned ahead
     assert [(it.request.id, it.start) for it in again] == [("a", 21), ("b", 6)]
     sch.update({"a": 9, "b": 9})
-    assert [r.computed for r in sch.running] == [21, 6] and [r.generated for r in sch.running] == [[7, 9], [8, 9]]
+    assert [r.generated for r in sch.running] == [[7, 9], [8, 9]]
     sch.update({"a": 1, "b": 1})
-    assert [r.computed for r in sch.running] == [22, 7]
+    assert [(r.computed, r.pending, r.tokens[-3:]) for r in sch.running] == [(22, 0, [7, 9, 1]), (7, 0, [8, 9, 1])]
     assert first and sch.stats["ahead_steps"] == 2
     cache.check_invariants()
 
 
-def test_no_planning_ahead_when_someone_waits_finishes_or_is_still_in_its_prompt():
-    sch, _ = make(slots=1)
-    sch.add(req("a", 8, max_new=3, ignore_eos=True)); sch.add(req("b", 8, ignore_eos=True))
-    sch.schedule()
-    assert sch.schedule_ahead() is None                      # b waits for a slot
-    sch, _ = make(budget=16)
+def test_prompt_portions_and_admissions_are_planned_ahead_too():
+    sch, cache = make(budget=16, slots=2)
     sch.add(req("a", 40, max_new=3, ignore_eos=True))
-    sch.schedule()
-    assert sch.schedule_ahead() is None                      # a portion that does not sample
+    assert plan_of(sch.schedule()) == [("a", 0, 16, False)]
+    assert plan_of(sch.schedule_ahead()) == [("a", 16, 16, False)]       # nothing of it is unknown
     sch.update({})
+    sch.add(req("b", 30, max_new=3, ignore_eos=True))
+    assert plan_of(sch.schedule_ahead()) == [("a", 32, 8, True), ("b", 0, 8, False)]   # b is admitted
+    sch.update({})
+    assert plan_of(sch.schedule_ahead()) == [("a", 40, [P], True), ("b", 8, 15, False)]
+    sch.update({"a": 7})
+    sch.add(req("c", 4))
+    ahead = sch.schedule_ahead()                             # c waits for a slot; the others go on
+    assert plan_of(ahead) == [("a", 41, [P], True), ("b", 23, 7, True)]
+    sch.update({"a": 8})
+    assert plan_of(sch.schedule_ahead()) == [("b", 30, [P], True)]       # a's third token is in flight: its last
+    assert [r.id for r in sch.update({"a": 9, "b": 5})] == ["a"]
+    assert plan_of(sch.schedule_ahead()) == [("b", 31, [P], True), ("c", 0, 4, True)]
+    assert sch.stats["ahead_steps"] == 6 and sch.stats["preemptions"] == 0
+    cache.check_invariants()
+
+
+def test_what_is_not_planned_ahead():
     sch, _ = make()
     sch.add(req("a", 8, max_new=2, ignore_eos=True))
     sch.schedule()
     assert sch.schedule_ahead() is not None                  # one more token to come after this one
     sch.update({"a": 5})
     assert sch.schedule_ahead() is None                      # the token in flight is its last
+    assert [r.id for r in sch.update({"a": 5})] == ["a"] and not sch.has_work()
+    sch, _ = make(max_len=10)
+    sch.add(req("a", 8, max_new=8, ignore_eos=True))
+    sch.schedule()
+    assert sch.schedule_ahead() is not None                  # position 8, the sequence grows to 10
     sch.update({"a": 5})
-    assert not sch.has_work()
+    assert sch.schedule_ahead() is None                      # the model's length ends it
+    assert [r.id for r in sch.update({"a": 5})] == ["a"] and sch.finished[0].generated == [5, 5]
     sch, _ = make()
     sch.add(Request("p", [1, 2, 3], 8, SamplingParams(0.7, repetition_penalty=1.3), True))
+    sch.add(req("a", 8))
     sch.schedule()
     assert sch.schedule_ahead() is None                      # the penalty needs the token on the host
 
 
-def test_no_planning_ahead_without_a_free_page():
-    sch, cache = make(pages=2, page=16)
-    sch.add(req("a", 31, max_new=8, ignore_eos=True))
+def test_a_step_planned_ahead_waits_for_pages_and_never_preempts():
+    sch, cache = make(pages=3, page=16)
+    sch.add(req("a", 31, max_new=8, ignore_eos=True)); sch.add(req("b", 10, max_new=8, ignore_eos=True))
     sch.schedule()
-    assert sch.schedule_ahead() is not None                  # position 31 still fits page 1
-    sch.update({"a": 5})
-    assert sch.schedule_ahead() is None                      # position 32 needs a third page
+    assert plan_of(sch.schedule_ahead()) == [("a", 31, [P], True), ("b", 10, [P], True)]
+    sch.update({"a": 5, "b": 5})
+    assert plan_of(sch.schedule_ahead()) == [("b", 11, [P], True)]       # a's position 32 finds no page: a waits
+    sch.update({"a": 5, "b": 5})
+    assert sch.stats["preemptions"] == 0
+    sch.update({"b": 5})
+    items = sch.schedule()                                   # the plain plan decides: the youngest gives way
+    assert plan_of(items) == [("a", 32, [5], True)] and sch.stats["preemptions"] == 1
     cache.check_invariants()
 
 
@@ -244,11 +281,13 @@ def test_a_request_that_stops_on_the_token_in_flight_is_skipped_in_the_step_plan
     assert [r.id for r in done] == ["a"]
     with pytest.raises(KeyError):
         cache.pages_of("a")                                  # everything it held is given back
-    assert sch.schedule_ahead() is None                      # the running set changed
+    a = next(r for r in sch.take_finished() if r.id == "a")
+    assert a.generated == [EOS] and a.tokens == list(range(10, 18)) + [EOS] and a.pending == 0
+    assert plan_of(sch.schedule_ahead()) == [("b", 9, [P], True)]
     done = sch.update({"a": 3, "b": 9})                      # a's token from the step ahead is dropped
     assert done == [] and sch.running[0].generated == [7, 9]
-    a = next(r for r in sch.take_finished() if r.id == "a")
-    assert a.generated == [EOS]
+    sch.update({"b": 4})
+    assert sch.running[0].tokens[-3:] == [7, 9, 4] and sch.running[0].pending == 0
     cache.check_invariants()
 
 
