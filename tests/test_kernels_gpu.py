@@ -443,6 +443,53 @@ def test_attention_window_edge(ops, dtype, window, offset, hd, q_len):
     assert worst <= _tol(dtype, 3.0)
 
 
+@pytest.mark.parametrize("q_lens, kv_lens", [([1, 200, 1, 130], [300, 330, 700, 130]), ([1, 100], [260, 100])])
+def test_kernels_address_a_pool_of_more_than_two_to_the_31_elements(ops, q_lens, kv_lens):
+    """300,000 pages of 8 x 16 x 64 are 2.46e9 elements per pool: offsets into it need 64 bits.  The
+    requests hold the topmost pages; decode kernel, both prompt kernels and the cache write."""
+    from llm_singularity_b200.cache.manager import KVCacheView
+    if torch.cuda.mem_get_info()[0] < 16 << 30:
+        pytest.skip("needs 10 GB of device memory")
+    nh, nkv, hd, page, n_pages, dtype = 32, 8, 64, 16, 300_000, torch.bfloat16
+    R, per = len(q_lens), -(-max(kv_lens) // page)
+    k = torch.zeros(n_pages, nkv, page, hd, dtype=dtype, device="cuda")
+    v = torch.zeros_like(k)
+    assert k.numel() > 2 ** 31
+    top = n_pages - 1 - torch.randperm(R * per, generator=torch.Generator().manual_seed(0))
+    cache = KVCacheView(k, v, top.view(R, per).to(torch.int32).cuda(), page, None, 0)
+    ctx = _make_ctx(q_lens, kv_lens)
+    T = sum(q_lens)
+    qkv = _rand(T, (nh + 2 * nkv) * hd, dtype=dtype, seed=1)
+    Ks = [_rand(n, nkv, hd, dtype=dtype, seed=10 + r).cpu() for r, n in enumerate(kv_lens)]
+    Vs = [_rand(n, nkv, hd, dtype=dtype, seed=20 + r).cpu() for r, n in enumerate(kv_lens)]
+    for r in range(R):
+        _fill(cache, r, Ks[r], Vs[r])
+    out = torch.empty(T, nh * hd, dtype=dtype, device="cuda")
+    scale = 1.0 / math.sqrt(hd)
+    ops.paged_attention(qkv, nh, nkv, hd, ctx, cache, scale, 0, out)
+    ops.check_status()
+    t = 0
+    for r in range(R):
+        q = qkv[t:t + q_lens[r], :nh * hd].double().cpu().view(q_lens[r], nh, hd)
+        want = _ref_attention(q, Ks[r].double(), Vs[r].double(), scale, 0)
+        got = out[t:t + q_lens[r]].double().cpu().view(q_lens[r], nh, hd)
+        assert (got - want).abs().max().item() < _tol(dtype, 2.0)
+        t += q_lens[r]
+    fresh = _rand(T, (nh + 2 * nkv) * hd, dtype=dtype, seed=3)
+    before = fresh.clone()
+    ops.rope_kv_store(fresh, nh, nkv, hd, ctx, cache, torch.rand(hd // 2, device="cuda"), hd)
+    ops.check_status()
+    t = 0
+    for r in range(R):
+        n, L = q_lens[r], kv_lens[r]
+        kd, vd = _dense(cache, r, L)
+        assert torch.equal(kd[L - n:], fresh[t:t + n, nh * hd:(nh + nkv) * hd].view(n, nkv, hd))
+        assert torch.equal(vd[L - n:], before[t:t + n, (nh + nkv) * hd:].view(n, nkv, hd))
+        t += n
+    del k, v, cache
+    torch.cuda.empty_cache()
+
+
 def test_attention_refuses_sizes_it_does_not_take(ops):
     ctx = _make_ctx([1], [1])
     for hd in (24, 272):
