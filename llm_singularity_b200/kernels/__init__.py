@@ -319,6 +319,20 @@ def tensor_core_attention_ok(dtype, hd: int, nh: int, nkv: int) -> bool:
     return dtype == torch.bfloat16 and hd in _TC_HEAD_DIMS and nh // nkv <= 16
 
 
+OVERLAP_ATTENTION = True        # decode kernel beside the prompt kernels in steps that hold both
+_side: Dict[torch.device, tuple] = {}
+
+
+def _fork_join(ctx, device):
+    """(the step's stream, a second stream, two events), looked up once per step."""
+    got = getattr(ctx, "_fork_join", None)
+    if got is None:
+        if device not in _side:
+            _side[device] = (torch.cuda.Stream(device), torch.cuda.Event(), torch.cuda.Event())
+        got = ctx._fork_join = (torch.cuda.current_stream(device),) + _side[device]
+    return got
+
+
 def _batch_shape(ctx):
     """(single-token requests, first and one past the last request with more tokens) of a step;
     worked out once per step and kept on the context."""
@@ -346,6 +360,20 @@ def rope_store_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cac
         paged_attention(qkv, nh, nkv, hd, ctx, cache, scale, window, out)
         return
     if n_decode < ctx.n_requests:
+        if OVERLAP_ATTENTION and not getattr(ctx, "fixed_launch", False):
+            # Single tokens and prompt portions are different requests with different pages: the
+            # decode kernel (memory-bound) runs on a second stream beside the rotation and the
+            # attention of the portions (compute-bound), and the step's stream waits for both.
+            main, side, fork, join = _fork_join(ctx, qkv.device)
+            fork.record(main)                                 # qkv is whole here
+            side.wait_event(fork)
+            paged_attention(qkv, nh, nkv, hd, ctx, cache, scale, window, out,
+                            decode_rope=(inv_freq, store), only="single", stream=side.cuda_stream)
+            join.record(side)
+            rope_kv_store(qkv, nh, nkv, hd, ctx, cache, inv_freq, rotary_dim, store, skip_single=True)
+            paged_attention(qkv, nh, nkv, hd, ctx, cache, scale, window, out, only="portions")
+            main.wait_event(join)
+            return
         rope_kv_store(qkv, nh, nkv, hd, ctx, cache, inv_freq, rotary_dim, store, skip_single=True)
     else:
         _req(inv_freq, "inv_freq", torch.float32, 1)
@@ -355,13 +383,16 @@ def rope_store_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cac
 
 
 def paged_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache, scale: float,
-                    window: int, out: torch.Tensor, decode_rope=None) -> None:
+                    window: int, out: torch.Tensor, decode_rope=None, only: Optional[str] = None,
+                    stream: Optional[int] = None) -> None:
     """Causal attention of this step's query rows over their requests' cached keys and values.
 
     bfloat16 with head size 64 or 128 runs on the tensor cores: single decode tokens in the
     split-KV kernel, prompt portions in the tiled kernel.  Everything else (32-bit, other head
     sizes) runs the generic kernel.  ``decode_rope = (inv_freq, store)`` says that single tokens
-    come unrotated and not yet in the cache (see ``rope_store_attention``)."""
+    come unrotated and not yet in the cache (see ``rope_store_attention``).  ``only``: "single"
+    or "portions" launches just that kernel; ``stream``: a raw stream to launch on instead of the
+    current one."""
     _req(qkv, "qkv", dim=2)
     _req(out, "out", qkv.dtype, 2)
     T = qkv.shape[0]
@@ -388,7 +419,8 @@ def paged_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache, s
         return
     R = ctx.n_requests
     n_decode, first, last = _batch_shape(ctx)
-    if n_decode:
+    on = _stream(out) if stream is None else ctypes.c_void_p(stream)
+    if n_decode and only != "portions":
         splits = decode_splits(n_decode, nkv)
         if not getattr(ctx, "fixed_launch", False):
             splits = min(splits, -(-ctx.max_kv_len // 128))
@@ -408,11 +440,11 @@ def paged_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache, s
                 _scratch[key] = scratch
         if decode_rope is None:
             _call("attention_tc", "lsb_decode_attention", *common, _p(scratch), _i(R), *tail,
-                  _i(splits), _stream(out))
+                  _i(splits), on)
         else:
             _call("attention_tc", "lsb_decode_attention_rope", *common, _p(scratch), _i(R), *tail,
-                  _i(splits), _p(decode_rope[0]), _i(1 if decode_rope[1] else 0), _stream(out))
-    if n_decode < R:
+                  _i(splits), _p(decode_rope[0]), _i(1 if decode_rope[1] else 0), on)
+    if n_decode < R and only != "single":
         # prompt portions: tcgen05 kernel for long ones (128-row tiles), mma.sync kernel otherwise
         # The grid has a slab of blocks per request, and blocks that find a single token leave at
         # once, but thousands of them still cost tens of microseconds: the kernels get only the
@@ -428,11 +460,11 @@ def paged_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache, s
             _call("attention_tc5", "lsb_prefill_attention_tc5", _p(qkv), _i(qkv.shape[1]), _i(T),
                   _p(cache.k_pages), _p(cache.v_pages), *per_request, _p(cache.block_table),
                   _i(cache.block_table.shape[1]), _p(out), _i(last - first), _i(ctx.max_q_len), *tail,
-                  skip, _stream(out))
+                  skip, on)
         else:
             _call("attention_tc", "lsb_prefill_attention", _p(qkv), _i(qkv.shape[1]), _p(cache.k_pages),
                   _p(cache.v_pages), *per_request, _p(cache.block_table), _i(cache.block_table.shape[1]),
-                  _p(out), _i(last - first), _i(ctx.max_q_len), *tail, skip, _stream(out))
+                  _p(out), _i(last - first), _i(ctx.max_q_len), *tail, skip, on)
 
 
 def sample(logits: torch.Tensor, params: torch.Tensor, top_k: torch.Tensor,

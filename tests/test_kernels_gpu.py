@@ -307,6 +307,39 @@ def test_decode_kernel_rotates_and_stores_like_the_separate_kernel(ops, nh, nkv,
         assert (out_a - out_b).abs().max() <= _tol(dtype, 3.0)
 
 
+@pytest.mark.parametrize("hd, q_lens, kv_lens", [(64, [1, 1, 150, 1, 40], [300, 17, 200, 4097, 40]),
+                                                 (128, [1, 9, 1], [900, 30, 64])])
+def test_decode_kernel_beside_the_prompt_kernels_gives_the_same_bits(ops, hd, q_lens, kv_lens):
+    """A step with single tokens and prompt portions: the decode kernel on a second stream beside
+    the rotation and the portions' attention, against all of them in a row."""
+    from llm_singularity_b200 import kernels
+    from llm_singularity_b200.parts.rotary import rotary_inv_freq
+    nh, nkv, page, dtype = 8, 2, 16, torch.bfloat16
+    R, T = len(q_lens), sum(q_lens)
+    inv = rotary_inv_freq(hd, 500000.0).float().cuda()
+    qkv0 = _rand(T, (nh + 2 * nkv) * hd, dtype=dtype, seed=3)
+    results = []
+    try:
+        for beside in (False, True, True):
+            kernels.OVERLAP_ATTENTION = beside
+            ctx = _make_ctx(q_lens, kv_lens)
+            cache = _make_cache(R, max(kv_lens), nkv, hd, page, dtype, seed=1)
+            for r in range(R):
+                _fill(cache, r, _rand(kv_lens[r], nkv, hd, dtype=dtype, seed=10 + r).cpu(),
+                      _rand(kv_lens[r], nkv, hd, dtype=dtype, seed=20 + r).cpu())
+            qkv = qkv0.clone()
+            out = torch.empty(T, nh * hd, dtype=dtype, device="cuda")
+            ops.rope_store_attention(qkv, nh, nkv, hd, ctx, cache, inv, hd, True, 1.0 / math.sqrt(hd), 0, out)
+            follow = out.float().sum()                   # the step's stream goes on after both
+            ops.check_status()
+            results.append((out.cpu(), cache.k_pages.cpu(), cache.v_pages.cpu(), follow.item()))
+    finally:
+        kernels.OVERLAP_ATTENTION = True
+    for other in results[1:]:
+        assert all(torch.equal(a, b) for a, b in zip(results[0][:3], other[:3]))
+        assert results[0][3] == other[3]
+
+
 def _ref_attention(q, K, V, scale, window):
     """q [n, nh, hd] are the last n positions of a sequence whose keys/values are K, V [len, nkv, hd]."""
     n, nh, hd = q.shape
