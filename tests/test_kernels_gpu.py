@@ -48,6 +48,31 @@ def test_scatter_i32(ops):
     assert torch.equal(dst.cpu().view(-1), want)
 
 
+def test_move_i32(ops):
+    """dst[dst_idx[i]] = src[src_idx[i]]: sampled tokens become input tokens of the next step."""
+    n = 700
+    g = torch.Generator().manual_seed(0)
+    src = torch.randint(0, 1 << 20, (900,), generator=g, dtype=torch.int32)
+    dst = torch.full((2048,), -1, dtype=torch.int32)
+    dst_idx = torch.randperm(2048, generator=g)[:n].to(torch.int32)
+    src_idx = torch.randint(0, 900, (n,), generator=g, dtype=torch.int32)
+    want = dst.clone()
+    want[dst_idx.long()] = src[src_idx.long()]
+    got = dst.cuda()
+    ops.move_i32(got, dst_idx.cuda(), src.cuda(), src_idx.cuda())
+    ops.check_status()
+    assert torch.equal(got.cpu(), want)
+    # an index outside either array is reported and nothing is written for it
+    got = dst.cuda()
+    ops.move_i32(got, torch.tensor([3, 2048], dtype=torch.int32, device="cuda"), src.cuda(),
+                 torch.tensor([900, 1], dtype=torch.int32, device="cuda"))
+    with pytest.raises(ops.KernelError, match="row index"):
+        ops.check_status()
+    assert torch.equal(got.cpu(), dst)
+    with pytest.raises(ops.KernelError, match="differ in length"):
+        ops.move_i32(got, dst_idx[:3].cuda(), src.cuda(), src_idx[:4].cuda())
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_embedding(ops, dtype):
     table = _rand(1000, 200, dtype=dtype)
