@@ -20,11 +20,14 @@ from __future__ import annotations
 from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
+import ctypes
+
 import numpy as np
 import torch
 
 from ..parts.base import PagedKVSpec, StateSpec
-from .pages import PageError, PagePool
+from . import native
+from .pages import PageError, PagePool, _Handle
 
 NO_PAGE = -1
 
@@ -49,24 +52,16 @@ class StateView:
 
 
 class _Group:
-    def __init__(self, window: Optional[int], num_pages: int, slots: int, max_pages: int):
+    """One group's Python face: its pool and its host table are views into the memory layer."""
+
+    def __init__(self, handle: _Handle, index: int, window: Optional[int], num_pages: int,
+                 slots: int, max_pages: int):
         self.window = window
-        self.pool = PagePool(num_pages)
+        self.pool = PagePool(num_pages, _handle=handle, _group=index)
         self.cache_ids: List[int] = []
-        self.table = np.full((slots, max_pages), NO_PAGE, dtype=np.int32)   # host mirror
+        ptr = handle.lib.lsbm_table(handle.ptr, index)
+        self.table = np.ctypeslib.as_array(ptr, shape=(slots, max_pages))   # host mirror (no copy)
         self.dev_table: Optional[torch.Tensor] = None
-        self.updates: List[Tuple[int, int]] = []       # (flat index, value) not yet on device
-        # per request: pages [0, first_live) have been released behind the window
-        self.first_live: Dict[Hashable, int] = {}
-
-
-class _Request:
-    __slots__ = ("slot", "length", "num_pages")
-
-    def __init__(self, slot: int):
-        self.slot = slot
-        self.length = 0
-        self.num_pages = 0     # logical pages covered so far (same count in every group)
 
 
 class CacheManager:
@@ -85,21 +80,31 @@ class CacheManager:
         self._specs = list(cache_specs)
         self._kv: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
         self._state: Dict[int, torch.Tensor] = {}
-        self._requests: Dict[Hashable, _Request] = {}
-        self._free_slots: List[int] = list(range(max_requests - 1, -1, -1))
+        self._slots: Dict[Hashable, int] = {}          # request id -> slot
 
-        by_window: Dict[Optional[int], int] = {}
+        windows: List[Optional[int]] = []              # one entry per group, in order of first use
+        members: List[List[int]] = []
         for cid, cs in enumerate(self._specs):
             if isinstance(cs, PagedKVSpec):
-                if cs.window not in by_window:
-                    n = num_pages[cs.window] if isinstance(num_pages, dict) else num_pages
-                    by_window[cs.window] = len(self.groups)
-                    self.groups.append(_Group(cs.window, n, max_requests, max_pages_per_request))
-                g = by_window[cs.window]
-                self.groups[g].cache_ids.append(cid)
+                if cs.window not in windows:
+                    windows.append(cs.window)
+                    members.append([])
+                g = windows.index(cs.window)
+                members[g].append(cid)
                 self._group_of[cid] = g
             elif not (cs is None or isinstance(cs, StateSpec)):
                 raise TypeError(f"cache {cid}: unknown cache spec {cs!r}")
+        sizes = [num_pages[w] if isinstance(num_pages, dict) else num_pages for w in windows]
+        if any(n <= 0 for n in sizes):
+            raise ValueError(f"a page pool needs at least one page, got {sizes}")
+        self._h = _Handle(page_size, max_requests, max_pages_per_request,
+                          [-1 if w is None else w for w in windows], sizes)
+        self._lib, self._ptr = self._h.lib, self._h.ptr
+        for g, (w, n) in enumerate(zip(windows, sizes)):
+            grp = _Group(self._h, g, w, n, max_requests, max_pages_per_request)
+            grp.cache_ids = members[g]
+            self.groups.append(grp)
+        self._page_buf = (ctypes.c_int * max_pages_per_request)()
         if rt is not None:
             self._allocate_device(rt)
 
@@ -124,119 +129,90 @@ class CacheManager:
                    for c in self.groups[group].cache_ids)
 
     # ---------------------------------------------------------------- requests
+    def _fail(self, request=None) -> PageError:
+        msg = self._lib.lsbm_last_error(self._ptr).decode()
+        return PageError(msg if request is None else f"request {request!r}: {msg}")
+
     def has(self, request: Hashable) -> bool:
-        return request in self._requests
+        return request in self._slots
 
     def open(self, request: Hashable) -> Optional[int]:
         """Give ``request`` a slot (block-table row and state row); None if all are taken."""
-        if request in self._requests:
+        if request in self._slots:
             raise KeyError(f"request {request!r} is already open")
-        if not self._free_slots:
+        slot = self._lib.lsbm_open(self._ptr)
+        if slot < 0:
             return None
-        slot = self._free_slots.pop()
-        self._requests[request] = _Request(slot)
-        for g in self.groups:
-            g.first_live[request] = 0
+        self._slots[request] = slot
         for st in self._state.values():
             st[slot].zero_()
         return slot
 
     def slot(self, request: Hashable) -> int:
-        return self._requests[request].slot
+        return self._slots[request]
 
     def length(self, request: Hashable) -> int:
-        return self._requests[request].length
+        return self._lib.lsbm_length(self._ptr, self._slots[request])
 
     def pages_for(self, length: int) -> int:
         return -(-length // self.page_size)
 
     def pages_needed(self, request: Hashable, new_length: int) -> int:
         """Pages each group must still hand out to cover ``new_length`` tokens."""
-        r = self._requests[request]
-        return max(0, self.pages_for(new_length) - r.num_pages)
+        return max(0, self.pages_for(new_length) - self._lib.lsbm_num_pages(self._ptr, self._slots[request]))
 
     def free_pages(self) -> int:
         """Pages free in the tightest group."""
-        return min((g.pool.num_free for g in self.groups), default=1 << 30)
+        return self._lib.lsbm_free_pages(self._ptr)
 
     def reserve(self, request: Hashable, new_length: int) -> bool:
         """Cover positions ``[0, new_length)`` with pages in every group, or change nothing."""
-        r = self._requests[request]
-        want = self.pages_for(new_length)
-        if want > self.max_pages:
-            raise PageError(f"request {request!r}: {new_length} tokens need {want} pages, "
-                            f"a block table holds {self.max_pages}")
-        need = want - r.num_pages
-        if need <= 0:
-            return True
-        if any(g.pool.num_free < need for g in self.groups):
-            return False
-        for g in self.groups:
-            for i in range(r.num_pages, want):
-                page = g.pool.allocate()
-                self._set(g, r.slot, i, page)
-        r.num_pages = want
-        return True
+        rc = self._lib.lsbm_reserve(self._ptr, self._slots[request], new_length)
+        if rc == native.ERR:
+            raise self._fail(request)
+        return rc == 1
 
     def commit(self, request: Hashable, new_length: int) -> None:
         """The request now holds ``new_length`` tokens; give back pages a window has passed."""
-        r = self._requests[request]
-        if self.pages_for(new_length) > r.num_pages:
-            raise PageError(f"request {request!r}: length {new_length} is not covered by its pages")
-        r.length = new_length
-        for g in self.groups:
-            if g.window is None:
-                continue
-            # the next query sits at position >= new_length and sees keys > pos - window
-            first_needed = max(0, new_length - g.window + 1)
-            dead = min(first_needed // self.page_size, r.num_pages)
-            for i in range(g.first_live[request], dead):
-                g.pool.release(int(g.table[r.slot, i]))
-                self._set(g, r.slot, i, NO_PAGE)
-            g.first_live[request] = max(g.first_live[request], dead)
+        if self._lib.lsbm_commit(self._ptr, self._slots[request], new_length) == native.ERR:
+            raise self._fail(request)
 
     def close(self, request: Hashable) -> None:
         """The request is over: every page it holds and its slot go back."""
-        r = self._requests.pop(request)
-        for g in self.groups:
-            for i in range(g.first_live.pop(request), r.num_pages):
-                g.pool.release(int(g.table[r.slot, i]))
-                self._set(g, r.slot, i, NO_PAGE)
-        self._free_slots.append(r.slot)
+        slot = self._slots.pop(request)
+        if self._lib.lsbm_close(self._ptr, slot) == native.ERR:
+            raise self._fail(request)
 
     def adopt(self, request: Hashable, pages_per_group: Sequence[Sequence[int]], length: int) -> None:
         """Start a fresh request on pages that already hold its first ``length`` tokens
         (shared through the prefix cache); takes one reference on each."""
-        r = self._requests[request]
-        if r.num_pages or length % self.page_size:
-            raise PageError("adopt needs a fresh request and a whole number of pages")
         n = length // self.page_size
-        for g, pages in zip(self.groups, pages_per_group):
-            if len(pages) != n:
-                raise PageError("adopt: page list does not match the length")
-            for i, p in enumerate(pages):
-                g.pool.retain(p)
-                self._set(g, r.slot, i, p)
-        r.num_pages = n
-        r.length = length
+        if len(pages_per_group) != len(self.groups) or any(len(p) != n for p in pages_per_group):
+            raise PageError("adopt: page list does not match the length")
+        flat = [p for pages in pages_per_group for p in pages]
+        if self._lib.lsbm_adopt(self._ptr, self._slots[request], native.ints(flat), n, length) == native.ERR:
+            raise self._fail()
 
     def pages_of(self, request: Hashable, group: int = 0) -> List[int]:
-        r = self._requests[request]
-        return [int(p) for p in self.groups[group].table[r.slot, :r.num_pages]]
+        n = self._lib.lsbm_pages_of(self._ptr, self._slots[request], group, self._page_buf, self.max_pages)
+        if n == native.ERR:
+            raise self._fail(request)
+        return self._page_buf[:n]
 
     def live_requests(self) -> List[Hashable]:
-        return list(self._requests)
+        return list(self._slots)
 
     # ------------------------------------------------------------------ tables
-    def _set(self, g: _Group, slot: int, index: int, page: int) -> None:
-        g.table[slot, index] = page
-        g.updates.append((slot * self.max_pages + index, page))
-
     def take_updates(self, group: int) -> List[Tuple[int, int]]:
         """Block-table cells changed since the last call, as (flat index, value)."""
-        g = self.groups[group]
-        ups, g.updates = g.updates, []
-        return ups
+        n = self._lib.lsbm_num_updates(self._ptr, group)
+        if n == 0:
+            return []
+        buf = (ctypes.c_int * (2 * n))()
+        if self._lib.lsbm_take_updates(self._ptr, group, buf, n) == native.ERR:
+            raise self._fail()
+        flat = buf[:]
+        return list(zip(flat[0::2], flat[1::2]))
 
     def group_of(self, cache_id: int) -> int:
         return self._group_of[cache_id]
@@ -254,37 +230,10 @@ class CacheManager:
 
     # -------------------------------------------------------------- invariants
     def check_invariants(self) -> None:
-        """No page lost, none held twice by different owners without a reference, none freed twice."""
-        for g in self.groups:
-            g.pool.check_invariants()
-            held: Dict[int, int] = {}
-            for req, r in self._requests.items():
-                for i in range(r.num_pages):
-                    p = int(g.table[r.slot, i])
-                    if i < g.first_live[req]:
-                        if p != NO_PAGE:
-                            raise PageError(f"released cell still names page {p}")
-                        continue
-                    if p == NO_PAGE:
-                        raise PageError(f"request {req!r} lacks page {i}")
-                    held[p] = held.get(p, 0) + 1
-                if (g.table[r.slot, r.num_pages:] != NO_PAGE).any():
-                    raise PageError(f"request {req!r}: cells past its pages are set")
-            for p, n in held.items():
-                if g.pool.refcount(p) < n:
-                    raise PageError(f"page {p} held {n} times with refcount {g.pool.refcount(p)}")
-            self._extra_refs_ok(g, held)
-        slots = [r.slot for r in self._requests.values()]
-        if len(set(slots)) != len(slots) or set(slots) & set(self._free_slots):
+        """No page lost, none held without a reference, none freed twice, no slot lost or held
+        twice; references beyond those of live requests are the prefix tree's, node by node."""
+        if self._lib.lsbm_check(self._ptr) == native.ERR:
+            raise self._fail()
+        slots = list(self._slots.values())
+        if len(set(slots)) != len(slots):
             raise PageError("a slot is held twice")
-        if len(slots) + len(self._free_slots) != self.max_requests:
-            raise PageError("a slot was lost")
-
-    def _extra_refs_ok(self, g: _Group, held: Dict[int, int]) -> None:
-        # references beyond those of live requests belong to the prefix cache, which
-        # registers them here so that nothing is lost
-        extra = getattr(self, "external_refs", None)
-        for p in range(g.pool.num_pages):
-            n = held.get(p, 0) + (extra(self.groups.index(g), p) if extra else 0)
-            if g.pool.refcount(p) != n:
-                raise PageError(f"page {p}: refcount {g.pool.refcount(p)} but {n} owners known")

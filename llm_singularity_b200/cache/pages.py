@@ -6,71 +6,81 @@ layer of its group, as in the reference (models/llama/llama_model.h:56-69), whos
 notices a page freed twice.  This pool counts references (a page shared through
 the prefix cache is held by several owners) and raises on a double free, a free
 of a page never handed out, or a retain of a free page.
+
+The counts live in the host memory layer (``csrc/host_memory.cpp``); this class is
+a view of one group's pool there, or of a pool of its own when made from a size.
 """
 from __future__ import annotations
 
-from typing import List, Optional
+from typing import Optional
+
+from . import native
 
 
 class PageError(RuntimeError):
     pass
 
 
+class _Handle:
+    """Owner of one native ``Memory`` object."""
+
+    def __init__(self, page_size, max_requests, max_pages, windows, num_pages):
+        self.lib = native.lib()
+        self.ptr = self.lib.lsbm_create(page_size, max_requests, max_pages, len(windows),
+                                        native.ints(windows), native.ints(num_pages))
+        if not self.ptr:
+            raise ValueError("the memory layer needs positive sizes "
+                             f"(page_size {page_size}, slots {max_requests}, table {max_pages}, "
+                             f"pages {list(num_pages)})")
+
+    def __del__(self):
+        if getattr(self, "ptr", None):
+            self.lib.lsbm_destroy(self.ptr)
+            self.ptr = None
+
+    def error(self) -> PageError:
+        return PageError(self.lib.lsbm_last_error(self.ptr).decode())
+
+
 class PagePool:
-    def __init__(self, num_pages: int):
-        if num_pages <= 0:
-            raise ValueError(f"a page pool needs at least one page, got {num_pages}")
+    def __init__(self, num_pages: int, _handle: Optional[_Handle] = None, _group: int = 0):
+        if _handle is None:
+            if num_pages <= 0:
+                raise ValueError(f"a page pool needs at least one page, got {num_pages}")
+            _handle = _Handle(1, 1, 1, [-1], [num_pages])
+        self._h, self._g = _handle, _group
         self.num_pages = num_pages
-        # stack: the page freed last is handed out first; fresh pool pops 0, 1, 2, ...
-        self._free: List[int] = list(range(num_pages - 1, -1, -1))
-        self._refs: List[int] = [0] * num_pages
 
     @property
     def num_free(self) -> int:
-        return len(self._free)
+        return self._h.lib.lsbm_pool_num_free(self._h.ptr, self._g)
 
     @property
     def num_used(self) -> int:
-        return self.num_pages - len(self._free)
+        return self.num_pages - self.num_free
 
     def allocate(self) -> Optional[int]:
         """A free page with one reference, or ``None`` if the pool is empty."""
-        if not self._free:
-            return None
-        p = self._free.pop()
-        assert self._refs[p] == 0
-        self._refs[p] = 1
-        return p
+        p = self._h.lib.lsbm_pool_allocate(self._h.ptr, self._g)
+        return None if p < 0 else p
 
     def retain(self, page: int) -> None:
-        self._check(page)
-        if self._refs[page] == 0:
-            raise PageError(f"page {page} is free and cannot be retained")
-        self._refs[page] += 1
+        if self._h.lib.lsbm_pool_retain(self._h.ptr, self._g, page) == native.ERR:
+            raise self._h.error()
 
     def release(self, page: int) -> bool:
         """Drop one reference; returns True if the page went back to the free list."""
-        self._check(page)
-        if self._refs[page] == 0:
-            raise PageError(f"page {page} freed twice")
-        self._refs[page] -= 1
-        if self._refs[page] == 0:
-            self._free.append(page)
-            return True
-        return False
+        rc = self._h.lib.lsbm_pool_release(self._h.ptr, self._g, page)
+        if rc == native.ERR:
+            raise self._h.error()
+        return rc == 1
 
     def refcount(self, page: int) -> int:
-        self._check(page)
-        return self._refs[page]
-
-    def _check(self, page: int) -> None:
-        if not 0 <= page < self.num_pages:
-            raise PageError(f"page id {page} outside pool of {self.num_pages}")
+        rc = self._h.lib.lsbm_pool_refcount(self._h.ptr, self._g, page)
+        if rc == native.ERR:
+            raise self._h.error()
+        return rc
 
     def check_invariants(self) -> None:
-        free = set(self._free)
-        if len(free) != len(self._free):
-            raise PageError("a page is on the free list twice")
-        for p in range(self.num_pages):
-            if (self._refs[p] == 0) != (p in free):
-                raise PageError(f"page {p}: refcount {self._refs[p]} disagrees with free list")
+        if self._h.lib.lsbm_pool_check(self._h.ptr, self._g) == native.ERR:
+            raise self._h.error()

@@ -18,172 +18,124 @@ cache its design notes intended.
 """
 from __future__ import annotations
 
-import itertools
-from typing import Dict, List, Optional, Sequence, Tuple
+import ctypes
+from typing import List, Sequence, Tuple
 
+from . import native
 from .manager import CacheManager
+from .pages import PageError
 
 
-class _Node:
-    __slots__ = ("key", "pages", "children", "parent", "users", "last_used")
+class NodeRef:
+    """A node of the tree (the tree itself lives in the host memory layer)."""
 
-    def __init__(self, key, pages, parent):
-        self.key: Tuple[int, ...] = key
-        self.pages: Tuple[int, ...] = pages          # one page id per cache group
-        self.children: Dict[Tuple[int, ...], "_Node"] = {}
-        self.parent: Optional["_Node"] = parent
-        self.users = 0                               # live requests whose prefix runs through here
-        self.last_used = 0
+    __slots__ = ("id", "_tree")
+
+    def __init__(self, node_id: int, tree: "RadixPrefixCache"):
+        self.id = node_id
+        self._tree = tree
+
+    @property
+    def users(self) -> int:
+        """Live requests whose prefix runs through this node."""
+        return self._tree._int(self._tree._lib.lsbp_node_users(self._tree._ptr, self.id))
+
+    @property
+    def pages(self) -> Tuple[int, ...]:
+        """One page id per cache group."""
+        t = self._tree
+        n = t._int(t._lib.lsbp_node_pages(t._ptr, self.id, t._group_buf))
+        return tuple(t._group_buf[:n])
+
+    def __eq__(self, other):
+        return isinstance(other, NodeRef) and other.id == self.id and other._tree is self._tree
+
+    def __hash__(self):
+        return hash(self.id)
+
+    def __repr__(self):
+        return f"NodeRef({self.id})"
 
 
 class RadixPrefixCache:
     def __init__(self, cache: CacheManager):
-        if any(g.window is not None for g in cache.groups):
-            raise ValueError("prefix sharing needs every layer to keep all its keys")
         self.cache = cache
         self.page_size = cache.page_size
-        self.root = _Node((), (), None)
-        self._clock = itertools.count(1)
-        self.num_nodes = 0
-        self.hits = 0                                # pages adopted instead of recomputed
-        self._idle = 0                               # nodes no live request uses (kept up to date)
-        cache.external_refs = self._owns
+        self._lib, self._ptr = cache._lib, cache._ptr
+        if self._lib.lsbp_enable(self._ptr) == native.ERR:
+            raise ValueError(self._lib.lsbm_last_error(self._ptr).decode())
+        self._group_buf = (ctypes.c_int * max(1, len(cache.groups)))()
+        self._node_buf = (ctypes.c_int * cache.max_pages)()
+
+    def _int(self, rc: int) -> int:
+        if rc == native.ERR:
+            raise PageError(self._lib.lsbm_last_error(self._ptr).decode())
+        return rc
+
+    def _ids(self, path: Sequence[NodeRef]):
+        return native.ints([n.id for n in path])
+
+    @property
+    def num_nodes(self) -> int:
+        return self._lib.lsbp_num_nodes(self._ptr)
+
+    @property
+    def hits(self) -> int:
+        """Pages adopted instead of recomputed."""
+        return self._lib.lsbp_hits(self._ptr)
 
     # ---------------------------------------------------------------- lookup
-    def match(self, tokens: Sequence[int]) -> List[_Node]:
+    def match(self, tokens: Sequence[int]) -> List[NodeRef]:
         """Nodes of the longest cached prefix of ``tokens`` (whole pages, never the last token)."""
-        ps = self.page_size
-        limit = (len(tokens) - 1) // ps
-        node, path = self.root, []
-        for i in range(limit):
-            child = node.children.get(tuple(tokens[i * ps:(i + 1) * ps]))
-            if child is None:
-                break
-            path.append(child)
-            node = child
-        return path
+        keep, ptr = native.token_array(tokens)
+        n = self._int(self._lib.lsbp_match(self._ptr, ptr, len(keep), self._node_buf, self.cache.max_pages))
+        return [NodeRef(i, self) for i in self._node_buf[:n]]
 
-    def adopt(self, request, path: List[_Node]) -> int:
+    def adopt(self, request, path: List[NodeRef]) -> int:
         """Start ``request`` (open, no pages yet) on the pages of ``path``; returns tokens covered."""
         if not path:
             return 0
-        now = next(self._clock)
-        for n in path:
-            if n.users == 0:
-                self._idle -= 1
-            n.users += 1
-            n.last_used = now
-        per_group = [[n.pages[g] for n in path] for g in range(len(self.cache.groups))]
-        self.cache.adopt(request, per_group, len(path) * self.page_size)
-        self.hits += len(path)
-        return len(path) * self.page_size
+        return self._int(self._lib.lsbp_adopt(self._ptr, self.cache.slot(request), self._ids(path), len(path)))
 
-    def release(self, path: List[_Node]) -> None:
+    def release(self, path: List[NodeRef]) -> None:
         """The request that adopted ``path`` is gone (its page references are dropped by close)."""
-        now = next(self._clock)
-        for n in path:
-            n.users -= 1
-            if n.users == 0:
-                self._idle += 1
-            n.last_used = now
+        self._int(self._lib.lsbp_release(self._ptr, self._ids(path), len(path)))
+
+    def idle_on(self, path: Sequence[NodeRef]) -> int:
+        """How many nodes of ``path`` no live request uses: they count among the evictable pages,
+        but not for a request that is about to adopt them."""
+        return self._int(self._lib.lsbp_idle_on(self._ptr, self._ids(path), len(path)))
 
     # ---------------------------------------------------------------- insert
     def insert(self, tokens: Sequence[int], request) -> int:
         """Keep the full pages of ``request`` (which holds ``tokens``) for later prompts.
         Call before the request is closed.  Returns the number of pages newly kept."""
-        ps = self.page_size
-        n_full = min(len(tokens), self.cache.length(request)) // ps
-        pages = [self.cache.pages_of(request, g) for g in range(len(self.cache.groups))]
-        node, kept, now = self.root, 0, next(self._clock)
-        for i in range(n_full):
-            key = tuple(tokens[i * ps:(i + 1) * ps])
-            child = node.children.get(key)
-            if child is None:
-                mine = tuple(pages[g][i] for g in range(len(pages)))
-                for g, p in enumerate(mine):
-                    self.cache.groups[g].pool.retain(p)
-                child = _Node(key, mine, node)
-                node.children[key] = child
-                self.num_nodes += 1
-                self._idle += 1
-                kept += 1
-            child.last_used = now
-            node = child
-        return kept
+        keep, ptr = native.token_array(tokens)
+        return self._int(self._lib.lsbp_insert(self._ptr, ptr, len(keep), self.cache.slot(request)))
 
-    def share(self, tokens: Sequence[int], request, held: Sequence[_Node]) -> List[_Node]:
+    def share(self, tokens: Sequence[int], request, held: Sequence[NodeRef]) -> List[NodeRef]:
         """Like :meth:`insert`, for a request that goes on running: the pages its ``tokens`` fill
         become visible to later prompts now (a prompt that arrives while this one still decodes
         need not recompute what they have in common).  ``held``: the nodes the request already counts
         as a user of (its adopted prefix).  Returns the further nodes whose pages are the
         request's own; it is a user of those too until :meth:`release`, so that they are not
         offered for eviction while evicting them would free nothing."""
-        ps = self.page_size
-        pages = [self.cache.pages_of(request, g) for g in range(len(self.cache.groups))]
-        # (the step that fills these pages may only be planned yet: whoever reads them is queued
-        # behind it, so the pages count as full as soon as they are the request's)
-        n_full = min([len(tokens) // ps] + [len(p) for p in pages])
-        mine_of = lambda i: tuple(pages[g][i] for g in range(len(pages)))
-        have = set(map(id, held))
-        node, now, added = self.root, next(self._clock), []
-        for i in range(n_full):
-            key = tuple(tokens[i * ps:(i + 1) * ps])
-            mine = mine_of(i)
-            child = node.children.get(key)
-            if child is None:
-                for g, p in enumerate(mine):
-                    self.cache.groups[g].pool.retain(p)
-                child = _Node(key, mine, node)
-                node.children[key] = child
-                self.num_nodes += 1
-                self._idle += 1
-            child.last_used = now
-            if child.pages == mine and id(child) not in have:
-                if child.users == 0:
-                    self._idle -= 1
-                child.users += 1
-                added.append(child)
-            node = child
-        return added
+        keep, ptr = native.token_array(tokens)
+        n = self._int(self._lib.lsbp_share(self._ptr, ptr, len(keep), self.cache.slot(request),
+                                           self._ids(held), len(held), self._node_buf, self.cache.max_pages))
+        return [NodeRef(i, self) for i in self._node_buf[:n]]
 
     # -------------------------------------------------------------- eviction
     def evictable_pages(self) -> int:
-        return self._idle
+        return self._lib.lsbp_evictable(self._ptr)
 
     def evict(self, pages_wanted: int) -> int:
-        """Give back up to ``pages_wanted`` pages per group; returns how many were freed."""
-        freed = 0
-        while freed < pages_wanted:
-            leaves = [n for n in self._nodes() if not n.children and n.users == 0]
-            if not leaves:
-                break
-            leaves.sort(key=lambda n: n.last_used)
-            for n in leaves:
-                if freed >= pages_wanted:
-                    break
-                for g, p in enumerate(n.pages):
-                    self.cache.groups[g].pool.release(p)
-                del n.parent.children[n.key]
-                self.num_nodes -= 1
-                self._idle -= 1
-                freed += 1
-        return freed
+        """Give back up to ``pages_wanted`` pages per group (unused leaves, least recently used
+        first); returns how many were freed."""
+        if pages_wanted <= 0:
+            return 0
+        return self._int(self._lib.lsbp_evict(self._ptr, pages_wanted))
 
     def check_invariants(self) -> None:
         """The counters agree with the tree (tests call this)."""
-        nodes = list(self._nodes())
-        if len(nodes) != self.num_nodes or sum(1 for n in nodes if n.users == 0) != self._idle:
-            raise AssertionError(f"prefix tree: {len(nodes)} nodes / {self.num_nodes} counted, "
-                                 f"{sum(1 for n in nodes if n.users == 0)} idle / {self._idle} counted")
-        if any(n.users < 0 for n in nodes):
-            raise AssertionError("prefix tree: a node has fewer than zero users")
-
-    def _nodes(self):
-        stack = list(self.root.children.values())
-        while stack:
-            n = stack.pop()
-            yield n
-            stack.extend(n.children.values())
-
-    def _owns(self, group: int, page: int) -> int:
-        return sum(1 for n in self._nodes() if n.pages[group] == page)
+        self.cache.check_invariants()

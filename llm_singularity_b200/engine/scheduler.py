@@ -240,7 +240,7 @@ class Scheduler:
             path = self.prefix.match(req.tokens) if self.prefix is not None else []
             need = self.cache.pages_for(len(req.tokens) + 1) - len(path)
             # pages on the matched path are in use by this request, not evictable for it
-            evictable_on_path = sum(1 for n in path if n.users == 0)
+            evictable_on_path = self.prefix.idle_on(path) if path else 0
             if need > self._free_pages() - evictable_on_path:
                 break
             if self.cache.open(req.id) is None:

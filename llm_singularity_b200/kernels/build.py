@@ -39,6 +39,7 @@ SOURCES: Dict[str, str] = {
     "gemm": "gemm.cu",
     "gemm_tc": "gemm_tc.cu",
     "sampling": "sampling.cu",
+    "host_memory": "host_memory.cpp",      # host code only: pools, block tables, prefix tree
 }
 HEADERS = ["common.cuh", "attention_tc_noalloc.h"]
 
