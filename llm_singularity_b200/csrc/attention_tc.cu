@@ -151,11 +151,13 @@ decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
     float* sCS = reinterpret_cast<float*>(sBT + kBtCache);   // [cos HD/2][sin HD/2] of the position
     lsb_pdl_launch_dependents();
 
-    // Before the wait on the previous kernel, what does not depend on it: the step's metadata was
-    // copied to the device before the step's first kernel started, so the block's key range and
-    // the sines and cosines of the token's position can be had while the projection is still
-    // being computed.  The block table may still be receiving this step's new pages: it is read
-    // after the wait.
+    // Before the wait on the previous kernel, what does not depend on it.  The step's metadata was
+    // copied to the device before the step's first kernel started, and the kernels that patch the
+    // block tables let nothing start before they have completed (cache_table.cu), so the block's
+    // key range, the sines and cosines of the token's position, its slice of the block table and
+    // the first keys and values of every warp can be had while the projection is still being
+    // computed.  Only the chunk that holds the token's own position must wait: its last row is
+    // written during this step (by this kernel, the rotary kernel or another layer's).
     const int split = blockIdx.x, g = blockIdx.y, r = blockIdx.z;
     const int qs = q_start[r];
     const bool single = q_start[r + 1] - qs == 1;
@@ -181,12 +183,71 @@ decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
         for (int i = threadIdx.x; i < HD / 2; i += kThreads)
             sincosf((float)p * inv_freq[i], &sCS[HD / 2 + i], &sCS[i]);
 
+    if (single && cached)                                    // from L2: another SM wrote it
+        for (int idx = threadIdx.x; idx < n_pages_here; idx += kThreads)
+            sBT[idx] = (page0 + idx < table_stride) ? __ldcg(bt + page0 + idx) : -1;
+    __syncthreads();
+
+    bf16* ring = sKV + (size_t)warp * kDecStages * kStageElems;
+    const int n_mine = (c1 - c0 - warp + 3) / 4;             // chunks c0 + warp, c0 + warp + 4, ...
+    auto issue = [&](int i) {
+        if (i < n_mine) {
+            const int chunk = c0 + warp + 4 * i;
+            bf16* dK = ring + (size_t)(i % kDecStages) * kStageElems;
+            bf16* dV = dK + kChunk * HD;
+            if (page_shift >= 0 && page_size >= kChunk) {
+                // the chunk lies inside one page: one table entry, then a contiguous run of rows
+                const int key0 = chunk * kChunk;
+                const int pi = key0 >> page_shift;
+                const int page = cached ? sBT[pi - page0] : (pi < table_stride ? bt[pi] : -1);
+                const bool page_ok = page >= 0 && page < num_pages;
+                if (!page_ok) lsb_set_status(LSB_BAD_PAGE);
+                const long long base = page_ok
+                    ? (((long long)page * nkv + g) * page_size + (key0 - (pi << page_shift))) * HD : 0;
+                const bf16* srcK = k_pages + base;
+                const bf16* srcV = v_pages + base;
+#pragma unroll
+                for (int idx = lane; idx < kChunk * CPR; idx += 32) {
+                    const int kk = idx / CPR, c = idx - kk * CPR;
+                    const bool valid = page_ok && key0 + kk >= lo && key0 + kk <= p;
+                    const int off = valid ? idx * 8 : 0;
+                    cp_async16(tile_ptr<HD>(dK, kk, c), srcK + off, valid);
+                    cp_async16(tile_ptr<HD>(dV, kk, c), srcV + off, valid);
+                }
+            } else
+#pragma unroll
+            for (int idx = lane; idx < kChunk * CPR; idx += 32) {
+                const int kk = idx / CPR, c = idx - kk * CPR;
+                const int key = chunk * kChunk + kk;
+                bool valid = key >= lo && key <= p;
+                long long off = 0;
+                if (valid) {
+                    const int pi = div_page(key, page_size, page_shift);
+                    const int page = cached ? sBT[pi - page0] : (pi < table_stride ? bt[pi] : -1);
+                    if (page < 0 || page >= num_pages) {
+                        lsb_set_status(LSB_BAD_PAGE);
+                        valid = false;
+                    } else {
+                        const int within = key - pi * page_size;
+                        off = (((long long)page * nkv + g) * page_size + within) * HD + c * 8;
+                    }
+                }
+                cp_async16(tile_ptr<HD>(dK, kk, c), k_pages + off, valid);
+                cp_async16(tile_ptr<HD>(dV, kk, c), v_pages + off, valid);
+            }
+        }
+        cp_async_commit();
+    };
+
+    // the warp's first chunks are on their way before the wait if none of them is the last one
+    const bool early = single && cached && c0 + warp + 4 * (kDecStages - 2) < p / kChunk;
+    if (early) {
+#pragma unroll
+        for (int i = 0; i < kDecStages - 1; ++i) issue(i);
+    }
+
     lsb_pdl_wait();
     if (!single) return;                                     // prompt portions go to the other kernel
-
-    if (cached)
-        for (int idx = threadIdx.x; idx < n_pages_here; idx += kThreads)
-            sBT[idx] = (page0 + idx < table_stride) ? bt[page0 + idx] : -1;
 
     const bf16* tok = qkv + (size_t)qs * qkv_stride;          // this token's row of the projection
     if (inv_freq) {
@@ -254,60 +315,10 @@ decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     const float sc = scale * kLog2e;
 
-    bf16* ring = sKV + (size_t)warp * kDecStages * kStageElems;
-    const int n_mine = (c1 - c0 - warp + 3) / 4;             // chunks c0 + warp, c0 + warp + 4, ...
-
-    auto issue = [&](int i) {
-        if (i < n_mine) {
-            const int chunk = c0 + warp + 4 * i;
-            bf16* dK = ring + (size_t)(i % kDecStages) * kStageElems;
-            bf16* dV = dK + kChunk * HD;
-            if (page_shift >= 0 && page_size >= kChunk) {
-                // the chunk lies inside one page: one table entry, then a contiguous run of rows
-                const int key0 = chunk * kChunk;
-                const int pi = key0 >> page_shift;
-                const int page = cached ? sBT[pi - page0] : (pi < table_stride ? bt[pi] : -1);
-                const bool page_ok = page >= 0 && page < num_pages;
-                if (!page_ok) lsb_set_status(LSB_BAD_PAGE);
-                const long long base = page_ok
-                    ? (((long long)page * nkv + g) * page_size + (key0 - (pi << page_shift))) * HD : 0;
-                const bf16* srcK = k_pages + base;
-                const bf16* srcV = v_pages + base;
+    if (!early) {
 #pragma unroll
-                for (int idx = lane; idx < kChunk * CPR; idx += 32) {
-                    const int kk = idx / CPR, c = idx - kk * CPR;
-                    const bool valid = page_ok && key0 + kk >= lo && key0 + kk <= p;
-                    const int off = valid ? idx * 8 : 0;
-                    cp_async16(tile_ptr<HD>(dK, kk, c), srcK + off, valid);
-                    cp_async16(tile_ptr<HD>(dV, kk, c), srcV + off, valid);
-                }
-            } else
-#pragma unroll
-            for (int idx = lane; idx < kChunk * CPR; idx += 32) {
-                const int kk = idx / CPR, c = idx - kk * CPR;
-                const int key = chunk * kChunk + kk;
-                bool valid = key >= lo && key <= p;
-                long long off = 0;
-                if (valid) {
-                    const int pi = div_page(key, page_size, page_shift);
-                    const int page = cached ? sBT[pi - page0] : (pi < table_stride ? bt[pi] : -1);
-                    if (page < 0 || page >= num_pages) {
-                        lsb_set_status(LSB_BAD_PAGE);
-                        valid = false;
-                    } else {
-                        const int within = key - pi * page_size;
-                        off = (((long long)page * nkv + g) * page_size + within) * HD + c * 8;
-                    }
-                }
-                cp_async16(tile_ptr<HD>(dK, kk, c), k_pages + off, valid);
-                cp_async16(tile_ptr<HD>(dV, kk, c), v_pages + off, valid);
-            }
-        }
-        cp_async_commit();
-    };
-
-#pragma unroll
-    for (int i = 0; i < kDecStages - 1; ++i) issue(i);
+        for (int i = 0; i < kDecStages - 1; ++i) issue(i);
+    }
 
     for (int i = 0; i < n_mine; ++i) {
         issue(i + kDecStages - 1);

@@ -8,7 +8,10 @@ LSB_DEFINE_STATUS()
 
 __global__ void scatter_i32_kernel(int* __restrict__ dst, const int* __restrict__ idx,
                                    const int* __restrict__ val, int n, long long dst_size) {
-    lsb_pdl_launch_dependents();
+    // No early launch of what follows: kernels later in the step read the block table before their
+    // own wait on their predecessor (the decode attention starts its first copies there), so
+    // nothing of the step may start until the table is whole.  The next kernel starts when this
+    // one has completed.
     lsb_pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
@@ -28,8 +31,7 @@ LSB_API int lsb_scatter_i32(int* dst, const int* idx, const int* val, int n, lon
 // hold this launch and still apply a different number of changes at every replay.
 __global__ void scatter_i32_counted_kernel(int* __restrict__ dst, const int* __restrict__ packed,
                                            int cap, long long dst_size) {
-    lsb_pdl_launch_dependents();
-    lsb_pdl_wait();
+    lsb_pdl_wait();              // as above: what follows starts when the table is whole
     int n = packed[0];
     if (n > cap) { if (threadIdx.x == 0) lsb_set_status(LSB_BAD_ROW); n = cap; }
     const int* idx = packed + 1;
