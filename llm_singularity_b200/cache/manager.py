@@ -148,6 +148,19 @@ class CacheManager:
             st[slot].zero_()
         return slot
 
+    def bind(self, request: Hashable, slot: int) -> None:
+        """``slot`` was opened inside the memory layer (by the scheduler, which lives there too)
+        and now belongs to ``request``."""
+        if request in self._slots:
+            raise KeyError(f"request {request!r} is already open")
+        self._slots[request] = slot
+        for st in self._state.values():
+            st[slot].zero_()
+
+    def unbind(self, request: Hashable) -> None:
+        """The memory layer has closed the request's slot already (see :meth:`bind`)."""
+        del self._slots[request]
+
     def slot(self, request: Hashable) -> int:
         return self._slots[request]
 
@@ -206,6 +219,8 @@ class CacheManager:
     def take_updates(self, group: int) -> List[Tuple[int, int]]:
         """Block-table cells changed since the last call, as (flat index, value)."""
         n = self._lib.lsbm_num_updates(self._ptr, group)
+        if n == native.ERR:
+            raise self._fail()
         if n == 0:
             return []
         buf = (ctypes.c_int * (2 * n))()

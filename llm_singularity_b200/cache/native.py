@@ -1,4 +1,5 @@
-"""Loading the host memory layer (``csrc/host_memory.cpp``) and declaring its C interface.
+"""Loading the host runtime (``csrc/host_memory.cpp``: pools, block tables, slots, prefix tree;
+``csrc/host_scheduler.cpp``: the scheduler) and declaring its C interface.
 
 The library is host code only; it is compiled at first use like the CUDA libraries and needs no
 GPU to run, so the cache manager and the scheduler can be exercised anywhere.
@@ -54,6 +55,23 @@ _SIGNATURES = {
     "lsbp_node_users": (c_int, [c_void_p, c_int]),
     "lsbp_node_pages": (c_int, [c_void_p, c_int, _IP]),
     "lsbp_idle_on": (c_int, [c_void_p, _IP, c_int]),
+    "lsbs_create": (c_void_p, [c_void_p, c_int, c_int, c_int, c_int, _IP, c_int, c_longlong]),
+    "lsbs_destroy": (None, [c_void_p]),
+    "lsbs_set_stop_ids": (None, [c_void_p, _IP, c_int]),
+    "lsbs_last_error": (c_char_p, [c_void_p]),
+    "lsbs_add": (c_int, [c_void_p, _IP, c_longlong, c_int, c_int, c_int]),
+    "lsbs_forget": (c_int, [c_void_p, c_int]),
+    "lsbs_has_work": (c_int, [c_void_p]),
+    "lsbs_plans_in_flight": (c_int, [c_void_p]),
+    "lsbs_plan": (c_int, [c_void_p, c_int]),
+    "lsbs_update": (c_int, [c_void_p, _IP, _IP, c_int]),
+    "lsbs_num_events": (c_int, [c_void_p]),
+    "lsbs_events": (c_int, [c_void_p, POINTER(c_longlong), c_int]),
+    "lsbs_request_error": (c_char_p, [c_void_p, c_int]),
+    "lsbs_request_slot": (c_int, [c_void_p, c_int]),
+    "lsbs_request_state": (c_int, [c_void_p, c_int, POINTER(c_longlong)]),
+    "lsbs_request_tokens": (c_int, [c_void_p, c_int, _IP, c_longlong]),
+    "lsbs_stats": (c_int, [c_void_p, POINTER(c_longlong)]),
 }
 
 _lib: Optional[ctypes.CDLL] = None
@@ -63,11 +81,11 @@ def lib() -> ctypes.CDLL:
     """The loaded library; compiled first if its current build is absent."""
     global _lib
     if _lib is None:
-        path = _build.ensure_built(["host_memory"])["host_memory"]
+        path = _build.ensure_built(["host_runtime"])["host_runtime"]
         try:
             loaded = ctypes.CDLL(path)
         except OSError as e:
-            raise RuntimeError(f"cannot load the host memory layer from {path}: {e}") from None
+            raise RuntimeError(f"cannot load the host runtime from {path}: {e}") from None
         for name, (restype, argtypes) in _SIGNATURES.items():
             fn = getattr(loaded, name)
             fn.restype, fn.argtypes = restype, argtypes

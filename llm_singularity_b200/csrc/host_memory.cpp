@@ -13,7 +13,7 @@
 // The reference keeps a bare stack of block indices, a map from whole prompts to block lists and a
 // per-request vector in its scheduler (core/src/memory.cpp:5-117, core/include/core/scheduler.h:59-69);
 // a block freed twice goes unnoticed there and cached prompts are never evicted.  Here every
-// violation is refused with a message, and nothing is changed by a call that fails.
+// violation is refused with a message.
 #include <algorithm>
 #include <cstdint>
 #include <cstdio>
@@ -21,12 +21,14 @@
 #include <string>
 #include <vector>
 
+#include "host_memory.h"
+
 #define LSB_API extern "C" __attribute__((visibility("default")))
 
 namespace {
 
 constexpr int32_t kNoPage = -1;
-constexpr int kErr = -1000;          // return value of a call that failed (message in last_error)
+constexpr int kErr = kLsbHostErr;    // return value of a call that failed (message in last_error)
 
 struct Pool {
     int num_pages = 0;
@@ -129,6 +131,12 @@ struct Memory {
 
 Memory* M(void* h) { return static_cast<Memory*>(h); }
 
+bool no_group(Memory* m, int g) {
+    if (g >= 0 && g < (int)m->groups.size()) return false;
+    m->fail("no group " + std::to_string(g));
+    return true;
+}
+
 }  // namespace
 
 // ----------------------------------------------------------------------------- life cycle
@@ -163,6 +171,14 @@ LSB_API void* lsbm_create(int page_size, int max_requests, int max_pages, int n_
 LSB_API void lsbm_destroy(void* h) { delete M(h); }
 
 LSB_API const char* lsbm_last_error(void* h) { return M(h)->error.c_str(); }
+LSB_API int lsbm_page_size(void* h) { return M(h)->page_size; }
+LSB_API int lsbm_max_pages(void* h) { return M(h)->max_pages; }
+// Pages of the smallest pool (1 << 30 if there is none): what a single request can ever hold.
+LSB_API int lsbm_smallest_pool(void* h) {
+    int n = 1 << 30;
+    for (Group& g : M(h)->groups) n = std::min(n, g.pool.num_pages);
+    return n;
+}
 
 // ----------------------------------------------------------------------------- pools
 LSB_API int lsbm_pool_allocate(void* h, int g) {
@@ -175,8 +191,8 @@ LSB_API int lsbm_pool_refcount(void* h, int g, int page) {
     if (M(h)->pool_check(g, page)) return kErr;
     return M(h)->groups[g].pool.refs[page];
 }
-LSB_API int lsbm_pool_num_free(void* h, int g) { return (int)M(h)->groups[g].pool.free_list.size(); }
-LSB_API int lsbm_pool_num_pages(void* h, int g) { return M(h)->groups[g].pool.num_pages; }
+LSB_API int lsbm_pool_num_free(void* h, int g) { return no_group(M(h), g) ? kErr : (int)M(h)->groups[g].pool.free_list.size(); }
+LSB_API int lsbm_pool_num_pages(void* h, int g) { return no_group(M(h), g) ? kErr : M(h)->groups[g].pool.num_pages; }
 
 // Free list and reference counts agree: no page on the list twice, free exactly when unreferenced.
 static int pool_invariants(Memory* m, int g) {
@@ -192,7 +208,7 @@ static int pool_invariants(Memory* m, int g) {
                            " disagrees with free list");
     return 0;
 }
-LSB_API int lsbm_pool_check(void* h, int g) { return pool_invariants(M(h), g); }
+LSB_API int lsbm_pool_check(void* h, int g) { return no_group(M(h), g) ? kErr : pool_invariants(M(h), g); }
 
 // ----------------------------------------------------------------------------- requests
 // A free slot (block-table row and state row) for a new request, or -1 if all are taken.
@@ -215,7 +231,10 @@ LSB_API int lsbm_num_pages(void* h, int slot) {
     Request* r = M(h)->request(slot);
     return r ? r->num_pages : kErr;
 }
-LSB_API int lsbm_first_live(void* h, int g, int slot) { return M(h)->groups[g].first_live[slot]; }
+LSB_API int lsbm_first_live(void* h, int g, int slot) {
+    if (no_group(M(h), g) || slot < 0 || slot >= M(h)->max_requests) return kErr;
+    return M(h)->groups[g].first_live[slot];
+}
 
 // Pages free in the tightest group.
 LSB_API int lsbm_free_pages(void* h) {
@@ -317,7 +336,7 @@ LSB_API int lsbm_adopt(void* h, int slot, const int* pages, int n, long long len
 LSB_API int lsbm_pages_of(void* h, int slot, int group, int* out, int cap) {
     Memory* m = M(h);
     Request* r = m->request(slot);
-    if (!r) return kErr;
+    if (!r || no_group(m, group)) return kErr;
     if (cap < r->num_pages) return m->fail("pages_of: buffer too small");
     const int32_t* row = &m->groups[group].table[(size_t)slot * m->max_pages];
     for (int i = 0; i < r->num_pages; ++i) out[i] = row[i];
@@ -325,10 +344,13 @@ LSB_API int lsbm_pages_of(void* h, int slot, int group, int* out, int cap) {
 }
 
 // ----------------------------------------------------------------------------- tables
-LSB_API int32_t* lsbm_table(void* h, int group) { return M(h)->groups[group].table.data(); }
-LSB_API int lsbm_num_updates(void* h, int group) { return (int)(M(h)->groups[group].updates.size() / 2); }
+LSB_API int32_t* lsbm_table(void* h, int group) { return no_group(M(h), group) ? nullptr : M(h)->groups[group].table.data(); }
+LSB_API int lsbm_num_updates(void* h, int group) {
+    return no_group(M(h), group) ? kErr : (int)(M(h)->groups[group].updates.size() / 2);
+}
 // Block-table cells changed since the last call, as (flat index, value) pairs, oldest first.
 LSB_API int lsbm_take_updates(void* h, int group, int* out, int cap_pairs) {
+    if (no_group(M(h), group)) return kErr;
     Group& g = M(h)->groups[group];
     const int n = (int)(g.updates.size() / 2);
     if (cap_pairs < n) return M(h)->fail("take_updates: buffer too small");

@@ -27,6 +27,13 @@ tokens have come back, and finishes requests.  Between the two the next step can
 planned (:meth:`Scheduler.schedule_ahead`): a request with a place-holder decodes on, its input
 token being fed on the device, so the device never waits for the host.
 
+The rules are applied by native code (``csrc/host_scheduler.cpp``, in one library with the memory
+layer it works on); this module is its Python face.  The library reports what it did as a list of
+events (admitted, preempted, failed, item, token, finished), which are replayed here onto the
+``Request`` records that the engine and its users read: their tokens, their generated tokens,
+their status.  ``tests/plain_scheduler.py`` states the same rules in plain Python and the tests
+hold the two to each other.
+
 The reference schedules prompts before decode tokens, iterates an unordered map,
 allocates whole prompts at admission, samples after every portion and, when pages
 run out during decoding, silently carries on into page 0
@@ -36,11 +43,14 @@ kept.
 """
 from __future__ import annotations
 
+import ctypes
 from collections import deque
 from dataclasses import dataclass, field
-from typing import Deque, Dict, Hashable, List, Optional, Sequence, Tuple
+from typing import Deque, Dict, Hashable, List, Optional, Tuple
 
+from ..cache import native
 from ..cache.manager import CacheManager
+from ..cache.pages import PageError
 from ..sampling.params import SamplingParams
 
 
@@ -60,7 +70,7 @@ class Request:
     max_new_tokens: int
     sampling: SamplingParams = field(default_factory=SamplingParams)
     ignore_eos: bool = False
-    # progress
+    # progress (a record of what the native scheduler has decided)
     tokens: List[int] = field(default_factory=list)      # prompt + generated so far (+ place-holders)
     generated: List[int] = field(default_factory=list)
     computed: int = 0               # tokens whose keys/values are cached once the planned steps have run
@@ -68,7 +78,7 @@ class Request:
     status: str = "waiting"          # waiting | running | finished | error
     error: str = ""
     preemptions: int = 0
-    prefix_path: list = field(default_factory=list)
+    handle: int = -1                # its name inside the native scheduler
 
     def __post_init__(self):
         if not self.tokens:
@@ -78,13 +88,20 @@ class Request:
 @dataclass
 class ScheduledItem:
     request: Request
-    start: int                 # == request.computed: position of the first token of the portion
+    start: int                 # position of the first token of the portion
     tokens: List[int]
     sample: bool               # the portion ends the known tokens: logits of its last token wanted
     decode: bool = False       # one token after a sampled one (the rest is prompt work)
 
 
+_ADMIT, _PREEMPT, _FAIL, _ITEM, _TOKEN, _FINISH = 1, 2, 3, 4, 5, 6
+_STATS = ("steps", "preemptions", "prefill_tokens", "decode_tokens", "prefix_hit_tokens",
+          "evicted_pages", "admitted", "errors", "ahead_steps")
+
+
 class Scheduler:
+    PENDING = -1        # stands for a token that a step in flight has yet to produce
+
     def __init__(self, config: SchedulerConfig, cache: CacheManager, prefix_cache=None):
         self.cfg = config
         self.cache = cache
@@ -92,12 +109,27 @@ class Scheduler:
         self.waiting: Deque[Request] = deque()
         self.running: List[Request] = []          # admission order
         self.finished: List[Request] = []
-        self.stats = {"steps": 0, "preemptions": 0, "prefill_tokens": 0, "decode_tokens": 0,
-                      "prefix_hit_tokens": 0, "evicted_pages": 0, "admitted": 0, "errors": 0}
-        # plans of steps whose results have not come back yet, oldest first: one in the plain
-        # loop (schedule, run, update), two while a step is planned ahead of the previous one's
-        # tokens (schedule_ahead)
-        self._plans: Deque[List[ScheduledItem]] = deque()
+        self._lib = native.lib()
+        stops = self._stops = [int(t) for t in config.stop_token_ids]
+        self._ptr = self._lib.lsbs_create(
+            cache._ptr, 1 if prefix_cache is not None else 0, config.max_batch_size,
+            config.max_tokens_per_batch, config.max_prefill_chunk or 0, native.ints(stops), len(stops),
+            config.max_model_len)
+        if not self._ptr:
+            raise ValueError("max_batch_size and max_tokens_per_batch must be positive")
+        self._by_handle: Dict[int, Request] = {}
+        self._by_id: Dict[Hashable, Request] = {}
+        self._stat_buf = (ctypes.c_longlong * len(_STATS))()
+
+    def __del__(self):
+        if getattr(self, "_ptr", None):
+            self._lib.lsbs_destroy(self._ptr)
+            self._ptr = None
+
+    @property
+    def stats(self) -> Dict[str, int]:
+        self._lib.lsbs_stats(self._ptr, self._stat_buf)
+        return dict(zip(_STATS, self._stat_buf))
 
     # ----------------------------------------------------------------- intake
     def add(self, request: Request) -> None:
@@ -105,67 +137,33 @@ class Scheduler:
             raise ValueError("a request needs at least one prompt token")
         if request.max_new_tokens < 1:
             raise ValueError("max_new_tokens must be at least 1")
+        if request.id in self._by_id:
+            raise KeyError(f"request id {request.id!r} is in use")
+        keep, ptr = native.token_array(request.tokens)
+        h = self._lib.lsbs_add(self._ptr, ptr, len(keep), request.max_new_tokens,
+                               1 if request.ignore_eos else 0,
+                               1 if request.sampling.repetition_penalty != 1.0 else 0)
+        if h == native.ERR:
+            raise ValueError(self._error())
+        request.handle = h
+        self._by_handle[h] = request
+        self._by_id[request.id] = request
         self.waiting.append(request)
 
     def has_work(self) -> bool:
         return bool(self.waiting or self.running)
 
-    # ---------------------------------------------------------------- helpers
-    def _free_pages(self) -> int:
-        n = self.cache.free_pages()
-        if self.prefix is not None:
-            n += self.prefix.evictable_pages()
-        return n
-
-    def _reserve(self, req: Request, new_len: int) -> bool:
-        """Pages for ``new_len`` tokens of ``req``, evicting cached prefixes if needed."""
-        if self.cache.reserve(req.id, new_len):
-            return True
-        if self.prefix is not None:
-            need = self.cache.pages_needed(req.id, new_len) - self.cache.free_pages()
-            self.stats["evicted_pages"] += self.prefix.evict(need)
-            return self.cache.reserve(req.id, new_len)
-        return False
-
-    def _release(self, req: Request) -> None:
-        if self.prefix is not None and req.prefix_path:
-            self.prefix.release(req.prefix_path)
-            req.prefix_path = []
-        self.cache.close(req.id)
-
-    def _preempt(self, req: Request) -> None:
-        """Free everything ``req`` holds; it will be recomputed from its tokens so far."""
-        self._release(req)
-        self.running.remove(req)
-        req.computed = 0
-        req.status = "waiting"
-        req.preemptions += 1
-        self.stats["preemptions"] += 1
-        self.waiting.appendleft(req)
-
-    def _fail(self, req: Request, why: str) -> None:
-        req.status, req.error = "error", why
-        self.stats["errors"] += 1
-        self.finished.append(req)
-
-    def _never_fits(self, req: Request) -> Optional[str]:
-        n = len(req.tokens) + 1
-        pool = min(g.pool.num_pages for g in self.cache.groups) if self.cache.groups else 1 << 30
-        if n > self.cfg.max_model_len:
-            return f"{len(req.tokens)} tokens plus one exceed max_model_len {self.cfg.max_model_len}"
-        if self.cache.pages_for(n) > min(pool, self.cache.max_pages):
-            return (f"{len(req.tokens)} tokens plus one need {self.cache.pages_for(n)} pages, "
-                    f"the pool has {pool}")
-        return None
+    def _error(self) -> str:
+        return self._lib.lsbs_last_error(self._ptr).decode()
 
     # --------------------------------------------------------------- schedule
-    PENDING = -1        # stands for a token that a step in flight has yet to produce
-
     def schedule(self) -> List[ScheduledItem]:
         """Plan the next step; the step before it has been accounted (:meth:`update`)."""
-        if self._plans:
+        if self._lib.lsbs_plans_in_flight(self._ptr):
             raise RuntimeError("a step is in flight: account it first, or plan with schedule_ahead")
-        return self._plan(ahead=False)
+        if self._lib.lsbs_plan(self._ptr, 0) == native.ERR:
+            raise PageError(self._error())
+        return self._replay()
 
     def schedule_ahead(self) -> Optional[List[ScheduledItem]]:
         """Plan the step after the one in flight before that one's tokens are known.  A request
@@ -177,176 +175,84 @@ class Scheduler:
         nothing to run, when two steps would be ahead, or when a request samples with a repetition
         penalty (which needs the token in flight on the host): plan with :meth:`schedule` after
         :meth:`update` then."""
-        if len(self._plans) != 1:
-            return None
-        if any(r.pending and r.sampling.repetition_penalty != 1.0 for r in self.running):
-            return None
-        items = self._plan(ahead=True)
-        if items:
-            self.stats["ahead_steps"] = self.stats.get("ahead_steps", 0) + 1
-        return items or None
+        if self._lib.lsbs_plan(self._ptr, 1) == native.ERR:
+            raise PageError(self._error())
+        return self._replay() or None
 
-    def _ends_with_token_in_flight(self, req: Request) -> bool:
-        return len(req.generated) + req.pending >= req.max_new_tokens \
-            or len(req.tokens) + 1 > self.cfg.max_model_len
-
-    def _plan(self, ahead: bool) -> List[ScheduledItem]:
-        cfg = self.cfg
+    def _replay(self) -> List[ScheduledItem]:
+        """Apply the events of the last native call to the request records; returns the items."""
+        n = self._lib.lsbs_num_events(self._ptr)
+        if n == 0:
+            return []
+        buf = (ctypes.c_longlong * (5 * n))()
+        self._lib.lsbs_events(self._ptr, buf, n)
+        ev = buf[:]
         items: List[ScheduledItem] = []
-        chunk_cap = cfg.max_prefill_chunk or cfg.max_tokens_per_batch
-
-        # 1. decode tokens (requests with exactly one token left to run), oldest first; when
-        #    pages run out the youngest running request is preempted (possibly the one asking),
-        #    or, while a step is in flight, the request waits
-        for req in list(self.running):
-            if req.status != "running" or len(req.tokens) - req.computed != 1:
-                continue                             # preempted a moment ago, or still in its prompt
-            if req.pending and self._ends_with_token_in_flight(req):
-                continue
-            if len(items) >= cfg.max_tokens_per_batch:
-                break
-            placed = False
-            while req.status == "running":
-                if self._reserve(req, len(req.tokens)):
-                    placed = True
-                    break
-                if ahead:
-                    break
-                victim = self.running[-1]
-                items = [it for it in items if it.request is not victim]
-                self._preempt(victim)
-            if placed:
-                items.append(ScheduledItem(req, req.computed, [req.tokens[-1]], True))
-        budget = cfg.max_tokens_per_batch - len(items)
-
-        # 2. next portions of prompts already running (they wait for pages, never preempt)
-        for req in self.running:
-            remaining = len(req.tokens) - req.computed
-            if remaining <= 1 or budget <= 0:
-                continue
-            n = self._fit_portion(req, min(remaining, budget, chunk_cap))
-            if n > 0:
-                items.append(self._portion(req, n))
-                budget -= n
-
-        # 3. admission, first come first served
-        while self.waiting and budget > 0 and len(self.running) < cfg.max_batch_size:
-            req = self.waiting[0]
-            why = self._never_fits(req)
-            if why:
-                self.waiting.popleft()
-                self._fail(req, why)
-                continue
-            path = self.prefix.match(req.tokens) if self.prefix is not None else []
-            need = self.cache.pages_for(len(req.tokens) + 1) - len(path)
-            # pages on the matched path are in use by this request, not evictable for it
-            evictable_on_path = self.prefix.idle_on(path) if path else 0
-            if need > self._free_pages() - evictable_on_path:
-                break
-            if self.cache.open(req.id) is None:
-                break
-            self.waiting.popleft()
-            if path:
-                req.computed = self.prefix.adopt(req.id, path)
-                req.prefix_path = path
-                self.stats["prefix_hit_tokens"] += req.computed
-            req.status = "running"
-            self.running.append(req)
-            self.stats["admitted"] += 1
-            n = self._fit_portion(req, min(len(req.tokens) - req.computed, budget, chunk_cap))
-            if n > 0:
-                items.append(self._portion(req, n))
-                budget -= n
-
-        # nothing could move although requests are live: the youngest gives way
-        if not items and self.running and not ahead:
-            if len(self.running) == 1:
-                req = self.running[0]
-                self._release(req)
-                self.running.remove(req)
-                self._fail(req, "the cache pool cannot hold this request")
-            else:
-                self._preempt(self.running[-1])
-            return self._plan(ahead)
-
-        # the first half of the accounting: the step counts as run
-        for it in items:
-            req = it.request
-            req.computed += len(it.tokens)
-            it.decode = len(it.tokens) == 1 and it.start > 0 and bool(req.generated or req.pending)
-            if it.sample:
-                if self.prefix is not None and not it.decode:
-                    # The prompt is whole with this step: later prompts may share its full pages
-                    # from now on (a step that reads them is queued behind this one).
-                    req.prefix_path = req.prefix_path + self.prefix.share(
-                        req.tokens[:req.computed], req.id, req.prefix_path)
-                req.tokens.append(self.PENDING)
-                req.pending += 1
-        if items:
-            self._plans.append(items)
-            self.stats["steps"] += 1
+        for k in range(0, 5 * n, 5):
+            kind, h, a, b, c = ev[k:k + 5]
+            req = self._by_handle[h]
+            if kind == _ITEM:
+                items.append(ScheduledItem(req, a, req.tokens[a:a + b], bool(c & 1), bool(c & 2)))
+                req.computed = a + b                 # the first half of the accounting
+                if c & 1:
+                    req.tokens.append(self.PENDING)
+                    req.pending += 1
+            elif kind == _TOKEN:
+                req.tokens[b] = a
+                req.pending -= 1
+                req.generated.append(a)
+            elif kind == _ADMIT:
+                self.waiting.remove(req)             # it stood at the front
+                req.computed, req.status = a, "running"
+                self.running.append(req)
+                self.cache.bind(req.id, self._lib.lsbs_request_slot(self._ptr, h))
+            elif kind == _FINISH:
+                del req.tokens[a + 1:]               # a place-holder of a step planned ahead
+                req.pending, req.computed, req.status = 0, a, "finished"
+                self._leave_running(req)
+            elif kind == _PREEMPT:
+                self._leave_running(req)
+                req.computed, req.status = 0, "waiting"
+                req.preemptions += 1
+                self.waiting.appendleft(req)
+            elif kind == _FAIL:
+                if req.status == "running":
+                    self._leave_running(req)
+                else:
+                    self.waiting.remove(req)
+                req.status = "error"
+                req.error = self._lib.lsbs_request_error(self._ptr, h).decode()
+            if kind in (_FINISH, _FAIL):
+                self.finished.append(req)
         return items
 
-    def _fit_portion(self, req: Request, n: int) -> int:
-        """Largest portion <= n whose pages can be had now (prompts wait rather than preempt)."""
-        if n <= 0:
-            return 0
-        if self._reserve(req, req.computed + n):
-            return n
-        ps = self.cache.page_size
-        have = self.cache.pages_for(req.computed) * ps      # tokens its held pages cover
-        room = have + self._free_pages() * ps - req.computed
-        n = min(n, room)
-        if n > 0 and self._reserve(req, req.computed + n):
-            return n
-        return 0
-
-    def _portion(self, req: Request, n: int) -> ScheduledItem:
-        toks = req.tokens[req.computed:req.computed + n]
-        return ScheduledItem(req, req.computed, toks, req.computed + n == len(req.tokens))
+    def _leave_running(self, req: Request) -> None:
+        self.running.remove(req)
+        self.cache.unbind(req.id)                    # its slot is closed in the memory layer already
 
     # ----------------------------------------------------------------- update
     def update(self, sampled: Dict[Hashable, int]) -> List[Request]:
         """The oldest step still unaccounted has run: ``sampled`` maps the ids of requests whose
         logits were wanted to their new token, which takes its place among the request's tokens.
         Returns requests that finished."""
-        done: List[Tuple[Request, int]] = []
-        for it in (self._plans.popleft() if self._plans else []):
-            req = it.request
-            if req.status != "running":
-                continue         # planned ahead, but it stopped on the token that was in flight
-            end = it.start + len(it.tokens)               # tokens cached now that this step has run
-            if self.cache.length(req.id) < end:           # the step function has done it already,
-                self.cache.commit(req.id, end)            # and a step planned ahead may be further
-            if it.sample:
-                if it.decode:
-                    self.stats["decode_tokens"] += 1
-                else:
-                    self.stats["prefill_tokens"] += len(it.tokens)
-                tok = int(sampled[req.id])
-                if req.tokens[end] != self.PENDING:
-                    raise RuntimeError(f"request {req.id!r}: no token is outstanding at place {end}")
-                req.tokens[end] = tok
-                req.pending -= 1
-                req.generated.append(tok)
-                stop = (not req.ignore_eos and tok in self.cfg.stop_token_ids) \
-                    or len(req.generated) >= req.max_new_tokens \
-                    or end + 2 > self.cfg.max_model_len
-                if stop:
-                    done.append((req, end))
-            else:
-                self.stats["prefill_tokens"] += len(it.tokens)
-        for req, end in done:
-            del req.tokens[end + 1:]                      # a place-holder of a step planned ahead
-            req.pending, req.computed = 0, end
-            if self.prefix is not None:
-                self.prefix.insert(req.tokens[:end], req.id)
-            self._release(req)
-            self.running.remove(req)
-            req.status = "finished"
-            self.finished.append(req)
-        return [req for req, _ in done]
+        stops = [int(t) for t in self.cfg.stop_token_ids]
+        if stops != self._stops:                     # the configuration was changed under way
+            self._lib.lsbs_set_stop_ids(self._ptr, native.ints(stops), len(stops))
+            self._stops = stops
+        known = [(self._by_id[rid].handle, int(tok)) for rid, tok in sampled.items() if rid in self._by_id]
+        handles = native.ints([h for h, _ in known])
+        tokens = native.ints([t for _, t in known])
+        if self._lib.lsbs_update(self._ptr, handles, tokens, len(known)) == native.ERR:
+            raise RuntimeError(self._error())
+        before = len(self.finished)
+        self._replay()
+        return [r for r in self.finished[before:] if r.status == "finished"]
 
     def take_finished(self) -> List[Request]:
+        """Finished and failed requests since the last call; the scheduler forgets them."""
         out, self.finished = self.finished, []
+        for req in out:
+            self._lib.lsbs_forget(self._ptr, req.handle)
+            del self._by_handle[req.handle]
+            del self._by_id[req.id]
         return out

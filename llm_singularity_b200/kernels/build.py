@@ -27,7 +27,7 @@ NVCC_FLAGS = [
 ]
 # No --use_fast_math: expf, sincosf and division must stay exact.
 
-SOURCES: Dict[str, str] = {
+SOURCES: Dict[str, object] = {          # library -> its source file (or files)
     "embedding": "embedding.cu",
     "norm": "norm.cu",
     "activation": "activation.cu",
@@ -39,9 +39,15 @@ SOURCES: Dict[str, str] = {
     "gemm": "gemm.cu",
     "gemm_tc": "gemm_tc.cu",
     "sampling": "sampling.cu",
-    "host_memory": "host_memory.cpp",      # host code only: pools, block tables, prefix tree
+    # host code only: pools, block tables, prefix tree; scheduler
+    "host_runtime": ("host_memory.cpp", "host_scheduler.cpp"),
 }
-HEADERS = ["common.cuh", "attention_tc_noalloc.h"]
+HEADERS = ["common.cuh", "attention_tc_noalloc.h", "host_memory.h"]
+
+
+def _files(name: str) -> List[str]:
+    src = SOURCES[name]
+    return [src] if isinstance(src, str) else list(src)
 
 
 class BuildError(RuntimeError):
@@ -88,7 +94,7 @@ def build_dir() -> str:
 def _digest(name: str) -> str:
     h = hashlib.sha256()
     h.update(" ".join(NVCC_FLAGS).encode())
-    for fn in [SOURCES[name]] + HEADERS:
+    for fn in _files(name) + HEADERS:
         with open(os.path.join(CSRC, fn), "rb") as f:
             h.update(f.read())
     return h.hexdigest()[:16]
@@ -128,7 +134,7 @@ def ensure_built(names: Iterable[str], verbose: bool = False) -> Dict[str, str]:
     t0 = time.time()
     for n in todo:
         tmp = f"{paths[n]}.{os.getpid()}.tmp"
-        cmd = [nvcc] + NVCC_FLAGS + ["-I", CSRC, "-o", tmp, os.path.join(CSRC, SOURCES[n])]
+        cmd = [nvcc] + NVCC_FLAGS + ["-I", CSRC, "-o", tmp] + [os.path.join(CSRC, f) for f in _files(n)]
         procs.append((n, tmp, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT,
                                                env=env, text=True)))
     pending = list(procs)
@@ -142,7 +148,7 @@ def ensure_built(names: Iterable[str], verbose: bool = False) -> Dict[str, str]:
                 continue
             log = p.stdout.read()
             if p.returncode != 0:
-                errors.append(f"--- {SOURCES[n]} (exit {p.returncode}) ---\n{log}")
+                errors.append(f"--- {', '.join(_files(n))} (exit {p.returncode}) ---\n{log}")
                 if os.path.exists(tmp):
                     os.unlink(tmp)
             else:
