@@ -42,7 +42,8 @@ SOURCES: Dict[str, object] = {          # library -> its source file (or files)
     # host code only: pools, block tables, prefix tree; scheduler
     "host_runtime": ("host_memory.cpp", "host_scheduler.cpp"),
 }
-HEADERS = ["common.cuh", "attention_tc_noalloc.h", "host_memory.h"]
+HEADERS = ["common.cuh", "attention_tc_noalloc.h"]     # of the CUDA libraries
+HOST_HEADERS = ["host_memory.h"]                          # of the host runtime
 
 
 def _files(name: str) -> List[str]:
@@ -94,7 +95,7 @@ def build_dir() -> str:
 def _digest(name: str) -> str:
     h = hashlib.sha256()
     h.update(" ".join(NVCC_FLAGS).encode())
-    for fn in _files(name) + HEADERS:
+    for fn in _files(name) + (HOST_HEADERS if name == "host_runtime" else HEADERS):
         with open(os.path.join(CSRC, fn), "rb") as f:
             h.update(f.read())
     return h.hexdigest()[:16]
