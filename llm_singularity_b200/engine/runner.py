@@ -113,6 +113,7 @@ class ModelRunner:
         # decode-only steps are captured once per batch size and replayed (no per-kernel launch
         # cost); only if every part launches the same kernels whatever the host-side values are
         self._graphs: Dict[int, "_DecodeGraph"] = {}
+        self._capture_stream = None
         self.cuda_graphs = (cuda_graphs and ops is None and self.rt.device.type == "cuda"
                             and all(getattr(p, "graph_safe", False)
                                     for p in self.model._owners().values()))
@@ -229,8 +230,21 @@ class ModelRunner:
             torch.cuda.synchronize(self.rt.device)
             graph = torch.cuda.CUDAGraph()
             try:
-                with torch.cuda.graph(graph):
-                    st.logits = run()
+                # Captured by hand on a side stream: the context manager of the library would also
+                # collect garbage and hand all cached device memory back before every capture, which
+                # costs tens of milliseconds each time a new batch size turns up in a serving run.
+                main = torch.cuda.current_stream(self.rt.device)
+                side = self._capture_stream
+                if side is None:
+                    side = self._capture_stream = torch.cuda.Stream(self.rt.device)
+                side.wait_stream(main)
+                with torch.cuda.stream(side):
+                    graph.capture_begin()
+                    try:
+                        st.logits = run()
+                    finally:
+                        graph.capture_end()
+                main.wait_stream(side)
             except RuntimeError as e:
                 # a driver that cannot capture these launches: decode kernel by kernel from now on
                 import warnings
