@@ -120,6 +120,8 @@ class Scheduler:
         self._by_handle: Dict[int, Request] = {}
         self._by_id: Dict[Hashable, Request] = {}
         self._stat_buf = (ctypes.c_longlong * len(_STATS))()
+        self._event_buf = (ctypes.c_longlong * (5 * 256))()
+        self._token_buf = (ctypes.c_int * (2 * config.max_batch_size))()   # handles, then tokens
 
     def __del__(self):
         if getattr(self, "_ptr", None):
@@ -184,9 +186,10 @@ class Scheduler:
         n = self._lib.lsbs_num_events(self._ptr)
         if n == 0:
             return []
-        buf = (ctypes.c_longlong * (5 * n))()
-        self._lib.lsbs_events(self._ptr, buf, n)
-        ev = buf[:]
+        if 5 * n > len(self._event_buf):
+            self._event_buf = (ctypes.c_longlong * (10 * n))()
+        self._lib.lsbs_events(self._ptr, self._event_buf, len(self._event_buf) // 5)
+        ev = self._event_buf[:5 * n]
         items: List[ScheduledItem] = []
         for k in range(0, 5 * n, 5):
             kind, h, a, b, c = ev[k:k + 5]
@@ -239,10 +242,17 @@ class Scheduler:
         if stops != self._stops:                     # the configuration was changed under way
             self._lib.lsbs_set_stop_ids(self._ptr, native.ints(stops), len(stops))
             self._stops = stops
-        known = [(self._by_id[rid].handle, int(tok)) for rid, tok in sampled.items() if rid in self._by_id]
-        handles = native.ints([h for h, _ in known])
-        tokens = native.ints([t for _, t in known])
-        if self._lib.lsbs_update(self._ptr, handles, tokens, len(known)) == native.ERR:
+        by_id, buf, cap, k = self._by_id, self._token_buf, len(self._token_buf) // 2, 0
+        if len(sampled) > cap:
+            buf = self._token_buf = (ctypes.c_int * (2 * len(sampled)))()
+            cap = len(sampled)
+        for rid, tok in sampled.items():
+            req = by_id.get(rid)
+            if req is not None:                      # else: finished and forgotten, a stray token
+                buf[k], buf[cap + k] = req.handle, tok
+                k += 1
+        tokens = ctypes.cast(ctypes.byref(buf, cap * ctypes.sizeof(ctypes.c_int)), ctypes.POINTER(ctypes.c_int))
+        if self._lib.lsbs_update(self._ptr, buf, tokens, k) == native.ERR:
             raise RuntimeError(self._error())
         before = len(self.finished)
         self._replay()

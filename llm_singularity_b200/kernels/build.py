@@ -127,8 +127,10 @@ def ensure_built(names: Iterable[str], verbose: bool = False) -> Dict[str, str]:
         return paths
     nvcc = find_nvcc()
     out = sys.stderr
-    print(f"[llm_singularity_b200] compiling {len(todo)} CUDA librar{'y' if len(todo) == 1 else 'ies'} "
-          f"for sm_100a ({', '.join(todo)}) into {build_dir()}", file=out, flush=True)
+    what = "host librar" if all(n == "host_runtime" for n in todo) else "CUDA librar"
+    print(f"[llm_singularity_b200] compiling {len(todo)} {what}{'y' if len(todo) == 1 else 'ies'} "
+          f"{'' if what.startswith('host') else 'for sm_100a '}({', '.join(todo)}) into {build_dir()}",
+          file=out, flush=True)
     env = dict(os.environ)
     env.setdefault("TMPDIR", tempfile.gettempdir())
     procs: List = []
