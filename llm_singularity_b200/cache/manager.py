@@ -17,10 +17,9 @@ length in every group or changes nothing and says so.
 """
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
-
-import ctypes
 
 import numpy as np
 import torch
