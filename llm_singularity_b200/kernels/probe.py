@@ -5,6 +5,12 @@
     python -m llm_singularity_b200.kernels.probe prefill_attention --tokens 2048
     python -m llm_singularity_b200.kernels.probe add_rmsnorm --tokens 2048 --hidden 2048
     python -m llm_singularity_b200.kernels.probe rope --tokens 2048
+    python -m llm_singularity_b200.kernels.probe decode_step --batch 8 --context 4096
+
+``decode_step`` runs whole decode steps of a model of the given sizes (random weights) through the
+captured graph and prints where one step's time goes: for every kernel of one layer in the middle
+of the model, the time from the previous kernel's end to its own end (kernels overlap: each starts
+under its predecessor), and the step's total by kernel.
 
 Times are CUDA-event times on the launching stream after warm-up, with a buffer larger than the
 L2 cache read between iterations (``--no-flush`` to keep it warm).  The same command line is
@@ -63,9 +69,71 @@ def _time(fn, iters, warmup, flush):
     return total / iters * 1e3          # microseconds
 
 
+def _decode_step(a) -> None:
+    from torch.profiler import ProfilerActivity, profile
+
+    from ..config.llama import LlamaConfig
+    from ..engine import StepEntry
+    from ..engine.engine import Engine
+    cfg = LlamaConfig.from_dict(dict(
+        architectures=["LlamaForCausalLM"], num_hidden_layers=a.layers, hidden_size=a.hidden,
+        num_attention_heads=a.heads, num_key_value_heads=a.kv_heads, head_dim=a.head_dim,
+        intermediate_size=a.intermediate, vocab_size=a.vocab, rope_theta=500000.0, rope_scaling=None,
+        rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=131072))
+    B, ctx_len = a.batch, a.context
+    eng = Engine(None, config=cfg, random_weights=True, dtype="bfloat16", kv_block_size=a.page,
+                 num_kv_blocks=B * (ctx_len // a.page + 2) + 8, max_batch_size=B, max_tokens_per_batch=2048,
+                 max_model_len=ctx_len + 64, prefix_cache=False)
+    r = eng.runner
+    g = torch.Generator().manual_seed(0)
+    ids = [f"r{i}" for i in range(B)]
+    for rid in ids:                                   # fill the contexts, 2,048 tokens a step
+        r.open(rid)
+        toks = torch.randint(0, cfg.vocab_size, (ctx_len - 16,), generator=g).tolist()
+        for s0 in range(0, len(toks), 2048):
+            r.step([StepEntry(rid, toks[s0:s0 + 2048], [])])
+
+    def step():
+        return r.step([StepEntry(rid, [5], [0]) for rid in ids])
+
+    for _ in range(3):                                # eager once, capture, replay
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(a.iters):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    print(f"decode step B={B} context={ctx_len} layers={a.layers} hidden={a.hidden}: "
+          f"{e0.elapsed_time(e1) / a.iters * 1e3:.1f} us per step (CUDA events, graph replay)")
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        step()
+        torch.cuda.synchronize()
+    evs = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA),
+                 key=lambda e: e.time_range.end)
+    names = [e.name.split("(")[0].replace("void ", "") for e in evs]
+    norms = [i for i, n in enumerate(names) if n.startswith("add_rmsnorm")]
+    if len(norms) >= 6:
+        mid = norms[(len(norms) // 2) & ~1]            # an input norm in the middle of the model
+        last = norms[((len(norms) // 2) & ~1) + 2]
+        print("one layer, time from the previous kernel's end to this kernel's end:")
+        for i in range(mid + 1, last + 1):
+            print(f"  {evs[i].time_range.end - evs[i - 1].time_range.end:7.1f} us  {names[i][:70]}")
+        print(f"  {evs[last].time_range.end - evs[mid].time_range.end:7.1f} us  the layer")
+    total = {}
+    for i in range(1, len(evs)):
+        total[names[i]] = total.get(names[i], 0.0) + evs[i].time_range.end - max(evs[i - 1].time_range.end,
+                                                                               evs[i].time_range.start)
+    print("the step by kernel (time not hidden under the previous kernel), under the profiler:")
+    for n, t in sorted(total.items(), key=lambda kv: -kv[1]):
+        print(f"  {t:8.1f} us  {n[:70]}")
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="probe", description=__doc__.split("\n\n")[0])
-    ap.add_argument("op", choices=["gemm", "decode_attention", "prefill_attention", "add_rmsnorm", "rope"])
+    ap.add_argument("op", choices=["gemm", "decode_attention", "prefill_attention", "add_rmsnorm", "rope",
+                                   "decode_step"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=16384)
     ap.add_argument("--k", type=int, default=2048)
@@ -79,6 +147,9 @@ def main(argv=None) -> int:
     ap.add_argument("--kv-heads", type=int, default=8)
     ap.add_argument("--head-dim", type=int, default=64)
     ap.add_argument("--page", type=int, default=16)
+    ap.add_argument("--layers", type=int, default=16)
+    ap.add_argument("--intermediate", type=int, default=8192)
+    ap.add_argument("--vocab", type=int, default=128256)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true")
@@ -87,7 +158,9 @@ def main(argv=None) -> int:
     torch.manual_seed(0)
     nh, nkv, hd = a.heads, a.kv_heads, a.head_dim
 
-    if a.op == "gemm":
+    if a.op == "decode_step":
+        _decode_step(a)
+    elif a.op == "gemm":
         x = torch.randn(a.m, a.k, device="cuda").to(torch.bfloat16)
         w = torch.randn(a.n, a.k, device="cuda").to(torch.bfloat16)
         od = torch.float32 if a.f32_out else torch.bfloat16
