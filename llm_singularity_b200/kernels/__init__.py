@@ -226,6 +226,13 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     out_dtype = out_dtype or x.dtype
     if out_dtype not in (x.dtype, torch.float32):
         raise KernelError(f"linear: output must be {x.dtype} or float32")
+    if x.dtype == torch.bfloat16 and SMALL_PRODUCTS and not gated and M <= 16 and small_gemm_ok(x, w):
+        # a few rows times a matrix that fits the chip's shared memory (decode: q/k/v, output
+        # projection): weights resident before the previous kernel has ended, no cluster
+        out = torch.empty((M, N), dtype=out_dtype, device=x.device)
+        _call("gemm_small", "lsb_gemm_small", _p(x), _p(w), _p(out), _i(1 if out_dtype == torch.float32 else 0),
+              _i(M), _i(N), _i(K), _stream(out))
+        return out
     if x.dtype == torch.bfloat16 and tensor_core_gemm_ok(x, w):
         out = torch.empty((M, N // 2 if gated else N), dtype=out_dtype, device=x.device)
         _call("gemm_tc", "lsb_gemm_tc", _p(x), _p(w), _p(out), _i(1 if out_dtype == torch.float32 else 0),
@@ -239,6 +246,19 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
         swiglu(out, act)
         return act
     return out
+
+
+SMALL_PRODUCTS = True           # products of at most 16 rows with a small matrix: csrc/gemm_small.cu
+
+
+def small_gemm_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
+    """Does the small-product kernel take x [M, K] times w [N, K] transposed?  (bfloat16, M <= 16,
+    K a multiple of 64, N / SMs rows of w and the rows of x within one block's shared memory.)"""
+    M, K = x.shape
+    N = w.shape[0]
+    if M > 16 or K % 64 or -(-N // NUM_SMS) > 32 or (-(-N // NUM_SMS) + 16) * K * 2 > 180 * 1024:
+        return False                                  # cheap refusals first; the library has the last word
+    return bool(_lib("gemm_small").lsb_gemm_small_supported(_p(x), _p(w), _i(M), _i(N), _i(K)))
 
 
 def tensor_core_gemm_ok(x: torch.Tensor, w: torch.Tensor) -> bool:

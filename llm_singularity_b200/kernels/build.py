@@ -38,6 +38,7 @@ SOURCES: Dict[str, object] = {          # library -> its source file (or files)
     "attention_tc5": "attention_tc5.cu",
     "gemm": "gemm.cu",
     "gemm_tc": "gemm_tc.cu",
+    "gemm_small": "gemm_small.cu",
     "sampling": "sampling.cu",
     # host code only: pools, block tables, prefix tree; scheduler
     "host_runtime": ("host_memory.cpp", "host_scheduler.cpp"),

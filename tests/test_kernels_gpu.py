@@ -174,11 +174,41 @@ def test_split_k_products_are_repeatable(ops, M, N, K):
     # tiles in split order, so the bits do not depend on arrival order, and the tile counters are
     # handed back zeroed for the next launch
     x, w = _rand(M, K, dtype=torch.bfloat16, seed=3), _rand(N, K, dtype=torch.bfloat16, seed=4)
-    first = ops.linear(x, w, out_dtype=torch.float32)
+    ops.SMALL_PRODUCTS = False             # the tile kernel, also where the small-product kernel would do
+    try:
+        first = ops.linear(x, w, out_dtype=torch.float32)
+        want = x.double() @ w.double().T
+        assert (first.double() - want).abs().max() <= 3e-7 * K * 8
+        for _ in range(5):
+            assert torch.equal(ops.linear(x, w, out_dtype=torch.float32), first)
+    finally:
+        ops.SMALL_PRODUCTS = True
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M, N, K", [(1, 3072, 2048), (8, 2048, 2048), (8, 3072, 2048), (16, 2048, 2048),
+                                     (9, 300, 64), (5, 4736, 128), (3, 7, 64), (13, 1000, 1024)])
+def test_small_products(ops, M, N, K, out_dtype):
+    # at most 16 rows times a matrix that fits the chip's shared memory: the kernel that keeps its
+    # weight rows resident (the decode step's q/k/v and output projections); whole and partial
+    # 16-row tiles, one and two 8-column tiles of the batch, fewer weight rows than SMs
+    x, w = _rand(M, K, dtype=torch.bfloat16, seed=5), _rand(N, K, dtype=torch.bfloat16, seed=6)
+    assert ops.small_gemm_ok(x, w)
+    y = ops.linear(x, w, out_dtype=out_dtype)
     want = x.double() @ w.double().T
-    assert (first.double() - want).abs().max() <= 3e-7 * K * 8
-    for _ in range(5):
-        assert torch.equal(ops.linear(x, w, out_dtype=torch.float32), first)
+    assert y.dtype == out_dtype and y.shape == (M, N)
+    tol = 3e-7 * K * 8 if out_dtype == torch.float32 else 1e-2 * want.abs().max().item()
+    assert (y.double() - want).abs().max() <= tol
+    for _ in range(3):
+        assert torch.equal(ops.linear(x, w, out_dtype=out_dtype), y)      # a fixed summation order
+    ops.SMALL_PRODUCTS = False
+    try:
+        other = ops.linear(x, w, out_dtype=torch.float32)                 # the tile kernel
+    finally:
+        ops.SMALL_PRODUCTS = True
+    assert (other.double() - want).abs().max() <= 3e-7 * K * 8
+    assert not ops.small_gemm_ok(_rand(17, K, dtype=torch.bfloat16, seed=1), w)
+    assert not ops.small_gemm_ok(x[:, :K - 8].contiguous(), w[:, :K - 8].contiguous())
 
 
 def test_linear_float32_is_true_32_bit(ops):
