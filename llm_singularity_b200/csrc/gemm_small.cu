@@ -11,7 +11,7 @@
 // partial tiles outside the block; the summation order is fixed, so results repeat bit for bit.
 //
 // The eight warps split K; each holds accumulators for the block's rows (one or two 16-row tiles)
-// and the batch (one or two 8-column tiles).  Operands lie in shared memory row by row with the
+// and the batch (one or two 8-column tiles), and copies and waits for its own slice alone.  Operands lie in shared memory row by row with the
 // 16-byte chunks of a row XOR-swizzled by the row number, so ldmatrix reads without bank conflicts.
 //
 // The reference calls cublasSgemm for every projection (kernels/src/cublas_provider.cpp:36-51).
@@ -68,28 +68,35 @@ gemm_small_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* 
     const int n0 = blockIdx.x * R;
     const int rows = min(R, N - n0);
     const int row_tiles = (rows + 15) >> 4;
-    const int chunks = K >> 3;                                         // 16-byte chunks per row
 
-    // Before the wait on the previous kernel: the block's weight rows, whole, and zeros for the
-    // batch rows that do not exist.
-    for (int idx = tid; idx < rows * chunks; idx += kThreads) {
-        const int r = idx / chunks, c = idx - r * chunks;
+    // The eight warps split K, and each is on its own until the final sum: it copies its columns of
+    // the block's weight rows before the wait on the previous kernel, its columns of the
+    // activations after it, and waits for its own copies only.  Which slice of K a warp takes
+    // rotates with the block, so that the blocks of the grid, which all want the same few
+    // activation rows at the same moment, do not all ask L2 for the same lines at once.
+    const int k_steps = K >> 4;
+    const int per = (k_steps + kWarps - 1) / kWarps;           // steps of 16 along K per warp
+    const int slice = (warp + blockIdx.x) % kWarps;
+    const int ks0 = min(slice * per, k_steps), ks1 = min(ks0 + per, k_steps);
+    const int c0 = 2 * ks0, nch = 2 * (ks1 - ks0);             // its 16-byte chunks of every row
+    for (int idx = lane; idx < rows * nch; idx += 32) {
+        const int r = idx / nch, c = c0 + idx - r * nch;
         cp_async16(at(sW, K, r, c), w + (size_t)(n0 + r) * K + (c << 3));
     }
     cp_async_commit();
-    for (int idx = tid; idx < (8 * NT - M) * chunks; idx += kThreads) {
-        const int r = M + idx / chunks, c = idx % chunks;
+    for (int idx = lane; idx < (8 * NT - M) * nch; idx += 32) {    // batch rows that do not exist
+        const int r = M + idx / nch, c = c0 + idx % nch;
         *reinterpret_cast<uint4*>(at(sX, K, r, c)) = make_uint4(0, 0, 0, 0);
     }
 
     lsb_pdl_wait();
-    for (int idx = tid; idx < M * chunks; idx += kThreads) {
-        const int r = idx / chunks, c = idx - r * chunks;
+    for (int idx = lane; idx < M * nch; idx += 32) {
+        const int r = idx / nch, c = c0 + idx - r * nch;
         cp_async16(at(sX, K, r, c), x + (size_t)r * K + (c << 3));
     }
     cp_async_commit();
     cp_async_wait_all();
-    __syncthreads();
+    __syncwarp();
 
     float acc[kMaxRowTiles][NT][4];
 #pragma unroll
@@ -97,10 +104,6 @@ gemm_small_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* 
 #pragma unroll
         for (int nt = 0; nt < NT; ++nt) acc[rt][nt][0] = acc[rt][nt][1] = acc[rt][nt][2] = acc[rt][nt][3] = 0.f;
 
-    // this warp's share of K, in steps of 16
-    const int k_steps = K >> 4;
-    const int per = (k_steps + kWarps - 1) / kWarps;
-    const int ks0 = warp * per, ks1 = min(ks0 + per, k_steps);
     // ldmatrix row addresses: A tiles (16 x 16): lanes 0-7 rows 0-7 / 8-15 rows 8-15 of the first
     // eight columns, lanes 16-31 the same rows of the next eight; B tiles (8 batch rows x 16)
     const int a_row = ((lane >> 3) & 1) * 8 + (lane & 7), a_half = lane >> 4;
@@ -120,7 +123,7 @@ gemm_small_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w, TOut* 
         }
     }
 
-    // sum over the warps in warp order, then one store per output
+    // sum over the warps in warp order (a fixed order for every output), then one store per output
     const int width = 8 * NT, height = 16 * row_tiles;
     float* mine = sRed + (size_t)warp * 16 * kMaxRowTiles * width;
 #pragma unroll
