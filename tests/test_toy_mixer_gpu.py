@@ -129,6 +129,12 @@ def _plain(cfg, w, toks):
 
 
 def test_toy_state_mixer_registers_builds_and_steps(tmp_path):
+    run_toy_model(tmp_path)
+
+
+def run_toy_model(tmp_path, **runner_options):
+    """Register, build and step the toy model; ``runner_options`` go to the ModelRunner (the
+    host-side test runs the same on the CPU with stand-in kernels)."""
     from llm_singularity_b200.engine import ModelRunner, StepEntry
     from llm_singularity_b200.engine.runner import expected_tensors_of
     from llm_singularity_b200.parts import StateSpec
@@ -143,7 +149,7 @@ def test_toy_state_mixer_registers_builds_and_steps(tmp_path):
     write_safetensors(os.path.join(d, "model.safetensors"), tensors)
     w = {k: v.double() for k, v in tensors.items()}
 
-    runner = ModelRunner(d, dtype="float32", page_size=16, num_pages=8, max_requests=2)
+    runner = ModelRunner(d, dtype="float32", page_size=16, num_pages=8, max_requests=2, **runner_options)
     specs = runner.model.cache_specs()
     assert isinstance(specs[0], StateSpec) and isinstance(specs[2], StateSpec) and len(specs) == 3
     a, b, c = (tiny_models.random_tokens(VOCAB, n, s) for n, s in ((23, 1), (40, 2), (9, 3)))

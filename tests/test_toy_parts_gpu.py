@@ -171,6 +171,12 @@ def _plain(cfg, w, toks):
 
 
 def test_toy_routed_feed_forward_and_learned_positions_register_build_and_step(tmp_path):
+    run_routed_model(tmp_path)
+
+
+def run_routed_model(tmp_path, **runner_options):
+    """``runner_options`` go to the ModelRunner (tests/test_toy_parts_host.py runs the same models
+    on the CPU with stand-in kernels)."""
     from llm_singularity_b200.engine import ModelRunner, StepEntry
     from llm_singularity_b200.engine.runner import expected_tensors_of
     from llm_singularity_b200.weights import random_tensors, write_safetensors
@@ -185,7 +191,7 @@ def test_toy_routed_feed_forward_and_learned_positions_register_build_and_step(t
     write_safetensors(os.path.join(d, "model.safetensors"), tensors)
     w = {k: v.double() for k, v in tensors.items()}
 
-    runner = ModelRunner(d, dtype="float32", page_size=8, num_pages=12, max_requests=2)
+    runner = ModelRunner(d, dtype="float32", page_size=8, num_pages=12, max_requests=2, **runner_options)
     seqs = {"a": tiny_models.random_tokens(VOCAB, 37, 5), "b": tiny_models.random_tokens(VOCAB, 50, 6)}
     got = {"a": [], "b": []}
     pos = {"a": 0, "b": 0}
@@ -270,6 +276,10 @@ def _plain_window(cfg, w, toks):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_a_windowed_layer_beside_a_full_one_keeps_pages_of_its_own(tmp_path, dtype):
+    run_windowed_model(tmp_path, dtype)
+
+
+def run_windowed_model(tmp_path, dtype, graphs=True, **runner_options):
     """Two attention layers, one seeing the last 40 keys only, one seeing all: two cache groups.
     Heads of 64, so bfloat16 runs the tensor-core kernels with their window arguments.  The
     windowed group gives pages back as the window passes them; logits match the plain model in
@@ -287,7 +297,7 @@ def test_a_windowed_layer_beside_a_full_one_keeps_pages_of_its_own(tmp_path, dty
     write_safetensors(os.path.join(d, "model.safetensors"), tensors)
     w = {k: v.double() for k, v in tensors.items()}
 
-    runner = ModelRunner(d, dtype=dtype, page_size=16, num_pages=40, max_requests=2)
+    runner = ModelRunner(d, dtype=dtype, page_size=16, num_pages=40, max_requests=2, **runner_options)
     cache = runner.cache
     assert sorted(g.window or 0 for g in cache.groups) == [0, 40]
     windowed = next(g for g in cache.groups if g.window)
@@ -306,7 +316,7 @@ def test_a_windowed_layer_beside_a_full_one_keeps_pages_of_its_own(tmp_path, dty
         for r, n in step:
             got[r].append(out[k:k + n].clone()); k += n; pos[r] += n      # graph logits are overwritten
     runner.check_kernels()
-    assert pos == {"a": 230, "b": 200} and runner.graph_replays >= 15
+    assert pos == {"a": 230, "b": 200} and (runner.graph_replays >= 15 or not graphs)
     # 430 tokens are held: 28 pages in the full group, only the windows' pages in the other
     assert full.pool.num_used == -(-230 // 16) + -(-200 // 16)
     assert windowed.pool.num_used <= 2 * (-(-40 // 16) + 1)
@@ -387,6 +397,10 @@ def _plain_shared(cfg, w, toks):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_a_layer_reads_another_layers_cache(tmp_path, dtype):
+    run_shared_cache_model(tmp_path, dtype)
+
+
+def run_shared_cache_model(tmp_path, dtype, graphs=True, **runner_options):
     """The run order lets the second layer attend over the keys and values the first one cached
     (it stores none of its own) and names the first block a second time with a cache of its own."""
     from llm_singularity_b200.engine import ModelRunner, StepEntry
@@ -401,7 +415,7 @@ def test_a_layer_reads_another_layers_cache(tmp_path, dtype):
                              dtype=torch.bfloat16, std=0.08, norm_noise=0.1)
     write_safetensors(os.path.join(d, "model.safetensors"), tensors)
     w = {k: v.double() for k, v in tensors.items()}
-    runner = ModelRunner(d, dtype=dtype, page_size=16, num_pages=24, max_requests=2)
+    runner = ModelRunner(d, dtype=dtype, page_size=16, num_pages=24, max_requests=2, **runner_options)
     assert len(runner.model.cache_specs()) == 2             # two caches for three layer calls
     seqs = {"a": tiny_models.random_tokens(157, 170, 3), "b": tiny_models.random_tokens(157, 60, 4)}
     plan = [[("a", 140)], [("a", 1), ("b", 33)], [("a", 1), ("b", 1)], [("a", 16), ("b", 14)]] + [[("a", 1), ("b", 1)]] * 12
@@ -414,7 +428,7 @@ def test_a_layer_reads_another_layers_cache(tmp_path, dtype):
         for r, n in step:
             got[r].append(out[k:k + n].clone()); k += n; pos[r] += n
     runner.check_kernels()
-    assert pos == {"a": 170, "b": 60} and runner.graph_replays >= 8
+    assert pos == {"a": 170, "b": 60} and (runner.graph_replays >= 8 or not graphs)
     for r in "ab":
         want = _plain_shared(cfg, w, seqs[r])
         have = torch.cat(got[r]).double().cpu()
