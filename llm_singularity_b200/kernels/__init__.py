@@ -156,6 +156,14 @@ def scatter_i32_counted(dst: torch.Tensor, packed: torch.Tensor, cap: int) -> No
           _stream(dst))
 
 
+def random_normal(out: torch.Tensor, key: int, mean: float, scale: float) -> None:
+    """out.flat[i] = mean + scale * normal(key, i): the counter-based stream of the random-weights
+    mode (``weights/random_init.py`` states the same arithmetic for the CPU)."""
+    _req(out, "out")
+    _call("random_init", "lsb_random_normal", _p(out), _i(_dt(out)), _ll(out.numel()),
+          ctypes.c_ulonglong(key & ((1 << 64) - 1)), _f(mean), _f(scale), _stream(out))
+
+
 def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
     """out[t, :] = float(table[ids[t], :])."""
     _req(table, "table", dim=2)

@@ -40,6 +40,7 @@ SOURCES: Dict[str, object] = {          # library -> its source file (or files)
     "gemm_tc": "gemm_tc.cu",
     "gemm_small": "gemm_small.cu",
     "sampling": "sampling.cu",
+    "random_init": "random_init.cu",
     # host code only: pools, block tables, prefix tree; scheduler
     "host_runtime": ("host_memory.cpp", "host_scheduler.cpp"),
 }

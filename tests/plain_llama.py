@@ -70,7 +70,7 @@ def sizes(cfg):
 # --------------------------------------------------------------------------- parts
 def embed(table, ids):
     """h0[t,:] = E[id_t,:] (kernels/src/embedding.cu:12-26)."""
-    return table[torch.as_tensor(ids, dtype=torch.long)]
+    return table[torch.as_tensor(ids, dtype=torch.long, device=table.device)]
 
 
 def rms_norm(x, w, eps):
@@ -107,8 +107,8 @@ def apply_rope(x, positions, inv_freq):
     (kernels/src/rope.cu:13-26: x0' = x0 cos - x1 sin, x1' = x0 sin + x1 cos).
     The angle is formed in 32-bit like the engine's (pos and f_i as floats)."""
     half = x.shape[-1] // 2
-    pos = torch.as_tensor(positions, dtype=torch.float32)
-    ang = (pos[:, None] * inv_freq.to(torch.float32)[None, :]).to(x.dtype)   # [n, half]
+    pos = torch.as_tensor(positions, dtype=torch.float32, device=x.device)
+    ang = (pos[:, None] * inv_freq.to(device=x.device, dtype=torch.float32)[None, :]).to(x.dtype)   # [n, half]
     cos, sin = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
     x0, x1 = x[..., :half], x[..., half:]
     return torch.cat([x0 * cos - x1 * sin, x0 * sin + x1 * cos], dim=-1)
@@ -126,7 +126,7 @@ def causal_attention(q, k, v, scale, window=None):
     for h in range(nh):
         g = h // group
         s = (q[:, h, :] @ k[:, g, :].T) * scale                 # [n, n]
-        i = torch.arange(n)
+        i = torch.arange(n, device=q.device)
         mask = i[None, :] <= i[:, None]
         if window is not None:
             mask &= i[None, :] > i[:, None] - window
@@ -177,23 +177,29 @@ def decoder_layer(x, w, i, cfg, positions, inv_freq, rnd=_no_rounding):
     return x + rnd(act @ w[p + "mlp.down_proj.weight"].T)
 
 
-def forward_logits(cfg, w, token_ids, dtype=torch.float64, act_round=None):
+def forward_logits(cfg, w, token_ids, dtype=torch.float64, act_round=None, rows=None, device=None):
     """Logits [n, vocab] at every position of one whole sequence
     (models/llama/llama_model.cpp:424-425,502-666; lm_head tied to the embedding when
     absent, :257-261).  ``act_round="bfloat16"`` rounds stored activations as a bfloat16
-    engine does, so that such an engine can be held to a tight tolerance."""
+    engine does, so that such an engine can be held to a tight tolerance.  ``rows``: only these
+    positions' logits are formed (the layers still run the whole sequence).  ``device``: where
+    the dense arithmetic runs (the CPU unless told otherwise; long sequences at large widths take
+    hours there); the result comes back to the CPU."""
     rnd = bf16_rounding if act_round == "bfloat16" else _no_rounding
-    w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in w.items()}
+    w = {k: (v.to(device=device, dtype=dtype) if v.is_floating_point() else v.to(device=device))
+         for k, v in w.items()}
     nh, nkv, hd = sizes(cfg)
     inv_freq = rope_inv_freq(hd, cfg.get("rope_theta", 10000.0), cfg.get("rope_scaling"))
     positions = list(range(len(token_ids)))
     x = embed(w["model.embed_tokens.weight"], token_ids)
     for i in range(cfg["num_hidden_layers"]):
         x = decoder_layer(x, w, i, cfg, positions, inv_freq, rnd)
+    if rows is not None:
+        x = x[torch.as_tensor(rows, dtype=torch.long, device=x.device)]
     x = rnd(rms_norm(x, w["model.norm.weight"], cfg.get("rms_norm_eps", 1e-5)))
     head = w["model.embed_tokens.weight"] if cfg.get("tie_word_embeddings", False) \
         else w["lm_head.weight"]
-    return x @ head.T
+    return (x @ head.T).cpu()
 
 
 def greedy_generate(cfg, w, prompt, n_new):

@@ -42,6 +42,34 @@ def replay_in_process(runner, steps, out_dir):
     return n
 
 
+def track_pages(runner):
+    """Wrap ``runner.step`` so that after every step the pages each of its requests holds are
+    noted; returns ``{group: {page id: set of requests that held it}}`` (filled as steps run)."""
+    held = {}
+    inner = runner.step
+
+    def step(entries, *a, **kw):
+        out = inner(entries, *a, **kw)
+        for e in entries:
+            for g in range(len(runner.cache.groups)):
+                for page in runner.cache.pages_of(e.request, g):
+                    held.setdefault(g, {}).setdefault(int(page), set()).add(e.request)
+        return out
+
+    runner.step = step
+    return held
+
+
+def assert_pages_were_used_again(held, seqs, max_tokens, what):
+    """The pool was smaller than what all requests need together, and at least one page id of
+    every group was held by two different requests over the run."""
+    total = sum(-(-len(t) // 64) * 64 for t in seqs.values())
+    assert max_tokens < total, f"{what}: pool of {max_tokens} tokens holds all requests ({total})"
+    for g, pages in held.items():
+        shared = [p for p, who in pages.items() if len(who) > 1]
+        assert shared, f"{what}: no page of group {g} was handed out twice"
+
+
 def replay_subprocess(model_dir, dtype, steps, out_dir, max_tokens, page_size=16, env=None):
     """Feed steps one at a time, waiting for each ``done`` line, as the protocol says."""
     cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir,

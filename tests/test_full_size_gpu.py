@@ -21,7 +21,7 @@ SIZES = dict(
     rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
                       original_max_position_embeddings=8192),
     rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=131072)
-LENGTHS = (150, 70, 33, 140)
+LENGTHS = (150, 70, 33, 140, 90, 129)     # six for four live places: pages are used again
 PAGE = 16
 F32_TOL = 2e-4       # observed 4.1e-5 on logits of up to 5.4 (float32 sums against float64 ones)
 BF16_REL = 4e-2      # of the largest plain logit, as for the tiny models; observed 1.9e-2
@@ -36,7 +36,7 @@ def full_size():
             for i, n in enumerate(LENGTHS)}
     with tempfile.TemporaryDirectory() as d:          # 2.5 GB, gone when the module is done
         write_random_model(d, LlamaConfig.from_dict(SIZES), seed=1, dtype=torch.bfloat16, std=0.02,
-                           norm_noise=0.0)
+                           norm_noise=0.0, device="cuda")
         cfg, w = plain_llama.load_model_dir(d)
         ref = {"float32": {r: plain_llama.forward_logits(cfg, w, t) for r, t in seqs.items()},
                "bfloat16": {r: plain_llama.forward_logits(cfg, w, t, act_round="bfloat16")
@@ -52,7 +52,10 @@ def test_replay_at_full_size_matches_plain(full_size, tmp_path, dtype, cut):
     steps, max_tokens = getattr(cuttings, cut)(seqs)
     runner = ModelRunner(d, dtype=dtype, page_size=PAGE, num_pages=max_tokens // PAGE, max_requests=4,
                          max_model_len=max_tokens)
+    held = replay_util.track_pages(runner)
     replay_util.replay_in_process(runner, steps, str(tmp_path))
+    if cut == "mixed":
+        replay_util.assert_pages_were_used_again(held, seqs, max_tokens, f"full size/{dtype}")
     rows = replay_util.collect(steps, str(tmp_path), SIZES["vocab_size"])
     largest = max(float(r.abs().max()) for r in ref[dtype].values())
     tol = F32_TOL if dtype == "float32" else BF16_REL * largest
@@ -73,16 +76,7 @@ def test_greedy_generation_at_full_size_matches_plain(full_size, dtype, margin):
                  max_tokens_per_batch=96)
     prompts = [seqs["r1"], seqs["r2"]]
     outs = eng.generate(prompts, max_new_tokens=4, ignore_eos=True)
-    compared = 0
-    for p, o in zip(prompts, outs):
-        toks = list(p)
-        for t in o:
-            logits = plain_llama.forward_logits(cfg, w, toks)[-1]
-            top = torch.topk(logits, 2).values
-            if float(top[0] - top[1]) < margin:
-                break                      # a near-tie: either token is a right answer
-            assert t == int(torch.argmax(logits)), (dtype, o)
-            toks.append(t)
-            compared += 1
+    from greedy_util import check_greedy
+    compared = sum(check_greedy(cfg, w, p, o, margin, dtype) for p, o in zip(prompts, outs))
     kernels.check_status()
     assert compared >= 4, f"only {compared} tokens could be compared"

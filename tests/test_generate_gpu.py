@@ -9,6 +9,7 @@ import torch
 
 import plain_llama
 import tiny_models
+from greedy_util import check_greedy
 
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
@@ -22,19 +23,6 @@ def _engine(model_dir, name, dtype, **kw):
     return Engine(model_dir, **opts)
 
 
-def _greedy_with_margin(cfg, w, prompt, n_new, margin):
-    """Plain greedy tokens, cut at the first step whose top-2 margin is below ``margin``."""
-    toks, out = list(prompt), []
-    for _ in range(n_new):
-        logits = plain_llama.forward_logits(cfg, w, toks)[-1]
-        top = torch.topk(logits, 2).values
-        if float(top[0] - top[1]) < margin:
-            break
-        t = int(torch.argmax(logits))
-        out.append(t); toks.append(t)
-    return out
-
-
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
 def test_greedy_generation_matches_plain(model_dirs, name, dtype):
@@ -45,14 +33,11 @@ def test_greedy_generation_matches_plain(model_dirs, name, dtype):
     margin = 1e-4 if dtype == "float32" else 0.05
     eng = _engine(model_dirs[name], name, dtype, prefill_chunk=24)
     outs = eng.generate(prompts, max_new_tokens=8, ignore_eos=True)
-    compared = 0
-    for p, o in zip(prompts, outs):
-        # tokens are compared up to the first step at which the plain top-2 margin is inside
-        # the dtype's rounding (a tie there may legitimately fall either way)
-        want = _greedy_with_margin(cfg, w, p, 8, margin)
-        assert len(o) == 8 and o[:len(want)] == want
-        compared += len(want)
-    assert compared >= 8
+    assert all(len(o) == 8 for o in outs)
+    # every token is checked; those at a step where the plain top-2 margin is inside the dtype's
+    # rounding may legitimately fall either way and are not counted
+    compared = sum(check_greedy(cfg, w, p, o, margin, f"{name}/{dtype}") for p, o in zip(prompts, outs))
+    assert compared >= 4 * len(prompts)
     eng.runner.cache.check_invariants()
 
 
@@ -119,16 +104,34 @@ def test_command_line(model_dirs, tmp_path):
     lines = [json.loads(l) for l in res.stdout.splitlines()]
     assert [l["tokens"] for l in lines] == [plain_llama.greedy_generate(cfg, w, p, 5) for p in prompts]
     assert '"stats"' in res.stderr
-    # random-weights mode needs only config.json
+
+
+@pytest.mark.parametrize("dtype, margin", [("fp32", 1e-5), ("bf16", 2e-3)])
+def test_command_line_random_weights_can_be_rebuilt_from_the_seed(tmp_path, dtype, margin):
+    """--random-weights needs only config.json, makes the weights on the device from --seed, and
+    the same weights made on the CPU from that seed give, in the plain implementation, the tokens
+    the command printed."""
+    from llm_singularity_b200.config.llama import LlamaConfig
+    from llm_singularity_b200.weights import write_random_model
     only_cfg = tmp_path / "cfg"
     only_cfg.mkdir()
     (only_cfg / "config.json").write_text(json.dumps(tiny_models.CONFIGS["tiny_b"]))
+    prompts = [tiny_models.random_tokens(512, n, 800 + n) for n in (9, 3, 30)]
+    (tmp_path / "p.json").write_text(json.dumps(prompts))
     cmd = [sys.executable, os.path.join(ROOT, "bin", "llm-serve-llama"), "--model-dir", str(only_cfg),
-           "--random-weights", "--seed", "7", "--prompt-len", "9", "--num-requests", "3",
-           "--max-new-tokens", "4", "--ignore-eos", "--num-kv-blocks", "32", "--max-batch-size", "4"]
+           "--random-weights", "--seed", "7", "--dtype", dtype, "--prompt-ids", str(tmp_path / "p.json"),
+           "--max-new-tokens", "6", "--ignore-eos", "--kv-block-size", "8", "--num-kv-blocks", "32",
+           "--max-batch-size", "4"]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
     assert res.returncode == 0, res.stderr
-    assert [len(json.loads(l)["tokens"]) for l in res.stdout.splitlines()] == [4, 4, 4]
+    got = [json.loads(l)["tokens"] for l in res.stdout.splitlines()]
+    rebuilt = str(tmp_path / "rebuilt")
+    write_random_model(rebuilt, LlamaConfig.from_dict(tiny_models.CONFIGS["tiny_b"]), seed=7,
+                       dtype=torch.float32 if dtype == "fp32" else torch.bfloat16)
+    cfg, w = plain_llama.load_model_dir(rebuilt)
+    assert all(len(o) == 6 for o in got)
+    compared = sum(check_greedy(cfg, w, p, o, margin, dtype) for p, o in zip(prompts, got))
+    assert compared >= 9, f"only {compared} tokens could be compared"
 
 
 @pytest.mark.parametrize("mode", ["decode", "prefill", "serve"])

@@ -38,6 +38,24 @@ def test_ops_refuse_cpu_tensors(ops):
         ops.swiglu(torch.zeros(2, 8), torch.zeros(2, 4))
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_random_weights_are_the_same_bits_on_the_device_and_on_the_cpu(ops, dtype):
+    """The random-weights stream: the kernel and the CPU statement of the same arithmetic."""
+    from llm_singularity_b200.weights.random_init import normal_tensor, random_tensors, tensor_key
+    key = tensor_key(12345, "model.layers.3.mlp.down_proj.weight")
+    for shape, mean, scale in (((1_000_003,), 0.0, 0.02), ((257, 129), 1.0, 0.1), ((1,), 0.0, 1.0)):
+        dev = normal_tensor(shape, key, mean, scale, dtype, "cuda")
+        cpu = normal_tensor(shape, key, mean, scale, dtype, "cpu")
+        assert dev.shape == cpu.shape
+        diff = (dev.cpu().view(torch.int16 if dtype == torch.bfloat16 else torch.int32)
+                != cpu.view(torch.int16 if dtype == torch.bfloat16 else torch.int32))
+        assert int(diff.sum()) == 0, f"{int(diff.sum())} of {diff.numel()} elements differ"
+    expected = {"a.weight": ((33, 65), "matrix", "normal"), "n.weight": ((65,), "vector", "ones")}
+    dev = random_tensors(expected, 9, dtype=dtype, std=0.05, norm_noise=0.1, device="cuda")
+    cpu = random_tensors(expected, 9, dtype=dtype, std=0.05, norm_noise=0.1)
+    assert all(torch.equal(dev[k].cpu(), cpu[k]) for k in expected)
+
+
 def test_scatter_i32(ops):
     dst = torch.full((5, 7), -1, dtype=torch.int32, device="cuda")
     idx = torch.tensor([0, 8, 34, 8], dtype=torch.int32, device="cuda")[:3]

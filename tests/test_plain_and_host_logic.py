@@ -102,7 +102,7 @@ def _requests(name, lengths, seed=0):
 @pytest.fixture(scope="module")
 def plain_refs(model_dirs):
     out = {}
-    for name, lengths in (("tiny_a", (5, 17, 33, 70)), ("tiny_b", (1, 9, 40, 70, 50, 23))):
+    for name, lengths in (("tiny_a", (5, 17, 33, 70, 100, 64, 20)), ("tiny_b", (1, 9, 40, 70, 50, 23))):
         cfg, w = plain_llama.load_model_dir(model_dirs[name])
         seqs = _requests(name, lengths)
         out[name] = (seqs, {rid: plain_llama.forward_logits(cfg, w, t) for rid, t in seqs.items()})
@@ -118,15 +118,19 @@ def test_host_logic_matches_plain_under_every_cutting(model_dirs, plain_refs, tm
     runner = ModelRunner(model_dirs[name], dtype="float32", device="cpu", page_size=ps,
                          num_pages=max_tokens // ps, max_requests=4, max_model_len=max_tokens,
                          ops=standin_ops)
+    held = replay_util.track_pages(runner)
     replay_util.replay_in_process(runner, steps, str(tmp_path))
     rows = replay_util.collect(steps, str(tmp_path), tiny_models.CONFIGS[name]["vocab_size"])
     replay_util.compare(rows, refs, 2e-5, f"{name}/{cut}")
+    if cut == "mixed":
+        replay_util.assert_pages_were_used_again(held, seqs, max_tokens, name)
     runner.cache.check_invariants()
     assert runner.cache.free_pages() == max_tokens // ps          # everything was given back
 
 
-def test_mixed_cutting_really_reuses_pages_and_mixes(plain_refs):
-    seqs, _ = plain_refs["tiny_b"]
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_mixed_cutting_really_reuses_pages_and_mixes(plain_refs, name):
+    seqs, _ = plain_refs[name]
     steps, max_tokens = cuttings.mixed(seqs)
     assert max_tokens < sum(-(-len(t) // 64) * 64 for t in seqs.values())      # pool < total
     assert any(len(s["entries"]) >= 3 for s in steps)

@@ -15,8 +15,10 @@ import tiny_models
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"tiny_a": (5, 17, 33, 70), "tiny_b": (1, 9, 40, 70, 50, 23), "tiny_c": (3, 64, 65, 47, 2),
-           "tiny_d": (130, 64, 7, 65, 200), "tiny_e": (150, 3, 129, 66)}
+# more requests than the mixed cutting keeps live (four), so that pages are handed out again
+LENGTHS = {"tiny_a": (5, 17, 33, 70, 100, 64, 20), "tiny_b": (1, 9, 40, 70, 50, 23),
+           "tiny_c": (3, 64, 65, 47, 2), "tiny_d": (130, 64, 7, 65, 200),
+           "tiny_e": (150, 3, 129, 66, 200, 40)}
 F32_TOL = 1e-4            # float32 logits against float64 plain logits (observed ~1e-6)
 # bfloat16 is held to the plain implementation with activations rounded to bfloat16 at the same
 # places; what is left is summation order and single-ulp (2^-8) flips, which the sharpened
@@ -69,9 +71,15 @@ def test_replay_matches_plain(model_dirs, refs, tmp_path, name, dtype, cut):
     seqs, ref = _pick(refs, name, dtype)
     steps, max_tokens = getattr(cuttings, cut)(seqs)
     runner = _runner(model_dirs[name], name, dtype, max_tokens)
+    held = replay_util.track_pages(runner)
     replay_util.replay_in_process(runner, steps, str(tmp_path))
     rows = replay_util.collect(steps, str(tmp_path), tiny_models.CONFIGS[name]["vocab_size"])
     replay_util.compare(rows, ref, _tol(dtype, ref), f"{name}/{dtype}/{cut}")
+    if cut == "mixed":
+        replay_util.assert_pages_were_used_again(held, seqs, max_tokens, f"{name}/{dtype}")
+        assert any(len(s["entries"]) >= 3 for s in steps)
+        assert any(min(len(e["tokens"]) for e in s["entries"]) == 1 <
+                   max(len(e["tokens"]) for e in s["entries"]) for s in steps)
     runner.cache.check_invariants()
     assert runner.cache.free_pages() == max_tokens // tiny_models.PAGE_SIZE[name]
 

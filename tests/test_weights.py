@@ -77,6 +77,32 @@ def test_random_weights_mode_writes_a_loadable_folder(tmp_path):
     assert json.load(open(os.path.join(d, "config.json")))["architectures"] == ["LlamaForCausalLM"]
 
 
+def test_random_stream_is_counter_based():
+    """Element i of a tensor is a function of (seed, name, i) alone: a piece made on its own is
+    the same piece, another name or seed gives another stream, and the values are standard normal.
+    The first values are written down here, so that a change of the arithmetic (which would make
+    models of earlier seeds unrepeatable) is seen."""
+    from llm_singularity_b200.weights.random_init import _normal_cpu, normal_tensor, tensor_key
+    key = tensor_key(7, "model.embed_tokens.weight")
+    head = _normal_cpu(key, 0, 6)
+    pinned = [-0.210832417011261, 0.22373543679714203, -1.0792911052703857, 0.40433570742607117,
+              0.9879299402236938, 0.8777292370796204]
+    assert head.tolist() == pinned
+    assert torch.equal(_normal_cpu(key, 3, 3), head[3:])
+    big = normal_tensor((1 << 20) + 5, key, 0.0, 1.0, torch.float32)        # crosses a chunk's edge
+    assert torch.equal(big[:6], head) and torch.equal(big[(1 << 20) - 2:], _normal_cpu(key, (1 << 20) - 2, 7))
+    assert not torch.equal(_normal_cpu(tensor_key(7, "lm_head.weight"), 0, 6), head)
+    assert not torch.equal(_normal_cpu(tensor_key(8, "model.embed_tokens.weight"), 0, 6), head)
+    x = big.double()
+    assert torch.isfinite(x).all()
+    assert abs(x.mean()) < 4e-3 and abs(x.var() - 1) < 6e-3
+    assert abs((x ** 3).mean()) < 1.5e-2 and abs((x ** 4).mean() - 3) < 5e-2
+    assert (x.abs() > 3).double().mean() == pytest.approx(0.0027, abs=4e-4)   # the tails are there
+    # mean and scale, and one rounding to the stored dtype
+    w = normal_tensor((4, 5), key, 1.0, 0.1, torch.bfloat16)
+    assert torch.equal(w.view(-1)[:6], (1.0 + torch.tensor(0.1) * head).to(torch.bfloat16))
+
+
 def test_32_bit_tensors_stay_32_bit(tmp_path):
     cfg = LlamaConfig.from_dict(tiny_models.CONFIGS["tiny_a"])
     d = str(tmp_path / "m")
