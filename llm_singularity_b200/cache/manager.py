@@ -24,38 +24,21 @@ from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
-from ..parts.base import PagedKVSpec, StateSpec
+from ..parts.base import CacheSpec, KVCacheView, StateView      # noqa: F401  (views re-exported)
 from . import native
 from .pages import PageError, PagePool, _Handle
 
 NO_PAGE = -1
 
 
-@dataclass
-class KVCacheView:
-    """What an attention call sees of its cache."""
-
-    k_pages: torch.Tensor          # [num_pages, kv_heads, page_size, head_dim]
-    v_pages: torch.Tensor
-    block_table: torch.Tensor      # int32 [slots, max_pages]; rows picked by ctx.table_rows
-    page_size: int
-    window: Optional[int]
-    group: int
-
-
-@dataclass
-class StateView:
-    """What a mixer with fixed-size state sees: ``state[ctx.table_rows[r]]`` is request r's."""
-
-    state: torch.Tensor            # [slots, *shape]
-
-
 class _Group:
     """One group's Python face: its pool and its host table are views into the memory layer."""
 
     def __init__(self, handle: _Handle, index: int, window: Optional[int], num_pages: int,
-                 slots: int, max_pages: int):
+                 slots: int, max_pages: int, page_size: int):
+        self.index = index
         self.window = window
+        self.page_size = page_size
         self.pool = PagePool(num_pages, _handle=handle, _group=index)
         self.cache_ids: List[int] = []
         ptr = handle.lib.lsbm_table(handle.ptr, index)
@@ -66,7 +49,7 @@ class _Group:
 class CacheManager:
     def __init__(self, cache_specs: Sequence[object], page_size: int, num_pages,
                  max_requests: int, max_pages_per_request: int, rt=None):
-        """``cache_specs[i]`` is what cache id ``i`` holds (PagedKVSpec, StateSpec or None);
+        """``cache_specs[i]`` is what cache id ``i`` holds (a ``CacheSpec`` or None);
         ``num_pages`` is an int (every group gets that many) or ``{window: pages}``."""
         if page_size <= 0:
             raise ValueError("page_size must be positive")
@@ -77,22 +60,23 @@ class CacheManager:
         self.groups: List[_Group] = []
         self._group_of: Dict[int, int] = {}
         self._specs = list(cache_specs)
-        self._kv: Dict[int, Tuple[torch.Tensor, torch.Tensor]] = {}
-        self._state: Dict[int, torch.Tensor] = {}
+        self._store: Dict[int, object] = {}            # cache id -> what its spec allocated
         self._slots: Dict[Hashable, int] = {}          # request id -> slot
 
         windows: List[Optional[int]] = []              # one entry per group, in order of first use
         members: List[List[int]] = []
         for cid, cs in enumerate(self._specs):
-            if isinstance(cs, PagedKVSpec):
+            if cs is None:
+                continue
+            if not isinstance(cs, CacheSpec):
+                raise TypeError(f"cache {cid}: {cs!r} is not a CacheSpec")
+            if cs.paged:                               # caches with one release rule share a group
                 if cs.window not in windows:
                     windows.append(cs.window)
                     members.append([])
                 g = windows.index(cs.window)
                 members[g].append(cid)
                 self._group_of[cid] = g
-            elif not (cs is None or isinstance(cs, StateSpec)):
-                raise TypeError(f"cache {cid}: unknown cache spec {cs!r}")
         sizes = [num_pages[w] if isinstance(num_pages, dict) else num_pages for w in windows]
         if any(n <= 0 for n in sizes):
             raise ValueError(f"a page pool needs at least one page, got {sizes}")
@@ -100,7 +84,7 @@ class CacheManager:
                           [-1 if w is None else w for w in windows], sizes)
         self._lib, self._ptr = self._h.lib, self._h.ptr
         for g, (w, n) in enumerate(zip(windows, sizes)):
-            grp = _Group(self._h, g, w, n, max_requests, max_pages_per_request)
+            grp = _Group(self._h, g, w, n, max_requests, max_pages_per_request, page_size)
             grp.cache_ids = members[g]
             self.groups.append(grp)
         self._page_buf = (ctypes.c_int * max_pages_per_request)()
@@ -112,19 +96,14 @@ class CacheManager:
         for g in self.groups:
             g.dev_table = torch.full(g.table.shape, NO_PAGE, dtype=torch.int32, device=rt.device)
         for cid, cs in enumerate(self._specs):
-            if isinstance(cs, PagedKVSpec):
-                n = self.groups[self._group_of[cid]].pool.num_pages
-                shape = (n, cs.num_kv_heads, self.page_size, cs.head_dim)
-                self._kv[cid] = (torch.zeros(shape, dtype=rt.dtype, device=rt.device),
-                                 torch.zeros(shape, dtype=rt.dtype, device=rt.device))
-            elif isinstance(cs, StateSpec):
-                self._state[cid] = torch.zeros((self.max_requests,) + tuple(cs.shape),
-                                               dtype=cs.dtype, device=rt.device)
+            if cs is not None:
+                n = self.groups[self._group_of[cid]].pool.num_pages if cs.paged else None
+                self._store[cid] = cs.allocate(rt, self.page_size, n, self.max_requests)
 
     def bytes_per_page(self, group: int) -> int:
         """Bytes one page id stands for, over all layers of the group (keys and values)."""
         esize = 4 if self.rt is None else torch.empty((), dtype=self.rt.dtype).element_size()
-        return sum(2 * self._specs[c].num_kv_heads * self.page_size * self._specs[c].head_dim * esize
+        return sum(self._specs[c].bytes_per_page(self.page_size, esize)
                    for c in self.groups[group].cache_ids)
 
     # ---------------------------------------------------------------- requests
@@ -143,8 +122,7 @@ class CacheManager:
         if slot < 0:
             return None
         self._slots[request] = slot
-        for st in self._state.values():
-            st[slot].zero_()
+        self._reset(slot)
         return slot
 
     def bind(self, request: Hashable, slot: int) -> None:
@@ -153,8 +131,11 @@ class CacheManager:
         if request in self._slots:
             raise KeyError(f"request {request!r} is already open")
         self._slots[request] = slot
-        for st in self._state.values():
-            st[slot].zero_()
+        self._reset(slot)
+
+    def _reset(self, slot: int) -> None:
+        for cid, store in self._store.items():
+            self._specs[cid].reset(store, slot)
 
     def unbind(self, request: Hashable) -> None:
         """The memory layer has closed the request's slot already (see :meth:`bind`)."""
@@ -233,14 +214,10 @@ class CacheManager:
 
     def view(self, cache_id: int, ctx=None):
         cs = self._specs[cache_id]
-        if isinstance(cs, PagedKVSpec):
-            gi = self._group_of[cache_id]
-            g = self.groups[gi]
-            k, v = self._kv[cache_id]
-            return KVCacheView(k, v, g.dev_table, self.page_size, g.window, gi)
-        if isinstance(cs, StateSpec):
-            return StateView(self._state[cache_id])
-        return None
+        if cs is None:
+            return None
+        group = self.groups[self._group_of[cache_id]] if cs.paged else None
+        return cs.view(self._store.get(cache_id), group)
 
     # -------------------------------------------------------------- invariants
     def check_invariants(self) -> None:

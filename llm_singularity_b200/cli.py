@@ -89,7 +89,8 @@ def run_bench(eng, args) -> dict:
                 eng.step()
             times.append(_sync_time(dev) - t0)
         best = min(times[1:])
-        out.update(seconds=round(best, 6), prompt_tokens_per_s=round(args.prompt_len / best, 1))
+        out.update(seconds=round(best, 6), prompt_tokens=args.prompt_len, runs=len(times),
+                   prompt_tokens_per_s=round(args.prompt_len / best, 1))
     elif args.bench == "decode":
         n_new = max(2, args.max_new_tokens)
         for i in range(args.num_requests):
@@ -103,7 +104,7 @@ def run_bench(eng, args) -> dict:
         for _ in range(n_new - 4):
             made += len(eng.step())
         dt = _sync_time(dev) - t0
-        out.update(seconds=round(dt, 6), decode_steps=n_new - 4,
+        out.update(seconds=round(dt, 6), decode_steps=n_new - 4, generated_tokens=made,
                    generated_tokens_per_s=round(made / dt, 1))
         while eng.has_work():
             eng.step()

@@ -129,8 +129,10 @@ class LlamaConfig:
             raise ConfigError(
                 f"num_attention_heads {self.num_attention_heads} must be a multiple of "
                 f"num_key_value_heads {self.num_key_value_heads}")
-        if self.head_dim <= 0 or self.head_dim % 2:
-            raise ConfigError(f"head_dim {self.head_dim} must be positive and even")
+        if self.head_dim <= 0 or self.head_dim % 16 or self.head_dim > 256:
+            # what the attention kernels take (csrc/attention.cu); refused here, when the
+            # configuration is read, not at the first step
+            raise ConfigError(f"head_dim {self.head_dim} must be a multiple of 16, at most 256")
         if self.rms_norm_eps <= 0:
             raise ConfigError(f"rms_norm_eps must be positive, got {self.rms_norm_eps}")
         if self.rope_theta <= 0:

@@ -808,11 +808,12 @@ static int decode_launch(const void* qkv, int qkv_stride, void* k_pages, void* v
                          const int* block_table, int table_stride, void* out, float* scratch,
                          int n_requests, int nh, int nkv, int hd, int page_size, int num_pages,
                          float scale, int window, int splits, const float* inv_freq, int store_kv,
-                         cudaStream_t stream) {
+                         int max_cluster_size, cudaStream_t stream) {
     if (n_requests <= 0) return 0;
     if (nkv <= 0 || nh % nkv || nh / nkv > 16 || splits < 1 || n_requests > 65535 || nkv > 65535)
         return (int)cudaErrorInvalidValue;
-    const int cluster_cap = lsb_decode_max_cluster(hd);
+    // up to this many splits merge inside a thread-block cluster (0: as many as the device takes)
+    const int cluster_cap = max_cluster_size > 0 ? max_cluster_size : lsb_decode_max_cluster(hd);
     if (splits > cluster_cap && !scratch) return (int)cudaErrorInvalidValue;
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)n_requests * nh * splits * hd : nullptr;
@@ -849,7 +850,7 @@ LSB_API int lsb_decode_attention(const void* qkv, int qkv_stride, const void* k_
                                  float scale, int window, int splits, cudaStream_t stream) {
     return decode_launch(qkv, qkv_stride, const_cast<void*>(k_pages), const_cast<void*>(v_pages), q_start,
                          kv_len, table_rows, block_table, table_stride, out, scratch, n_requests, nh, nkv,
-                         hd, page_size, num_pages, scale, window, splits, nullptr, 0, stream);
+                         hd, page_size, num_pages, scale, window, splits, nullptr, 0, 0, stream);
 }
 
 // The same over a projection that has not been rotated yet: the kernel rotates the queries and the
@@ -865,7 +866,7 @@ LSB_API int lsb_decode_attention_rope(const void* qkv, int qkv_stride, void* k_p
     if (!inv_freq) return (int)cudaErrorInvalidValue;
     return decode_launch(qkv, qkv_stride, k_pages, v_pages, q_start, kv_len, table_rows, block_table,
                          table_stride, out, scratch, n_requests, nh, nkv, hd, page_size, num_pages,
-                         scale, window, splits, inv_freq, store_kv, stream);
+                         scale, window, splits, inv_freq, store_kv, 0, stream);
 }
 
 // Prompt portions (and, unless skip_single, single tokens too).  bf16, hd 64 or 128.
@@ -905,6 +906,7 @@ static __device__ __align__(256) float lsb_noalloc_scratch[kNoAllocFloats];
 // In host code `lsb_noalloc_scratch` is only a handle for the runtime, not an address a
 // kernel could use: the device address is looked up once per device and kept here.
 constexpr int kNoAllocMaxDevices = 64;
+constexpr int kNoAllocCluster = 8;
 static float* g_noalloc_dev_ptr[kNoAllocMaxDevices] = {};
 
 LSB_API long long lsb_decode_attention_noalloc_max_floats(void) { return kNoAllocFloats; }
@@ -912,7 +914,7 @@ LSB_API long long lsb_decode_attention_noalloc_max_floats(void) { return kNoAllo
 LSB_API const char* lsb_decode_attention_noalloc_error(int code) {
     if (code == LSB_NOALLOC_TOO_LARGE)
         return "decode attention (no-alloc): n_requests * nh * splits * (hd + 2) exceeds the "
-               "built-in scratch array; use fewer splits or the regular entry point";
+               "built-in scratch array; use at most 8 splits (they need none) or the regular entry point";
     if (code == LSB_NOALLOC_BAD_DEVICE)
         return "decode attention (no-alloc): current device index is outside the library's table";
     return cudaGetErrorString((cudaError_t)code);
@@ -928,8 +930,10 @@ LSB_API int lsb_decode_attention_noalloc(const void* qkv, int qkv_stride, const 
     if (nkv <= 0 || nh % nkv || nh / nkv > 16 || splits < 1 || n_requests > 65535 || nkv > 65535 ||
         (hd != 64 && hd != 128))
         return (int)cudaErrorInvalidValue;
+    // Up to kNoAllocCluster splits (the portable cluster size) merge through distributed shared
+    // memory and touch no scratch; only more splits than that go through the array.
     float* scratch = nullptr;
-    if (splits > 1) {
+    if (splits > kNoAllocCluster) {
         if (lsb_decode_scratch_floats(n_requests, nh, hd, splits) > kNoAllocFloats)
             return LSB_NOALLOC_TOO_LARGE;
         int dev = -1;
@@ -944,31 +948,7 @@ LSB_API int lsb_decode_attention_noalloc(const void* qkv, int qkv_stride, const 
         }
         scratch = g_noalloc_dev_ptr[dev];
     }
-    float* part_o = scratch;
-    float* part_ml = scratch ? scratch + (size_t)n_requests * nh * splits * hd : nullptr;
-    dim3 grid(splits, nkv, n_requests);
-    const bool in_cluster = splits > 1 && splits <= 8;      // x is the cluster dimension
-#define LAUNCH_DECODE_NOALLOC(HD)                                                                  \
-    do {                                                                                           \
-        int rc = configure_once<HD>();                                                             \
-        if (rc) return rc;                                                                         \
-        rc = lsb_launch(nh / nkv <= 8 ? decode_attention_kernel<HD, true>                          \
-                                      : decode_attention_kernel<HD, false>,                        \
-            grid, dim3(kThreads), decode_smem<HD>(), stream,                                       \
-            in_cluster ? splits : 1,                                                               \
-            (const bf16*)qkv, qkv_stride, (bf16*)const_cast<void*>(k_pages),                      \
-            (bf16*)const_cast<void*>(v_pages), q_start,                                            \
-            kv_len, table_rows, block_table, table_stride, (bf16*)out, part_o, part_ml, nh, nkv,  \
-            page_size, num_pages, scale, window, splits, in_cluster ? 1 : 0,                       \
-            (const float*)nullptr, 0);                                                             \
-        if (rc) return rc;                                                                         \
-        if (splits > 1 && !in_cluster)                                                             \
-            rc = lsb_launch(decode_merge_kernel<HD>, dim3(nh, n_requests), dim3(64), 0, stream, 1, \
-                (const float*)part_o, (const float*)part_ml, q_start, (bf16*)out, nh, splits);     \
-        if (rc) return rc;                                                                         \
-    } while (0)
-    if (hd == 64) LAUNCH_DECODE_NOALLOC(64);
-    else LAUNCH_DECODE_NOALLOC(128);
-#undef LAUNCH_DECODE_NOALLOC
-    return 0;
+    return decode_launch(qkv, qkv_stride, const_cast<void*>(k_pages), const_cast<void*>(v_pages), q_start,
+                         kv_len, table_rows, block_table, table_stride, out, scratch, n_requests, nh, nkv,
+                         hd, page_size, num_pages, scale, window, splits, nullptr, 0, kNoAllocCluster, stream);
 }

@@ -13,13 +13,14 @@
 //
 // Rules for callers:
 //   * Inputs and the output are still the caller's buffers.
-//   * n_requests * nh * splits * (hd + 2) must not exceed the maximum when
-//     splits > 1; larger problems are refused with LSB_NOALLOC_TOO_LARGE and
-//     nothing is launched.  With splits == 1 no scratch is used at all, and up
-//     to 8 splits are merged inside a thread-block cluster without touching it.
-//   * The first call on each device looks up the array's device address (with
-//     that device current).  Make that first call before starting any stream
-//     capture, and from one thread.
+//   * With up to 8 splits no scratch is used at all (one split needs none, and
+//     2 to 8 splits are merged inside a thread-block cluster), so any size is
+//     taken.  With more than 8 splits n_requests * nh * splits * (hd + 2) must
+//     not exceed the maximum; larger problems are refused with
+//     LSB_NOALLOC_TOO_LARGE and nothing is launched.
+//   * The first call with more than 8 splits on each device looks up the
+//     array's device address (with that device current).  Make that first call
+//     before starting any stream capture, and from one thread.
 //   * All calls share the one array, and it keeps whatever the previous call
 //     left there.  The kernels write every slot before they read it, so nothing
 //     has to be cleared, but two calls that overlap on the GPU (different

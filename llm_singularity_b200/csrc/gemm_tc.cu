@@ -51,8 +51,9 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     return ok != 0;
 }
 // Bounded wait: false if the limit ran out or another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag,
+                                          uint32_t limit = kSpinLimit) {
+    for (uint32_t it = 0; it < limit; ++it) {
         if (mbar_try_wait(bar, parity)) return true;
         if ((it & 255u) == 255u) {
             if (*abort_flag) return false;
@@ -149,6 +150,7 @@ struct GemmParams {
     int splits;                   // > 1: the blocks of one tile form a cluster along z
     int out_f32;                  // output element type
     int swiglu;                   // 0: plain; 1: weight rows alternate gate/up along j; 2: along i.
+    int act;                      // gated products: 1 silu, 2 gelu (tanh form), 3 none (gate * up)
                                   // The output then has half as many columns: silu(gate) * up.
     int static_operand;           // 1: P holds weights, 2: Q does (loaded before the PDL wait)
     void* out;                    // bf16 or float
@@ -167,13 +169,19 @@ __device__ __forceinline__ void load_acc(uint32_t tmem_base, int q, int c0, bool
     }
 }
 
-// silu(g) * u with the special-function unit: ex2 and an approximate division (each good to about
-// 1e-7 relative, far inside the rounding of the bfloat16 result).  The division must be the
-// approximate one: for very negative gates 1 + e^-g is huge or infinite and an IEEE reciprocal
-// drops into its slow denormal path, which cost 15 us per tile on random data.
-__device__ __forceinline__ float silu_mul(float g, float u) {
-    return __fdividef(g, 1.f + __expf(-g)) * u;
+// act(g) * u for a gated product, with the special-function unit: ex2 and an approximate division
+// (each good to about 1e-7 relative, far inside the rounding of the bfloat16 result).  silu(g) =
+// g / (1 + e^-g); the tanh form of gelu, 0.5 g (1 + tanh(c (g + 0.044715 g^3))), is the same
+// expression with another exponent, g / (1 + e^(-2 c (g + 0.044715 g^3))), c = sqrt(2 / pi).  The
+// division must be the approximate one: for very negative gates 1 + e^-g is huge or infinite and
+// an IEEE reciprocal drops into its slow denormal path, which cost 15 us per tile on random data.
+enum : int { LSB_ACT_SILU = 1, LSB_ACT_GELU_TANH = 2, LSB_ACT_NONE = 3 };
+__device__ __forceinline__ float gate_mul(float g, float u, int act) {
+    if (act == LSB_ACT_NONE) return g * u;
+    const float a = act == LSB_ACT_GELU_TANH ? 1.5957691216f * (g + 0.044715f * g * g * g) : g;
+    return __fdividef(g, 1.f + __expf(-a)) * u;
 }
+#define silu_mul(g, u) gate_mul((g), (u), prm.act)
 
 template <typename T> __device__ __forceinline__ void put(void* base, long long off, float v);
 template <> __device__ __forceinline__ void put<float>(void* base, long long off, float v) {
@@ -764,6 +772,43 @@ static int launch_persistent(const CUtensorMap& mp, const CUtensorMap& mq, const
                       mp, mq, prm, tiles_m, tiles_n);
 }
 
+// What happens when a wait runs out, shown without a fault: one block, a barrier that nothing
+// arrives at.  Thread 0 waits on it with a limit of `limit` polls, gives up, raises the block's
+// abort flag and records LSB_WAIT_TIMEOUT in the status word; thread 32 waits with the kernels'
+// full limit and leaves as soon as it sees the flag.  result[0], result[1]: 1 where the wait
+// returned false.  The kernel always ends by itself; the host then reads the status word.
+__global__ void wait_timeout_probe_kernel(uint32_t limit, int* __restrict__ result) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) result[0] = mbar_wait(&bar, 0, &abort_flag, limit) ? 0 : 1;
+    if (threadIdx.x == 32) result[1] = mbar_wait(&bar, 0, &abort_flag) ? 0 : 1;
+}
+
+LSB_API int lsb_gemm_tc_wait_probe(int limit, int* result, cudaStream_t stream) {
+    if (limit < 1 || limit > (1 << 16)) return (int)cudaErrorInvalidValue;
+    wait_timeout_probe_kernel<<<1, 64, 0, stream>>>((uint32_t)limit, result);
+    return LSB_LAUNCH_CHECK();
+}
+
+// SMs of the current device (asked once per device).
+static int num_sms() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 1;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 1;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
 // Can this kernel take the product?  (TMA needs 16-byte aligned bases and row strides.)
 LSB_API int lsb_gemm_tc_supported(const void* x, const void* w, int M, int N, int K) {
     return M > 0 && N > 0 && K > 0 && K % 8 == 0 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0;
@@ -775,13 +820,15 @@ LSB_API int lsb_gemm_tc_supported(const void* x, const void* w, int M, int N, in
 // portable cluster size limits the splits to 8.
 LSB_API int lsb_gemm_tc_plan(int M, int N, int K, int swiglu, int* swap, int* bn, int* splits) {
     const int num_kb = (K + kBK - 1) / kBK;
+    const int sms = num_sms();
+    const int most = sms * 13 / 16;              // "nearly every SM has a tile" (120 of 148)
     if (M <= 128) {
         *swap = 1;
         *bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
         const int tiles = (N + kBM - 1) / kBM;
         int s = 1;
-        if (tiles < 120 && !swiglu) {            // too few slabs to fill 148 SMs: split K
-            s = (148 + tiles - 1) / tiles;
+        if (tiles < most && !swiglu) {           // too few slabs to fill the SMs: split K
+            s = (sms + tiles - 1) / tiles;
             if (s > 8) s = 8;
             if (s > num_kb / 4) s = num_kb / 4 > 0 ? num_kb / 4 : 1;   // at least 4 K blocks each
             if (s < 1) s = 1;
@@ -800,24 +847,24 @@ LSB_API int lsb_gemm_tc_plan(int M, int N, int K, int swiglu, int* swap, int* bn
         const int cands[3] = {256, 128, 64};
         for (int c = 0; c < 3; ++c) {
             const int t = mt * ((N + cands[c] - 1) / cands[c]);
-            const int waves = (t + 147) / 148;
-            double eff = (double)t / (waves * 148.0);
+            const int waves = (t + sms - 1) / sms;
+            double eff = (double)t / ((double)waves * sms);
             if (cands[c] == 64) eff *= 0.8;      // narrower tiles reuse P less
             else if (cands[c] == 128) eff *= 0.93;
             if (eff > best_eff + 1e-9) { best_eff = eff; best = cands[c]; }
         }
         // persistent blocks walk the tile list, so whole waves no longer matter: take the widest
         // tile unless that leaves SMs without any
-        if (mt * ((N + 255) / 256) >= 120 || N >= 2048) best = 256;
+        if (mt * ((N + 255) / 256) >= most || N >= 2048) best = 256;
         *bn = best;
         *splits = 1;
-        // A few hundred tokens make too few 128 x 256 tiles for 148 SMs.  Where the walk through K
+        // A few hundred tokens make too few 128 x 256 tiles for the SMs.  Where the walk through K
         // is long (the down projection), K is split over a cluster, as many ways as fit in one
         // wave; summing the partial tiles costs about as much as 2048 of K, so shorter walks stay
         // whole.  (The gated epilogue needs whole sums: gated products stay unsplit too.)
         const int tiles = mt * ((N + 255) / 256);
-        if (best == 256 && tiles < 120 && !swiglu) {
-            int s = 148 / tiles;
+        if (best == 256 && tiles < most && !swiglu) {
+            int s = sms / tiles;
             if (s > 8) s = 8;
             if (s > num_kb / 32) s = num_kb / 32;
             if (s > 1) {
@@ -827,18 +874,19 @@ LSB_API int lsb_gemm_tc_plan(int M, int N, int K, int swiglu, int* swap, int* bn
         }
         // Unsplit and at most half the SMs busy: tiles half as wide bring the rest in (each
         // block's stream of operands, which is what a lone tile waits for, gets shorter).
-        if (*splits == 1 && best == 256 && tiles <= 74 && N > 128) *bn = 128;
+        if (*splits == 1 && best == 256 && tiles <= sms / 2 && N > 128) *bn = 128;
     }
     return 0;
 }
 
 // out[M, N] = x[M, K] * w[N, K]^T, bf16 inputs, bf16 or float output.
 // swiglu != 0: w has 2 * N_out rows alternating gate_i, up_i; out is [M, N / 2] with
-// out[m, i] = silu(d[m, 2i]) * d[m, 2i + 1].
+// out[m, i] = act(d[m, 2i]) * d[m, 2i + 1], act named by swiglu: 1 silu, 2 gelu (tanh form), 3 none.
 LSB_API int lsb_gemm_tc(const void* x, const void* w, void* out, int out_f32, int M, int N, int K,
                         int swiglu, cudaStream_t stream) {
     if (!lsb_gemm_tc_supported(x, w, M, N, K)) return (int)cudaErrorInvalidValue;
     if (swiglu && (N % 2)) return (int)cudaErrorInvalidValue;
+    if (swiglu < 0 || swiglu > LSB_ACT_NONE) return (int)cudaErrorInvalidValue;
     int swap, bn, splits;
     lsb_gemm_tc_plan(M, N, K, swiglu, &swap, &bn, &splits);
     const int n_out = swiglu ? N / 2 : N;
@@ -849,6 +897,8 @@ LSB_API int lsb_gemm_tc(const void* x, const void* w, void* out, int out_f32, in
     prm.splits = splits;
     prm.out_f32 = out_f32;
     prm.out = out;
+    prm.act = swiglu;
+    const int sms = num_sms();
     CUtensorMap mp, mq;
     int rc;
     dim3 grid;
@@ -888,7 +938,7 @@ LSB_API int lsb_gemm_tc(const void* x, const void* w, void* out, int out_f32, in
             case 128: rc = launch<128, 4>(mp, mq, prm, grid, stream); break;
             default: return (int)cudaErrorInvalidValue;
         }
-    } else if (swap && !swiglu && grid.x >= 2 * 148) {
+    } else if (swap && !swiglu && (int)grid.x >= 2 * sms) {
         // Many more weight slabs than SMs (the output head): persistent blocks walk the slabs, the
         // loads of the next slab run under the epilogue of this one and no SM idles between waves.
         const int tm = (int)grid.x;
@@ -899,7 +949,7 @@ LSB_API int lsb_gemm_tc(const void* x, const void* w, void* out, int out_f32, in
             case 128: rc = launch_persistent<128, 5>(mp, mq, prm, tm, 1, stream); break;
             default: return (int)cudaErrorInvalidValue;
         }
-    } else if (swap && grid.x > 148 && bn <= 64) {
+    } else if (swap && (int)grid.x > sms && bn <= 64) {
         // More weight slabs than SMs, fewer than two rounds of them (a wide gated product): with
         // the deep ring one block fits an SM and the second round would run half empty; four
         // stages let two blocks share an SM, so all slabs stream at once (28,672 x 4,096 gated:

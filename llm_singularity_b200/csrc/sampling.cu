@@ -179,10 +179,20 @@ sample_kernel(const float* __restrict__ logits, float* __restrict__ work, int vo
         float total = 0.f;
         for (int t = 0; t < kSampleThreads; ++t) total += chunk_sum[t];
         const float target = u * total;
-        float run = 0.f;
-        int t = 0;
-        while (t < kSampleThreads - 1 && run + chunk_sum[t] < target) { run += chunk_sum[t]; ++t; }
-        // skip empty chunks at the end so that a fallback lands on a kept token
+        // the first chunk at which the running sum reaches the target; chunks without a kept token
+        // are passed over, so that if rounding leaves the sum short of the target at the very end,
+        // the scan below ends on the last kept token (the reference's fallback, sampling.cpp:113-116)
+        float run = 0.f, before = 0.f;
+        int t = -1, last_full = 0;
+        for (int c = 0; c < kSampleThreads; ++c) {
+            if (!(chunk_sum[c] > 0.f)) continue;
+            last_full = c;
+            before = run;
+            if (run + chunk_sum[c] >= target) { t = c; break; }
+            run += chunk_sum[c];
+        }
+        if (t < 0) t = last_full;
+        run = before;
         const int tb = min(vocab, t * per), te = min(vocab, tb + per);
         int pick = -1, last_kept = -1;
         for (int i = tb; i < te; ++i) {

@@ -19,7 +19,6 @@ import numpy as np
 import torch
 
 from ..cache.prefix import RadixPrefixCache
-from ..parts.base import PagedKVSpec
 from ..sampling import Sampler, SamplingParams
 from .batch import StepEntry
 from .runner import ModelRunner
@@ -63,7 +62,7 @@ class Engine:
                                   max_model_len=max_model_len, ops=ops, verbose=verbose)
         cache = self.runner.cache
         shareable = prefix_cache and cache.groups and all(g.window is None for g in cache.groups) \
-            and all(isinstance(s, PagedKVSpec) for s in self.runner.model.cache_specs())
+            and all(s is not None and s.shareable for s in self.runner.model.cache_specs())
         self.prefix = RadixPrefixCache(cache) if shareable else None
         self.scheduler = Scheduler(
             SchedulerConfig(max_batch_size=max_batch_size,
@@ -74,7 +73,8 @@ class Engine:
             cache, self.prefix)
         self.sampler = Sampler(self.runner.rt)
         self._ids = itertools.count()
-        self._requests: Dict[Hashable, Request] = {}
+        self._requests: Dict[Hashable, Request] = {}       # live requests (and those generate() waits for)
+        self._kept: set = set()                            # ids that generate() collects itself
         self.run_ahead = run_ahead
         self._inflight: Optional[_Launched] = None
         pin = torch.device(device).type == "cuda" and ops is None
@@ -114,6 +114,13 @@ class Engine:
         input token from the device, where the sampler left it, prompt portions and admissions
         are known anyway, and the host's work for the step happens while the device is busy.
         Each call still returns the tokens of exactly one step."""
+        out = self._step()
+        for rid, _, finished in out:         # a finished request is forgotten: its id is free again
+            if finished and rid not in self._kept:
+                self._requests.pop(rid, None)
+        return out
+
+    def _step(self) -> List[Tuple[Hashable, int, bool]]:
         out: List[Tuple[Hashable, int, bool]] = []
         cur = self._inflight
         if cur is None:
@@ -190,8 +197,12 @@ class Engine:
         generated tokens (stop token included), in the order of the prompts."""
         ids = [self.add_request(p, max_new_tokens, temperature, top_k, top_p, repetition_penalty,
                                 seed + i, ignore_eos) for i, p in enumerate(prompts)]
-        while self.has_work():
-            self.step()
+        self._kept.update(ids)
+        try:
+            while self.has_work():
+                self.step()
+        finally:
+            self._kept.difference_update(ids)
         outs = []
         for rid in ids:
             req = self._requests.pop(rid)
@@ -201,6 +212,7 @@ class Engine:
         return outs
 
     def request(self, rid: Hashable) -> Request:
+        """The record of a live request (one that ``step()`` has reported finished is forgotten)."""
         return self._requests[rid]
 
     def forward_logits(self, entries: Sequence[StepEntry]) -> torch.Tensor:

@@ -157,15 +157,22 @@ class ModelRunner:
         for e in entries:
             if len(e.tokens) and not (0 <= min(e.tokens) and max(e.tokens) < V):
                 raise ValueError(f"request {e.request!r}: token id outside [0, {V})")
+        # pages for the whole step or for none of it: lengths first, then the pools' room for all
+        # entries together (every group hands out the same number of pages), then the reservations
         for e, s in zip(entries, starts):
-            new_len = s + len(e.tokens)
-            if new_len > self.max_model_len:
-                raise OutOfPages(f"request {e.request!r}: {new_len} tokens exceed the "
+            if s + len(e.tokens) > self.max_model_len:
+                raise OutOfPages(f"request {e.request!r}: {s + len(e.tokens)} tokens exceed the "
                                  f"engine's max_model_len {self.max_model_len}")
-            if not cache.reserve(e.request, new_len):
-                raise OutOfPages(
-                    f"request {e.request!r} needs {cache.pages_needed(e.request, new_len)} more "
-                    f"pages, {cache.free_pages()} are free")
+        need = [cache.pages_needed(e.request, s + len(e.tokens)) for e, s in zip(entries, starts)]
+        if sum(need) > cache.free_pages():
+            short = next(e for e, n in zip(entries, need) if n)
+            raise OutOfPages(
+                f"the step needs {sum(need)} more pages (request {short.request!r}: "
+                f"{cache.pages_needed(short.request, cache.length(short.request) + len(short.tokens))}), "
+                f"{cache.free_pages()} are free")
+        for e, s in zip(entries, starts):
+            if not cache.reserve(e.request, s + len(e.tokens)):
+                raise OutOfPages(f"request {e.request!r}: no pages left")     # not reached: checked above
         moves: List[np.ndarray] = []
         if feed is not None:
             lens = np.fromiter((len(e.tokens) for e in entries), dtype=np.int32, count=len(entries))

@@ -211,8 +211,19 @@ def gather_add_rmsnorm(residual: torch.Tensor, delta: Optional[torch.Tensor], ro
           _i(_dt(out)), _i(rows.shape[0]), _i(T), _i(H), _f(eps), _stream(out))
 
 
+ACTIVATIONS = {"silu": 1, "gelu_tanh": 2, "none": 3}     # act(gate) * up of a gated product
+
+
+def _activation_id(name: str) -> int:
+    try:
+        return ACTIVATIONS[name]
+    except KeyError:
+        raise KernelError(f"activation '{name}' is not implemented "
+                          f"(known: {', '.join(sorted(ACTIVATIONS))})") from None
+
+
 def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
-           gated: bool = False) -> torch.Tensor:
+           gated: bool = False, activation: str = "silu") -> torch.Tensor:
     """x [M, K] times w [N, K] transposed -> [M, N]; 32-bit accumulation.
 
     float32 operands run on the CUDA cores in true 32-bit.  bfloat16 operands run on the
@@ -220,9 +231,11 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     cores as well.
 
     ``gated``: the rows of ``w`` alternate gate_i, up_i and the result is [M, N / 2] with
-    ``out[m, i] = silu(d[m, 2i]) * d[m, 2i + 1]`` (applied in the product's epilogue on the
-    tensor-core path, by the activation kernel otherwise).
+    ``out[m, i] = act(d[m, 2i]) * d[m, 2i + 1]`` (applied in the product's epilogue on the
+    tensor-core path, by the activation kernel otherwise); ``activation`` names act: "silu",
+    "gelu_tanh" or "none".
     """
+    act = _activation_id(activation) if gated else 0
     _req(x, "x", dim=2)
     _req(w, "w", x.dtype, 2)
     M, K = x.shape
@@ -244,15 +257,15 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     if x.dtype == torch.bfloat16 and tensor_core_gemm_ok(x, w):
         out = torch.empty((M, N // 2 if gated else N), dtype=out_dtype, device=x.device)
         _call("gemm_tc", "lsb_gemm_tc", _p(x), _p(w), _p(out), _i(1 if out_dtype == torch.float32 else 0),
-              _i(M), _i(N), _i(K), _i(1 if gated else 0), _stream(out))
+              _i(M), _i(N), _i(K), _i(act), _stream(out))
         return out
     out = torch.empty((M, N), dtype=out_dtype, device=x.device)
     _call("gemm", "lsb_gemm_nt", _p(x), _p(w), _p(out), _i(_dt(x)), _i(_dt(out)), _i(M), _i(N), _i(K),
           _ll(K), _ll(K), _ll(N), _stream(out))
     if gated:
-        act = torch.empty((M, N // 2), dtype=out_dtype, device=x.device)
-        swiglu(out, act)
-        return act
+        half = torch.empty((M, N // 2), dtype=out_dtype, device=x.device)
+        gated_activation(out, half, activation)
+        return half
     return out
 
 
@@ -264,7 +277,8 @@ def small_gemm_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
     K a multiple of 64, N / SMs rows of w and the rows of x within one block's shared memory.)"""
     M, K = x.shape
     N = w.shape[0]
-    if M > 16 or K % 64 or -(-N // NUM_SMS) > 32 or (-(-N // NUM_SMS) + 16) * K * 2 > 180 * 1024:
+    per_sm = -(-N // num_sms(x.device))
+    if M > 16 or K % 64 or per_sm > 32 or (per_sm + 16) * K * 2 > 180 * 1024:
         return False                                  # cheap refusals first; the library has the last word
     return bool(_lib("gemm_small").lsb_gemm_small_supported(_p(x), _p(w), _i(M), _i(N), _i(K)))
 
@@ -274,14 +288,20 @@ def tensor_core_gemm_ok(x: torch.Tensor, w: torch.Tensor) -> bool:
     return (x.shape[1] % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0)
 
 
-def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, i] = silu(gate_up[t, 2i]) * gate_up[t, 2i + 1] (gate and up alternate)."""
+def gated_activation(gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> None:
+    """out[t, i] = act(gate_up[t, 2i]) * gate_up[t, 2i + 1] (gate and up alternate)."""
     _req(gate_up, "gate_up", dim=2)
     _req(out, "out", gate_up.dtype, 2)
     T, I = out.shape
     if gate_up.shape != (T, 2 * I):
-        raise KernelError(f"swiglu: gate_up is {tuple(gate_up.shape)}, out is {tuple(out.shape)}")
-    _call("activation", "lsb_swiglu", _p(gate_up), _p(out), _i(_dt(out)), _i(T), _i(I), _stream(out))
+        raise KernelError(f"gated_activation: gate_up is {tuple(gate_up.shape)}, out is {tuple(out.shape)}")
+    _call("activation", "lsb_gated_act", _p(gate_up), _p(out), _i(_dt(out)), _i(T), _i(I),
+          _i(_activation_id(activation)), _stream(out))
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, i] = silu(gate_up[t, 2i]) * gate_up[t, 2i + 1]."""
+    gated_activation(gate_up, out, "silu")
 
 
 def _check_cache(cache, nkv: int, hd: int, dtype) -> None:
@@ -320,17 +340,29 @@ def rope_kv_store(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache,
           _i(1 if store else 0), _p(ctx.q_start if skip_single else None), _stream(qkv))
 
 
-NUM_SMS = 148                   # B200: 2 dies x 74
+_sm_counts: Dict[int, int] = {}
+
+
+def num_sms(device=None) -> int:
+    """Streaming multiprocessors of ``device`` (the current one by default), asked once."""
+    index = torch.cuda.current_device() if device is None else torch.device(device).index
+    if index is None:
+        index = torch.cuda.current_device()
+    if index not in _sm_counts:
+        _sm_counts[index] = torch.cuda.get_device_properties(index).multi_processor_count
+    return _sm_counts[index]
+
+
 USE_TCGEN05_ATTENTION = True    # prompt portions of 128 tokens and more
 FUSE_DECODE_ROPE = True         # single tokens: rotation and cache write inside the decode kernel
 _TC_HEAD_DIMS = (64, 128)
 
 
-def decode_splits(n_decode: int, nkv: int) -> int:
+def decode_splits(n_decode: int, nkv: int, device=None) -> int:
     """How many ways each request's keys are split among thread blocks in the decode kernel:
     enough blocks for three per SM; a function of the batch alone, so that a captured launch
     stays valid as sequences grow."""
-    return max(1, min(32, (3 * NUM_SMS) // max(1, n_decode * nkv)))
+    return max(1, min(32, (3 * num_sms(device)) // max(1, n_decode * nkv)))
 
 
 _cluster_caps: Dict[int, int] = {}
@@ -449,7 +481,7 @@ def paged_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache, s
     n_decode, first, last = _batch_shape(ctx)
     on = _stream(out) if stream is None else ctypes.c_void_p(stream)
     if n_decode and only != "portions":
-        splits = decode_splits(n_decode, nkv)
+        splits = decode_splits(n_decode, nkv, qkv.device)
         if not getattr(ctx, "fixed_launch", False):
             splits = min(splits, -(-ctx.max_kv_len // 128))
         cluster_cap = _decode_cluster_cap(hd)

@@ -18,7 +18,8 @@ Norm            ``add_norm(residual, delta) -> normed``: ``residual += delta`` i
 PositionEncoding ``rotary_table() -> (inv_freq, rotary_dim) | None`` for encodings
                 that rotate q and k (fused with the cache write), and
                 ``apply(q, k, ctx)`` for anything else.
-Mixer           ``cache_spec() -> PagedKVSpec | StateSpec | None`` and
+Mixer           ``cache_spec() -> CacheSpec | None`` (``PagedKVSpec``, ``StateSpec`` or a
+                kind of the mixer's own) and
                 ``forward(x, ctx, cache, writes_cache) -> delta``.
 FeedForward     ``forward(x, ctx) -> delta``.
 Block           ``forward(residual, pending, ctx, cache, writes_cache) -> pending``
@@ -49,21 +50,102 @@ class ParamSpec:
 
 
 # ------------------------------------------------------------------ cache needs
+class CacheSpec:
+    """What a mixer keeps between steps, as the cache manager sees it.
+
+    A mixer returns one of these from ``cache_spec()`` (or ``None``).  The manager knows no
+    cache kind by name: it asks the spec.  ``paged`` says whether the kind lives in pages that
+    grow with the sequence (it then gets page ids through the block table of its group; kinds
+    with the same ``window`` share a group, and a page id addresses one slot in the storage of
+    every cache of the group) or in one row per request slot.  Another kind (pages of another
+    shape, a compressed cache, a second state) is a subclass; nothing in the manager changes.
+
+    ``allocate(rt, page_size, num_pages, slots)`` -> device storage, any object (``num_pages``
+    is the group's pool size for paged kinds, ``None`` otherwise);
+    ``view(storage, group)`` -> what the mixer's ``forward`` gets as ``cache`` (``group`` has
+    ``dev_table`` int32 [slots, max_pages], ``window``, ``index`` and ``page_size`` for paged
+    kinds; it is ``None`` otherwise);
+    ``reset(storage, slot)`` is called when a request takes a slot;
+    ``bytes_per_page(page_size, element_size)`` -> bytes one page id stands for in this cache.
+    ``shareable``: full pages of this kind mean the same for every request with the same
+    tokens before them, so a prefix tree may hand them to other requests.
+    """
+
+    paged = False
+    shareable = False
+    window: Optional[int] = None
+
+    def allocate(self, rt, page_size: int, num_pages: Optional[int], slots: int):
+        raise NotImplementedError
+
+    def view(self, storage, group):
+        raise NotImplementedError
+
+    def reset(self, storage, slot: int) -> None:
+        pass
+
+    def bytes_per_page(self, page_size: int, element_size: int) -> int:
+        return 0
+
+
+@dataclass
+class KVCacheView:
+    """What an attention call sees of its cache."""
+
+    k_pages: torch.Tensor          # [num_pages, kv_heads, page_size, head_dim]
+    v_pages: torch.Tensor
+    block_table: torch.Tensor      # int32 [slots, max_pages]; rows picked by ctx.table_rows
+    page_size: int
+    window: Optional[int]
+    group: int
+
+
+@dataclass
+class StateView:
+    """What a mixer with fixed-size state sees: ``state[ctx.table_rows[r]]`` is request r's."""
+
+    state: torch.Tensor            # [slots, *shape]
+
+
 @dataclass(frozen=True)
-class PagedKVSpec:
+class PagedKVSpec(CacheSpec):
     """Keys and values of every past token (or of the last ``window`` tokens)."""
 
     num_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    paged = True
+    shareable = True
+
+    def allocate(self, rt, page_size, num_pages, slots):
+        shape = (num_pages, self.num_kv_heads, page_size, self.head_dim)
+        return (torch.zeros(shape, dtype=rt.dtype, device=rt.device),
+                torch.zeros(shape, dtype=rt.dtype, device=rt.device))
+
+    def view(self, storage, group):
+        return KVCacheView(storage[0], storage[1], group.dev_table, group.page_size, group.window,
+                           group.index)
+
+    def bytes_per_page(self, page_size, element_size):
+        return 2 * self.num_kv_heads * page_size * self.head_dim * element_size
 
 
 @dataclass(frozen=True)
-class StateSpec:
-    """Per-request state of fixed size (one tensor of ``shape`` per request)."""
+class StateSpec(CacheSpec):
+    """Per-request state of fixed size (one tensor of ``shape`` per request), zero when a
+    request begins."""
 
     shape: Tuple[int, ...]
     dtype: torch.dtype = torch.float32
+
+    def allocate(self, rt, page_size, num_pages, slots):
+        return torch.zeros((slots,) + tuple(self.shape), dtype=self.dtype, device=rt.device)
+
+    def view(self, storage, group):
+        return StateView(storage)
+
+    def reset(self, storage, slot):
+        storage[slot].zero_()
 
 
 # ---------------------------------------------------------------------- runtime

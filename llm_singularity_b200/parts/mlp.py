@@ -1,4 +1,5 @@
-"""Dense gated feed-forward: ``down( act(gate(x)) * up(x) )``, no bias.
+"""Dense gated feed-forward: ``down( act(gate(x)) * up(x) )``, no bias; ``act`` is named by
+the spec (silu in this architecture; the tanh form of gelu and none are there for others).
 
 Reference: two products, ``silu(g) * u`` with ``silu(g) = g / (1 + exp(-g))``,
 then the down product (models/llama/llama_model.cpp:634-649;
@@ -23,8 +24,10 @@ class GatedMLP(Part):
 
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
-        if spec.activation != "silu":
-            raise ValueError(f"activation '{spec.activation}' is not implemented (silu only)")
+        known = getattr(rt.ops, "ACTIVATIONS", None)
+        if known is not None and spec.activation not in known:
+            raise ValueError(f"activation '{spec.activation}' is not implemented "
+                             f"(known: {', '.join(sorted(known))})")
 
     @classmethod
     def params(cls, spec) -> Dict[str, ParamSpec]:
@@ -40,5 +43,5 @@ class GatedMLP(Part):
 
     def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
         ops = self.rt.ops
-        act = ops.linear(x, self.w_gate_up, gated=True)         # [T, I]
+        act = ops.linear(x, self.w_gate_up, gated=True, activation=self.spec.activation)   # [T, I]
         return ops.linear(act, self.w_down)

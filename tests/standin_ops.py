@@ -45,11 +45,22 @@ def gather_add_rmsnorm(residual, delta, rows, weight, eps, out):
     out.copy_(_rms(x, weight, eps).to(out.dtype))
 
 
-def linear(x, w, out_dtype=None, gated=False):
+ACTIVATIONS = {"silu": 1, "gelu_tanh": 2, "none": 3}
+
+
+def _act(g, name):
+    if name == "silu":
+        return g / (1 + torch.exp(-g))
+    if name == "gelu_tanh":
+        return 0.5 * g * (1 + torch.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3)))
+    assert name == "none"
+    return g
+
+
+def linear(x, w, out_dtype=None, gated=False, activation="silu"):
     y = x.float() @ w.float().T
     if gated:
-        g, u = y[:, 0::2], y[:, 1::2]
-        y = g / (1 + torch.exp(-g)) * u
+        y = _act(y[:, 0::2], activation) * y[:, 1::2]
     return y.to(out_dtype or x.dtype)
 
 

@@ -43,7 +43,9 @@ def test_head_dim_may_differ_from_hidden_over_heads():
 
 @pytest.mark.parametrize("patch, word", [
     ({"num_attention_heads": 5, "num_key_value_heads": 2}, "multiple"),
-    ({"head_dim": 15}, "even"),
+    ({"head_dim": 15}, "multiple of 16"),
+    ({"head_dim": 24}, "multiple of 16"),
+    ({"head_dim": 272}, "at most 256"),
     ({"rope_scaling": {"rope_type": "yarn", "factor": 2.0}}, "yarn"),
     ({"rope_scaling": {"rope_type": "llama3", "factor": 8.0}}, "lacks"),
     ({"hidden_act": "gelu"}, "gelu"),

@@ -137,17 +137,36 @@ def test_command_line_random_weights_can_be_rebuilt_from_the_seed(tmp_path, dtyp
 @pytest.mark.parametrize("mode", ["decode", "prefill", "serve"])
 def test_command_line_bench_modes(model_dirs, mode):
     cmd = [sys.executable, os.path.join(ROOT, "bin", "llm-serve-llama"), "--model-dir", model_dirs["tiny_b"],
-           "--bench", mode, "--prompt-len", "40", "--num-requests", "5", "--max-new-tokens", "12",
-           "--ignore-eos", "--kv-block-size", "8", "--num-kv-blocks", "24", "--max-batch-size", "4"]
+           "--bench", mode, "--prompt-len", "40", "--num-requests", "4" if mode == "decode" else "5",
+           "--max-new-tokens", "12",
+           "--ignore-eos", "--kv-block-size", "8", "--num-kv-blocks", "40" if mode == "decode" else "24",
+           "--max-batch-size", "4"]
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
     assert res.returncode == 0, res.stderr
     line = json.loads(res.stdout.splitlines()[-1])
     assert line["bench"] == mode and line["seconds"] > 0
+    stats = line["stats"]
     if mode == "serve":
+        # five requests of twelve new tokens each, every prompt token run exactly once or taken
+        # from the prefix tree, every page given back
         assert line["generated_tokens"] == 5 * 12
-        assert line["stats"]["pages_free"] + line["stats"]["prefix_nodes"] >= 0
+        # a token comes from a decode step or from the end of a prompt (again after a preemption)
+        assert stats["decode_tokens"] <= 5 * 11 and stats["decode_tokens"] + stats["admitted"] >= 5 * 12
+        assert 5 <= line["prompt_tokens"] <= 5 * 40
+        assert stats["prefill_tokens"] + stats["prefix_hit_tokens"] >= line["prompt_tokens"]
+        assert stats["admitted"] >= 5 and stats["errors"] == 0
+        assert line["total_tokens_per_s"] == pytest.approx(
+            (line["generated_tokens"] + line["prompt_tokens"]) / line["seconds"], rel=1e-3)
     if mode == "decode":
-        assert line["generated_tokens_per_s"] > 0
+        # four requests fit the batch; the timed region is eight steps of four tokens
+        assert line["num_requests"] == 4 and line["decode_steps"] == 12 - 4
+        assert line["generated_tokens"] == line["decode_steps"] * 4
+        assert line["generated_tokens_per_s"] == pytest.approx(line["generated_tokens"] / line["seconds"], rel=1e-3)
+        assert stats["prefill_tokens"] == 4 * 40
+    if mode == "prefill":
+        assert line["prompt_tokens"] == 40 and line["runs"] == 4
+        assert line["prompt_tokens_per_s"] == pytest.approx(40 / line["seconds"], rel=1e-3)
+        assert stats["prefill_tokens"] == 4 * 40 and stats["admitted"] == 4
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

@@ -56,6 +56,27 @@ def test_random_weights_are_the_same_bits_on_the_device_and_on_the_cpu(ops, dtyp
     assert all(torch.equal(dev[k].cpu(), cpu[k]) for k in expected)
 
 
+def test_a_wait_that_runs_out_returns_and_is_reported(ops):
+    """The kernels' waits on barriers are bounded.  A probe kernel of the matrix-product library
+    waits, with a limit of 4,096 polls, on a barrier that nothing arrives at: it gives up and
+    ends by itself, a second waiter of the block leaves on seeing that, and the status word the
+    host reads afterwards says so (and is cleared by the reading)."""
+    import ctypes
+    lib = ops._lib("gemm_tc")
+    result = torch.full((2,), -1, dtype=torch.int32, device="cuda")
+    rc = lib.lsb_gemm_tc_wait_probe(ctypes.c_int(4096), ctypes.c_void_p(result.data_ptr()),
+                                    ctypes.c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert result.tolist() == [1, 1]
+    with pytest.raises(ops.KernelError, match="bounded wait"):
+        ops.check_status()
+    ops.check_status()                     # read and cleared: the library is usable again
+    x = _rand(8, 64, dtype=torch.bfloat16, seed=1)
+    w = _rand(32, 64, dtype=torch.bfloat16, seed=2)
+    assert torch.allclose(ops.linear(x, w).float(), x.float() @ w.float().T, atol=0.5)
+
+
 def test_scatter_i32(ops):
     dst = torch.full((5, 7), -1, dtype=torch.int32, device="cuda")
     idx = torch.tensor([0, 8, 34, 8], dtype=torch.int32, device="cuda")[:3]
@@ -658,6 +679,22 @@ def test_greedy_takes_the_first_maximum(ops):
     params = torch.tensor([[0.0, 1.0, 1.0, 0.5]] * 3, device="cuda")
     ops.sample(logits, params, torch.zeros(3, dtype=torch.int32, device="cuda"), None, None, out)
     assert out.cpu().tolist() == [123, 69999, 0]
+
+
+def test_sampling_falls_back_to_the_last_kept_token(ops):
+    """When the running sum never reaches u * total (rounding at the very end of the scan; forced
+    here by a draw above one), the token is the last kept one in index order, as in the reference
+    (core/src/sampling.cpp:113-116), also when every later stretch of the vocabulary is empty."""
+    vocab = 128256
+    logits = torch.full((2, vocab), -5.0)
+    for i, x in ((5, 4.0), (900, 3.0), (70000, 3.5)):
+        logits[:, i] = x
+    params = torch.tensor([[1.0, 1.0, 1.0, 1.5], [1.0, 1.0, 1.0, 0.999]], device="cuda")
+    out = torch.empty(2, dtype=torch.int32, device="cuda")
+    ops.sample(logits.cuda(), params, torch.tensor([3, 3], dtype=torch.int32, device="cuda"), None, None, out)
+    row = logits[0].tolist()
+    assert out.tolist() == [plain_llama.sample_plain(row, 1.0, 3, 1.0, 1.0, (), 1.5),
+                            plain_llama.sample_plain(row, 1.0, 3, 1.0, 1.0, (), 0.999)] == [70000, 70000]
 
 
 def test_sampling_follows_the_distribution(ops):

@@ -205,24 +205,34 @@ def test_engine_under_a_random_load_yields_each_requests_own_tokens(model_dirs, 
     alone.scheduler.cfg.stop_token_ids = stops
     for j in jobs:
         rid = alone.add_request(**j)
+        rec, seen = alone.request(rid), []
         while alone.has_work():
-            alone.step()
-        want.append(alone.request(rid).generated)
+            seen += [tok for r, tok, _ in alone.step() if r == rid]
+        want.append(rec.generated)
+        assert seen == rec.generated                # what step() reported is what the record holds
+        with pytest.raises(KeyError):               # a finished request is forgotten ...
+            alone.request(rid)
+    again = alone.add_request(**dict(jobs[0], request_id=0))   # ... and its id can be used again
+    while alone.has_work():
+        alone.step()
+    assert again == 0
     assert any(w[-1] in stops and len(w) < j["max_new_tokens"] for w, j in zip(want, jobs))
 
     for ahead, prefix, pages in ((True, True, 20), (True, False, 14), (False, True, 14)):
         eng = engine(num_kv_blocks=pages, max_batch_size=5, max_tokens_per_batch=24, prefill_chunk=9,
                      prefix_cache=prefix, run_ahead=ahead)
         eng.scheduler.cfg.stop_token_ids = stops
-        ids, todo, order = [], list(jobs), random.Random(seed + 100)
+        ids, recs, todo, order = [], [], list(jobs), random.Random(seed + 100)
         while todo or eng.has_work():
             for _ in range(order.randrange(0, 3)):
                 if todo:
                     ids.append(eng.add_request(**todo.pop(0)))
+                    recs.append(eng.request(ids[-1]))
             eng.step()
-        got = [eng.request(r).generated for r in ids]
+        got = [r.generated for r in recs]
         assert got == want, (ahead, prefix, pages)
-        assert all(eng.request(r).status == "finished" and eng.request(r).pending == 0 for r in ids)
+        assert all(r.status == "finished" and r.pending == 0 for r in recs)
+        assert not eng._requests
         eng.runner.cache.check_invariants()
         if prefix:
             eng.prefix.check_invariants()
@@ -253,3 +263,21 @@ def test_engine_shares_prompt_pages_between_live_requests_and_yields_the_same_to
             eng.prefix.check_invariants()
     assert outs[0] == outs[1]
     assert stats[1]["prefix_hit_pages"] >= 3 * 3 and stats[0]["prefix_hit_pages"] == 0
+
+
+def test_a_step_that_does_not_fit_reserves_nothing(model_dirs):
+    """Pages are taken for all entries of a step or for none: a step whose second entry finds no
+    room leaves the first entry's request as it was (no page held back, no table update queued),
+    and the first entry can then run alone."""
+    from llm_singularity_b200.engine import OutOfPages, StepEntry
+    runner = ModelRunner(model_dirs["tiny_a"], dtype="float32", device="cpu", page_size=16, num_pages=4,
+                         max_requests=2, max_model_len=64, ops=standin_ops)
+    runner.open("a"); runner.open("b")
+    toks = tiny_models.random_tokens(256, 40, 3)
+    with pytest.raises(OutOfPages, match="needs 5 more pages"):
+        runner.step([StepEntry("a", toks[:30], []), StepEntry("b", toks[:40], [])])
+    assert runner.cache.free_pages() == 4 and runner.cache.pages_of("a") == []
+    assert runner.cache.take_updates(0) == []
+    runner.step([StepEntry("a", toks[:30], [])])
+    assert runner.cache.free_pages() == 2
+    runner.cache.check_invariants()
