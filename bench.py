@@ -11,7 +11,10 @@ entry point (``Engine.step``): host token ids in (pinned memory, one host-to-dev
 the step's metadata), sampled token ids out (device-to-host) every step.  ``prefill`` times a
 2,048-token prompt in one step; ``roofline`` sets the bytes a decode step must read (every
 weight once and the cache of the live requests) against the measured copy bandwidth;
-``points`` gives decode tokens per second at batch 1 and 64.  Weights are random (N(0, 0.02),
+``points`` gives decode tokens per second at batch 1 and 64; ``more`` two larger serving runs
+(3B sizes with mixed prompts, 8B sizes with a shared prefix; ``--no-more`` leaves them out).  The
+headline is the median of ``--windows`` timed windows of K steps each, with the clocks sampled
+over all of them.  Weights are random (N(0, 0.02),
 norms 1), prompts are uniform random token ids: synthetic data throughout.  Every decode step
 reads more than 2.4 GB of weights, far more than the 126 MB L2, so no L2 flush is needed
 between iterations.
@@ -176,7 +179,11 @@ def run_ours(args):
             kernels.sample(logits, greedy, topk, None, None, out)
         return out
 
-    def time_decode(batch, steps, warmup):
+    def time_decode(batch, steps, warmup, windows=1):
+        """``windows`` timed windows of exactly ``steps`` decode steps each (the requests are
+        refilled to the same lengths before each), after ``warmup`` steps; returns the median
+        window's milliseconds per step, every window's, the launches of one window and the mean
+        context length inside a window."""
         start = ctx_len - (steps + warmup + 2)
         ids = fill(batch, start)
         feed = torch.randint(0, V, (batch,), generator=g).tolist()
@@ -186,21 +193,28 @@ def run_ours(args):
         per_step = kernels.launch_count() - n0
         runner.cuda_graphs = keep
         decode_steps(ids, max(warmup - 1, 2), feed)
-        torch.cuda.synchronize()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        launches0 = kernels.launch_count()
-        e0.record()
-        decode_steps(ids, steps, feed)
-        e1.record()
-        torch.cuda.synchronize()
-        ms = e0.elapsed_time(e1) / steps
+        all_ms = []
+        for w in range(windows):
+            if w:                                   # same lengths again: close, refill, warm up
+                for rid in ids:
+                    runner.close(rid)
+                ids = fill(batch, start)
+                decode_steps(ids, warmup, feed)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            launches0 = kernels.launch_count()
+            e0.record()
+            decode_steps(ids, steps, feed)
+            e1.record()
+            torch.cuda.synchronize()
+            all_ms.append(e0.elapsed_time(e1) / steps)
         # replayed graphs launch the same kernels as the counted step did, without the wrappers
         launches = per_step * steps if runner.graph_replays else kernels.launch_count() - launches0
         kernels.check_status()
         for rid in ids:
             runner.close(rid)
         mean_ctx = ctx_len - steps / 2
-        return ms, launches, mean_ctx
+        return statistics.median(all_ms), all_ms, launches, mean_ctx
 
     # ---- prefill: one 2,048-token prompt in one step, logits for its last token
     def time_prefill(reps=5, warm=3):
@@ -227,13 +241,13 @@ def run_ours(args):
     for b in batches:
         if b == args.batch:
             continue
-        ms, _, _ = time_decode(b, min(args.steps, 32), args.warmup)
+        ms, _, _, _ = time_decode(b, min(args.steps, 32), args.warmup, windows=3)
         points[f"decode_b{b}"] = round(b / ms * 1e3, 1)
 
     # ---- the headline: decode at --batch, device-timed, clocks sampled meanwhile
     sampler.start()
     time.sleep(0.3)
-    ms, launches, mean_ctx = time_decode(args.batch, args.steps, args.warmup)
+    ms, window_ms, launches, mean_ctx = time_decode(args.batch, args.steps, args.warmup, windows=args.windows)
     clocks = sampler.stop()
     value = args.batch / ms * 1e3
 
@@ -293,7 +307,16 @@ def run_ours(args):
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peaks["hbm_gbs"],
                      "unit": "GB/s", "frac": round(achieved / peaks["hbm_gbs"], 4)},
         "points": points,
+        "windows": {"n": len(window_ms), "ms_per_step": [round(x, 4) for x in window_ms]},
     }
+    if not args.no_more:
+        # the two larger configurations, through the entry point (host tokens in and out)
+        from llm_singularity_b200.measure import workloads
+        import gc
+        del eng, runner
+        gc.collect()
+        torch.cuda.empty_cache()
+        line["more"] = {"mixed_3b": workloads.mixed_3b(), "shared_prefix_8b": workloads.shared_prefix_8b()}
     print(json.dumps(line))
     return 0
 
@@ -307,6 +330,8 @@ def main():
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=FULL_LAYERS,
                     help=f"decoder layers (the full model has {FULL_LAYERS})")
+    ap.add_argument("--windows", type=int, default=5, help="timed windows of K steps; the median is reported")
+    ap.add_argument("--no-more", action="store_true", help="leave out the 3B and 8B serving runs")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     args = ap.parse_args()
     if args.impl == "reference":

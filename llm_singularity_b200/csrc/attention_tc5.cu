@@ -28,15 +28,10 @@ LSB_DEFINE_STATUS()
 typedef __nv_bfloat16 bf16;
 
 constexpr int kRows = 128;            // queries per block = TMEM lanes
-#ifndef LSB_ATT5_KEYS
-#define LSB_ATT5_KEYS 64
-#endif
-constexpr int kKeys = LSB_ATT5_KEYS;  // keys per tile (64: three blocks of head 64 fit per SM)
+constexpr int kKeys = 64;             // keys per tile
 constexpr int kThreads = 224;        // warps: TMA, MMA for S, four softmax warps, MMA for P V
-#ifndef LSB_ATT5_STAGES
-#define LSB_ATT5_STAGES 4
-#endif
-constexpr int kKvStages = LSB_ATT5_STAGES;
+constexpr int kKvStages = 4;          // K/V tiles in flight
+constexpr int kBlocksPerSm64 = 2;     // blocks of head size 64 that share an SM (head 128: one)
 constexpr int kBtCache = 512;         // block-table entries of this block's key range kept in smem
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr uint32_t kSpinLimit = 1u << 22;
@@ -179,11 +174,8 @@ struct Smem {
                                      kBtCache * 4 + 16 * 8 + 16;
 };
 
-#ifndef LSB_ATT5_BLOCKS
-#define LSB_ATT5_BLOCKS 2
-#endif
 template <int HD>
-__global__ void __launch_bounds__(kThreads, HD == 64 ? LSB_ATT5_BLOCKS : 1)
+__global__ void __launch_bounds__(kThreads, HD == 64 ? kBlocksPerSm64 : 1)
 prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                              const __grid_constant__ CUtensorMap map_v, const AttnParams prm) {
     using L = Smem<HD>;

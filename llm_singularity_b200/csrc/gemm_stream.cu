@@ -1,0 +1,463 @@
+// out[M, N] = x[M, K] * w[N, K]^T for a handful of rows (M <= 16) and a weight matrix of any size:
+// the feed-forward products of a decode step (gate/up with its activation, down), which are pure
+// weight traffic.  What such a product needs is every SM pulling its share of the weights all the
+// time, nothing else.
+//
+// * The weight rows are dealt over one block per SM row by row (pairs of rows for a gated
+//   product), not tile by tile: 2,048 rows over 148 SMs are 13 or 14 rows each, where 128-row
+//   slabs would leave 20 SMs without work and a K split would need a sum across blocks.  A block
+//   walks K for its own rows alone, so there is no cluster, no partial tile outside the block,
+//   and the order of every sum is fixed: results repeat bit for bit.
+// * One producer thread streams the block's rows through a ring of K chunks in shared memory by
+//   TMA: one tiled copy per stage whose box is (64 of K) x (the block's rows) x (the chunk's 64-wide
+//   pieces), through a three-dimensional tensor map over the weight matrix, completion counted by
+//   an mbarrier per stage; the matching chunk of the activations rides along the same way.  (A
+//   bulk copy per row segment was tried first: the copy unit takes some 50 ns per request, however
+//   small, and 256-byte requests capped the product at 0.8 TB/s.)  Weights depend on nothing, so
+//   the ring is filled before the wait on the previous kernel of the stream (programmatic
+//   dependent launch); the activations are requested after it.  The ring takes most of an SM's
+//   shared memory (200 KB a block).  Half of that, so that the blocks of two consecutive products
+//   share an SM and the second one's ring is full when the first one ends, was slower: what the
+//   memory system wants is bytes in flight (gate/up at 8 rows inside a decode step: 15.3 us with
+//   112 KB a block, 13.7 us with 200 KB; the down product 14.3 and 11.5 us).
+// * Eight consumer warps split each chunk along K and run mma.sync (m16n8k16: sixteen weight rows
+//   by up to sixteen activation rows); their partial sums meet in shared memory at the end, in
+//   warp order.  Rows of a 16-row tile that are not the block's own, and activation rows beyond
+//   M, are never loaded (the latter are filled with zeros by the copy): what the tensor core
+//   makes of them lands in outputs nobody stores.  Rows lie in shared memory as 128-byte pieces
+//   whose 16-byte chunks the copy swizzles by the piece's index, which spreads the eight rows of
+//   an ldmatrix over all banks.
+//
+// act != 0: w has 2 * N_out rows alternating gate_i, up_i and out is [M, N / 2] with
+// out[m, i] = act(d[m, 2i]) * d[m, 2i + 1] (1 silu, 2 gelu in its tanh form, 3 none), in 32-bit.
+//
+// The reference calls cublasSgemm for every projection (kernels/src/cublas_provider.cpp:36-51) and
+// a separate kernel for silu(g) * u (kernels/src/activations.cu:11-21).  No load here uses cluster
+// multicast.
+#include "common.cuh"
+
+#include <cuda.h>
+
+LSB_DEFINE_STATUS()
+
+typedef __nv_bfloat16 bf16;
+
+constexpr int kWarps = 8;                       // consumer warps; warp kWarps is the producer
+constexpr int kThreads = 32 * (kWarps + 1);
+constexpr int kMaxStages = 8;
+constexpr int kSmemBudget = 200 * 1024;         // one block per SM; most of it is the ring
+constexpr uint32_t kSpinLimit = 1u << 22;
+enum : int { LSB_ACT_SILU = 1, LSB_ACT_GELU_TANH = 2, LSB_ACT_NONE = 3 };
+
+struct StreamParams {
+    const bf16* x;
+    const bf16* w;
+    void* out;
+    int M, N, K;
+    int out_f32;
+    int act;            // 0: plain product; else the activation of a gated product
+    int kc;             // K per stage (a multiple of 128)
+    int stages;
+    int unit;           // rows are dealt in units of this many (2 for a gated product)
+    int w_bytes;        // shared memory a stage keeps for weights (a multiple of 1024)
+    int rows_a, rows_b, rows_c;   // rows of the boxes of the three weight maps
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait: false if the limit ran out or another warp of the block already gave up.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t it = 0; it < kSpinLimit; ++it) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((it & 255u) == 255u) {
+            if (*abort_flag) return false;
+            __nanosleep(64);
+        }
+    }
+    *abort_flag = 1;
+    lsb_set_status(LSB_WAIT_TIMEOUT);
+    return false;
+}
+// One box of a three-dimensional tensor map into shared memory (1024-byte aligned).
+__device__ __forceinline__ void tma_load_3d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1, int c2) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1), "r"(c2) : "memory");
+}
+// Byte offset of 16-byte chunk `chunk` of 128-byte piece `piece` of a box (128-byte swizzle; the box
+// starts on a 1024-byte boundary).
+__device__ __forceinline__ uint32_t swz(int piece, int chunk) {
+    return (uint32_t)((piece << 7) + (((chunk ^ piece) & 7) << 4));
+}
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x2(uint32_t (&r)[2], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x2.shared.b16 {%0, %1}, [%2];\n"
+                 : "=r"(r[0]), "=r"(r[1]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, "
+                 "{%8, %9}, {%0, %1, %2, %3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(32 * kWarps) : "memory"); }
+
+__device__ __forceinline__ float gate_act(float g, int act) {
+    if (act == LSB_ACT_SILU) return g / (1.f + expf(-g));
+    if (act == LSB_ACT_GELU_TANH) return 0.5f * g * (1.f + tanhf(0.7978845608f * (g + 0.044715f * g * g * g)));
+    return g;
+}
+
+// RT: 16-row tiles of weights per pass (a block with more rows than 16 * RT walks K once per pass);
+// NT: 8-row tiles of activations (M <= 8 * NT).
+template <int RT, int NT>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+                   const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_x,
+                   const StreamParams prm) {
+    extern __shared__ unsigned char smem_dyn[];
+    unsigned char* smem_raw = (unsigned char*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
+    lsb_pdl_launch_dependents();
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int K = prm.K, kc = prm.kc, stages = prm.stages;
+    const int pieces = kc >> 6;                                   // 64-wide pieces of a chunk
+    const int w_bytes = prm.w_bytes, x_bytes = pieces * 8 * NT * 128;   // (x_bytes: a multiple of 1024)
+    const int stage_bytes = w_bytes + x_bytes;
+
+    unsigned char* ring = smem_raw;
+    float* red = reinterpret_cast<float*>(ring + (size_t)stages * stage_bytes);   // [2][kWarps][16][8 * NT]
+    float* held = red + 2 * kWarps * 16 * 8 * NT;                                  // [8 * NT][16 * RT]: a pass's results
+    uint64_t* full_w = reinterpret_cast<uint64_t*>(held + 8 * NT * 16 * RT);       // [kMaxStages] each
+    uint64_t* full_x = full_w + kMaxStages;
+    uint64_t* empty = full_x + kMaxStages;
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + kMaxStages);
+
+    // this block's rows
+    const int units = prm.N / prm.unit;
+    const int r0 = (int)((long long)blockIdx.x * units / gridDim.x) * prm.unit;
+    const int r1 = (int)((long long)(blockIdx.x + 1) * units / gridDim.x) * prm.unit;
+    const int rows = r1 - r0;
+    const int rows_cap = 16 * RT;
+    const int passes = (rows + rows_cap - 1) / rows_cap;
+    const int nk = (K + kc - 1) / kc;
+    const int n_it = passes * nk;
+    // Every block needs the same activations.  Each starts its walk through K at another chunk, so
+    // that at any moment the blocks ask L2 for different lines (all of them on the same few lines
+    // at once is a queue at those lines' L2 slices); the order of a block's sums is still fixed.
+    const int k_shift = (int)(blockIdx.x % (unsigned)nk);
+
+    if (tid == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < stages; ++s) {
+            mbar_init(&full_w[s], 1);
+            mbar_init(&full_x[s], 1);
+            mbar_init(&empty[s], kWarps);
+        }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == kWarps) {
+        // ------------------------------------------------------------------ producer
+        // (one thread: a stage is one copy of weights and one of activations)
+        auto issue_w = [&](int it) {
+            const int s = it % stages, pass = it / nk, kb = (it - pass * nk + k_shift) % nk;
+            const int pr0 = pass * rows_cap, prows = min(rows_cap, rows - pr0);
+            const CUtensorMap* map = prows == prm.rows_a ? &map_a : prows == prm.rows_b ? &map_b : &map_c;
+            mbar_expect_tx(&full_w[s], (uint32_t)(prows * kc * 2));
+            tma_load_3d(ring + (size_t)s * stage_bytes, map, &full_w[s], 0, r0 + pr0, kb * pieces);
+        };
+        auto issue_x = [&](int it) {
+            const int s = it % stages, pass = it / nk, kb = (it - pass * nk + k_shift) % nk;
+            mbar_expect_tx(&full_x[s], (uint32_t)x_bytes);
+            tma_load_3d(ring + (size_t)s * stage_bytes + w_bytes, &map_x, &full_x[s], 0, 0, kb * pieces);
+        };
+        if (lane != 0) return;
+        const int ahead = min(stages, n_it);
+        for (int it = 0; it < ahead; ++it) issue_w(it);           // weights depend on nothing
+        lsb_pdl_wait();
+        bool ok = true;
+        int issued_w = ahead, issued_x = 0;
+        for (int it = 0; it < n_it && ok; ++it) {
+            if (it >= stages) {
+                ok = mbar_wait(&empty[it % stages], (uint32_t)(((it / stages) & 1) ^ 1), abort_flag);
+                if (!ok) break;
+                issue_w(it);
+                issued_w = it + 1;
+            }
+            issue_x(it);
+            issued_x = it + 1;
+        }
+        if (!ok) {
+            // gave up: copies still in flight must land before the block's shared memory goes away
+            for (int it = max(0, issued_w - stages); it < issued_w; ++it)
+                for (uint32_t n = 0; n < (1u << 16) && !mbar_try_wait(&full_w[it % stages], (it / stages) & 1); ++n)
+                    __nanosleep(64);
+            for (int it = max(0, issued_x - stages); it < issued_x; ++it)
+                for (uint32_t n = 0; n < (1u << 16) && !mbar_try_wait(&full_x[it % stages], (it / stages) & 1); ++n)
+                    __nanosleep(64);
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------------- consumers
+    lsb_pdl_wait();          // before anything of this kernel is stored (its output buffer may be one
+                             // that an earlier kernel of the stream still reads)
+    const int a_row = ((lane >> 3) & 1) * 8 + (lane & 7), a_half = lane >> 4;
+    const int b_row = lane & 7, b_half = (lane >> 3) & 1;
+    const int width = 8 * NT;
+    const int n_out = prm.act ? prm.N / 2 : prm.N;
+    int it = 0;
+    bool ok = true;
+    for (int pass = 0; pass < passes && ok; ++pass) {
+        float acc[RT][NT][4];
+#pragma unroll
+        for (int rt = 0; rt < RT; ++rt)
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) acc[rt][nt][0] = acc[rt][nt][1] = acc[rt][nt][2] = acc[rt][nt][3] = 0.f;
+        const int pr0 = pass * rows_cap, prows = min(rows_cap, rows - pr0);
+        const int row_tiles = (prows + 15) >> 4;
+        for (int kb = 0; kb < nk; ++kb, ++it) {
+            const int s = it % stages;
+            const uint32_t parity = (uint32_t)((it / stages) & 1);
+            if (!mbar_wait(&full_w[s], parity, abort_flag) || !mbar_wait(&full_x[s], parity, abort_flag)) {
+                ok = false;
+                break;
+            }
+            const uint32_t sw = smem_u32(ring + (size_t)s * stage_bytes);
+            const uint32_t sx = sw + (uint32_t)w_bytes;
+            const int k_steps = kc >> 4;           // (beyond K the copy has filled in zeros)
+            for (int ks = warp; ks < k_steps; ks += kWarps) {
+                const int piece = ks >> 2, chunk = (ks & 3) * 2;
+                uint32_t b[NT][2];
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt)
+                    ldmatrix_x2(b[nt], sx + swz(piece * 8 * NT + nt * 8 + b_row, chunk + b_half));
+#pragma unroll
+                for (int rt = 0; rt < RT; ++rt) {
+                    if (rt < row_tiles) {
+                        uint32_t a[4];
+                        ldmatrix_x4(a, sw + swz(piece * prows + rt * 16 + a_row, chunk + a_half));
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt) mma_bf16(acc[rt][nt], a, b[nt][0], b[nt][1]);
+                    }
+                }
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&empty[s]);
+        }
+        if (!ok) break;
+        // the eight warps' partial sums, tile by tile, through two alternating buffers
+#pragma unroll
+        for (int rt = 0; rt < RT; ++rt) {
+            if (rt < row_tiles) {
+                float* buf = red + (size_t)(rt & 1) * kWarps * 16 * width;
+                float* mine = buf + (size_t)warp * 16 * width;
+#pragma unroll
+                for (int nt = 0; nt < NT; ++nt) {
+                    const int r = lane >> 2, c = nt * 8 + 2 * (lane & 3);
+                    mine[r * width + c] = acc[rt][nt][0];
+                    mine[r * width + c + 1] = acc[rt][nt][1];
+                    mine[(r + 8) * width + c] = acc[rt][nt][2];
+                    mine[(r + 8) * width + c + 1] = acc[rt][nt][3];
+                }
+                consumer_sync();
+                const int tile_rows = min(16, prows - rt * 16);
+                // (results wait in shared memory and go to global memory once per pass: a barrier
+                // after stores to global memory costs a round trip to L2 each time)
+                if (prm.act) {
+                    for (int idx = tid; idx < prm.M * (tile_rows >> 1); idx += 32 * kWarps) {
+                        const int m = idx / (tile_rows >> 1), p = idx - m * (tile_rows >> 1);
+                        float g = 0.f, u = 0.f;
+#pragma unroll
+                        for (int wi = 0; wi < kWarps; ++wi) {
+                            g += buf[((size_t)wi * 16 + 2 * p) * width + m];
+                            u += buf[((size_t)wi * 16 + 2 * p + 1) * width + m];
+                        }
+                        held[m * rows_cap + rt * 8 + p] = gate_act(g, prm.act) * u;
+                    }
+                } else {
+                    for (int idx = tid; idx < prm.M * tile_rows; idx += 32 * kWarps) {
+                        const int m = idx / tile_rows, r = idx - m * tile_rows;
+                        float v = 0.f;
+#pragma unroll
+                        for (int wi = 0; wi < kWarps; ++wi) v += buf[((size_t)wi * 16 + r) * width + m];
+                        held[m * rows_cap + rt * 16 + r] = v;
+                    }
+                }
+            }
+        }
+        consumer_sync();        // all results of the pass are in `held`; both buffers are free again
+        {
+            const int n_local = prm.act ? prows >> 1 : prows;
+            const size_t first = prm.act ? (size_t)((r0 + pr0) >> 1) : (size_t)(r0 + pr0);
+            for (int idx = tid; idx < prm.M * n_local; idx += 32 * kWarps) {
+                const int m = idx / n_local, j = idx - m * n_local;
+                const size_t o = (size_t)m * n_out + first + j;
+                const float v = held[m * rows_cap + j];
+                if (prm.out_f32) reinterpret_cast<float*>(prm.out)[o] = v;
+                else reinterpret_cast<bf16*>(prm.out)[o] = __float2bfloat16_rn(v);
+            }
+        }
+        consumer_sync();        // `held` is free for the next pass
+    }
+}
+
+// ------------------------------------------------------------------------------- host
+struct Plan {
+    int rt, nt, kc, stages, unit, blocks;
+    int rows_a, rows_b, rows_c;     // rows of a full pass, of the last pass of the longer blocks, of the shorter
+    int w_bytes;
+    size_t smem;
+};
+
+static int sm_count() {
+    static int cached[64] = {0};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 1;
+    if (cached[dev] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 1;
+        cached[dev] = n;
+    }
+    return cached[dev];
+}
+
+// The shape of the launch, or 0 if the kernel does not take the product: bfloat16, M <= 16, K a
+// multiple of 64 (the width of a copied piece), an even number of rows for a gated product, and at
+// least two stages within the shared-memory budget.
+static int make_plan(int M, int N, int K, int act, int sms, Plan* p) {
+    if (M <= 0 || M > 16 || N <= 0 || K <= 0 || K % 64) return 0;
+    if (act < 0 || act > LSB_ACT_NONE || (act && (N % 2))) return 0;
+    p->unit = act ? 2 : 1;
+    const int units = N / p->unit;
+    p->blocks = units < sms ? units : sms;
+    const int hi = ((units + p->blocks - 1) / p->blocks) * p->unit, lo = (units / p->blocks) * p->unit;
+    p->rt = hi <= 16 ? 1 : hi <= 32 ? 2 : hi <= 64 ? 4 : 8;
+    const int cap = 16 * p->rt;
+    p->rows_a = hi < cap ? hi : cap;
+    p->rows_b = hi - ((hi + cap - 1) / cap - 1) * cap;
+    p->rows_c = lo - ((lo + cap - 1) / cap - 1) * cap;
+    p->nt = M <= 8 ? 1 : 2;
+    const size_t red = (size_t)(2 * kWarps * 16 + 16 * p->rt) * 8 * p->nt * sizeof(float);   // sums + a pass's results
+    const size_t room = (size_t)kSmemBudget - 1024 - 256 - red;
+    p->kc = 0;
+    const int cands[5] = {1024, 512, 256, 128, 64};
+    for (int c = 0; c < 5; ++c) {
+        const int kc = cands[c];
+        if (kc > K && kc != 128) continue;
+        const size_t w_bytes = ((size_t)p->rows_a * kc * 2 + 1023) & ~(size_t)1023;
+        const size_t stage = w_bytes + (size_t)(kc / 64) * 8 * p->nt * 128;
+        // three stages at least, unless even the shortest chunk does not allow them
+        if (3 * stage <= room || (kc <= 128 && 2 * stage <= room)) {
+            p->kc = kc;
+            p->w_bytes = (int)w_bytes;
+            p->stages = (int)(room / stage);
+            if (p->stages > kMaxStages) p->stages = kMaxStages;
+            p->smem = 1024 + (size_t)p->stages * stage + red + 256;
+            break;
+        }
+    }
+    return p->kc != 0;
+}
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode() {
+    static EncodeTiledFn fn = nullptr;
+    static bool tried = false;
+    if (!tried) {
+        tried = true;
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    }
+    return fn;
+}
+
+// A [rows, K] bf16 row-major matrix seen as (64 of K) x rows x (K / 64 pieces); boxes of
+// 64 x box_rows x pieces, 128-byte swizzle, zeros outside.
+static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_rows, int pieces) {
+    EncodeTiledFn enc = get_encode();
+    if (!enc) return (int)cudaErrorNotSupported;
+    cuuint64_t dims[3] = {64, (cuuint64_t)rows, (cuuint64_t)(K / 64)};
+    cuuint64_t strides[2] = {(cuuint64_t)K * 2, 128};
+    cuuint32_t box[3] = {64, (cuuint32_t)box_rows, (cuuint32_t)pieces};
+    cuuint32_t estr[3] = {1, 1, 1};
+    CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box, estr,
+                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+LSB_API int lsb_gemm_stream_supported(const void* x, const void* w, int M, int N, int K, int act) {
+    Plan p;
+    return ((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0 && make_plan(M, N, K, act, sm_count(), &p) &&
+           get_encode() != nullptr;
+}
+
+template <int RT, int NT>
+static int launch(const CUtensorMap* maps, const StreamParams& prm, const Plan& p, cudaStream_t stream) {
+    static int configured = -1;
+    if (configured < 0)
+        configured = (int)cudaFuncSetAttribute(gemm_stream_kernel<RT, NT>,
+                                               cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
+    if (configured) return configured;
+    return lsb_launch(gemm_stream_kernel<RT, NT>, dim3(p.blocks), dim3(kThreads), p.smem, stream, 1, maps[0],
+                      maps[1], maps[2], maps[3], prm);
+}
+
+// x [M, K] and w [N, K] bfloat16; out [M, N] (or [M, N / 2] with act != 0) bfloat16 or (out_f32) float.
+LSB_API int lsb_gemm_stream(const void* x, const void* w, void* out, int out_f32, int M, int N, int K,
+                            int act, cudaStream_t stream) {
+    Plan p;
+    if (!lsb_gemm_stream_supported(x, w, M, N, K, act)) return (int)cudaErrorInvalidValue;
+    make_plan(M, N, K, act, sm_count(), &p);
+    StreamParams prm;
+    prm.x = (const bf16*)x; prm.w = (const bf16*)w; prm.out = out;
+    prm.M = M; prm.N = N; prm.K = K;
+    prm.out_f32 = out_f32; prm.act = act;
+    prm.kc = p.kc; prm.stages = p.stages; prm.unit = p.unit; prm.w_bytes = p.w_bytes;
+    prm.rows_a = p.rows_a; prm.rows_b = p.rows_b; prm.rows_c = p.rows_c;
+    CUtensorMap maps[4];
+    int rc;
+    if ((rc = make_map(&maps[0], w, N, K, p.rows_a, p.kc / 64))) return rc;
+    if ((rc = make_map(&maps[1], w, N, K, p.rows_b, p.kc / 64))) return rc;
+    if ((rc = make_map(&maps[2], w, N, K, p.rows_c, p.kc / 64))) return rc;
+    if ((rc = make_map(&maps[3], x, M, K, 8 * p.nt, p.kc / 64))) return rc;
+#define LSB_STREAM_CASE(RT_)                                                                       \
+    case RT_: return p.nt == 1 ? launch<RT_, 1>(maps, prm, p, stream) : launch<RT_, 2>(maps, prm, p, stream)
+    switch (p.rt) {
+        LSB_STREAM_CASE(1);
+        LSB_STREAM_CASE(2);
+        LSB_STREAM_CASE(4);
+        LSB_STREAM_CASE(8);
+    }
+#undef LSB_STREAM_CASE
+    return (int)cudaErrorInvalidValue;
+}

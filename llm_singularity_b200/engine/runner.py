@@ -154,9 +154,13 @@ class ModelRunner:
                 raise ValueError(f"request {e.request!r} appears twice in one step")
             seen.add(e.request)
         V = self.spec.embedding.vocab_size
-        for e in entries:
-            if len(e.tokens) and not (0 <= min(e.tokens) and max(e.tokens) < V):
+        # (a prompt portion comes as a list of thousands of Python ints: turned into an array once,
+        # checked and later packed as an array)
+        arrays = [np.asarray(e.tokens, dtype=np.int64) for e in entries]
+        for e, a in zip(entries, arrays):
+            if a.size and not (0 <= int(a.min()) and int(a.max()) < V):
                 raise ValueError(f"request {e.request!r}: token id outside [0, {V})")
+        tokens = [a.astype(np.int32) for a in arrays]
         # pages for the whole step or for none of it: lengths first, then the pools' room for all
         # entries together (every group hands out the same number of pages), then the reservations
         for e, s in zip(entries, starts):
@@ -179,10 +183,10 @@ class ModelRunner:
             first = np.concatenate(([0], np.cumsum(lens[:-1]))).astype(np.int32)   # entry -> its first token
             moves = [first[np.asarray(which, dtype=np.int64)], np.asarray(places, dtype=np.int32)]
         if self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
-            logits = self._decode_with_graph(entries, starts, moves, None if feed is None else source)
+            logits = self._decode_with_graph(entries, starts, moves, None if feed is None else source, tokens)
             n_tokens = len(entries)
         else:
-            ctx, dev_moves = self.prepare_context(entries, starts, moves)
+            ctx, dev_moves = self.prepare_context(entries, starts, moves, tokens)
             if feed is not None:
                 self.rt.ops.move_i32(ctx.token_ids, dev_moves[0], source, dev_moves[1])
             logits, n_tokens = self.model.forward(ctx, cache), ctx.n_tokens
@@ -194,7 +198,8 @@ class ModelRunner:
 
     # ------------------------------------------------------------ decode graphs
     def _decode_with_graph(self, entries: Sequence[StepEntry], starts: Sequence[int],
-                           moves: List[np.ndarray], source: Optional[torch.Tensor]) -> torch.Tensor:
+                           moves: List[np.ndarray], source: Optional[torch.Tensor],
+                           tokens: Sequence[np.ndarray]) -> torch.Tensor:
         """A step of single decode tokens, all wanted: replay the graph captured for this batch
         size.  The step's metadata and the block-table cells that changed are copied into buffers
         at fixed addresses first; everything else happens inside the graph.  The returned logits
@@ -219,7 +224,7 @@ class ModelRunner:
                                                                     count=len(last))
             extra.append(packed)
         ctx, dev_extra = self._ctx.build(
-            [e.tokens for e in entries], list(starts), [cache.slot(e.request) for e in entries],
+            tokens, list(starts), [cache.slot(e.request) for e in entries],
             [e.want for e in entries], extra + moves, static=st.meta)
         ctx.fixed_launch = True
         if moves:                                    # after the metadata copy, before the graph
@@ -273,7 +278,7 @@ class ModelRunner:
             check()
 
     def prepare_context(self, entries: Sequence[StepEntry], starts: Sequence[int],
-                        more: Sequence[np.ndarray] = ()):
+                        more: Sequence[np.ndarray] = (), tokens: Optional[Sequence[np.ndarray]] = None):
         """Build the step's device metadata and bring the device block tables up to date.
         Returns the context and the int32 arrays of ``more`` on the device (they ride along in
         the metadata's one copy)."""
@@ -285,8 +290,10 @@ class ModelRunner:
             last = dict(ups)
             extra.append(np.fromiter(last.keys(), dtype=np.int32, count=len(last)))
             extra.append(np.fromiter(last.values(), dtype=np.int32, count=len(last)))
+        if tokens is None:
+            tokens = [e.tokens for e in entries]
         ctx, dev_extra = self._ctx.build(
-            [e.tokens for e in entries], list(starts),
+            tokens, list(starts),
             [cache.slot(e.request) for e in entries], [e.want for e in entries], extra + list(more))
         for gi, g in enumerate(cache.groups):
             idx, val = dev_extra[2 * gi], dev_extra[2 * gi + 1]

@@ -254,6 +254,13 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
         _call("gemm_small", "lsb_gemm_small", _p(x), _p(w), _p(out), _i(1 if out_dtype == torch.float32 else 0),
               _i(M), _i(N), _i(K), _stream(out))
         return out
+    if x.dtype == torch.bfloat16 and STREAM_PRODUCTS and M <= 16 and stream_gemm_ok(x, w, act):
+        # a few rows times a matrix of any size (decode: gate/up, down): every SM streams its own
+        # share of the weight rows, the first chunks before the previous kernel has ended
+        out = torch.empty((M, N // 2 if gated else N), dtype=out_dtype, device=x.device)
+        _call("gemm_stream", "lsb_gemm_stream", _p(x), _p(w), _p(out), _i(1 if out_dtype == torch.float32 else 0),
+              _i(M), _i(N), _i(K), _i(act), _stream(out))
+        return out
     if x.dtype == torch.bfloat16 and tensor_core_gemm_ok(x, w):
         out = torch.empty((M, N // 2 if gated else N), dtype=out_dtype, device=x.device)
         _call("gemm_tc", "lsb_gemm_tc", _p(x), _p(w), _p(out), _i(1 if out_dtype == torch.float32 else 0),
@@ -270,6 +277,20 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
 
 
 SMALL_PRODUCTS = True           # products of at most 16 rows with a small matrix: csrc/gemm_small.cu
+STREAM_PRODUCTS = True          # products of at most 16 rows with any matrix: csrc/gemm_stream.cu
+STREAM_MAX_ROWS = 65536         # weight rows beyond which the tile kernel's persistent form is used
+
+
+def stream_gemm_ok(x: torch.Tensor, w: torch.Tensor, act: int = 0) -> bool:
+    """Does the streaming kernel take x [M, K] times w [N, K] transposed?  (bfloat16, M <= 16, K a
+    multiple of 64; the output head, far more rows than the SMs can share out in a few passes,
+    stays with the persistent tile kernel.)"""
+    M, K = x.shape
+    N = w.shape[0]
+    if M > 16 or K % 64 or N > STREAM_MAX_ROWS:
+        return False
+    return bool(_lib("gemm_stream").lsb_gemm_stream_supported(_p(x), _p(w), _i(M), _i(N), _i(K), _i(act)))
+
 
 
 def small_gemm_ok(x: torch.Tensor, w: torch.Tensor) -> bool:

@@ -39,6 +39,7 @@ SOURCES: Dict[str, object] = {          # library -> its source file (or files)
     "gemm": "gemm.cu",
     "gemm_tc": "gemm_tc.cu",
     "gemm_small": "gemm_small.cu",
+    "gemm_stream": "gemm_stream.cu",
     "sampling": "sampling.cu",
     "random_init": "random_init.cu",
     # host code only: pools, block tables, prefix tree; scheduler

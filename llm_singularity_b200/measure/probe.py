@@ -1,16 +1,18 @@
 """Run one kernel on a given size, a few times, and print its time and achieved rate.
 
-    python -m llm_singularity_b200.kernels.probe gemm --m 8 --n 16384 --k 2048 [--gated] [--f32-out]
-    python -m llm_singularity_b200.kernels.probe decode_attention --batch 8 --context 4096
-    python -m llm_singularity_b200.kernels.probe prefill_attention --tokens 2048
-    python -m llm_singularity_b200.kernels.probe add_rmsnorm --tokens 2048 --hidden 2048
-    python -m llm_singularity_b200.kernels.probe rope --tokens 2048
-    python -m llm_singularity_b200.kernels.probe decode_step --batch 8 --context 4096
+    python -m llm_singularity_b200.measure.probe gemm --m 8 --n 16384 --k 2048 [--gated] [--f32-out]
+    python -m llm_singularity_b200.measure.probe decode_attention --batch 8 --context 4096
+    python -m llm_singularity_b200.measure.probe prefill_attention --tokens 2048
+    python -m llm_singularity_b200.measure.probe add_rmsnorm --tokens 2048 --hidden 2048
+    python -m llm_singularity_b200.measure.probe rope --tokens 2048
+    python -m llm_singularity_b200.measure.probe decode_step --batch 8 --context 4096
+    python -m llm_singularity_b200.measure.probe prefill_step --tokens 2048
 
 ``decode_step`` runs whole decode steps of a model of the given sizes (random weights) through the
 captured graph and prints where one step's time goes: for every kernel of one layer in the middle
 of the model, the time from the previous kernel's end to its own end (kernels overlap: each starts
-under its predecessor), and the step's total by kernel.
+under its predecessor), and the step's total by kernel.  ``prefill_step`` does the same for one
+prompt of ``--tokens`` tokens run as one step.
 
 Times are CUDA-event times on the launching stream after warm-up, with a buffer larger than the
 L2 cache read between iterations (``--no-flush`` to keep it warm).  The same command line is
@@ -70,8 +72,6 @@ def _time(fn, iters, warmup, flush):
 
 
 def _decode_step(a) -> None:
-    from torch.profiler import ProfilerActivity, profile
-
     from ..config.llama import LlamaConfig
     from ..engine import StepEntry
     from ..engine.engine import Engine
@@ -107,6 +107,26 @@ def _decode_step(a) -> None:
     torch.cuda.synchronize()
     print(f"decode step B={B} context={ctx_len} layers={a.layers} hidden={a.hidden}: "
           f"{e0.elapsed_time(e1) / a.iters * 1e3:.1f} us per step (CUDA events, graph replay)")
+    _timeline(step, "step")
+
+
+def _model(a, batch, max_len):
+    from ..config.llama import LlamaConfig
+    from ..engine.engine import Engine
+    cfg = LlamaConfig.from_dict(dict(
+        architectures=["LlamaForCausalLM"], num_hidden_layers=a.layers, hidden_size=a.hidden,
+        num_attention_heads=a.heads, num_key_value_heads=a.kv_heads, head_dim=a.head_dim,
+        intermediate_size=a.intermediate, vocab_size=a.vocab, rope_theta=500000.0, rope_scaling=None,
+        rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=131072))
+    eng = Engine(None, config=cfg, random_weights=True, dtype="bfloat16", kv_block_size=a.page,
+                 num_kv_blocks=batch * (max_len // a.page + 2) + 8, max_batch_size=batch,
+                 max_tokens_per_batch=max(2048, a.tokens), max_model_len=max_len + 64, prefix_cache=False)
+    return cfg, eng
+
+
+def _timeline(step, what):
+    """Profile one call of ``step`` and print one layer's kernels and the step's total by kernel."""
+    from torch.profiler import ProfilerActivity, profile
     with profile(activities=[ProfilerActivity.CUDA]) as prof:
         step()
         torch.cuda.synchronize()
@@ -125,15 +145,49 @@ def _decode_step(a) -> None:
     for i in range(1, len(evs)):
         total[names[i]] = total.get(names[i], 0.0) + evs[i].time_range.end - max(evs[i - 1].time_range.end,
                                                                                evs[i].time_range.start)
-    print("the step by kernel (time not hidden under the previous kernel), under the profiler:")
+    span = evs[-1].time_range.end - evs[0].time_range.start if evs else 0.0
+    print(f"the {what} by kernel (time not hidden under the previous kernel), under the profiler; "
+          f"first start to last end {span:.1f} us, {len(evs)} kernels:")
     for n, t in sorted(total.items(), key=lambda kv: -kv[1]):
         print(f"  {t:8.1f} us  {n[:70]}")
+
+
+def _prefill_step(a) -> None:
+    from ..engine import StepEntry
+    cfg, eng = _model(a, 2, a.tokens)
+    r = eng.runner
+    toks = torch.randint(0, cfg.vocab_size, (a.tokens,), generator=torch.Generator().manual_seed(0)).tolist()
+    n = [0]
+
+    def step():
+        rid = f"p{n[0]}"
+        n[0] += 1
+        r.open(rid)
+        out = r.step([StepEntry(rid, toks, [a.tokens - 1])])
+        r.close(rid)
+        return out
+
+    for _ in range(max(a.warmup, 2)):
+        step()
+    times = []
+    for _ in range(a.iters):
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        step()
+        e1.record()
+        torch.cuda.synchronize()
+        times.append(e0.elapsed_time(e1))
+    times.sort()
+    print(f"prefill step T={a.tokens} layers={a.layers} hidden={a.hidden}: median {times[len(times) // 2] * 1e3:.1f} us, "
+          f"best {times[0] * 1e3:.1f} us (CUDA events, launched kernel by kernel)")
+    _timeline(step, "step")
 
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="probe", description=__doc__.split("\n\n")[0])
     ap.add_argument("op", choices=["gemm", "decode_attention", "prefill_attention", "add_rmsnorm", "rope",
-                                   "decode_step"])
+                                   "decode_step", "prefill_step"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=16384)
     ap.add_argument("--k", type=int, default=2048)
@@ -160,6 +214,8 @@ def main(argv=None) -> int:
 
     if a.op == "decode_step":
         _decode_step(a)
+    elif a.op == "prefill_step":
+        _prefill_step(a)
     elif a.op == "gemm":
         x = torch.randn(a.m, a.k, device="cuda").to(torch.bfloat16)
         w = torch.randn(a.n, a.k, device="cuda").to(torch.bfloat16)

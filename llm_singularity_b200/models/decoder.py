@@ -101,7 +101,7 @@ class DecoderModel:
                 if k not in names:
                     names.append(k)
         if self.rt.dtype == torch.bfloat16 and "gemm" in names:
-            names += ["gemm_tc", "gemm_small"]    # bfloat16 products run on the tensor cores
+            names += ["gemm_tc", "gemm_small", "gemm_stream"]    # bfloat16 products run on the tensor cores
         return names
 
     # ------------------------------------------------------------------ forward

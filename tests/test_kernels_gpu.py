@@ -22,7 +22,7 @@ def _tol(dtype, scale=1.0):
 def ops():
     from llm_singularity_b200 import kernels
     kernels.prepare(["embedding", "norm", "activation", "cache_table", "rope_cache", "attention",
-                     "attention_tc", "gemm", "gemm_tc", "sampling"])
+                     "attention_tc", "gemm", "gemm_tc", "gemm_stream", "sampling"])
     yield kernels
     kernels.check_status()
 
@@ -213,7 +213,7 @@ def test_split_k_products_are_repeatable(ops, M, N, K):
     # tiles in split order, so the bits do not depend on arrival order, and the tile counters are
     # handed back zeroed for the next launch
     x, w = _rand(M, K, dtype=torch.bfloat16, seed=3), _rand(N, K, dtype=torch.bfloat16, seed=4)
-    ops.SMALL_PRODUCTS = False             # the tile kernel, also where the small-product kernel would do
+    ops.SMALL_PRODUCTS = ops.STREAM_PRODUCTS = False     # the tile kernel, also where the others would do
     try:
         first = ops.linear(x, w, out_dtype=torch.float32)
         want = x.double() @ w.double().T
@@ -221,7 +221,7 @@ def test_split_k_products_are_repeatable(ops, M, N, K):
         for _ in range(5):
             assert torch.equal(ops.linear(x, w, out_dtype=torch.float32), first)
     finally:
-        ops.SMALL_PRODUCTS = True
+        ops.SMALL_PRODUCTS = ops.STREAM_PRODUCTS = True
 
 
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
@@ -240,14 +240,56 @@ def test_small_products(ops, M, N, K, out_dtype):
     assert (y.double() - want).abs().max() <= tol
     for _ in range(3):
         assert torch.equal(ops.linear(x, w, out_dtype=out_dtype), y)      # a fixed summation order
-    ops.SMALL_PRODUCTS = False
+    ops.SMALL_PRODUCTS = ops.STREAM_PRODUCTS = False
     try:
         other = ops.linear(x, w, out_dtype=torch.float32)                 # the tile kernel
     finally:
-        ops.SMALL_PRODUCTS = True
+        ops.SMALL_PRODUCTS = ops.STREAM_PRODUCTS = True
     assert (other.double() - want).abs().max() <= 3e-7 * K * 8
     assert not ops.small_gemm_ok(_rand(17, K, dtype=torch.bfloat16, seed=1), w)
     assert not ops.small_gemm_ok(x[:, :K - 8].contiguous(), w[:, :K - 8].contiguous())
+
+
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("M, N, K, act", [
+    (8, 16384, 2048, "silu"), (8, 2048, 8192, None), (1, 2048, 8192, None), (16, 2048, 8192, None),
+    (16, 16384, 2048, "silu"), (13, 1000, 384, None), (3, 14, 128, None), (5, 28672, 4096, "gelu_tanh"),
+    (9, 40000, 256, None), (2, 302, 1152, "none"), (7, 6, 128, "silu"), (16, 5000, 128, None),
+    (4, 300, 192, None), (11, 2050, 64, "silu")])
+def test_streamed_products(ops, M, N, K, act, out_dtype):
+    """At most 16 rows times a matrix of any size, every SM streaming its own share of the weight
+    rows (the decode step's gate/up and down products): whole and partial 16-row tiles, one and
+    two 8-row tiles of activations, fewer rows than SMs, more rows than one pass holds, every
+    activation of a gated product; against 64-bit sums, bit for bit from call to call, and beside
+    the tile kernel."""
+    x = _rand(M, K, dtype=torch.bfloat16, seed=7, scale=0.5)
+    w = _rand(N, K, dtype=torch.bfloat16, seed=8, scale=0.2)
+    gated = act is not None
+    assert ops.stream_gemm_ok(x, w, ops.ACTIVATIONS[act] if gated else 0)
+    ops.SMALL_PRODUCTS = False
+    try:
+        y = ops.linear(x, w, out_dtype=out_dtype, gated=gated, activation=act or "silu")
+        again = [ops.linear(x, w, out_dtype=out_dtype, gated=gated, activation=act or "silu") for _ in range(3)]
+        ops.STREAM_PRODUCTS = False
+        tile = ops.linear(x, w, out_dtype=torch.float32, gated=gated, activation=act or "silu")
+    finally:
+        ops.SMALL_PRODUCTS = ops.STREAM_PRODUCTS = True
+    d = x.double() @ w.double().T
+    if gated:
+        g, u = d[:, 0::2], d[:, 1::2]
+        a = {"silu": g / (1 + torch.exp(-g)), "none": g,
+             "gelu_tanh": 0.5 * g * (1 + torch.tanh(math.sqrt(2 / math.pi) * (g + 0.044715 * g ** 3)))}[act]
+        want = a * u
+    else:
+        want = d
+    assert y.dtype == out_dtype and y.shape == want.shape
+    scale = want.abs().max().item() + 1
+    tol = 3e-7 * K * 8 * scale if out_dtype == torch.float32 else 1e-2 * scale
+    assert (y.double() - want).abs().max() <= tol
+    assert all(torch.equal(t, y) for t in again)                       # a fixed summation order
+    assert (tile.double() - want).abs().max() <= 2e-3 * scale          # (its activation is approximate)
+    assert not ops.stream_gemm_ok(_rand(17, K, dtype=torch.bfloat16, seed=1), w)
+    assert not ops.stream_gemm_ok(x[:, :K - 8].contiguous(), w[:, :K - 8].contiguous())
 
 
 def test_linear_float32_is_true_32_bit(ops):
