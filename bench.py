@@ -170,14 +170,13 @@ def run_ours(args):
         return ids
 
     def decode_steps(ids, n, feed):
-        """n decode steps with device-side greedy sampling; tokens fed are `feed` (host list)."""
-        greedy = torch.tensor([[0.0, 1.0, 1.0, 0.5]] * len(ids), device="cuda")
-        topk = torch.zeros(len(ids), dtype=torch.int32, device="cuda")
-        out = torch.empty(len(ids), dtype=torch.int32, device="cuda")
+        """n decode steps with device-side greedy sampling (inside the step's captured graph, as in
+        Engine.step); tokens fed are `feed` (host list)."""
+        from llm_singularity_b200.sampling import SamplingParams
+        greedy = eng.sampler.stage([SamplingParams(temperature=0.0)] * len(ids), [0] * len(ids))
         for _ in range(n):
-            logits = runner.step([StepEntry(rid, [t], [0]) for rid, t in zip(ids, feed)])
-            kernels.sample(logits, greedy, topk, None, None, out)
-        return out
+            runner.step([StepEntry(rid, [t], [0]) for rid, t in zip(ids, feed)], after=greedy)
+        return runner.after_result
 
     def time_decode(batch, steps, warmup, windows=1):
         """``windows`` timed windows of exactly ``steps`` decode steps each (the requests are

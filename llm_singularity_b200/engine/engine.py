@@ -156,14 +156,20 @@ class Engine:
                 tokens = [0]
             entries.append(StepEntry(it.request.id, tokens, [len(tokens) - 1] if it.sample else []))
         feed = (after.dev_tokens, places, which) if which else None
-        logits = self.runner.step(entries, feed=feed)
         wanted = [it.request for it in items if it.sample]
+        # a request's tokens still in flight count towards its place in the sampling stream
+        draws = [len(r.generated) + r.pending - 1 for r in wanted]
+        # sampling rides behind the model on the device (inside the captured graph of a decode
+        # step) wherever its parameters can be staged ahead: everything but a repetition penalty
+        staged = self.sampler.stage([r.sampling for r in wanted], draws) if wanted else None
+        logits = self.runner.step(entries, feed=feed, after=staged)
         launched = _Launched(wanted)
         if wanted:
-            # a request's tokens still in flight count towards its place in the sampling stream
-            launched.dev_tokens = self.sampler.sample(
-                logits, [r.sampling for r in wanted],
-                [len(r.generated) + r.pending - 1 for r in wanted], [r.generated for r in wanted])
+            if staged is not None:
+                launched.dev_tokens = self.runner.after_result
+            else:
+                launched.dev_tokens = self.sampler.sample(
+                    logits, [r.sampling for r in wanted], draws, [r.generated for r in wanted])
             if launched.dev_tokens.is_cuda:
                 host = self._host_tokens[self._host_turn][:len(wanted)]
                 self._host_turn ^= 1

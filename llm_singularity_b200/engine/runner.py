@@ -65,6 +65,7 @@ class _DecodeGraph:
         self.meta = torch.zeros(n, dtype=torch.int32, device=device)
         self.graph = None
         self.logits: Optional[torch.Tensor] = None
+        self.after_result = None                         # what the step's ``after`` returned at capture
         self.warm = 0
 
 
@@ -112,7 +113,8 @@ class ModelRunner:
         self.tokens_run = 0
         # decode-only steps are captured once per batch size and replayed (no per-kernel launch
         # cost); only if every part launches the same kernels whatever the host-side values are
-        self._graphs: Dict[int, "_DecodeGraph"] = {}
+        self._graphs: Dict[tuple, "_DecodeGraph"] = {}     # (batch size, key of the step's ``after``)
+        self.after_result = None
         self._capture_stream = None
         self.cuda_graphs = (cuda_graphs and ops is None and self.rt.device.type == "cuda"
                             and all(getattr(p, "graph_safe", False)
@@ -133,9 +135,15 @@ class ModelRunner:
         self.cache.close(request)
 
     # -------------------------------------------------------------------- step
-    def step(self, entries: Sequence[StepEntry], feed=None) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], feed=None, after=None) -> torch.Tensor:
         """Run the entries' tokens as one batch from the cache; returns the logits at the wanted
         places, float32 [wanted, vocab] on the device, in the order of the entries.
+
+        ``after``: a callable run on the logits right behind the model (sampling on the device);
+        what it returns is kept in ``after_result``.  In a decode step that is replayed from a
+        captured graph it is part of the graph, so it has to launch the same work on arrays at the
+        same addresses every time it is called for a batch size; ``after.key`` names it (a graph
+        is kept per batch size and key).
 
         ``feed = (source, places, which)`` says that some tokens of this step are on the device
         already (the previous step sampled them there and the host has not read them yet): entry
@@ -183,13 +191,15 @@ class ModelRunner:
             first = np.concatenate(([0], np.cumsum(lens[:-1]))).astype(np.int32)   # entry -> its first token
             moves = [first[np.asarray(which, dtype=np.int64)], np.asarray(places, dtype=np.int32)]
         if self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
-            logits = self._decode_with_graph(entries, starts, moves, None if feed is None else source, tokens)
+            logits = self._decode_with_graph(entries, starts, moves, None if feed is None else source, tokens,
+                                             after)
             n_tokens = len(entries)
         else:
             ctx, dev_moves = self.prepare_context(entries, starts, moves, tokens)
             if feed is not None:
                 self.rt.ops.move_i32(ctx.token_ids, dev_moves[0], source, dev_moves[1])
             logits, n_tokens = self.model.forward(ctx, cache), ctx.n_tokens
+            self.after_result = after(logits) if after is not None and logits.shape[0] else None
         for e, s in zip(entries, starts):
             cache.commit(e.request, s + len(e.tokens))
         self.steps += 1
@@ -199,15 +209,16 @@ class ModelRunner:
     # ------------------------------------------------------------ decode graphs
     def _decode_with_graph(self, entries: Sequence[StepEntry], starts: Sequence[int],
                            moves: List[np.ndarray], source: Optional[torch.Tensor],
-                           tokens: Sequence[np.ndarray]) -> torch.Tensor:
+                           tokens: Sequence[np.ndarray], after=None) -> torch.Tensor:
         """A step of single decode tokens, all wanted: replay the graph captured for this batch
         size.  The step's metadata and the block-table cells that changed are copied into buffers
         at fixed addresses first; everything else happens inside the graph.  The returned logits
         live in the graph's own memory and are overwritten by the next step of the same size."""
         cache, R = self.cache, len(entries)
-        st = self._graphs.get(R)
+        key = (R, getattr(after, "key", None) if after is not None else None)
+        st = self._graphs.get(key)
         if st is None:
-            st = self._graphs[R] = _DecodeGraph(R, len(cache.groups), self.rt.device)
+            st = self._graphs[key] = _DecodeGraph(R, len(cache.groups), self.rt.device)
         extra: List[np.ndarray] = []
         for gi in range(len(cache.groups)):
             last = dict(cache.take_updates(gi))
@@ -233,12 +244,16 @@ class ModelRunner:
         def run():
             for gi, g in enumerate(cache.groups):
                 self.rt.ops.scatter_i32_counted(g.dev_table, dev_extra[gi], st.cap)
-            return self.model.forward(ctx, cache)
+            logits = self.model.forward(ctx, cache)
+            st.after_result = after(logits) if after is not None else None
+            return logits
 
         if st.graph is None:
             if st.warm < 1:                              # once eagerly: loads libraries, sizes scratch
                 st.warm += 1
-                return run()
+                logits = run()
+                self.after_result = st.after_result
+                return logits
             torch.cuda.synchronize(self.rt.device)
             graph = torch.cuda.CUDAGraph()
             try:
@@ -263,11 +278,14 @@ class ModelRunner:
                 warnings.warn(f"CUDA graph capture failed ({e}); decode steps run without graphs")
                 self.cuda_graphs = False
                 torch.cuda.synchronize(self.rt.device)
-                return run()
+                logits = run()
+                self.after_result = st.after_result
+                return logits
             st.graph = graph
             # the capture did not execute anything: the replay below runs this step
         st.graph.replay()
         self.graph_replays += 1
+        self.after_result = st.after_result
         return st.logits
 
     def check_kernels(self) -> None:
