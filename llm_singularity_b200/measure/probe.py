@@ -1,6 +1,6 @@
 """Run one kernel on a given size, a few times, and print its time and achieved rate.
 
-    python -m llm_singularity_b200.measure.probe gemm --m 8 --n 16384 --k 2048 [--gated] [--f32-out]
+    python -m llm_singularity_b200.measure.probe gemm --m 8 --n 16384 --k 2048 [--gated] [--f32-out] [--tile-kernel]
     python -m llm_singularity_b200.measure.probe decode_attention --batch 8 --context 4096
     python -m llm_singularity_b200.measure.probe prefill_attention --tokens 2048
     python -m llm_singularity_b200.measure.probe add_rmsnorm --tokens 2048 --hidden 2048
@@ -193,6 +193,8 @@ def main(argv=None) -> int:
     ap.add_argument("--k", type=int, default=2048)
     ap.add_argument("--gated", action="store_true")
     ap.add_argument("--f32-out", action="store_true")
+    ap.add_argument("--tile-kernel", action="store_true",
+                    help="gemm: the tcgen05 tile kernel also where the small or streaming kernel would run")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--tokens", type=int, default=2048)
@@ -217,6 +219,8 @@ def main(argv=None) -> int:
     elif a.op == "prefill_step":
         _prefill_step(a)
     elif a.op == "gemm":
+        if a.tile_kernel:
+            K.SMALL_PRODUCTS = K.STREAM_PRODUCTS = False
         x = torch.randn(a.m, a.k, device="cuda").to(torch.bfloat16)
         w = torch.randn(a.n, a.k, device="cuda").to(torch.bfloat16)
         od = torch.float32 if a.f32_out else torch.bfloat16
