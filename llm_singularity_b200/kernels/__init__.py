@@ -82,9 +82,75 @@ def _call(libname: str, fn: str, *args) -> None:
     global _launches
     lib = _lib(libname)
     _launches += 1
-    rc = getattr(lib, fn)(*args)
+    cfn = getattr(lib, fn)
+    rc = cfn(*args)
     if rc != 0:
         raise KernelError(f"{fn} failed: {lib.lsb_error_string(rc).decode()} (code {rc})")
+    if _recording is not None:
+        _recording.ops.append([cfn, list(args), fn, lib, ()])
+
+
+# ------------------------------------------------------ a layer's launches, recorded
+# The layers of a model are the same sequence of launches with other weights.  What the host does
+# per launch (checks, choosing a kernel, sizing grids, allocating the output) is the same work for
+# every layer of a step, and in steps that hold prompt portions (launched kernel by kernel, unlike
+# decode steps, which replay a captured graph) it is most of the host's time.  So the model records
+# the launches of one layer call and repeats them for the calls after it that have the same shape,
+# with the pointers of that layer's own tensors (weights, cache pages, the delta coming in and
+# going out) exchanged for the next layer's; every other buffer is the recorded layer's, reused in
+# stream order.
+LAYER_REPLAY = True
+_recording: Optional["LayerRecording"] = None
+
+
+class LayerRecording:
+    """The launches of one layer call: C entry points with their packed arguments and, between
+    them, stream operations (the second stream of steps that hold decode tokens and portions)."""
+
+    def __init__(self):
+        self.ops = []          # [cfunction, args, name, lib, slots] or a callable (a stream operation)
+        self.keep = []         # tensors whose memory the recorded launches use
+        self._before = None
+
+    def __enter__(self):
+        global _recording
+        self._before, _recording = _recording, self
+        return self
+
+    def __exit__(self, *exc):
+        global _recording
+        _recording = self._before
+        return False
+
+    def bind(self, roles: Dict[int, object]) -> None:
+        """``roles``: device address -> name, for every tensor that is the recorded layer's own.
+        Arguments that hold such an address become slots that :meth:`replay` fills."""
+        for op in self.ops:
+            if not callable(op):
+                op[4] = tuple((i, roles[a.value]) for i, a in enumerate(op[1])
+                              if isinstance(a, ctypes.c_void_p) and a.value in roles)
+
+    def replay(self, addresses: Dict[object, int]) -> None:
+        """Launch everything again with the slots pointing at ``addresses[name]``."""
+        global _launches
+        for op in self.ops:
+            if callable(op):
+                op()
+                continue
+            cfn, args, name, lib, slots = op
+            for i, role in slots:
+                args[i] = ctypes.c_void_p(addresses[role])
+            _launches += 1
+            rc = cfn(*args)
+            if rc != 0:
+                raise KernelError(f"{name} failed: {lib.lsb_error_string(rc).decode()} (code {rc})")
+
+
+def _stream_op(fn) -> None:
+    """Do a stream or event operation now and, when a layer is being recorded, again at every replay."""
+    fn()
+    if _recording is not None:
+        _recording.ops.append(fn)
 
 
 # ------------------------------------------------------------------- helpers
@@ -109,6 +175,8 @@ def _req(t: torch.Tensor, name: str, dtype=None, dim: Optional[int] = None, cont
 
 
 def _p(t: Optional[torch.Tensor]):
+    if _recording is not None and t is not None:
+        _recording.keep.append(t)
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 
 
@@ -446,14 +514,14 @@ def rope_store_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cac
             # decode kernel (memory-bound) runs on a second stream beside the rotation and the
             # attention of the portions (compute-bound), and the step's stream waits for both.
             main, side, fork, join = _fork_join(ctx, qkv.device)
-            fork.record(main)                                 # qkv is whole here
-            side.wait_event(fork)
+            _stream_op(lambda: fork.record(main))             # qkv is whole here
+            _stream_op(lambda: side.wait_event(fork))
             paged_attention(qkv, nh, nkv, hd, ctx, cache, scale, window, out,
                             decode_rope=(inv_freq, store), only="single", stream=side.cuda_stream)
-            join.record(side)
+            _stream_op(lambda: join.record(side))
             rope_kv_store(qkv, nh, nkv, hd, ctx, cache, inv_freq, rotary_dim, store, skip_single=True)
             paged_attention(qkv, nh, nkv, hd, ctx, cache, scale, window, out, only="portions")
-            main.wait_event(join)
+            _stream_op(lambda: main.wait_event(join))
             return
         rope_kv_store(qkv, nh, nkv, hd, ctx, cache, inv_freq, rotary_dim, store, skip_single=True)
     else:

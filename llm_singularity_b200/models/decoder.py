@@ -105,13 +105,82 @@ class DecoderModel:
         return names
 
     # ------------------------------------------------------------------ forward
+    @staticmethod
+    def _own_tensors(block: Part, view) -> Dict[tuple, torch.Tensor]:
+        """(path, attribute) -> tensor, for every tensor a block's parts hold and its cache view."""
+        out: Dict[tuple, torch.Tensor] = {}
+
+        def walk(path: str, part: Part):
+            for name, val in vars(part).items():
+                if isinstance(val, torch.Tensor):
+                    out[(path, name)] = val
+            for cname, child in part.children().items():
+                walk(f"{path}.{cname}", child)
+
+        walk("block", block)
+        if view is not None:
+            for name, val in vars(view).items():
+                if isinstance(val, torch.Tensor):
+                    out[("cache", name)] = val
+        return out
+
+    def _replay_key(self, call, view):
+        """What two layer calls must have in common for one's recorded launches to serve the other
+        (None: this call cannot be recorded or replayed)."""
+        block = self.blocks[call.block]
+        parts = [block]
+        k = 0
+        while k < len(parts):
+            parts.extend(parts[k].children().values())
+            k += 1
+        if not all(p.replayable for p in parts):
+            return None
+        shapes = tuple((key, tuple(t.shape), t.dtype) for key, t in sorted(self._own_tensors(block, view).items()))
+        return (self.spec.blocks[call.block], call.writes_cache, type(view).__name__,
+                getattr(view, "group", None), getattr(view, "window", None), shapes)
+
     def forward(self, ctx, caches) -> torch.Tensor:
-        """Run this step's tokens through every layer call; logits ``[wanted, vocab]``."""
+        """Run this step's tokens through every layer call; logits ``[wanted, vocab]``.
+
+        A layer call whose parts are all ``replayable`` is recorded launch by launch the first
+        time its kind comes up in a step (from the second layer on: the first has no delta coming
+        in), and the calls of the same kind after it repeat those launches with their own weights
+        and cache pages; the delta between layers alternates between the recorded call's input
+        and output buffers."""
+        ops = self.rt.ops
+        replay = getattr(ops, "LAYER_REPLAY", False) and hasattr(ops, "LayerRecording")
         residual = self.embedding.forward(ctx.token_ids)
         pending = None
-        for call in self.spec.order:
-            pending = self.blocks[call.block].forward(
-                residual, pending, ctx, caches.view(call.cache, ctx), call.writes_cache)
+        rec = rec_key = None
+        order = self.spec.order
+        memo = self.__dict__.setdefault("_replay_memo", {})     # per layer call: its key and addresses
+        for i, call in enumerate(order):
+            block, view = self.blocks[call.block], caches.view(call.cache, ctx)
+            if replay and i not in memo:
+                key = self._replay_key(call, view)
+                memo[i] = (key, None if key is None else
+                           {name: t.data_ptr() for name, t in self._own_tensors(block, view).items()})
+            key = memo[i][0] if replay and pending is not None else None
+            if key is not None and rec is not None and key == rec_key:
+                own = dict(memo[i][1])
+                own["delta in"], own["delta out"] = pending.data_ptr(), rec_bufs[pending is rec_bufs[0]].data_ptr()
+                rec.replay(own)
+                pending = rec_bufs[pending is rec_bufs[0]]
+                continue
+            worth = key is not None and i + 1 < len(order) and rec_key != key
+            if worth:
+                with ops.LayerRecording() as rec:
+                    out = block.forward(residual, pending, ctx, view, call.writes_cache)
+                roles = {t.data_ptr(): name for name, t in self._own_tensors(block, view).items()}
+                if pending.data_ptr() in roles or out.data_ptr() in roles or pending.data_ptr() == out.data_ptr():
+                    rec = rec_key = None                         # (cannot tell the buffers apart)
+                else:
+                    roles[pending.data_ptr()], roles[out.data_ptr()] = "delta in", "delta out"
+                    rec.bind(roles)
+                    rec_key, rec_bufs = key, (pending, out)
+                pending = out
+                continue
+            pending = block.forward(residual, pending, ctx, view, call.writes_cache)
         if ctx.n_wanted == 0:
             return torch.empty(0, self.spec.head.vocab_size, dtype=torch.float32,
                                device=self.rt.device)

@@ -21,6 +21,7 @@ from .base import POSITIONS, PagedKVSpec, ParamSpec, Part, register_mixer
 @register_mixer("attention")
 class PagedAttention(Part):
     graph_safe = True
+    replayable = True
     kernels = ("gemm", "rope_cache", "attention")
 
     def __init__(self, spec, rt):
@@ -32,6 +33,8 @@ class PagedAttention(Part):
         if s.window is not None and s.window < 1:
             raise ValueError(f"window must be at least 1, got {s.window}")
         self.position = POSITIONS.build(s.position, rt)
+        if self.position.rotary_table() is None:
+            self.replayable = False          # a position encoding applied with tensor operations
         if rt.dtype == torch.bfloat16 and s.head_dim in (64, 128):
             self.kernels = self.kernels + ("attention_tc", "attention_tc5")
         self.q_size = s.num_heads * s.head_dim

@@ -185,6 +185,11 @@ class Part:
     """
 
     graph_safe = False
+    # ``replayable``: everything ``forward`` does on the device goes through the kernel entry points
+    # (no tensor-library operations, no values read back), with the same launches for another part
+    # of the same spec and the same step, so that a layer's launches can be recorded once and
+    # repeated for the layers after it (``kernels.LayerRecording``).
+    replayable = False
 
     def __init__(self, spec, rt: Runtime):
         self.spec = spec

@@ -18,6 +18,7 @@ from .base import FEED_FORWARDS, MIXERS, NORMS, Part, register_block
 @register_block("pre_norm")
 class PreNormBlock(Part):
     graph_safe = True
+    replayable = True
     def __init__(self, spec, rt):
         super().__init__(spec, rt)
         self.mixer_norm = NORMS.build(spec.mixer_norm, rt)

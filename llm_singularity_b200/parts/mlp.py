@@ -20,6 +20,7 @@ from .base import ParamSpec, Part, register_feed_forward
 @register_feed_forward("gated_mlp")
 class GatedMLP(Part):
     graph_safe = True
+    replayable = True
     kernels = ("gemm", "activation")
 
     def __init__(self, spec, rt):

@@ -18,6 +18,7 @@ from .base import ParamSpec, Part, register_norm
 @register_norm("rmsnorm")
 class RMSNorm(Part):
     graph_safe = True
+    replayable = True
     kernels = ("norm",)
 
     @classmethod

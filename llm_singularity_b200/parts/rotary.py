@@ -42,6 +42,7 @@ def rotary_inv_freq(rotary_dim: int, theta: float, scaling=None) -> torch.Tensor
 @register_position("rotary")
 class RotaryEncoding(Part):
     graph_safe = True
+    replayable = True
     kernels = ("rope_cache",)
 
     def __init__(self, spec, rt):

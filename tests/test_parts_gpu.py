@@ -193,3 +193,50 @@ def test_block_part_carries_the_pending_delta(dtype):
     want = plain_llama.swiglu_mlp(h, d["gate_proj"], d["up_proj"], d["down_proj"])
     assert (res.double().cpu() - x).abs().max() <= _tol(dtype, 4)          # residual after attention
     assert (out.double().cpu() - want).abs().max() <= _tol(dtype, want.abs().max().item() + 1)
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_replayed_layers_give_the_same_bits_as_layers_run_one_by_one(tmp_path, dtype):
+    """From the second layer on a step records a layer's launches and repeats them for the layers
+    after it with their own weights and pages.  A step of decode tokens beside prompt portions
+    (two streams), a prompt alone and a decode step (captured graph), each against the same step
+    with the repetition switched off: identical logits, identical cache pages."""
+    from llm_singularity_b200 import kernels
+    from llm_singularity_b200.engine import ModelRunner, StepEntry
+    import tiny_models
+    import json, os
+    from llm_singularity_b200.config.llama import LlamaConfig
+    from llm_singularity_b200.weights import write_random_model
+    name = "tiny_b" if dtype == "float32" else "tiny_d"      # generic kernels / heads of 64, five layers each
+    cfg = dict(tiny_models.CONFIGS[name], num_hidden_layers=5)
+    model_dir = str(tmp_path / "five_layers")
+    write_random_model(model_dir, LlamaConfig.from_dict(cfg), seed=77, std=0.08, norm_noise=0.1)
+    json.dump(cfg, open(os.path.join(model_dir, "config.json"), "w"))
+    vocab = cfg["vocab_size"]
+    ps = tiny_models.PAGE_SIZE[name]
+    toks = {r: tiny_models.random_tokens(vocab, n, 70 + i) for i, (r, n) in enumerate((("a", 150), ("b", 40), ("c", 9)))}
+    results = []
+    launches = []
+    try:
+        for on in (False, True):
+            kernels.LAYER_REPLAY = on
+            runner = ModelRunner(model_dir, dtype=dtype, page_size=ps, num_pages=64, max_requests=4)
+            for r in toks:
+                runner.open(r)
+            n0 = kernels.launch_count()
+            outs = [runner.step([StepEntry("b", toks["b"][:30], [29]), StepEntry("c", toks["c"][:8], [7])]).clone()]
+            outs.append(runner.step([StepEntry("b", toks["b"][30:31], [0]), StepEntry("c", toks["c"][8:], [0]),
+                                     StepEntry("a", toks["a"][:140], [0, 139])]).clone())
+            for k in range(31, 35):                                              # decode steps: eager, captured, replayed
+                outs.append(runner.step([StepEntry("b", [toks["b"][k]], [0]), StepEntry("a", [toks["a"][109 + k]], [0])]).clone())
+            launches.append(kernels.launch_count() - n0)
+            runner.check_kernels()
+            pages = [t.clone() for cid in range(len(runner.model.cache_specs())) for t in runner.cache._store[cid]]
+            results.append((outs, pages))
+    finally:
+        kernels.LAYER_REPLAY = True
+    for a, b in zip(results[0][0], results[1][0]):
+        assert torch.equal(a, b)
+    for a, b in zip(results[0][1], results[1][1]):
+        assert torch.equal(a, b)
+    assert launches[0] == launches[1]                 # the same kernels were launched, as many times
