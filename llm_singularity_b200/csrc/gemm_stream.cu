@@ -61,6 +61,9 @@ struct StreamParams {
     int unit;           // rows are dealt in units of this many (2 for a gated product)
     int w_bytes;        // shared memory a stage keeps for weights (a multiple of 1024)
     int rows_a, rows_b, rows_c;   // rows of the boxes of the three weight maps
+    int rt, rt_log2;    // 16-row tiles of a pass (1, 2, 4 or 8)
+    int rows_hi, rows_lo, n_hi;   // the first n_hi blocks have rows_hi rows, the others rows_lo
+    int nk;             // chunks of K
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -123,14 +126,18 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(32 * kWarps) : "memory"); }
 
 __device__ __forceinline__ float gate_act(float g, int act) {
-    if (act == LSB_ACT_SILU) return g / (1.f + expf(-g));
+    if (act == LSB_ACT_SILU) return g / (1.f + __expf(-g));
     if (act == LSB_ACT_GELU_TANH) return 0.5f * g * (1.f + tanhf(0.7978845608f * (g + 0.044715f * g * g * g)));
     return g;
 }
 
-// RT: 16-row tiles of weights per pass (a block with more rows than 16 * RT walks K once per pass);
-// NT: 8-row tiles of activations (M <= 8 * NT).
-template <int RT, int NT>
+// A pass covers 16 * rt rows of the block (rt = 1, 2, 4 or 8 tiles); the eight consumer warps are
+// rt tiles x (8 / rt) parts of every chunk's K, one 16-row tile and one part each.  A warp keeps kInFlight
+// k-steps going at once, each with an accumulator of its own (one mma at a time on one accumulator
+// would wait out the tensor core's latency at every step).  NT: 8-row tiles of activations.
+constexpr int kInFlight = 4;
+
+template <int NT>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                    const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_x,
@@ -139,187 +146,190 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     unsigned char* smem_raw = (unsigned char*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
     lsb_pdl_launch_dependents();
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int K = prm.K, kc = prm.kc, stages = prm.stages;
+    const int kc = prm.kc, stages = prm.stages;
     const int pieces = kc >> 6;                                   // 64-wide pieces of a chunk
     const int w_bytes = prm.w_bytes, x_bytes = pieces * 8 * NT * 128;   // (x_bytes: a multiple of 1024)
     const int stage_bytes = w_bytes + x_bytes;
+    constexpr int width = 8 * NT;
 
     unsigned char* ring = smem_raw;
-    float* red = reinterpret_cast<float*>(ring + (size_t)stages * stage_bytes);   // [2][kWarps][16][8 * NT]
-    float* held = red + 2 * kWarps * 16 * 8 * NT;                                  // [8 * NT][16 * RT]: a pass's results
-    uint64_t* full_w = reinterpret_cast<uint64_t*>(held + 8 * NT * 16 * RT);       // [kMaxStages] each
+    float* red = reinterpret_cast<float*>(ring + (size_t)stages * stage_bytes);   // [2][kWarps * 16][width]
+    uint64_t* full_w = reinterpret_cast<uint64_t*>(red + 2 * kWarps * 16 * width);   // [kMaxStages] each
     uint64_t* full_x = full_w + kMaxStages;
     uint64_t* empty = full_x + kMaxStages;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + kMaxStages);
 
     // this block's rows
-    const int units = prm.N / prm.unit;
-    const int r0 = (int)((long long)blockIdx.x * units / gridDim.x) * prm.unit;
-    const int r1 = (int)((long long)(blockIdx.x + 1) * units / gridDim.x) * prm.unit;
-    const int rows = r1 - r0;
-    const int rows_cap = 16 * RT;
-    const int passes = (rows + rows_cap - 1) / rows_cap;
-    const int nk = (K + kc - 1) / kc;
-    const int n_it = passes * nk;
+    // (worked out without a division: a kernel that lives ten microseconds cannot spend half of one
+    // on index arithmetic before its first copy is asked for)
+    const int blk = (int)blockIdx.x;
+    const bool longer = blk < prm.n_hi;
+    const int rows = longer ? prm.rows_hi : prm.rows_lo;
+    const int r0 = longer ? blk * prm.rows_hi : prm.n_hi * prm.rows_hi + (blk - prm.n_hi) * prm.rows_lo;
+    const int rt = prm.rt, rows_cap = 16 * rt;
+    const int passes = (rows + rows_cap - 1) >> (4 + prm.rt_log2);
+    const int nk = prm.nk;
     // Every block needs the same activations.  Each starts its walk through K at another chunk, so
     // that at any moment the blocks ask L2 for different lines (all of them on the same few lines
     // at once is a queue at those lines' L2 slices); the order of a block's sums is still fixed.
     const int k_shift = (int)(blockIdx.x % (unsigned)nk);
 
-    if (tid == 0) {
-        *abort_flag = 0;
-        for (int s = 0; s < stages; ++s) {
-            mbar_init(&full_w[s], 1);
-            mbar_init(&full_x[s], 1);
-            mbar_init(&empty[s], kWarps);
-        }
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    __syncthreads();
-
     if (warp == kWarps) {
         // ------------------------------------------------------------------ producer
-        // (one thread: a stage is one copy of weights and one of activations)
-        auto issue_w = [&](int it) {
-            const int s = it % stages, pass = it / nk, kb = (it - pass * nk + k_shift) % nk;
-            const int pr0 = pass * rows_cap, prows = min(rows_cap, rows - pr0);
+        // (one thread: a stage is one copy of weights and one of activations.  It sets up the
+        // barriers itself and asks for the first stages before the block meets.)
+        // A walk through (pass, chunk of K, stage of the ring), one step at a time; `turn` counts the
+        // trips around the ring (its lowest bit is the parity a stage's barriers complete with).
+        struct Walk { int pass, kb, s, turn; };
+        auto step = [&](Walk& w) {
+            if (++w.kb == nk) { w.kb = 0; ++w.pass; }
+            if (++w.s == stages) { w.s = 0; ++w.turn; }
+        };
+        auto chunk_of = [&](const Walk& w) { const int c = w.kb + k_shift; return c >= nk ? c - nk : c; };
+        auto issue_w = [&](const Walk& w) {
+            const int pr0 = w.pass * rows_cap, prows = min(rows_cap, rows - pr0);
             const CUtensorMap* map = prows == prm.rows_a ? &map_a : prows == prm.rows_b ? &map_b : &map_c;
-            mbar_expect_tx(&full_w[s], (uint32_t)(prows * kc * 2));
-            tma_load_3d(ring + (size_t)s * stage_bytes, map, &full_w[s], 0, r0 + pr0, kb * pieces);
+            mbar_expect_tx(&full_w[w.s], (uint32_t)(prows * kc * 2));
+            tma_load_3d(ring + (size_t)w.s * stage_bytes, map, &full_w[w.s], 0, r0 + pr0, chunk_of(w) * pieces);
         };
-        auto issue_x = [&](int it) {
-            const int s = it % stages, pass = it / nk, kb = (it - pass * nk + k_shift) % nk;
-            mbar_expect_tx(&full_x[s], (uint32_t)x_bytes);
-            tma_load_3d(ring + (size_t)s * stage_bytes + w_bytes, &map_x, &full_x[s], 0, 0, kb * pieces);
+        auto issue_x = [&](const Walk& w) {
+            mbar_expect_tx(&full_x[w.s], (uint32_t)x_bytes);
+            tma_load_3d(ring + (size_t)w.s * stage_bytes + w_bytes, &map_x, &full_x[w.s], 0, 0, chunk_of(w) * pieces);
         };
-        if (lane != 0) return;
-        const int ahead = min(stages, n_it);
-        for (int it = 0; it < ahead; ++it) issue_w(it);           // weights depend on nothing
-        lsb_pdl_wait();
-        bool ok = true;
-        int issued_w = ahead, issued_x = 0;
-        for (int it = 0; it < n_it && ok; ++it) {
-            if (it >= stages) {
-                ok = mbar_wait(&empty[it % stages], (uint32_t)(((it / stages) & 1) ^ 1), abort_flag);
-                if (!ok) break;
-                issue_w(it);
-                issued_w = it + 1;
+        Walk ww = {0, 0, 0, 0};          // the next weights to ask for
+        if (lane == 0) {
+            *abort_flag = 0;
+            for (int s = 0; s < stages; ++s) {
+                mbar_init(&full_w[s], 1);
+                mbar_init(&full_x[s], 1);
+                mbar_init(&empty[s], kWarps);
             }
-            issue_x(it);
-            issued_x = it + 1;
+            asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+            while (ww.turn == 0 && ww.pass < passes) {             // weights depend on nothing
+                issue_w(ww);
+                step(ww);
+            }
+        }
+        __syncthreads();
+        if (lane != 0) return;
+        lsb_pdl_wait();
+        Walk wx = {0, 0, 0, 0};          // the next activations to ask for
+        bool ok = true;
+        while (wx.pass < passes) {
+            if (wx.turn > 0) {
+                ok = mbar_wait(&empty[wx.s], (uint32_t)((wx.turn & 1) ^ 1), abort_flag);
+                if (!ok) break;
+                issue_w(ww);
+                step(ww);
+            }
+            issue_x(wx);
+            step(wx);
         }
         if (!ok) {
             // gave up: copies still in flight must land before the block's shared memory goes away
-            for (int it = max(0, issued_w - stages); it < issued_w; ++it)
-                for (uint32_t n = 0; n < (1u << 16) && !mbar_try_wait(&full_w[it % stages], (it / stages) & 1); ++n)
+            // (every stage's last copy of weights, and of activations, that was asked for)
+            for (int back = 0; back < stages; ++back) {
+                Walk w = ww;
+                for (int n = 0; n <= back; ++n) { if (w.s == 0) { w.s = stages; --w.turn; } --w.s; }
+                if (w.turn < 0) break;
+                for (uint32_t n = 0; n < (1u << 16) && !mbar_try_wait(&full_w[w.s], (uint32_t)(w.turn & 1)); ++n)
                     __nanosleep(64);
-            for (int it = max(0, issued_x - stages); it < issued_x; ++it)
-                for (uint32_t n = 0; n < (1u << 16) && !mbar_try_wait(&full_x[it % stages], (it / stages) & 1); ++n)
+            }
+            for (int back = 0; back < stages; ++back) {
+                Walk w = wx;
+                for (int n = 0; n <= back; ++n) { if (w.s == 0) { w.s = stages; --w.turn; } --w.s; }
+                if (w.turn < 0) break;
+                for (uint32_t n = 0; n < (1u << 16) && !mbar_try_wait(&full_x[w.s], (uint32_t)(w.turn & 1)); ++n)
                     __nanosleep(64);
+            }
         }
         return;
     }
 
     // ---------------------------------------------------------------------- consumers
+    __syncthreads();         // the barriers are set up
     lsb_pdl_wait();          // before anything of this kernel is stored (its output buffer may be one
                              // that an earlier kernel of the stream still reads)
     const int a_row = ((lane >> 3) & 1) * 8 + (lane & 7), a_half = lane >> 4;
     const int b_row = lane & 7, b_half = (lane >> 3) & 1;
-    const int width = 8 * NT;
+    const int my_tile = warp & (rt - 1), my_part = warp / rt, parts = kWarps / rt;
     const int n_out = prm.act ? prm.N / 2 : prm.N;
-    int it = 0;
-    bool ok = true;
-    for (int pass = 0; pass < passes && ok; ++pass) {
-        float acc[RT][NT][4];
+    const int k_steps = kc >> 4;               // a multiple of kInFlight (beyond K the copy has filled in zeros)
+    int s = 0;
+    uint32_t parity = 0;
+    for (int pass = 0; pass < passes; ++pass) {
+        float acc[kInFlight][NT][4];
 #pragma unroll
-        for (int rt = 0; rt < RT; ++rt)
+        for (int u = 0; u < kInFlight; ++u)
 #pragma unroll
-            for (int nt = 0; nt < NT; ++nt) acc[rt][nt][0] = acc[rt][nt][1] = acc[rt][nt][2] = acc[rt][nt][3] = 0.f;
+            for (int nt = 0; nt < NT; ++nt) acc[u][nt][0] = acc[u][nt][1] = acc[u][nt][2] = acc[u][nt][3] = 0.f;
         const int pr0 = pass * rows_cap, prows = min(rows_cap, rows - pr0);
-        const int row_tiles = (prows + 15) >> 4;
-        for (int kb = 0; kb < nk; ++kb, ++it) {
-            const int s = it % stages;
-            const uint32_t parity = (uint32_t)((it / stages) & 1);
-            if (!mbar_wait(&full_w[s], parity, abort_flag) || !mbar_wait(&full_x[s], parity, abort_flag)) {
-                ok = false;
-                break;
-            }
+        const bool active = my_tile * 16 < prows;
+        for (int kb = 0; kb < nk; ++kb) {
+            if (!mbar_wait(&full_w[s], parity, abort_flag) || !mbar_wait(&full_x[s], parity, abort_flag)) return;
             const uint32_t sw = smem_u32(ring + (size_t)s * stage_bytes);
             const uint32_t sx = sw + (uint32_t)w_bytes;
-            const int k_steps = kc >> 4;           // (beyond K the copy has filled in zeros)
-            for (int ks = warp; ks < k_steps; ks += kWarps) {
-                const int piece = ks >> 2, chunk = (ks & 3) * 2;
-                uint32_t b[NT][2];
+            if (active) {
+                for (int ks0 = my_part * kInFlight; ks0 < k_steps; ks0 += parts * kInFlight) {
+                    uint32_t a[kInFlight][4], b[kInFlight][NT][2];
 #pragma unroll
-                for (int nt = 0; nt < NT; ++nt)
-                    ldmatrix_x2(b[nt], sx + swz(piece * 8 * NT + nt * 8 + b_row, chunk + b_half));
+                    for (int u = 0; u < kInFlight; ++u) {
+                        const int ks = ks0 + u, piece = ks >> 2, chunk = (ks & 3) * 2;
 #pragma unroll
-                for (int rt = 0; rt < RT; ++rt) {
-                    if (rt < row_tiles) {
-                        uint32_t a[4];
-                        ldmatrix_x4(a, sw + swz(piece * prows + rt * 16 + a_row, chunk + a_half));
-#pragma unroll
-                        for (int nt = 0; nt < NT; ++nt) mma_bf16(acc[rt][nt], a, b[nt][0], b[nt][1]);
+                        for (int nt = 0; nt < NT; ++nt)
+                            ldmatrix_x2(b[u][nt], sx + swz(piece * 8 * NT + nt * 8 + b_row, chunk + b_half));
+                        ldmatrix_x4(a[u], sw + swz(piece * prows + my_tile * 16 + a_row, chunk + a_half));
                     }
+#pragma unroll
+                    for (int u = 0; u < kInFlight; ++u)
+#pragma unroll
+                        for (int nt = 0; nt < NT; ++nt) mma_bf16(acc[u][nt], a[u], b[u][nt][0], b[u][nt][1]);
                 }
             }
             __syncwarp();
             if (lane == 0) mbar_arrive(&empty[s]);
+            if (++s == stages) { s = 0; parity ^= 1u; }
         }
-        if (!ok) break;
-        // the eight warps' partial sums, tile by tile, through two alternating buffers
-#pragma unroll
-        for (int rt = 0; rt < RT; ++rt) {
-            if (rt < row_tiles) {
-                float* buf = red + (size_t)(rt & 1) * kWarps * 16 * width;
-                float* mine = buf + (size_t)warp * 16 * width;
-#pragma unroll
-                for (int nt = 0; nt < NT; ++nt) {
-                    const int r = lane >> 2, c = nt * 8 + 2 * (lane & 3);
-                    mine[r * width + c] = acc[rt][nt][0];
-                    mine[r * width + c + 1] = acc[rt][nt][1];
-                    mine[(r + 8) * width + c] = acc[rt][nt][2];
-                    mine[(r + 8) * width + c + 1] = acc[rt][nt][3];
-                }
-                consumer_sync();
-                const int tile_rows = min(16, prows - rt * 16);
-                // (results wait in shared memory and go to global memory once per pass: a barrier
-                // after stores to global memory costs a round trip to L2 each time)
-                if (prm.act) {
-                    for (int idx = tid; idx < prm.M * (tile_rows >> 1); idx += 32 * kWarps) {
-                        const int m = idx / (tile_rows >> 1), p = idx - m * (tile_rows >> 1);
-                        float g = 0.f, u = 0.f;
-#pragma unroll
-                        for (int wi = 0; wi < kWarps; ++wi) {
-                            g += buf[((size_t)wi * 16 + 2 * p) * width + m];
-                            u += buf[((size_t)wi * 16 + 2 * p + 1) * width + m];
-                        }
-                        held[m * rows_cap + rt * 8 + p] = gate_act(g, prm.act) * u;
-                    }
-                } else {
-                    for (int idx = tid; idx < prm.M * tile_rows; idx += 32 * kWarps) {
-                        const int m = idx / tile_rows, r = idx - m * tile_rows;
-                        float v = 0.f;
-#pragma unroll
-                        for (int wi = 0; wi < kWarps; ++wi) v += buf[((size_t)wi * 16 + r) * width + m];
-                        held[m * rows_cap + rt * 16 + r] = v;
-                    }
-                }
-            }
-        }
-        consumer_sync();        // all results of the pass are in `held`; both buffers are free again
+        // every warp's sum into shared memory (two buffers by turns: one meeting a pass), then each
+        // output is the sum of its tile's K parts, in their order
+        float* buf = red + (size_t)(pass & 1) * kWarps * 16 * width;
         {
-            const int n_local = prm.act ? prows >> 1 : prows;
-            const size_t first = prm.act ? (size_t)((r0 + pr0) >> 1) : (size_t)(r0 + pr0);
-            for (int idx = tid; idx < prm.M * n_local; idx += 32 * kWarps) {
-                const int m = idx / n_local, j = idx - m * n_local;
-                const size_t o = (size_t)m * n_out + first + j;
-                const float v = held[m * rows_cap + j];
-                if (prm.out_f32) reinterpret_cast<float*>(prm.out)[o] = v;
-                else reinterpret_cast<bf16*>(prm.out)[o] = __float2bfloat16_rn(v);
+            float* mine = buf + (size_t)(my_part * rt + my_tile) * 16 * width;
+            const int r = lane >> 2;
+#pragma unroll
+            for (int nt = 0; nt < NT; ++nt) {
+                const int c = nt * 8 + 2 * (lane & 3);
+                float v[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) v[e] = (acc[0][nt][e] + acc[1][nt][e]) + (acc[2][nt][e] + acc[3][nt][e]);
+                *reinterpret_cast<float2*>(&mine[r * width + c]) = make_float2(v[0], v[1]);
+                *reinterpret_cast<float2*>(&mine[(r + 8) * width + c]) = make_float2(v[2], v[3]);
             }
         }
-        consumer_sync();        // `held` is free for the next pass
+        consumer_sync();
+        const int n_local = prm.act ? prows >> 1 : prows;
+        const size_t first = prm.act ? (size_t)((r0 + pr0) >> 1) : (size_t)(r0 + pr0);
+        const int part_stride = rt * 16 * width;
+        for (int m = warp; m < prm.M; m += kWarps)
+        for (int j = lane; j < n_local; j += 32) {
+            float v;
+            if (prm.act) {
+                const float* src = buf + (size_t)(2 * j) * width + m;      // (rows of tile t lie at 16 t ...)
+                float g = 0.f, u = 0.f;
+                for (int p = 0; p < parts; ++p) {
+                    g += src[(size_t)p * part_stride];
+                    u += src[(size_t)p * part_stride + width];
+                }
+                v = gate_act(g, prm.act) * u;
+            } else {
+                const float* src = buf + (size_t)j * width + m;
+                v = 0.f;
+                for (int p = 0; p < parts; ++p) v += src[(size_t)p * part_stride];
+            }
+            const size_t o = (size_t)m * n_out + first + j;
+            if (prm.out_f32) reinterpret_cast<float*>(prm.out)[o] = v;
+            else reinterpret_cast<bf16*>(prm.out)[o] = __float2bfloat16_rn(v);
+        }
     }
 }
 
@@ -327,6 +337,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 struct Plan {
     int rt, nt, kc, stages, unit, blocks;
     int rows_a, rows_b, rows_c;     // rows of a full pass, of the last pass of the longer blocks, of the shorter
+    int rows_hi, rows_lo, n_hi;     // the first n_hi blocks have rows_hi rows, the others rows_lo
     int w_bytes;
     size_t smem;
 };
@@ -354,12 +365,15 @@ static int make_plan(int M, int N, int K, int act, int sms, Plan* p) {
     p->blocks = units < sms ? units : sms;
     const int hi = ((units + p->blocks - 1) / p->blocks) * p->unit, lo = (units / p->blocks) * p->unit;
     p->rt = hi <= 16 ? 1 : hi <= 32 ? 2 : hi <= 64 ? 4 : 8;
+    p->rows_hi = hi;
+    p->rows_lo = lo;
+    p->n_hi = hi == lo ? p->blocks : units - (lo / p->unit) * p->blocks;
     const int cap = 16 * p->rt;
     p->rows_a = hi < cap ? hi : cap;
     p->rows_b = hi - ((hi + cap - 1) / cap - 1) * cap;
     p->rows_c = lo - ((lo + cap - 1) / cap - 1) * cap;
     p->nt = M <= 8 ? 1 : 2;
-    const size_t red = (size_t)(2 * kWarps * 16 + 16 * p->rt) * 8 * p->nt * sizeof(float);   // sums + a pass's results
+    const size_t red = (size_t)(2 * kWarps * 16) * 8 * p->nt * sizeof(float);   // the warps' sums, two buffers
     const size_t room = (size_t)kSmemBudget - 1024 - 256 - red;
     p->kc = 0;
     const int cands[5] = {1024, 512, 256, 128, 64};
@@ -421,14 +435,14 @@ LSB_API int lsb_gemm_stream_supported(const void* x, const void* w, int M, int N
            get_encode() != nullptr;
 }
 
-template <int RT, int NT>
+template <int NT>
 static int launch(const CUtensorMap* maps, const StreamParams& prm, const Plan& p, cudaStream_t stream) {
     static int configured = -1;
     if (configured < 0)
-        configured = (int)cudaFuncSetAttribute(gemm_stream_kernel<RT, NT>,
+        configured = (int)cudaFuncSetAttribute(gemm_stream_kernel<NT>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
     if (configured) return configured;
-    return lsb_launch(gemm_stream_kernel<RT, NT>, dim3(p.blocks), dim3(kThreads), p.smem, stream, 1, maps[0],
+    return lsb_launch(gemm_stream_kernel<NT>, dim3(p.blocks), dim3(kThreads), p.smem, stream, 1, maps[0],
                       maps[1], maps[2], maps[3], prm);
 }
 
@@ -443,21 +457,14 @@ LSB_API int lsb_gemm_stream(const void* x, const void* w, void* out, int out_f32
     prm.M = M; prm.N = N; prm.K = K;
     prm.out_f32 = out_f32; prm.act = act;
     prm.kc = p.kc; prm.stages = p.stages; prm.unit = p.unit; prm.w_bytes = p.w_bytes;
-    prm.rows_a = p.rows_a; prm.rows_b = p.rows_b; prm.rows_c = p.rows_c;
+    prm.rows_a = p.rows_a; prm.rows_b = p.rows_b; prm.rows_c = p.rows_c; prm.rt = p.rt;
+    prm.rt_log2 = p.rt == 1 ? 0 : p.rt == 2 ? 1 : p.rt == 4 ? 2 : 3;
+    prm.rows_hi = p.rows_hi; prm.rows_lo = p.rows_lo; prm.n_hi = p.n_hi; prm.nk = (K + p.kc - 1) / p.kc;
     CUtensorMap maps[4];
     int rc;
     if ((rc = make_map(&maps[0], w, N, K, p.rows_a, p.kc / 64))) return rc;
     if ((rc = make_map(&maps[1], w, N, K, p.rows_b, p.kc / 64))) return rc;
     if ((rc = make_map(&maps[2], w, N, K, p.rows_c, p.kc / 64))) return rc;
     if ((rc = make_map(&maps[3], x, M, K, 8 * p.nt, p.kc / 64))) return rc;
-#define LSB_STREAM_CASE(RT_)                                                                       \
-    case RT_: return p.nt == 1 ? launch<RT_, 1>(maps, prm, p, stream) : launch<RT_, 2>(maps, prm, p, stream)
-    switch (p.rt) {
-        LSB_STREAM_CASE(1);
-        LSB_STREAM_CASE(2);
-        LSB_STREAM_CASE(4);
-        LSB_STREAM_CASE(8);
-    }
-#undef LSB_STREAM_CASE
-    return (int)cudaErrorInvalidValue;
+    return p.nt == 1 ? launch<1>(maps, prm, p, stream) : launch<2>(maps, prm, p, stream);
 }
