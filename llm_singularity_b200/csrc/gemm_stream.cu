@@ -47,6 +47,10 @@ constexpr int kThreads = 32 * (kWarps + 1);
 constexpr int kMaxStages = 8;
 constexpr int kSmemBudget = 200 * 1024;         // one block per SM; most of it is the ring
 constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr int kSsPerLane = 5;                  // parts of a row's sum of squares a lane adds up: 160 parts at most
+constexpr int kTailBytes = 320;                // barriers, the give-up flag, the rows' scales
+static_assert(3 * kMaxStages * 8 + 16 + 16 * 4 <= kTailBytes, "barriers, flag and scales fit the tail");
+constexpr int kFoldBytes = (16 * 128 + kWarps * 128 + 16) * 4;   // more shared memory if the product adds to the residual
 enum : int { LSB_ACT_SILU = 1, LSB_ACT_GELU_TANH = 2, LSB_ACT_NONE = 3 };
 
 struct StreamParams {
@@ -64,6 +68,13 @@ struct StreamParams {
     int rt, rt_log2;    // 16-row tiles of a pass (1, 2, 4 or 8)
     int rows_hi, rows_lo, n_hi;   // the first n_hi blocks have rows_hi rows, the others rows_lo
     int nk;             // chunks of K
+    // A norm folded into the products on either side of it (see lsb_gemm_stream_folded):
+    const float* ss_in;     // [ss_parts][16]: sums of squares of the rows x stands for, in parts; or null
+    int ss_parts;
+    float inv_size, eps;    // the rows' scale is rsqrt(sum * inv_size + eps)
+    float* residual;        // [M, N] 32-bit, += the product in place; or null
+    const float* norm_w;    // [N]: out = (residual + product) * norm_w
+    float* ss_out;          // [blocks][16]: this block's part of the new rows' sums of squares
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) {
@@ -123,6 +134,10 @@ __device__ __forceinline__ void mma_bf16(float (&d)[4], const uint32_t (&a)[4], 
                  : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
                  : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
 }
+__device__ __forceinline__ void cp_async_4(void* dst, const void* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(smem_u32(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.wait_all;" ::: "memory"); }
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(32 * kWarps) : "memory"); }
 
 __device__ __forceinline__ float gate_act(float g, int act) {
@@ -158,6 +173,12 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     uint64_t* full_x = full_w + kMaxStages;
     uint64_t* empty = full_x + kMaxStages;
     volatile int* abort_flag = reinterpret_cast<volatile int*>(empty + kMaxStages);
+    float* scale_s = reinterpret_cast<float*>(empty + kMaxStages) + 4;      // [16]: the rows' scales
+    // (only there if the product adds to the residual: the block's piece of the residual [16][128],
+    // the norm's weights once per warp [kWarps][128], sums of squares [16])
+    float* res_s = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(full_w) + kTailBytes);
+    float* nw_s = res_s + 16 * 128;
+    float* ss_s = nw_s + kWarps * 128;
 
     // this block's rows
     // (worked out without a division: a kernel that lives ten microseconds cannot spend half of one
@@ -255,6 +276,19 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     const int my_tile = warp & (rt - 1), my_part = warp / rt, parts = kWarps / rt;
     const int n_out = prm.act ? prm.N / 2 : prm.N;
     const int k_steps = kc >> 4;               // a multiple of kInFlight (beyond K the copy has filled in zeros)
+    // The scale of the rows, if x stands for rows whose norm is still owed: the parts of their sums
+    // of squares are asked for now and added up, in a fixed order, when the first pass ends.
+    float ssq[2][kSsPerLane];
+    if (prm.ss_in) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i)
+#pragma unroll
+            for (int q = 0; q < kSsPerLane; ++q) {
+                const int m = warp + kWarps * i, part = lane + 32 * q;
+                ssq[i][q] = (m < prm.M && part < prm.ss_parts) ? prm.ss_in[part * 16 + m] : 0.f;
+            }
+    }
+    if (prm.residual && lane == 0) ss_s[warp] = ss_s[warp + kWarps] = 0.f;
     int s = 0;
     uint32_t parity = 0;
     for (int pass = 0; pass < passes; ++pass) {
@@ -266,6 +300,15 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         const int pr0 = pass * rows_cap, prows = min(rows_cap, rows - pr0);
         const bool active = my_tile * 16 < prows;
         for (int kb = 0; kb < nk; ++kb) {
+            if (prm.residual && kb == nk - 1) {
+                // what the outputs of this pass are added to, on its way while the last chunk is
+                // (each thread fetches what it will use itself)
+                const size_t first = (size_t)(r0 + pr0);
+                for (int m = warp; m < prm.M; m += kWarps)
+                    for (int j = lane; j < prows; j += 32)
+                        cp_async_4(&res_s[m * 128 + j], prm.residual + (size_t)m * prm.N + first + j);
+                for (int j = lane; j < prows; j += 32) cp_async_4(&nw_s[warp * 128 + j], prm.norm_w + first + j);
+            }
             if (!mbar_wait(&full_w[s], parity, abort_flag) || !mbar_wait(&full_x[s], parity, abort_flag)) return;
             const uint32_t sw = smem_u32(ring + (size_t)s * stage_bytes);
             const uint32_t sx = sw + (uint32_t)w_bytes;
@@ -306,11 +349,23 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 *reinterpret_cast<float2*>(&mine[(r + 8) * width + c]) = make_float2(v[2], v[3]);
             }
         }
+        if (prm.ss_in && pass == 0) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                float t = ((ssq[i][0] + ssq[i][1]) + (ssq[i][2] + ssq[i][3])) + ssq[i][4];
+#pragma unroll
+                for (int off = 16; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
+                if (lane == 0) scale_s[warp + kWarps * i] = rsqrtf(t * prm.inv_size + prm.eps);
+            }
+        }
+        if (prm.residual) cp_async_wait_all();
         consumer_sync();
         const int n_local = prm.act ? prows >> 1 : prows;
         const size_t first = prm.act ? (size_t)((r0 + pr0) >> 1) : (size_t)(r0 + pr0);
         const int part_stride = rt * 16 * width;
-        for (int m = warp; m < prm.M; m += kWarps)
+        for (int m = warp; m < prm.M; m += kWarps) {
+        const float scale = prm.ss_in ? scale_s[m] : 1.f;
+        float ss_row = 0.f;
         for (int j = lane; j < n_local; j += 32) {
             float v;
             if (prm.act) {
@@ -320,17 +375,32 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                     g += src[(size_t)p * part_stride];
                     u += src[(size_t)p * part_stride + width];
                 }
-                v = gate_act(g, prm.act) * u;
+                v = gate_act(g * scale, prm.act) * (u * scale);
             } else {
                 const float* src = buf + (size_t)j * width + m;
                 v = 0.f;
                 for (int p = 0; p < parts; ++p) v += src[(size_t)p * part_stride];
+                v *= scale;
             }
             const size_t o = (size_t)m * n_out + first + j;
+            if (prm.residual) {
+                const float h = res_s[m * 128 + j] + v;
+                prm.residual[o] = h;
+                ss_row += h * h;
+                v = h * nw_s[warp * 128 + j];
+            }
             if (prm.out_f32) reinterpret_cast<float*>(prm.out)[o] = v;
             else reinterpret_cast<bf16*>(prm.out)[o] = __float2bfloat16_rn(v);
         }
+        if (prm.residual) {
+#pragma unroll
+            for (int off = 16; off > 0; off >>= 1) ss_row += __shfl_xor_sync(0xffffffffu, ss_row, off);
+            if (lane == 0) ss_s[m] += ss_row;
+        }
+        }
     }
+    if (prm.residual && lane == 0)
+        for (int m = warp; m < prm.M; m += kWarps) prm.ss_out[(size_t)blockIdx.x * 16 + m] = ss_s[m];
 }
 
 // ------------------------------------------------------------------------------- host
@@ -357,7 +427,7 @@ static int sm_count() {
 // The shape of the launch, or 0 if the kernel does not take the product: bfloat16, M <= 16, K a
 // multiple of 64 (the width of a copied piece), an even number of rows for a gated product, and at
 // least two stages within the shared-memory budget.
-static int make_plan(int M, int N, int K, int act, int sms, Plan* p) {
+static int make_plan(int M, int N, int K, int act, int fold, int sms, Plan* p) {
     if (M <= 0 || M > 16 || N <= 0 || K <= 0 || K % 64) return 0;
     if (act < 0 || act > LSB_ACT_NONE || (act && (N % 2))) return 0;
     p->unit = act ? 2 : 1;
@@ -374,7 +444,8 @@ static int make_plan(int M, int N, int K, int act, int sms, Plan* p) {
     p->rows_c = lo - ((lo + cap - 1) / cap - 1) * cap;
     p->nt = M <= 8 ? 1 : 2;
     const size_t red = (size_t)(2 * kWarps * 16) * 8 * p->nt * sizeof(float);   // the warps' sums, two buffers
-    const size_t room = (size_t)kSmemBudget - 1024 - 256 - red;
+    const size_t tail = kTailBytes + (fold ? kFoldBytes : 0);
+    const size_t room = (size_t)kSmemBudget - 1024 - tail - red;
     p->kc = 0;
     const int cands[5] = {1024, 512, 256, 128, 64};
     for (int c = 0; c < 5; ++c) {
@@ -388,7 +459,7 @@ static int make_plan(int M, int N, int K, int act, int sms, Plan* p) {
             p->w_bytes = (int)w_bytes;
             p->stages = (int)(room / stage);
             if (p->stages > kMaxStages) p->stages = kMaxStages;
-            p->smem = 1024 + (size_t)p->stages * stage + red + 256;
+            p->smem = 1024 + (size_t)p->stages * stage + red + tail;
             break;
         }
     }
@@ -431,8 +502,14 @@ static int make_map(CUtensorMap* map, const void* ptr, int rows, int K, int box_
 
 LSB_API int lsb_gemm_stream_supported(const void* x, const void* w, int M, int N, int K, int act) {
     Plan p;
-    return ((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0 && make_plan(M, N, K, act, sm_count(), &p) &&
+    return ((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0 && make_plan(M, N, K, act, 1, sm_count(), &p) &&
            get_encode() != nullptr;
+}
+
+// The number of blocks a product of these sizes runs with: the parts its sums of squares come in.
+LSB_API int lsb_gemm_stream_blocks(int M, int N, int K, int act) {
+    Plan p;
+    return make_plan(M, N, K, act, 1, sm_count(), &p) ? p.blocks : 0;
 }
 
 template <int NT>
@@ -446,20 +523,37 @@ static int launch(const CUtensorMap* maps, const StreamParams& prm, const Plan& 
                       maps[1], maps[2], maps[3], prm);
 }
 
-// x [M, K] and w [N, K] bfloat16; out [M, N] (or [M, N / 2] with act != 0) bfloat16 or (out_f32) float.
-LSB_API int lsb_gemm_stream(const void* x, const void* w, void* out, int out_f32, int M, int N, int K,
-                            int act, cudaStream_t stream) {
+// The product with an RMS norm folded into it on either side, so that the norm needs no kernel of
+// its own between two products of a decode step.
+//
+// ss_in != null: x holds rows r * g (a residual row times the norm's weight, rounded to bfloat16)
+// whose normalisation is still owed; ss_in[part * 16 + m] are `ss_parts` (<= 160) parts of
+// sum(r[m]^2), and every output row is scaled by rsqrt(sum / size + eps) before the activation,
+// which is the same as normalising x first: the scale is one number per row.
+//
+// residual != null (act == 0): the product is added to residual [M, N] (32-bit, in place), out
+// is (residual * norm_w) in bfloat16, the input of the next product in the sense above, and
+// ss_out[block * 16 + m] gets this block's part of sum(residual[m]^2) over its own columns;
+// lsb_gemm_stream_blocks gives the number of parts.  All sums are taken in a fixed order.
+LSB_API int lsb_gemm_stream_folded(const void* x, const void* w, void* out, int out_f32, int M, int N, int K,
+                                   int act, const float* ss_in, int ss_parts, int size, float eps,
+                                   float* residual, const float* norm_w, float* ss_out, cudaStream_t stream) {
     Plan p;
     if (!lsb_gemm_stream_supported(x, w, M, N, K, act)) return (int)cudaErrorInvalidValue;
-    make_plan(M, N, K, act, sm_count(), &p);
+    if (ss_in && (ss_parts <= 0 || ss_parts > 32 * kSsPerLane || size <= 0)) return (int)cudaErrorInvalidValue;
+    if (residual && (act || out_f32 || !norm_w || !ss_out)) return (int)cudaErrorInvalidValue;
+    make_plan(M, N, K, act, residual != nullptr, sm_count(), &p);
     StreamParams prm;
     prm.x = (const bf16*)x; prm.w = (const bf16*)w; prm.out = out;
     prm.M = M; prm.N = N; prm.K = K;
     prm.out_f32 = out_f32; prm.act = act;
     prm.kc = p.kc; prm.stages = p.stages; prm.unit = p.unit; prm.w_bytes = p.w_bytes;
-    prm.rows_a = p.rows_a; prm.rows_b = p.rows_b; prm.rows_c = p.rows_c; prm.rt = p.rt;
+    prm.rows_a = p.rows_a; prm.rows_b = p.rows_b; prm.rows_c = p.rows_c;
+    prm.rt = p.rt;
     prm.rt_log2 = p.rt == 1 ? 0 : p.rt == 2 ? 1 : p.rt == 4 ? 2 : 3;
     prm.rows_hi = p.rows_hi; prm.rows_lo = p.rows_lo; prm.n_hi = p.n_hi; prm.nk = (K + p.kc - 1) / p.kc;
+    prm.ss_in = ss_in; prm.ss_parts = ss_parts; prm.inv_size = ss_in ? 1.f / (float)size : 0.f; prm.eps = eps;
+    prm.residual = residual; prm.norm_w = norm_w; prm.ss_out = ss_out;
     CUtensorMap maps[4];
     int rc;
     if ((rc = make_map(&maps[0], w, N, K, p.rows_a, p.kc / 64))) return rc;
@@ -467,4 +561,11 @@ LSB_API int lsb_gemm_stream(const void* x, const void* w, void* out, int out_f32
     if ((rc = make_map(&maps[2], w, N, K, p.rows_c, p.kc / 64))) return rc;
     if ((rc = make_map(&maps[3], x, M, K, 8 * p.nt, p.kc / 64))) return rc;
     return p.nt == 1 ? launch<1>(maps, prm, p, stream) : launch<2>(maps, prm, p, stream);
+}
+
+// x [M, K] and w [N, K] bfloat16; out [M, N] (or [M, N / 2] with act != 0) bfloat16 or (out_f32) float.
+LSB_API int lsb_gemm_stream(const void* x, const void* w, void* out, int out_f32, int M, int N, int K,
+                            int act, cudaStream_t stream) {
+    return lsb_gemm_stream_folded(x, w, out, out_f32, M, N, K, act, nullptr, 0, 0, 0.f, nullptr, nullptr,
+                                  nullptr, stream);
 }

@@ -226,3 +226,32 @@ LSB_API int lsb_gather_add_rmsnorm(const float* residual, const void* delta, con
         (float*)residual, (const T*)delta, rows, weight, (T*)out, hidden, n_rows_total, eps));
     return 0;
 }
+
+// The second half of a norm that a product folded in (gemm_stream.cu): values[m, :] holds a
+// residual row times the norm's weight, parts[p * 16 + m] the parts of the row's sum of squares;
+// out[m, :] = values[m, :] * rsqrt(sum / hidden + eps).  For a consumer that cannot scale its own
+// rows; one block per row, parts added in index order within a lane, then across lanes.
+template <typename T>
+__global__ void __launch_bounds__(kNormThreads)
+finish_norm_kernel(const T* __restrict__ values, const float* __restrict__ parts, int n_parts,
+                   T* __restrict__ out, int hidden, float eps) {
+    __shared__ float scratch[33];
+    lsb_pdl_launch_dependents();
+    lsb_pdl_wait();
+    const int m = blockIdx.x;
+    float t = 0.f;
+    for (int p = threadIdx.x; p < n_parts; p += kNormThreads) t += parts[p * 16 + m];
+    t = lsb_block_sum(t, scratch);
+    const float inv = rsqrtf(t / (float)hidden + eps);
+    for (int i = threadIdx.x; i < hidden; i += kNormThreads)
+        out[(size_t)m * hidden + i] = lsb_from_float<T>(lsb_to_float(values[(size_t)m * hidden + i]) * inv);
+}
+
+LSB_API int lsb_finish_norm(const void* values, const float* parts, int n_parts, void* out, int dtype,
+                            int rows, int hidden, float eps, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (rows > 16 || n_parts <= 0) return (int)cudaErrorInvalidValue;
+    LSB_DISPATCH_DTYPE(dtype, return lsb_launch(finish_norm_kernel<T>, dim3(rows), dim3(kNormThreads), 0, stream, 1,
+                                                (const T*)values, parts, n_parts, (T*)out, hidden, eps));
+    return 0;
+}

@@ -290,9 +290,52 @@ def _activation_id(name: str) -> int:
                           f"(known: {', '.join(sorted(ACTIVATIONS))})") from None
 
 
-def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
-           gated: bool = False, activation: str = "silu") -> torch.Tensor:
+class NormOut:
+    """Rows as they leave an RMS norm that a product folded in.  ``values`` [M, H] is the residual
+    row times the norm's weight, rounded to the compute dtype; ``parts`` [P, 16] holds each row's
+    sum of squares in P parts (row m in column m), and the factor ``rsqrt(sum / H + eps)`` per row
+    is still owed: the next product scales its output rows by it (``linear`` takes a NormOut for
+    ``x``), which is the same as normalising first.  ``parts`` None: nothing is owed, ``values``
+    are the normalised rows (where no kernel could fold the norm).  ``finish_norm`` gives the
+    normalised rows in either case."""
+    __slots__ = ("values", "parts", "eps")
+
+    def __init__(self, values: torch.Tensor, parts: Optional[torch.Tensor] = None, eps: float = 0.0):
+        self.values, self.parts, self.eps = values, parts, float(eps)
+
+    shape = property(lambda self: self.values.shape)
+    dtype = property(lambda self: self.values.dtype)
+    device = property(lambda self: self.values.device)
+
+
+FOLD_NORMS = True               # decode steps fold each norm into the products on either side of it
+
+
+def folds_norm(rows: int, dtype: torch.dtype) -> bool:
+    """Does a step of this many rows fold its norms into the neighbouring products?  (The products
+    of at most 16 bfloat16 rows, which one kernel streams: there a norm's own kernel costs more
+    than the bytes it moves.)"""
+    return FOLD_NORMS and STREAM_PRODUCTS and dtype == torch.bfloat16 and 0 < rows <= 16
+
+
+def finish_norm(x: NormOut) -> torch.Tensor:
+    """The normalised rows a NormOut stands for."""
+    if x.parts is None:
+        return x.values
+    M, H = x.values.shape
+    out = torch.empty_like(x.values)
+    _call("norm", "lsb_finish_norm", _p(x.values), _p(x.parts), _i(x.parts.shape[0]), _p(out), _i(_dt(out)),
+          _i(M), _i(H), _f(x.eps), _stream(out))
+    return out
+
+
+def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+           gated: bool = False, activation: str = "silu", into=None):
     """x [M, K] times w [N, K] transposed -> [M, N]; 32-bit accumulation.
+
+    ``x`` may be a ``NormOut`` (the norm before this product, possibly half done: see there).
+    ``into = (residual, norm_weight, eps)``: the product is added to ``residual`` ([M, N] 32-bit, in
+    place) and what comes back is a ``NormOut``: what follows the RMS norm with that weight.
 
     float32 operands run on the CUDA cores in true 32-bit.  bfloat16 operands run on the
     tensor cores (tcgen05, accumulators in TMEM) when K is a multiple of 8, else on the CUDA
@@ -304,6 +347,9 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     "gelu_tanh" or "none".
     """
     act = _activation_id(activation) if gated else 0
+    owed = None
+    if isinstance(x, NormOut):
+        owed, x = (x if x.parts is not None else None), x.values
     _req(x, "x", dim=2)
     _req(w, "w", x.dtype, 2)
     M, K = x.shape
@@ -315,6 +361,36 @@ def linear(x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = 
     out_dtype = out_dtype or x.dtype
     if out_dtype not in (x.dtype, torch.float32):
         raise KernelError(f"linear: output must be {x.dtype} or float32")
+    if into is not None:
+        residual, norm_w, eps = into
+        if gated or out_dtype != x.dtype:
+            raise KernelError("linear: a product into the residual is plain and in the compute dtype")
+        _req(residual, "residual", torch.float32, 2)
+        _req(norm_w, "norm weight", torch.float32, 1)
+        if residual.shape != (M, N) or norm_w.shape[0] != N:
+            raise KernelError("linear: residual and norm weight do not fit the product")
+    if (owed is not None or into is not None) and x.dtype == torch.bfloat16 and STREAM_PRODUCTS \
+            and M <= 16 and stream_gemm_ok(x, w, act):
+        lib = _lib("gemm_stream")
+        out = torch.empty((M, N // 2 if gated else N), dtype=out_dtype, device=x.device)
+        parts = None
+        if into is not None:
+            parts = torch.empty((lib.lsb_gemm_stream_blocks(_i(M), _i(N), _i(K), _i(act)), 16),
+                                dtype=torch.float32, device=x.device)
+        _call("gemm_stream", "lsb_gemm_stream_folded", _p(x), _p(w), _p(out),
+              _i(1 if out_dtype == torch.float32 else 0), _i(M), _i(N), _i(K), _i(act),
+              _p(owed.parts if owed is not None else None), _i(owed.parts.shape[0] if owed is not None else 0),
+              _i(K), _f(owed.eps if owed is not None else 0.0),
+              _p(into[0] if into is not None else None), _p(into[1] if into is not None else None), _p(parts),
+              _stream(out))
+        return NormOut(out, parts, into[2]) if into is not None else out
+    if owed is not None:
+        x = finish_norm(owed)
+    if into is not None:
+        delta = linear(x, w, out_dtype)
+        out = torch.empty_like(delta)
+        add_rmsnorm(into[0], delta, into[1], into[2], out)
+        return NormOut(out)
     if x.dtype == torch.bfloat16 and SMALL_PRODUCTS and not gated and M <= 16 and small_gemm_ok(x, w):
         # a few rows times a matrix that fits the chip's shared memory (decode: q/k/v, output
         # projection): weights resident before the previous kernel has ended, no cluster

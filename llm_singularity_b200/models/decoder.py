@@ -146,10 +146,16 @@ class DecoderModel:
         time its kind comes up in a step (from the second layer on: the first has no delta coming
         in), and the calls of the same kind after it repeat those launches with their own weights
         and cache pages; the delta between layers alternates between the recorded call's input
-        and output buffers."""
+        and output buffers.
+
+        In a step of a few rows (``ops.folds_norm``) a block that can is told which norm its output
+        meets first, the next block's, and may fold it into its last product; such steps are not
+        recorded."""
         ops = self.rt.ops
-        replay = getattr(ops, "LAYER_REPLAY", False) and hasattr(ops, "LayerRecording")
         residual = self.embedding.forward(ctx.token_ids)
+        fold = getattr(ops, "folds_norm", None)
+        fold = fold is not None and fold(residual.shape[0], self.rt.dtype)
+        replay = getattr(ops, "LAYER_REPLAY", False) and hasattr(ops, "LayerRecording") and not fold
         pending = None
         rec = rec_key = None
         order = self.spec.order
@@ -180,7 +186,14 @@ class DecoderModel:
                     rec_key, rec_bufs = key, (pending, out)
                 pending = out
                 continue
-            pending = block.forward(residual, pending, ctx, view, call.writes_cache)
+            next_norm = None
+            if fold and block.folds_next and i + 1 < len(order):
+                first = getattr(self.blocks[order[i + 1].block], "first_norm", None)
+                next_norm = first() if first is not None else None
+            if next_norm is not None:
+                pending = block.forward(residual, pending, ctx, view, call.writes_cache, next_norm=next_norm)
+            else:
+                pending = block.forward(residual, pending, ctx, view, call.writes_cache)
         if ctx.n_wanted == 0:
             return torch.empty(0, self.spec.head.vocab_size, dtype=torch.float32,
                                device=self.rt.device)

@@ -22,6 +22,8 @@ from .base import POSITIONS, PagedKVSpec, ParamSpec, Part, register_mixer
 class PagedAttention(Part):
     graph_safe = True
     replayable = True
+    folds_norm = True
+    takes_unnormed = True
     kernels = ("gemm", "rope_cache", "attention")
 
     def __init__(self, spec, rt):
@@ -58,7 +60,7 @@ class PagedAttention(Part):
     def cache_spec(self):
         return PagedKVSpec(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window)
 
-    def forward(self, x: torch.Tensor, ctx, cache, writes_cache: bool = True) -> torch.Tensor:
+    def forward(self, x, ctx, cache, writes_cache: bool = True, into=None):
         s, ops = self.spec, self.rt.ops
         qkv = ops.linear(x, self.wqkv)
         table = self.position.rotary_table()
@@ -73,4 +75,6 @@ class PagedAttention(Part):
             inv_freq, rotary_dim = table
             ops.rope_store_attention(qkv, s.num_heads, s.num_kv_heads, s.head_dim, ctx, cache,
                                      inv_freq, rotary_dim, writes_cache, s.scale, s.window or 0, out)
+        if into is not None:
+            return ops.linear(out, self.wo, into=into)
         return ops.linear(out, self.wo)

@@ -190,6 +190,19 @@ class Part:
     # of the same spec and the same step, so that a layer's launches can be recorded once and
     # repeated for the layers after it (``kernels.LayerRecording``).
     replayable = False
+    # Folding a norm into the products on either side of it (a step of a few rows, where a norm's
+    # own kernel costs more than the bytes it moves; ``ops.folds_norm`` says when).  A mixer or
+    # feed-forward with ``folds_norm`` takes ``into=(residual, weight, eps)`` in ``forward``: its last
+    # product adds its result to the residual stream and hands back what follows the norm with
+    # that weight, an ``ops.NormOut``, as ``ops.linear`` does with the same argument.  One with
+    # ``takes_unnormed`` accepts an ``ops.NormOut`` for ``x`` and passes it to its first product
+    # (any other gets the finished rows).  A norm with ``foldable`` has ``fold() -> (weight, eps)``.
+    # A block with ``folds_next`` takes ``next_norm`` in ``forward`` (the norm its output will meet
+    # first) and tells through ``first_norm()`` which norm of its own the block before may fold.
+    folds_norm = False
+    takes_unnormed = False
+    foldable = False
+    folds_next = False
 
     def __init__(self, spec, rt: Runtime):
         self.spec = spec

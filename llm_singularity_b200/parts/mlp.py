@@ -21,6 +21,8 @@ from .base import ParamSpec, Part, register_feed_forward
 class GatedMLP(Part):
     graph_safe = True
     replayable = True
+    folds_norm = True
+    takes_unnormed = True
     kernels = ("gemm", "activation")
 
     def __init__(self, spec, rt):
@@ -42,7 +44,9 @@ class GatedMLP(Part):
             2 * self.spec.intermediate_size, self.spec.hidden_size).contiguous()
         self.w_down = tensors["down_proj"].contiguous()
 
-    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+    def forward(self, x, ctx, into=None):
         ops = self.rt.ops
         act = ops.linear(x, self.w_gate_up, gated=True, activation=self.spec.activation)   # [T, I]
+        if into is not None:
+            return ops.linear(act, self.w_down, into=into)
         return ops.linear(act, self.w_down)

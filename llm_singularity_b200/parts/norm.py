@@ -19,6 +19,7 @@ from .base import ParamSpec, Part, register_norm
 class RMSNorm(Part):
     graph_safe = True
     replayable = True
+    foldable = True
     kernels = ("norm",)
 
     @classmethod
@@ -27,6 +28,10 @@ class RMSNorm(Part):
 
     def load(self, tensors):
         self.weight = tensors["weight"]
+
+    def fold(self):
+        """What a product needs to take this norm upon itself: the weight and eps."""
+        return self.weight, self.spec.eps
 
     def add_norm(self, residual: torch.Tensor, delta: Optional[torch.Tensor]) -> torch.Tensor:
         out = self.rt.empty(*residual.shape)

@@ -292,6 +292,65 @@ def test_streamed_products(ops, M, N, K, act, out_dtype):
     assert not ops.stream_gemm_ok(x[:, :K - 8].contiguous(), w[:, :K - 8].contiguous())
 
 
+@pytest.mark.parametrize("M, K, H, N, act", [
+    (8, 8192, 2048, 16384, "silu"), (8, 2048, 2048, 3072, None), (1, 2048, 2048, 3072, None),
+    (16, 8192, 2048, 16384, "silu"), (13, 320, 192, 1000, None), (3, 128, 64, 28, "gelu_tanh"),
+    (5, 192, 2112, 302, "none"), (9, 64, 40000 // 64 * 64, 66, None)])
+def test_products_with_a_norm_folded_in(ops, M, K, H, N, act):
+    """A product that adds its result to the residual stream and leaves the next norm half done
+    (residual times weight, the rows' sums of squares in parts), and the product after it, which
+    pays the rest by scaling its output rows: against residual add, RMS norm and product in 64-bit;
+    the half-done norm finished by its own kernel; and the fallback where no kernel folds."""
+    eps = 3e-5
+    x = _rand(M, K, dtype=torch.bfloat16, seed=11, scale=0.5)
+    w1 = _rand(H, K, dtype=torch.bfloat16, seed=12, scale=0.2)
+    w2 = _rand(N, H, dtype=torch.bfloat16, seed=13, scale=0.2)
+    g = (1 + 0.3 * _rand(H, seed=14)).contiguous()
+    r0 = _rand(M, H, seed=15, scale=2.0)
+    r0[0, 5] = 300.0                                  # one element that dominates its row's sum
+    gated = act is not None
+    residual = r0.clone()
+    h = ops.linear(x, w1, into=(residual, g, eps))
+    assert isinstance(h, ops.NormOut) and h.parts is not None and h.values.shape == (M, H)
+    want_r = r0.double() + x.double() @ w1.double().T
+    rs = want_r.abs().max().item()
+    assert (residual.double() - want_r).abs().max() <= 3e-7 * K * 8 * (rs + 1)
+    assert (h.values.double() - residual.double() * g.double()).abs().max() <= 4e-3 * (rs * 1.3 + 1)
+    ss = h.parts.double().sum(0)[:M]
+    assert ((ss - (residual.double() ** 2).sum(1)).abs() <= 1e-5 * ss).all()
+    normed = want_r * torch.rsqrt((want_r ** 2).mean(1, keepdim=True) + eps) * g.double()
+    fin = ops.finish_norm(h)
+    assert (fin.double() - normed).abs().max() <= 1.2e-2 * (normed.abs().max().item() + 1)
+    y = ops.linear(h, w2, gated=gated, activation=act or "silu", out_dtype=torch.float32)
+    d = normed @ w2.double().T
+    if gated:
+        gg, u = d[:, 0::2], d[:, 1::2]
+        a = {"silu": gg / (1 + torch.exp(-gg)), "none": gg,
+             "gelu_tanh": 0.5 * gg * (1 + torch.tanh(math.sqrt(2 / math.pi) * (gg + 0.044715 * gg ** 3)))}[act]
+        want = a * u
+    else:
+        want = d
+    # (the inputs of the second product are rounded to bfloat16: 2^-9 relative each, summed at random)
+    tol = 2.0 ** -8 * (normed.abs().double() @ w2.abs().double().T).max().item() / math.sqrt(H) * 4
+    if gated:
+        tol *= d.abs().max().item() + 1
+    assert y.shape == want.shape and (y.double() - want).abs().max() <= tol + 1e-6
+    again = ops.linear(h, w2, gated=gated, activation=act or "silu", out_dtype=torch.float32)
+    assert torch.equal(again, y)
+    # where no kernel folds (the streaming products off): the same meaning through separate kernels
+    ops.STREAM_PRODUCTS = False
+    try:
+        residual2 = r0.clone()
+        h2 = ops.linear(x, w1, into=(residual2, g, eps))
+        assert isinstance(h2, ops.NormOut) and h2.parts is None
+        y2 = ops.linear(h2, w2, gated=gated, activation=act or "silu", out_dtype=torch.float32)
+    finally:
+        ops.STREAM_PRODUCTS = True
+    assert (residual2.double() - want_r).abs().max() <= 3e-7 * K * 8 * (rs + 1) + 1e-2 * (x.double() @ w1.double().T).abs().max().item()
+    assert (h2.values.double() - normed).abs().max() <= 1.2e-2 * (normed.abs().max().item() + 1)
+    assert (y2.double() - want).abs().max() <= 2 * tol + 1e-6
+
+
 def test_linear_float32_is_true_32_bit(ops):
     # (1 + 2^-20) * 1 + 1 * (-1) = 2^-20 exactly in 32-bit; a reduced-precision matrix mode
     # (10-bit mantissa operands) rounds the first factor to 1 and returns 0

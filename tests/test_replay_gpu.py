@@ -84,24 +84,43 @@ def test_replay_matches_plain(model_dirs, refs, tmp_path, name, dtype, cut):
     assert runner.cache.free_pages() == max_tokens // tiny_models.PAGE_SIZE[name]
 
 
-@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_cuttings_agree_with_each_other(model_dirs, refs, tmp_path, dtype):
+@pytest.mark.parametrize("dtype, fold", [("float32", False), ("bfloat16", False), ("bfloat16", True)])
+def test_cuttings_agree_with_each_other(model_dirs, refs, tmp_path, dtype, fold):
     """The logits at a position do not depend on how the tokens were cut, on what else is in the
-    batch or on which pages were used, beyond rounding: all four cuttings against the first."""
+    batch or on which pages were used, beyond rounding: all four cuttings against the first.
+
+    With the same arithmetic for every step size (32-bit; bfloat16 with each norm in a kernel of
+    its own) the cuttings round at the same places and must agree far closer than they agree with
+    the exact logits.  Steps of a few bfloat16 rows fold their norms into the neighbouring products
+    (``fold``): other places of rounding, so there the bound is rounding itself, measured: no
+    position further from the whole prompt's logits than the tolerance against the exact ones,
+    and on average closer to them than those are to the exact ones."""
+    from llm_singularity_b200 import kernels
     name = "tiny_b"
     seqs, ref = _pick(refs, name, dtype)
+    exact = refs[name][1]
     got = {}
-    for cut in ("whole", "tail_decode", "portions", "mixed"):
-        steps, max_tokens = getattr(cuttings, cut)(seqs)
-        d = tmp_path / cut
-        replay_util.replay_in_process(_runner(model_dirs[name], name, dtype, max_tokens), steps, str(d))
-        got[cut] = replay_util.collect(steps, str(d), 512)
+    kernels.FOLD_NORMS = fold
+    try:
+        for cut in ("whole", "tail_decode", "portions", "mixed"):
+            steps, max_tokens = getattr(cuttings, cut)(seqs)
+            d = tmp_path / cut
+            replay_util.replay_in_process(_runner(model_dirs[name], name, dtype, max_tokens), steps, str(d))
+            got[cut] = replay_util.collect(steps, str(d), 512)
+    finally:
+        kernels.FOLD_NORMS = True
     scale = max(float(r.abs().max()) for r in ref.values())
-    tol = 2e-5 if dtype == "float32" else 1.5e-2 * scale
+    tol = 2e-5 if dtype == "float32" else (BF16_REL if fold else 1.5e-2) * scale
+    rounding = np.sqrt(np.mean([np.square(row - exact[key[0]][key[1]].numpy()).mean()
+                                for key, row in got["whole"].items()]))
     for cut in ("tail_decode", "portions", "mixed"):
+        sq = []
         for key, row in got["whole"].items():
             d = float(np.abs(row - got[cut][key]).max())
             assert d <= tol, f"{cut} differs from whole at {key}: {d:.3e}"
+            sq.append(np.square(row - got[cut][key]).mean())
+        if dtype == "bfloat16":
+            assert np.sqrt(np.mean(sq)) <= (0.6 if fold else 0.2) * rounding, (cut, np.sqrt(np.mean(sq)), rounding)
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
