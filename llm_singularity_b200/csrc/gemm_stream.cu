@@ -35,6 +35,7 @@
 // a separate kernel for silu(g) * u (kernels/src/activations.cu:11-21).  No load here uses cluster
 // multicast.
 #include "common.cuh"
+#include "stream_warm.cuh"
 
 #include <cuda.h>
 
@@ -48,6 +49,7 @@ constexpr int kMaxStages = 8;
 constexpr int kSmemBudget = 200 * 1024;         // one block per SM; most of it is the ring
 constexpr uint32_t kSpinLimit = 1u << 22;
 constexpr int kSsPerLane = 5;                  // parts of a row's sum of squares a lane adds up: 160 parts at most
+constexpr int kWarmBytes = 112 * 1024;          // of the next product's weights, a block asks L2 for this much
 constexpr int kTailBytes = 320;                // barriers, the give-up flag, the rows' scales
 static_assert(3 * kMaxStages * 8 + 16 + 16 * 4 <= kTailBytes, "barriers, flag and scales fit the tail");
 constexpr int kFoldBytes = (16 * 128 + kWarps * 128 + 16) * 4;   // more shared memory if the product adds to the residual
@@ -152,14 +154,19 @@ __device__ __forceinline__ float gate_act(float g, int act) {
 // would wait out the tensor core's latency at every step).  NT: 8-row tiles of activations.
 constexpr int kInFlight = 4;
 
-template <int NT>
+// FOLDS: the kernel can take rows whose norm is still owed (prm.ss_in) and add its product to the
+// residual, leaving the next norm half done (prm.residual).  The kernel without that code, for
+// plain products, is 0.4 us shorter a launch (gate/up and down of a 1B layer in a chain: 19.4
+// against 20.2 us a pair): these kernels run once, cold, and every line of instructions counts.
+template <int NT, bool FOLDS>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
                    const __grid_constant__ CUtensorMap map_c, const __grid_constant__ CUtensorMap map_x,
-                   const StreamParams prm) {
+                   const StreamParams prm, const __grid_constant__ StreamWarm warm) {
     extern __shared__ unsigned char smem_dyn[];
     unsigned char* smem_raw = (unsigned char*)(((uintptr_t)smem_dyn + 1023) & ~(uintptr_t)1023);
     lsb_pdl_launch_dependents();
+    const bool SCALED = FOLDS && prm.ss_in != nullptr, ADDS = FOLDS && prm.residual != nullptr;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kc = prm.kc, stages = prm.stages;
     const int pieces = kc >> 6;                                   // 64-wide pieces of a chunk
@@ -246,6 +253,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             issue_x(wx);
             step(wx);
         }
+        if (ok) stream_warm_issue(warm, blk);      // everything of this product is asked for: on to the next
         if (!ok) {
             // gave up: copies still in flight must land before the block's shared memory goes away
             // (every stage's last copy of weights, and of activations, that was asked for)
@@ -279,7 +287,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     // The scale of the rows, if x stands for rows whose norm is still owed: the parts of their sums
     // of squares are asked for now and added up, in a fixed order, when the first pass ends.
     float ssq[2][kSsPerLane];
-    if (prm.ss_in) {
+    if (SCALED) {
 #pragma unroll
         for (int i = 0; i < 2; ++i)
 #pragma unroll
@@ -288,7 +296,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 ssq[i][q] = (m < prm.M && part < prm.ss_parts) ? prm.ss_in[part * 16 + m] : 0.f;
             }
     }
-    if (prm.residual && lane == 0) ss_s[warp] = ss_s[warp + kWarps] = 0.f;
+    if (ADDS && lane == 0) ss_s[warp] = ss_s[warp + kWarps] = 0.f;
     int s = 0;
     uint32_t parity = 0;
     for (int pass = 0; pass < passes; ++pass) {
@@ -300,7 +308,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         const int pr0 = pass * rows_cap, prows = min(rows_cap, rows - pr0);
         const bool active = my_tile * 16 < prows;
         for (int kb = 0; kb < nk; ++kb) {
-            if (prm.residual && kb == nk - 1) {
+            if (ADDS && kb == nk - 1) {
                 // what the outputs of this pass are added to, on its way while the last chunk is
                 // (each thread fetches what it will use itself)
                 const size_t first = (size_t)(r0 + pr0);
@@ -349,7 +357,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 *reinterpret_cast<float2*>(&mine[(r + 8) * width + c]) = make_float2(v[2], v[3]);
             }
         }
-        if (prm.ss_in && pass == 0) {
+        if (SCALED && pass == 0) {
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
                 float t = ((ssq[i][0] + ssq[i][1]) + (ssq[i][2] + ssq[i][3])) + ssq[i][4];
@@ -358,13 +366,13 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 if (lane == 0) scale_s[warp + kWarps * i] = rsqrtf(t * prm.inv_size + prm.eps);
             }
         }
-        if (prm.residual) cp_async_wait_all();
+        if (ADDS) cp_async_wait_all();
         consumer_sync();
         const int n_local = prm.act ? prows >> 1 : prows;
         const size_t first = prm.act ? (size_t)((r0 + pr0) >> 1) : (size_t)(r0 + pr0);
         const int part_stride = rt * 16 * width;
         for (int m = warp; m < prm.M; m += kWarps) {
-        const float scale = prm.ss_in ? scale_s[m] : 1.f;
+        const float scale = SCALED ? scale_s[m] : 1.f;
         float ss_row = 0.f;
         for (int j = lane; j < n_local; j += 32) {
             float v;
@@ -383,7 +391,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 v *= scale;
             }
             const size_t o = (size_t)m * n_out + first + j;
-            if (prm.residual) {
+            if (ADDS) {
                 const float h = res_s[m * 128 + j] + v;
                 prm.residual[o] = h;
                 ss_row += h * h;
@@ -392,14 +400,14 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             if (prm.out_f32) reinterpret_cast<float*>(prm.out)[o] = v;
             else reinterpret_cast<bf16*>(prm.out)[o] = __float2bfloat16_rn(v);
         }
-        if (prm.residual) {
+        if (ADDS) {
 #pragma unroll
             for (int off = 16; off > 0; off >>= 1) ss_row += __shfl_xor_sync(0xffffffffu, ss_row, off);
             if (lane == 0) ss_s[m] += ss_row;
         }
         }
     }
-    if (prm.residual && lane == 0)
+    if (ADDS && lane == 0)
         for (int m = warp; m < prm.M; m += kWarps) prm.ss_out[(size_t)blockIdx.x * 16 + m] = ss_s[m];
 }
 
@@ -512,15 +520,16 @@ LSB_API int lsb_gemm_stream_blocks(int M, int N, int K, int act) {
     return make_plan(M, N, K, act, 1, sm_count(), &p) ? p.blocks : 0;
 }
 
-template <int NT>
-static int launch(const CUtensorMap* maps, const StreamParams& prm, const Plan& p, cudaStream_t stream) {
+template <int NT, bool FOLDS>
+static int launch(const CUtensorMap* maps, const StreamParams& prm, const Plan& p, const StreamWarm& warm,
+                  cudaStream_t stream) {
     static int configured = -1;
     if (configured < 0)
-        configured = (int)cudaFuncSetAttribute(gemm_stream_kernel<NT>,
+        configured = (int)cudaFuncSetAttribute(gemm_stream_kernel<NT, FOLDS>,
                                                cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBudget);
     if (configured) return configured;
-    return lsb_launch(gemm_stream_kernel<NT>, dim3(p.blocks), dim3(kThreads), p.smem, stream, 1, maps[0],
-                      maps[1], maps[2], maps[3], prm);
+    return lsb_launch(gemm_stream_kernel<NT, FOLDS>, dim3(p.blocks), dim3(kThreads), p.smem, stream, 1,
+                      maps[0], maps[1], maps[2], maps[3], prm, warm);
 }
 
 // The product with an RMS norm folded into it on either side, so that the norm needs no kernel of
@@ -535,9 +544,13 @@ static int launch(const CUtensorMap* maps, const StreamParams& prm, const Plan& 
 // is (residual * norm_w) in bfloat16, the input of the next product in the sense above, and
 // ss_out[block * 16 + m] gets this block's part of sum(residual[m]^2) over its own columns;
 // lsb_gemm_stream_blocks gives the number of parts.  All sums are taken in a fixed order.
+//
+// warm != null: a StreamWarm that lsb_gemm_stream_warm filled in for the streaming product that
+// follows this one in the stream; its first weights are pulled toward L2 while this one ends.
 LSB_API int lsb_gemm_stream_folded(const void* x, const void* w, void* out, int out_f32, int M, int N, int K,
                                    int act, const float* ss_in, int ss_parts, int size, float eps,
-                                   float* residual, const float* norm_w, float* ss_out, cudaStream_t stream) {
+                                   float* residual, const float* norm_w, float* ss_out, const void* warm,
+                                   cudaStream_t stream) {
     Plan p;
     if (!lsb_gemm_stream_supported(x, w, M, N, K, act)) return (int)cudaErrorInvalidValue;
     if (ss_in && (ss_parts <= 0 || ss_parts > 32 * kSsPerLane || size <= 0)) return (int)cudaErrorInvalidValue;
@@ -560,12 +573,35 @@ LSB_API int lsb_gemm_stream_folded(const void* x, const void* w, void* out, int 
     if ((rc = make_map(&maps[1], w, N, K, p.rows_b, p.kc / 64))) return rc;
     if ((rc = make_map(&maps[2], w, N, K, p.rows_c, p.kc / 64))) return rc;
     if ((rc = make_map(&maps[3], x, M, K, 8 * p.nt, p.kc / 64))) return rc;
-    return p.nt == 1 ? launch<1>(maps, prm, p, stream) : launch<2>(maps, prm, p, stream);
+    StreamWarm none;
+    none.base = nullptr;
+    none.blocks = 0;
+    const StreamWarm& wm = warm ? *reinterpret_cast<const StreamWarm*>(warm) : none;
+    if (ss_in || residual)
+        return p.nt == 1 ? launch<1, true>(maps, prm, p, wm, stream) : launch<2, true>(maps, prm, p, wm, stream);
+    return p.nt == 1 ? launch<1, false>(maps, prm, p, wm, stream) : launch<2, false>(maps, prm, p, wm, stream);
 }
+
+// Fills `out` (sizeof(StreamWarm) bytes, see lsb_stream_warm_bytes) with what the kernel before a
+// streaming product of these sizes needs to warm it; `adds`: the product adds to the residual.
+// Returns 0, or an error if the streaming kernel does not take the product.
+LSB_API int lsb_gemm_stream_warm(const void* w, int M, int N, int K, int act, int adds, void* out) {
+    Plan p;
+    if (((uintptr_t)w % 16) || !make_plan(M, N, K, act, adds, sm_count(), &p)) return (int)cudaErrorInvalidValue;
+    StreamWarm* sw = reinterpret_cast<StreamWarm*>(out);
+    sw->base = reinterpret_cast<const unsigned char*>(w);
+    sw->row_bytes = (long long)K * 2;
+    sw->blocks = p.blocks;
+    sw->rows_hi = p.rows_hi; sw->rows_lo = p.rows_lo; sw->n_hi = p.n_hi;
+    sw->bytes = kWarmBytes;
+    return 0;
+}
+
+LSB_API int lsb_stream_warm_bytes() { return (int)sizeof(StreamWarm); }
 
 // x [M, K] and w [N, K] bfloat16; out [M, N] (or [M, N / 2] with act != 0) bfloat16 or (out_f32) float.
 LSB_API int lsb_gemm_stream(const void* x, const void* w, void* out, int out_f32, int M, int N, int K,
                             int act, cudaStream_t stream) {
     return lsb_gemm_stream_folded(x, w, out, out_f32, M, N, K, act, nullptr, 0, 0, 0.f, nullptr, nullptr,
-                                  nullptr, stream);
+                                  nullptr, nullptr, stream);
 }

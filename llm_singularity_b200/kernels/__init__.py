@@ -10,6 +10,7 @@ wrongly.
 from __future__ import annotations
 
 import ctypes
+import weakref
 from typing import Dict, Iterable, Optional
 
 import torch
@@ -310,6 +311,50 @@ class NormOut:
 
 FOLD_NORMS = True               # decode steps fold each norm into the products on either side of it
 
+# Warming.  A streaming product (csrc/gemm_stream.cu) can ask L2, while it ends, for the first
+# weights of the streaming product after it, so that HBM works through the gap between the two
+# kernels (csrc/stream_warm.cuh).  Which product comes next is not something a part knows; it is
+# learnt here: the matrix that followed a matrix the last time is expected to follow it again,
+# which holds from a model's second step on (and a decode step runs once before it is captured in
+# a graph).  A wrong guess costs a few prefetched bytes; nothing depends on it.  Any other product
+# in between (more than 16 rows, the output head) ends the chain.
+WARM_NEXT = True
+_follows: Dict[int, tuple] = {}         # address of a matrix -> (weak reference to its follower, gated)
+_warm_structs: Dict[tuple, object] = {}  # (address, rows, gated) -> (weak reference, filled-in StreamWarm)
+_last_streamed: Optional[int] = None
+
+
+def _warm_after(w: torch.Tensor, gated: bool, M: int):
+    """Note that ``w`` is being streamed now; the StreamWarm for what followed it last time, or None."""
+    global _last_streamed
+    if not WARM_NEXT:
+        return None
+    here = w.data_ptr()
+    if _last_streamed is not None and _last_streamed != here:
+        _follows[_last_streamed] = (weakref.ref(w), gated)
+    _last_streamed = here
+    nxt = _follows.get(here)
+    if nxt is None:
+        return None
+    t = nxt[0]()
+    if t is None:
+        del _follows[here]
+        return None
+    key = (t.data_ptr(), M, nxt[1])
+    made = _warm_structs.get(key)
+    if made is None or made[0]() is not t:
+        lib = _lib("gemm_stream")
+        buf = ctypes.create_string_buffer(lib.lsb_stream_warm_bytes())
+        rc = lib.lsb_gemm_stream_warm(_p(t), _i(M), _i(t.shape[0]), _i(t.shape[1]),
+                                      _i(ACTIVATIONS["silu"] if nxt[1] else 0), _i(0), buf)
+        made = _warm_structs[key] = (weakref.ref(t), buf if rc == 0 else None)
+    return made[1]
+
+
+def _chain_ends() -> None:
+    global _last_streamed
+    _last_streamed = None
+
 
 def folds_norm(rows: int, dtype: torch.dtype) -> bool:
     """Does a step of this many rows fold its norms into the neighbouring products?  (The products
@@ -382,7 +427,7 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
               _p(owed.parts if owed is not None else None), _i(owed.parts.shape[0] if owed is not None else 0),
               _i(K), _f(owed.eps if owed is not None else 0.0),
               _p(into[0] if into is not None else None), _p(into[1] if into is not None else None), _p(parts),
-              _stream(out))
+              _warm_after(w, gated, M), _stream(out))
         return NormOut(out, parts, into[2]) if into is not None else out
     if owed is not None:
         x = finish_norm(owed)
@@ -394,6 +439,7 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
     if x.dtype == torch.bfloat16 and SMALL_PRODUCTS and not gated and M <= 16 and small_gemm_ok(x, w):
         # a few rows times a matrix that fits the chip's shared memory (decode: q/k/v, output
         # projection): weights resident before the previous kernel has ended, no cluster
+        _chain_ends()
         out = torch.empty((M, N), dtype=out_dtype, device=x.device)
         _call("gemm_small", "lsb_gemm_small", _p(x), _p(w), _p(out), _i(1 if out_dtype == torch.float32 else 0),
               _i(M), _i(N), _i(K), _stream(out))
@@ -402,9 +448,11 @@ def linear(x, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
         # a few rows times a matrix of any size (decode: gate/up, down): every SM streams its own
         # share of the weight rows, the first chunks before the previous kernel has ended
         out = torch.empty((M, N // 2 if gated else N), dtype=out_dtype, device=x.device)
-        _call("gemm_stream", "lsb_gemm_stream", _p(x), _p(w), _p(out), _i(1 if out_dtype == torch.float32 else 0),
-              _i(M), _i(N), _i(K), _i(act), _stream(out))
+        _call("gemm_stream", "lsb_gemm_stream_folded", _p(x), _p(w), _p(out),
+              _i(1 if out_dtype == torch.float32 else 0), _i(M), _i(N), _i(K), _i(act), _p(None), _i(0), _i(K),
+              _f(0.0), _p(None), _p(None), _p(None), _warm_after(w, gated, M), _stream(out))
         return out
+    _chain_ends()
     if x.dtype == torch.bfloat16 and tensor_core_gemm_ok(x, w):
         out = torch.empty((M, N // 2 if gated else N), dtype=out_dtype, device=x.device)
         _call("gemm_tc", "lsb_gemm_tc", _p(x), _p(w), _p(out), _i(1 if out_dtype == torch.float32 else 0),

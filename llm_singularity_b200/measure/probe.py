@@ -98,16 +98,22 @@ def _decode_step(a) -> None:
 
     for _ in range(3):                                # eager once, capture, replay
         step()
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for _ in range(a.iters):
-        step()
-    e1.record()
-    torch.cuda.synchronize()
+    windows = []
+    for _ in range(5):                                # (a step's time moves by a per cent or two from
+        torch.cuda.synchronize()                      # window to window: the median of five)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(a.iters):
+            step()
+        e1.record()
+        torch.cuda.synchronize()
+        windows.append(e0.elapsed_time(e1) / a.iters * 1e3)
+    windows.sort()
     print(f"decode step B={B} context={ctx_len} layers={a.layers} hidden={a.hidden}: "
-          f"{e0.elapsed_time(e1) / a.iters * 1e3:.1f} us per step (CUDA events, graph replay)")
-    _timeline(step, "step")
+          f"{windows[2]:.1f} us per step (CUDA events, graph replay; median of five windows of {a.iters} steps, "
+          f"{windows[0]:.1f} .. {windows[-1]:.1f})")
+    if not a.no_timeline:
+        _timeline(step, "step")
 
 
 def _model(a, batch, max_len):
@@ -133,11 +139,10 @@ def _timeline(step, what):
     evs = sorted((e for e in prof.events() if e.device_type == torch.autograd.DeviceType.CUDA),
                  key=lambda e: e.time_range.end)
     names = [e.name.split("(")[0].replace("void ", "") for e in evs]
-    norms = [i for i, n in enumerate(names) if n.startswith("add_rmsnorm")]
-    if len(norms) >= 6:
-        mid = norms[(len(norms) // 2) & ~1]            # an input norm in the middle of the model
-        last = norms[((len(norms) // 2) & ~1) + 2]
-        print("one layer, time from the previous kernel's end to this kernel's end:")
+    marks = [i for i, n in enumerate(names) if "attention" in n]    # one attention kernel a layer
+    if len(marks) >= 4:
+        mid, last = marks[len(marks) // 2], marks[len(marks) // 2 + 1]
+        print("one layer in the middle, time from the previous kernel's end to this kernel's end:")
         for i in range(mid + 1, last + 1):
             print(f"  {evs[i].time_range.end - evs[i - 1].time_range.end:7.1f} us  {names[i][:70]}")
         print(f"  {evs[last].time_range.end - evs[mid].time_range.end:7.1f} us  the layer")
@@ -208,6 +213,7 @@ def main(argv=None) -> int:
     ap.add_argument("--vocab", type=int, default=128256)
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--no-timeline", action="store_true", help="decode_step: the step's time only")
     ap.add_argument("--no-flush", action="store_true")
     a = ap.parse_args(argv)
     from .. import kernels as K

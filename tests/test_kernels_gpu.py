@@ -351,6 +351,46 @@ def test_products_with_a_norm_folded_in(ops, M, K, H, N, act):
     assert (y2.double() - want).abs().max() <= 2 * tol + 1e-6
 
 
+def test_streamed_products_warm_what_followed_them_last_time(ops):
+    """A streaming product asks L2 for the first weights of the product that followed it the last
+    time.  That changes no result; the follower is learnt from the calls themselves, forgotten
+    when its tensor is gone, and any other kind of product ends the chain."""
+    M = 8
+    x = _rand(M, 2048, dtype=torch.bfloat16, seed=21, scale=0.5)
+    a = _rand(4096, 2048, dtype=torch.bfloat16, seed=22, scale=0.2)      # gated: 2048 outputs
+    b = _rand(2048, 2048, dtype=torch.bfloat16, seed=23, scale=0.2)
+    big = _rand(300, 2048, dtype=torch.bfloat16, seed=24, scale=0.2)
+    ops.SMALL_PRODUCTS = False
+    try:
+        def chain():
+            h = ops.linear(x, a, gated=True)
+            return ops.linear(h, b)
+        ops.WARM_NEXT = False
+        want = chain()
+        ops.WARM_NEXT = True
+        ops._follows.clear()
+        ops._chain_ends()
+        first = chain()                                   # learns: b follows a
+        assert ops._follows[a.data_ptr()][0]() is b and ops._follows[a.data_ptr()][1] is False
+        assert b.data_ptr() not in ops._follows
+        second = chain()                                  # a warms b; and learns: a (gated) follows b
+        assert ops._follows[b.data_ptr()][0]() is a and ops._follows[b.data_ptr()][1] is True
+        third = chain()                                   # both warm
+        assert ops._warm_after(a, True, M) is not None
+        ops.linear(_rand(40, 2048, dtype=torch.bfloat16, seed=25), big)   # another kind of product
+        assert ops._last_streamed is None
+        assert torch.equal(first, want) and torch.equal(second, want) and torch.equal(third, want)
+        gone = b.data_ptr()
+        del b, chain
+        import gc
+        gc.collect()
+        assert ops._warm_after(a, True, M) is None and a.data_ptr() not in ops._follows and gone
+    finally:
+        ops.SMALL_PRODUCTS = ops.WARM_NEXT = True
+        ops._follows.clear()
+        ops._chain_ends()
+
+
 def test_linear_float32_is_true_32_bit(ops):
     # (1 + 2^-20) * 1 + 1 * (-1) = 2^-20 exactly in 32-bit; a reduced-precision matrix mode
     # (10-bit mantissa operands) rounds the first factor to 1 and returns 0
