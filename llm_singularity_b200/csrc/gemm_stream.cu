@@ -282,7 +282,19 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
     const int a_row = ((lane >> 3) & 1) * 8 + (lane & 7), a_half = lane >> 4;
     const int b_row = lane & 7, b_half = (lane >> 3) & 1;
     const int my_tile = warp & (rt - 1), my_part = warp / rt, parts = kWarps / rt;
-    const int n_out = prm.act ? prm.N / 2 : prm.N;
+    // What the end of a pass needs of the kernel's parameters is read now, into registers: a
+    // parameter read for the first time costs a trip past the constant cache (some 0.3 us each,
+    // one after the other, in a kernel whose whole end is 1 us), and here it hides under the wait
+    // for the first weights.
+    int e_M = prm.M, e_N = prm.N, e_act = prm.act, e_f32 = prm.out_f32;
+    void* e_out = prm.out;
+    float e_inv = prm.inv_size, e_eps = prm.eps;
+    float* e_res = prm.residual;
+    const float* e_nw = prm.norm_w;
+    float* e_ss = prm.ss_out;
+    asm volatile("" : "+r"(e_M), "+r"(e_N), "+r"(e_act), "+r"(e_f32), "+l"(e_out), "+f"(e_inv), "+f"(e_eps),
+                      "+l"(e_res), "+l"(e_nw), "+l"(e_ss));
+    const int n_out = e_act ? e_N / 2 : e_N;
     const int k_steps = kc >> 4;               // a multiple of kInFlight (beyond K the copy has filled in zeros)
     // The scale of the rows, if x stands for rows whose norm is still owed: the parts of their sums
     // of squares are asked for now and added up, in a fixed order, when the first pass ends.
@@ -293,7 +305,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
 #pragma unroll
             for (int q = 0; q < kSsPerLane; ++q) {
                 const int m = warp + kWarps * i, part = lane + 32 * q;
-                ssq[i][q] = (m < prm.M && part < prm.ss_parts) ? prm.ss_in[part * 16 + m] : 0.f;
+                ssq[i][q] = (m < e_M && part < prm.ss_parts) ? prm.ss_in[part * 16 + m] : 0.f;
             }
     }
     if (ADDS && lane == 0) ss_s[warp] = ss_s[warp + kWarps] = 0.f;
@@ -308,14 +320,14 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         const int pr0 = pass * rows_cap, prows = min(rows_cap, rows - pr0);
         const bool active = my_tile * 16 < prows;
         for (int kb = 0; kb < nk; ++kb) {
-            if (ADDS && kb == nk - 1) {
-                // what the outputs of this pass are added to, on its way while the last chunk is
+            if (ADDS && kb == 0) {
+                // what the outputs of this pass are added to, on its way while the weights are
                 // (each thread fetches what it will use itself)
                 const size_t first = (size_t)(r0 + pr0);
-                for (int m = warp; m < prm.M; m += kWarps)
+                for (int m = warp; m < e_M; m += kWarps)
                     for (int j = lane; j < prows; j += 32)
-                        cp_async_4(&res_s[m * 128 + j], prm.residual + (size_t)m * prm.N + first + j);
-                for (int j = lane; j < prows; j += 32) cp_async_4(&nw_s[warp * 128 + j], prm.norm_w + first + j);
+                        cp_async_4(&res_s[m * 128 + j], e_res + (size_t)m * e_N + first + j);
+                for (int j = lane; j < prows; j += 32) cp_async_4(&nw_s[warp * 128 + j], e_nw + first + j);
             }
             if (!mbar_wait(&full_w[s], parity, abort_flag) || !mbar_wait(&full_x[s], parity, abort_flag)) return;
             const uint32_t sw = smem_u32(ring + (size_t)s * stage_bytes);
@@ -363,27 +375,27 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
                 float t = ((ssq[i][0] + ssq[i][1]) + (ssq[i][2] + ssq[i][3])) + ssq[i][4];
 #pragma unroll
                 for (int off = 16; off > 0; off >>= 1) t += __shfl_xor_sync(0xffffffffu, t, off);
-                if (lane == 0) scale_s[warp + kWarps * i] = rsqrtf(t * prm.inv_size + prm.eps);
+                if (lane == 0) scale_s[warp + kWarps * i] = rsqrtf(t * e_inv + e_eps);
             }
         }
         if (ADDS) cp_async_wait_all();
         consumer_sync();
-        const int n_local = prm.act ? prows >> 1 : prows;
-        const size_t first = prm.act ? (size_t)((r0 + pr0) >> 1) : (size_t)(r0 + pr0);
+        const int n_local = e_act ? prows >> 1 : prows;
+        const size_t first = e_act ? (size_t)((r0 + pr0) >> 1) : (size_t)(r0 + pr0);
         const int part_stride = rt * 16 * width;
-        for (int m = warp; m < prm.M; m += kWarps) {
+        for (int m = warp; m < e_M; m += kWarps) {
         const float scale = SCALED ? scale_s[m] : 1.f;
         float ss_row = 0.f;
         for (int j = lane; j < n_local; j += 32) {
             float v;
-            if (prm.act) {
+            if (e_act) {
                 const float* src = buf + (size_t)(2 * j) * width + m;      // (rows of tile t lie at 16 t ...)
                 float g = 0.f, u = 0.f;
                 for (int p = 0; p < parts; ++p) {
                     g += src[(size_t)p * part_stride];
                     u += src[(size_t)p * part_stride + width];
                 }
-                v = gate_act(g * scale, prm.act) * (u * scale);
+                v = gate_act(g * scale, e_act) * (u * scale);
             } else {
                 const float* src = buf + (size_t)j * width + m;
                 v = 0.f;
@@ -393,12 +405,12 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
             const size_t o = (size_t)m * n_out + first + j;
             if (ADDS) {
                 const float h = res_s[m * 128 + j] + v;
-                prm.residual[o] = h;
+                e_res[o] = h;
                 ss_row += h * h;
                 v = h * nw_s[warp * 128 + j];
             }
-            if (prm.out_f32) reinterpret_cast<float*>(prm.out)[o] = v;
-            else reinterpret_cast<bf16*>(prm.out)[o] = __float2bfloat16_rn(v);
+            if (e_f32) reinterpret_cast<float*>(e_out)[o] = v;
+            else reinterpret_cast<bf16*>(e_out)[o] = __float2bfloat16_rn(v);
         }
         if (ADDS) {
 #pragma unroll
@@ -408,7 +420,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_const
         }
     }
     if (ADDS && lane == 0)
-        for (int m = warp; m < prm.M; m += kWarps) prm.ss_out[(size_t)blockIdx.x * 16 + m] = ss_s[m];
+        for (int m = warp; m < e_M; m += kWarps) e_ss[(size_t)blockIdx.x * 16 + m] = ss_s[m];
 }
 
 // ------------------------------------------------------------------------------- host
@@ -467,6 +479,10 @@ static int make_plan(int M, int N, int K, int act, int fold, int sms, Plan* p) {
             p->w_bytes = (int)w_bytes;
             p->stages = (int)(room / stage);
             if (p->stages > kMaxStages) p->stages = kMaxStages;
+            // no more stages than a block has chunks to walk: what a short product leaves of the
+            // SM's shared memory lets blocks of the next kernel in beside it, to set themselves up
+            const int walk = ((hi + cap - 1) / cap) * ((K + kc - 1) / kc);
+            if (p->stages > walk) p->stages = walk < 2 ? 2 : walk;
             p->smem = 1024 + (size_t)p->stages * stage + red + tail;
             break;
         }
