@@ -84,6 +84,17 @@ __device__ __forceinline__ void block_argmax(float& v, int& idx, BlockScratch& s
     idx = s.i[32];
 }
 
+// A greedy row without a repetition penalty is scanned by kGreedyParts blocks (blockIdx.y), each its
+// slice; the partial maxima meet in device memory and the block that arrives last picks the first
+// maximum among them (the order of arrival does not matter: ties go to the lowest index).  One block
+// reading a row of 128,256 logits took 12 - 14 us, as long as a layer of the decode step.  Every other
+// row is the work of its first block alone.
+constexpr int kGreedyParts = 16;
+constexpr int kGreedyRows = 1024;                 // rows beyond this are scanned by one block each
+__device__ float greedy_part_v[kGreedyRows * kGreedyParts];
+__device__ int greedy_part_i[kGreedyRows * kGreedyParts];
+__device__ unsigned int greedy_arrived[kGreedyRows];
+
 // params per row: {temperature, top_p, repetition_penalty, u}
 __global__ void __launch_bounds__(kSampleThreads)
 sample_kernel(const float* __restrict__ logits, float* __restrict__ work, int vocab,
@@ -101,6 +112,9 @@ sample_kernel(const float* __restrict__ logits, float* __restrict__ work, int vo
     const float* src = logits + (size_t)row * vocab;
 
     const int pb = prev_start ? prev_start[row] : 0, pe = prev_start ? prev_start[row + 1] : 0;
+    const int parts = (int)gridDim.y;
+    const bool shared_scan = parts > 1 && temperature == 0.0f && !(penalty != 1.0f && pe > pb);
+    if (blockIdx.y > 0 && !shared_scan) return;
     if (penalty != 1.0f && pe > pb) {
         float* w = work + (size_t)row * vocab;
         for (int i = tid; i < vocab; i += kSampleThreads) w[i] = src[i];
@@ -118,9 +132,73 @@ sample_kernel(const float* __restrict__ logits, float* __restrict__ work, int vo
     if (temperature == 0.0f) {
         float bv = -FLT_MAX;
         int bi = 0x7fffffff;
-        for (int i = tid; i < vocab; i += kSampleThreads) argmax_merge(bv, bi, src[i], i);
+        // (one block reads the whole row: four 16-byte loads in flight per thread; with one 4-byte
+        // load at a time a row of 128,256 took 14 us, the length of a layer of the decode step)
+        if ((vocab & 3) == 0 && (reinterpret_cast<uintptr_t>(src) & 15) == 0) {
+            const float4* s4 = reinterpret_cast<const float4*>(src);
+            int n4 = vocab >> 2, first4 = 0;
+            if (shared_scan) {                      // this block's slice of the row
+                const int per = (n4 + parts - 1) / parts;
+                first4 = min(n4, (int)blockIdx.y * per);
+                n4 = min(n4, first4 + per);
+            }
+            for (int i0 = first4 + tid; i0 < n4; i0 += 4 * kSampleThreads) {
+                float4 v[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int i = i0 + q * kSampleThreads;
+                    v[q] = i < n4 ? s4[i] : make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
+                }
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    const int i = 4 * (i0 + q * kSampleThreads);
+                    if (i < 4 * n4) {
+                        argmax_merge(bv, bi, v[q].x, i);
+                        argmax_merge(bv, bi, v[q].y, i + 1);
+                        argmax_merge(bv, bi, v[q].z, i + 2);
+                        argmax_merge(bv, bi, v[q].w, i + 3);
+                    }
+                }
+            }
+        } else {
+            int b = 0, e = vocab;
+            if (shared_scan) {
+                const int per = (vocab + parts - 1) / parts;
+                b = min(vocab, (int)blockIdx.y * per);
+                e = min(vocab, b + per);
+            }
+            for (int i = b + tid; i < e; i += kSampleThreads) argmax_merge(bv, bi, src[i], i);
+        }
         block_argmax(bv, bi, sc);
-        if (tid == 0) out[row] = bi;
+        if (!shared_scan) {
+            if (tid == 0) out[row] = bi;
+            return;
+        }
+        __shared__ bool last;
+        if (tid == 0) {
+            greedy_part_v[row * kGreedyParts + blockIdx.y] = bv;
+            greedy_part_i[row * kGreedyParts + blockIdx.y] = bi;
+            __threadfence();
+            last = atomicAdd(&greedy_arrived[row], 1u) == (unsigned int)parts - 1u;
+        }
+        __syncthreads();
+        if (!last) return;
+        if (tid < 32) {
+            __threadfence();
+            float v = -FLT_MAX;
+            int idx = 0x7fffffff;
+            if (tid < parts) {
+                v = __ldcg(&greedy_part_v[row * kGreedyParts + tid]);
+                idx = __ldcg(&greedy_part_i[row * kGreedyParts + tid]);
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1)
+                argmax_merge(v, idx, __shfl_xor_sync(0xffffffffu, v, o), __shfl_xor_sync(0xffffffffu, idx, o));
+            if (tid == 0) {
+                out[row] = idx;
+                greedy_arrived[row] = 0u;           // for the next launch
+            }
+        }
         return;
     }
     // x_i = src[i] / temperature, recomputed in every pass (division as the reference does)
@@ -217,6 +295,9 @@ LSB_API int lsb_sample(const float* logits, float* work, int rows, int vocab, co
                        cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) return (int)cudaErrorInvalidValue;
-    return lsb_launch(sample_kernel, dim3(rows), dim3(kSampleThreads), 0, stream, 1, logits, work, vocab,
+    // (few rows: their greedy scans are shared out over more blocks; many rows fill the SMs by themselves)
+    const int parts = rows <= 64 && vocab >= 16384 ? kGreedyParts : 1;
+    static_assert(kGreedyParts <= 32, "the last block merges the parts with one warp");
+    return lsb_launch(sample_kernel, dim3(rows, parts), dim3(kSampleThreads), 0, stream, 1, logits, work, vocab,
                       params, top_k, prev_start, prev_tokens, out);
 }

@@ -93,8 +93,13 @@ def _decode_step(a) -> None:
         for s0 in range(0, len(toks), 2048):
             r.step([StepEntry(rid, toks[s0:s0 + 2048], [])])
 
+    staged = None
+    if a.sample:                                      # greedy sampling behind the model, inside the graph
+        from ..sampling import SamplingParams
+        staged = eng.sampler.stage([SamplingParams(temperature=0.0)] * B, [0] * B)
+
     def step():
-        return r.step([StepEntry(rid, [5], [0]) for rid in ids])
+        return r.step([StepEntry(rid, [5], [0]) for rid in ids], after=staged)
 
     for _ in range(3):                                # eager once, capture, replay
         step()
@@ -214,6 +219,7 @@ def main(argv=None) -> int:
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-timeline", action="store_true", help="decode_step: the step's time only")
+    ap.add_argument("--sample", action="store_true", help="decode_step: with greedy sampling inside the graph")
     ap.add_argument("--no-flush", action="store_true")
     a = ap.parse_args(argv)
     from .. import kernels as K

@@ -822,6 +822,38 @@ def test_greedy_takes_the_first_maximum(ops):
     assert out.cpu().tolist() == [123, 69999, 0]
 
 
+@pytest.mark.parametrize("vocab", [128256, 20001, 16384])
+def test_greedy_rows_scanned_by_several_blocks(ops, vocab):
+    """A few greedy rows over a large vocabulary are scanned by several blocks each, whose partial
+    maxima meet in device memory: equal maxima in different blocks' slices still give the first one,
+    again and again (the arrival counter is left at zero), also beside rows that sample and rows
+    with a repetition penalty (which one block scans alone)."""
+    g = torch.Generator().manual_seed(3)
+    R = 7
+    logits = torch.randn(R, vocab, generator=g)
+    per = -(-vocab // 16)
+    logits[0, [per - 1, per, 5 * per + 3, vocab - 1]] = 9.0          # ties on both sides of a slice's edge
+    logits[1, vocab - 1] = 9.0
+    logits[2, 0] = 9.0
+    logits[3] = 0.0                                                  # every value equal: index 0
+    logits[5, [7 * per + 1, 12 * per]] = 9.0
+    params = [[0.0, 1.0, 1.0, 0.5]] * 4 + [[1.0, 1.0, 1.0, 0.3], [0.0, 1.0, 4.0, 0.5], [0.0, 1.0, 1.0, 0.5]]
+    prev_start = [0, 0, 0, 0, 0, 0, 2, 2]
+    prev = [7 * per + 1, 3]                                          # row 5: its first maximum is penalised
+    out = torch.full((R,), -1, dtype=torch.int32, device="cuda")
+    dev = logits.cuda()
+    for _ in range(3):
+        out.fill_(-1)
+        ops.sample(dev, torch.tensor(params, device="cuda"), torch.zeros(R, dtype=torch.int32, device="cuda"),
+                   torch.tensor(prev_start, dtype=torch.int32, device="cuda"),
+                   torch.tensor(prev, dtype=torch.int32, device="cuda"), out)
+        got = out.cpu().tolist()
+        assert got[0] == per - 1 and got[1] == vocab - 1 and got[2] == 0 and got[3] == 0
+        assert got[4] == plain_llama.sample_plain(logits[4].tolist(), 1.0, 0, 1.0, 1.0, (), 0.3)
+        assert got[5] == 12 * per
+        assert got[6] == int(logits[6].argmax())
+
+
 def test_sampling_falls_back_to_the_last_kept_token(ops):
     """When the running sum never reaches u * total (rounding at the very end of the scan; forced
     here by a draw above one), the token is the last kept one in index order, as in the reference
