@@ -81,9 +81,10 @@ def _decode_step(a) -> None:
         intermediate_size=a.intermediate, vocab_size=a.vocab, rope_theta=500000.0, rope_scaling=None,
         rms_norm_eps=1e-5, tie_word_embeddings=True, max_position_embeddings=131072))
     B, ctx_len = a.batch, a.context
+    grow = 6 * a.iters + 16                           # steps run below: every one adds a token a request
     eng = Engine(None, config=cfg, random_weights=True, dtype="bfloat16", kv_block_size=a.page,
-                 num_kv_blocks=B * (ctx_len // a.page + 2) + 8, max_batch_size=B, max_tokens_per_batch=2048,
-                 max_model_len=ctx_len + 64, prefix_cache=False)
+                 num_kv_blocks=B * ((ctx_len + grow) // a.page + 2) + 8, max_batch_size=B,
+                 max_tokens_per_batch=2048, max_model_len=ctx_len + grow + 64, prefix_cache=False)
     r = eng.runner
     g = torch.Generator().manual_seed(0)
     ids = [f"r{i}" for i in range(B)]
@@ -203,6 +204,8 @@ def main(argv=None) -> int:
     ap.add_argument("--k", type=int, default=2048)
     ap.add_argument("--gated", action="store_true")
     ap.add_argument("--f32-out", action="store_true")
+    ap.add_argument("--scaled", action="store_true", help="gemm: x is a NormOut (the row scale owed)")
+    ap.add_argument("--adds", action="store_true", help="gemm: the product is added to a residual (into=)")
     ap.add_argument("--tile-kernel", action="store_true",
                     help="gemm: the tcgen05 tile kernel also where the small or streaming kernel would run")
     ap.add_argument("--batch", type=int, default=8)
@@ -236,7 +239,13 @@ def main(argv=None) -> int:
         x = torch.randn(a.m, a.k, device="cuda").to(torch.bfloat16)
         w = torch.randn(a.n, a.k, device="cuda").to(torch.bfloat16)
         od = torch.float32 if a.f32_out else torch.bfloat16
-        us = _time(lambda: K.linear(x, w, out_dtype=od, gated=a.gated), a.iters, a.warmup, not a.no_flush)
+        xin, into = x, None
+        if a.scaled:        # x as the product before left it: the norm's row scale still owed
+            xin = K.NormOut(x, torch.rand(148, 16, device="cuda") * a.k / 148, 1e-5)
+        if a.adds:          # the product added to the residual, the next norm half done
+            into = (torch.randn(a.m, a.n, device="cuda"), torch.ones(a.n, device="cuda"), 1e-5)
+        us = _time(lambda: K.linear(xin, w, out_dtype=od, gated=a.gated, into=into), a.iters, a.warmup,
+                   not a.no_flush)
         flop, byt = 2.0 * a.m * a.n * a.k, 2.0 * (a.n * a.k + a.m * a.k) + a.m * a.n * (4 if a.f32_out else 2)
         print(f"gemm M={a.m} N={a.n} K={a.k} gated={a.gated}: {us:.1f} us  {flop / us / 1e6:.1f} TFLOP/s  "
               f"{byt / us / 1e3:.0f} GB/s")
