@@ -573,9 +573,11 @@ _TC_HEAD_DIMS = (64, 128)
 
 def decode_splits(n_decode: int, nkv: int, device=None) -> int:
     """How many ways each request's keys are split among thread blocks in the decode kernel:
-    enough blocks for three per SM; a function of the batch alone, so that a captured launch
-    stays valid as sequences grow."""
-    return max(1, min(32, (3 * num_sms(device)) // max(1, n_decode * nkv)))
+    enough blocks for three per SM, rounded up (32 requests of 8 kv heads are 256 blocks for 148 SMs:
+    in two splits a decode step at 32 x 4096 takes 1.64 ms, unsplit 1.87 ms; 8 requests in seven
+    splits 1 % less than in six); a function of the batch alone, so that a captured launch stays
+    valid as sequences grow."""
+    return max(1, min(32, -(-3 * num_sms(device) // max(1, n_decode * nkv))))
 
 
 _cluster_caps: Dict[int, int] = {}
