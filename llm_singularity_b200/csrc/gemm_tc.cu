@@ -361,34 +361,33 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_p, const __grid_constant_
     const int kb1 = min(prm.num_kb, kb0 + prm.kb_per_split);
     const int nkb = max(0, kb1 - kb0);
 
+    lsb_pdl_launch_dependents();
+    const int pre = min(nkb, STAGES);
     if (threadIdx.x == 0) {
         abort_flag = 0;
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         mbar_init(acc_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        // Weights are not written by anything in the stream: their first STAGES boxes are
+        // requested at once, before the block meets (tensor memory is being allocated meanwhile)
+        // and before the wait on the previous kernel; the activations after it.
+        for (int kb = 0; kb < pre; ++kb) {
+            unsigned char* st = stages + (size_t)kb * L::kStageBytes;
+            mbar_expect_tx(&full[kb], L::kStageBytes);
+            if (prm.static_operand == 1) tma_load_2d(st, &map_p, &full[kb], (kb0 + kb) * kBK, i0);
+            else tma_load_2d(st + L::kPBytes, &map_q, &full[kb], (kb0 + kb) * kBK, j0);
+        }
     }
     if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    lsb_pdl_launch_dependents();
     if (threadIdx.x != 0) lsb_pdl_wait();      // thread 0 (the TMA producer) waits after its prefetch
 
     if (warp == 0) {
         if (lane == 0) {
-            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_p) : "memory");
-            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
-            // Weights are not written by anything in the stream: their first STAGES boxes are
-            // requested before the wait on the previous kernel, the activations after it.
-            const int pre = min(nkb, STAGES);
-            for (int kb = 0; kb < pre; ++kb) {
-                unsigned char* st = stages + (size_t)kb * L::kStageBytes;
-                mbar_expect_tx(&full[kb], L::kStageBytes);
-                if (prm.static_operand == 1) tma_load_2d(st, &map_p, &full[kb], (kb0 + kb) * kBK, i0);
-                else tma_load_2d(st + L::kPBytes, &map_q, &full[kb], (kb0 + kb) * kBK, j0);
-            }
             lsb_pdl_wait();
             for (int kb = 0; kb < pre; ++kb) {
                 unsigned char* st = stages + (size_t)kb * L::kStageBytes;
@@ -577,39 +576,38 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_p, const __gri
     const int n_tiles = tiles_m * tiles_n;
     const int nkb = prm.num_kb;
 
+    lsb_pdl_launch_dependents();
+    // tile t -> (row block, column block); neighbouring blocks share the weight columns
+    const bool weights_p = prm.static_operand == 1;
+    int pre = 0;
     if (threadIdx.x == 0) {
         abort_flag = 0;
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         for (int a = 0; a < 2; ++a) { mbar_init(&acc_full[a], 1); mbar_init(&acc_empty[a], 128); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        // The weights are not written by anything in the stream: the boxes of the first ring fill are
+        // requested at once, before the block meets (tensor memory is being allocated meanwhile) and
+        // before the wait on the previous kernel; the activations after it.
+        for (int t = blockIdx.x; t < n_tiles && pre < STAGES; t += gridDim.x) {
+            const int i0 = (t % tiles_m) * kBM, j0 = (t / tiles_m) * BN;
+            for (int kb = 0; kb < nkb && pre < STAGES; ++kb, ++pre) {
+                unsigned char* st = stages + (size_t)pre * L::kStageBytes;
+                mbar_expect_tx(&full[pre], L::kStageBytes);
+                if (weights_p) tma_load_2d(st, &map_p, &full[pre], kb * kBK, i0);
+                else tma_load_2d(st + L::kPBytes, &map_q, &full[pre], kb * kBK, j0);
+            }
+        }
     }
     if (warp == 1) tmem_alloc(tmem_slot, kTmemCols);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    lsb_pdl_launch_dependents();
     if (threadIdx.x != 0) lsb_pdl_wait();      // thread 0 (the TMA producer) waits after its first weight boxes
 
-    // tile t -> (row block, column block); neighbouring blocks share the weight columns
     if (warp == 0) {
         if (lane == 0) {
-            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_p) : "memory");
-            asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
-            // The weights are not written by anything in the stream: the boxes of the first ring
-            // fill are requested before the wait on the previous kernel, the activations after it.
-            const bool weights_p = prm.static_operand == 1;
-            int pre = 0;
-            for (int t = blockIdx.x; t < n_tiles && pre < STAGES; t += gridDim.x) {
-                const int i0 = (t % tiles_m) * kBM, j0 = (t / tiles_m) * BN;
-                for (int kb = 0; kb < nkb && pre < STAGES; ++kb, ++pre) {
-                    unsigned char* st = stages + (size_t)pre * L::kStageBytes;
-                    mbar_expect_tx(&full[pre], L::kStageBytes);
-                    if (weights_p) tma_load_2d(st, &map_p, &full[pre], kb * kBK, i0);
-                    else tma_load_2d(st + L::kPBytes, &map_q, &full[pre], kb * kBK, j0);
-                }
-            }
             lsb_pdl_wait();
             long long it = 0;                                  // K blocks issued so far, over all tiles
             bool ok = true;
