@@ -794,6 +794,23 @@ template <int HD> static int max_cluster() {
     return value;
 }
 
+// Blocks of the decode kernel that fit an SM at once (registers and shared memory), for query groups
+// of `group` heads: what the number of key splits is sized by.
+LSB_API int lsb_decode_blocks_per_sm(int hd, int group) {
+    if ((hd != 64 && hd != 128) || group < 1) return 1;
+    if ((hd == 64 ? configure_once<64>() : configure_once<128>())) return 1;
+    int n = 0;
+    cudaError_t e;
+    if (hd == 64)
+        e = group <= 8 ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, decode_attention_kernel<64, true>, kThreads, decode_smem<64>())
+                       : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, decode_attention_kernel<64, false>, kThreads, decode_smem<64>());
+    else
+        e = group <= 8 ? cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, decode_attention_kernel<128, true>, kThreads, decode_smem<128>())
+                       : cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, decode_attention_kernel<128, false>, kThreads, decode_smem<128>());
+    if (e != cudaSuccess) { (void)cudaGetLastError(); return 1; }
+    return n < 1 ? 1 : n;
+}
+
 LSB_API int lsb_decode_max_cluster(int hd) { return hd == 64 ? max_cluster<64>() : hd == 128 ? max_cluster<128>() : 8; }
 
 // floats of scratch the decode kernel needs for `splits` > 1: outputs, then (max, sum) pairs

@@ -571,13 +571,26 @@ FUSE_DECODE_ROPE = True         # single tokens: rotation and cache write inside
 _TC_HEAD_DIMS = (64, 128)
 
 
-def decode_splits(n_decode: int, nkv: int, device=None) -> int:
-    """How many ways each request's keys are split among thread blocks in the decode kernel:
-    enough blocks for three per SM, rounded up (32 requests of 8 kv heads are 256 blocks for 148 SMs:
-    in two splits a decode step at 32 x 4096 takes 1.64 ms, unsplit 1.87 ms; 8 requests in seven
-    splits 1 % less than in six); a function of the batch alone, so that a captured launch stays
-    valid as sequences grow."""
-    return max(1, min(32, -(-3 * num_sms(device) // max(1, n_decode * nkv))))
+_decode_occupancy: Dict[tuple, int] = {}
+
+
+def decode_splits(n_decode: int, nkv: int, device=None, hd: int = 64, group: int = 4) -> int:
+    """How many ways each request's keys are split among thread blocks in the decode kernel: as many
+    as fill four fifths of the blocks the SMs hold at once (four an SM at head size 64, two at 128,
+    where a block has twice the registers and shared memory), never a second round of blocks.
+    Measured inside decode steps at context 4096: head size 64, 8 requests: 7 splits (6: 1 % slower,
+    9: 10 %); 32 requests: 2 (1: 14 % slower, 3: 10 %); head size 128, 8 requests: 4 or 5 splits 27 -
+    28 us a layer, 7 splits (a second round for four blocks) 42 us; 32 requests: 1 split 84 us, 2
+    splits 108 us.  A function of the batch alone, so that a captured launch stays valid as
+    sequences grow."""
+    key = (hd, group)
+    if key not in _decode_occupancy:
+        fits = 4
+        if hd in _TC_HEAD_DIMS:
+            fits = int(_lib("attention_tc").lsb_decode_blocks_per_sm(_i(hd), _i(group)))
+        _decode_occupancy[key] = max(1, fits)
+    room = _decode_occupancy[key] * num_sms(device)
+    return max(1, min(32, int(0.8 * room / max(1, n_decode * nkv) + 0.5)))
 
 
 _cluster_caps: Dict[int, int] = {}
@@ -696,7 +709,7 @@ def paged_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache, s
     n_decode, first, last = _batch_shape(ctx)
     on = _stream(out) if stream is None else ctypes.c_void_p(stream)
     if n_decode and only != "portions":
-        splits = decode_splits(n_decode, nkv, qkv.device)
+        splits = decode_splits(n_decode, nkv, qkv.device, hd, nh // nkv)
         if not getattr(ctx, "fixed_launch", False):
             splits = min(splits, -(-ctx.max_kv_len // 128))
         cluster_cap = _decode_cluster_cap(hd)
