@@ -192,11 +192,15 @@ def test_linear(ops, in_dtype, out_dtype, M, N, K):
 
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("M, N, K", [(1, 256, 64), (8, 16384, 2048), (40, 200, 72), (300, 1000, 136),
-                                     (2048, 512, 256), (5, 64, 2048), (8, 19200, 200), (40, 30000, 64)])
+                                     (2048, 512, 256), (5, 64, 2048), (8, 19200, 200), (40, 30000, 64),
+                                     (64, 16384, 2048), (17, 1616, 128), (128, 4096, 256), (100, 272, 64),
+                                     (33, 16384, 2048)])
 def test_gated_linear(ops, dtype, M, N, K):
     # out[m, i] = silu(x . w[2i]) * (x . w[2i + 1]); small N with large K makes the decode
     # orientation split K, so the activation has to wait for the sum of all splits; the last two
-    # have more 128-row weight slabs than SMs and less than twice as many (two blocks share an SM)
+    # have more 128-row weight slabs than SMs and less than twice as many (two blocks share an SM);
+    # the ones after them are batches of 17 to 128 rows, whose outputs leave the tile kernel through
+    # a transposing epilogue (whole and partial slabs, whole and partial batch tiles)
     x, w = _rand(M, K, dtype=dtype, seed=1, scale=0.5), _rand(N, K, dtype=dtype, seed=2, scale=0.2)
     y = ops.linear(x, w, gated=True)
     d = x.double() @ w.double().T
