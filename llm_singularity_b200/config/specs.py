@@ -71,6 +71,10 @@ class AttentionSpec(PartSpec):
     scale: float = 0.0            # multiplies q.k before the softmax
     window: Optional[int] = None  # keys further back than this many are not seen
     position: PartSpec = field(default_factory=NoPositionSpec)
+    # score modifiers (this architecture has neither): cap * tanh(s / cap) on the scaled scores, and
+    # a linear position bias -slope[h] * distance with the usual geometric slopes over the heads
+    logit_softcap: Optional[float] = None
+    linear_bias: bool = False
     kind: str = field(init=False, default="attention")
 
 

@@ -8,6 +8,11 @@
 // head h reads kv head h / (nh / nkv).  Scores (q.k) * scale, softmax by running
 // maximum and sum, weighted sum of values, division by the sum at the end.
 //
+// Two score modifiers that other architectures use are taken here (the reference has neither;
+// the tensor-core kernels do not take them, so a mixer that asks for one runs this kernel):
+// a soft cap, s <- cap * tanh(s / cap), and a linear position bias per head,
+// s <- s - slope[h] * (p - key position), applied in that order before the softmax.
+//
 // Replaces paged_attention_kernel of the reference (kernels/src/attention.cu:27-172:
 // 32 threads per (head, row), per-thread v_acc[128] in registers, shared-memory tree
 // merge, one launch per request during prefill, models/llama/llama_model.cpp:603-614).
@@ -61,7 +66,8 @@ paged_attention_generic_kernel(
     const int* __restrict__ q_start, const int* __restrict__ kv_len_arr,
     const int* __restrict__ table_rows, const int* __restrict__ block_table, int table_stride,
     T* __restrict__ out,                                    // [tokens, nh*hd]
-    int nh, int nkv, int hd, int page_size, int num_pages, float scale, int window) {
+    int nh, int nkv, int hd, int page_size, int num_pages, float scale, int window,
+    float softcap, const float* __restrict__ slopes) {
     __shared__ float q_sh[kAttnWarps][kMaxHeadDim];
     lsb_pdl_launch_dependents();
     lsb_pdl_wait();
@@ -77,6 +83,7 @@ paged_attention_generic_kernel(
     const int g = h / (nh / nkv);
     const int t = qs + i;
     const int* bt = block_table + (size_t)table_rows[r] * table_stride;
+    const float slope = slopes ? slopes[h] : 0.f;
 
     const T* q = qkv + (size_t)t * qkv_stride + (size_t)h * hd;
     for (int d = lane; d < hd; d += 32) q_sh[warp][d] = lsb_to_float(q[d]) * scale;
@@ -99,6 +106,8 @@ paged_attention_generic_kernel(
             } else {
                 off = (((long long)page * nkv + g) * page_size + (kj % page_size)) * hd;
                 s = dot_row<T>(q_sh[warp], k_pages + off, hd);
+                if (softcap > 0.f) s = softcap * tanhf(s / softcap);
+                s -= slope * (float)(p - kj);
             }
         }
         const float m_new = fmaxf(m, lsb_warp_max(s));
@@ -130,13 +139,14 @@ paged_attention_generic_kernel(
     }
 }
 
-// qkv: [tokens, qkv_stride] with the nh*hd query values first in each row.
+// qkv: [tokens, qkv_stride] with the nh*hd query values first in each row.  softcap: 0 for none;
+// slopes: float [nh] or null.
 LSB_API int lsb_paged_attention_generic(
     const void* qkv, int qkv_stride, const void* k_pages, const void* v_pages,
     const int* q_start, const int* kv_len, const int* table_rows, const int* block_table,
     int table_stride, void* out, int dtype, int n_requests, int max_q_len,
     int nh, int nkv, int hd, int page_size, int num_pages, float scale, int window,
-    cudaStream_t stream) {
+    float softcap, const float* slopes, cudaStream_t stream) {
     if (n_requests <= 0 || max_q_len <= 0) return 0;
     if (hd % 16 || hd <= 0 || hd > kMaxHeadDim || nkv <= 0 || nh % nkv) return (int)cudaErrorInvalidValue;
     if (n_requests > 65535 || nh > 65535) return (int)cudaErrorInvalidValue;
@@ -145,6 +155,6 @@ LSB_API int lsb_paged_attention_generic(
         paged_attention_generic_kernel<T>, grid, dim3(kAttnWarps * 32), 0, stream, 1,
         (const T*)qkv, qkv_stride, (const T*)k_pages, (const T*)v_pages, q_start, kv_len,
         table_rows, block_table, table_stride, (T*)out, nh, nkv, hd, page_size, num_pages,
-        scale, window));
+        scale, window, softcap, slopes));
     return 0;
 }

@@ -635,11 +635,16 @@ def _batch_shape(ctx):
 
 def rope_store_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache,
                          inv_freq: Optional[torch.Tensor], rotary_dim: int, store: bool,
-                         scale: float, window: int, out: torch.Tensor) -> None:
+                         scale: float, window: int, out: torch.Tensor, softcap: float = 0.0,
+                         slopes: Optional[torch.Tensor] = None) -> None:
     """``rope_kv_store`` followed by ``paged_attention``, as one operation.  Where the decode
     kernel can do the rotation and the cache write of single tokens itself (tensor-core path,
-    the whole head rotary), the separate kernel runs only for the tokens of prompt portions, or
-    not at all."""
+    the whole head rotary, no score modifier), the separate kernel runs only for the tokens of
+    prompt portions, or not at all."""
+    if softcap or slopes is not None:
+        rope_kv_store(qkv, nh, nkv, hd, ctx, cache, inv_freq, rotary_dim, store)
+        paged_attention(qkv, nh, nkv, hd, ctx, cache, scale, window, out, softcap=softcap, slopes=slopes)
+        return
     fuse = (FUSE_DECODE_ROPE and rotary_dim == hd and inv_freq is not None
             and tensor_core_attention_ok(qkv.dtype, hd, nh, nkv))
     n_decode = _batch_shape(ctx)[0] if fuse else 0
@@ -672,8 +677,13 @@ def rope_store_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cac
 
 def paged_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache, scale: float,
                     window: int, out: torch.Tensor, decode_rope=None, only: Optional[str] = None,
-                    stream: Optional[int] = None) -> None:
+                    stream: Optional[int] = None, softcap: float = 0.0,
+                    slopes: Optional[torch.Tensor] = None) -> None:
     """Causal attention of this step's query rows over their requests' cached keys and values.
+
+    Score modifiers: ``softcap`` > 0 replaces a scaled score s by ``softcap * tanh(s / softcap)``;
+    ``slopes`` (float32 [heads]) subtracts ``slopes[h] * (query position - key position)``.  A
+    call with either runs the generic kernel, whatever the dtype and head size.
 
     bfloat16 with head size 64 or 128 runs on the tensor cores: single decode tokens in the
     split-KV kernel, prompt portions in the tiled kernel.  Everything else (32-bit, other head
@@ -699,11 +709,18 @@ def paged_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache, s
               _i(cache.block_table.shape[1]), _p(out))
     tail = (_i(nh), _i(nkv), _i(hd), _i(cache.page_size), _i(cache.k_pages.shape[0]), _f(scale),
             _i(window))
-    if not tensor_core_attention_ok(qkv.dtype, hd, nh, nkv):
+    modified = bool(softcap) or slopes is not None
+    if slopes is not None:
+        _req(slopes, "slopes", torch.float32, 1)
+        if slopes.shape[0] != nh:
+            raise KernelError(f"attention: {slopes.shape[0]} slopes for {nh} heads")
+    if softcap < 0:
+        raise KernelError("attention: the soft cap must be positive (0: none)")
+    if modified or not tensor_core_attention_ok(qkv.dtype, hd, nh, nkv):
         if decode_rope is not None:
             raise KernelError("attention: only the tensor-core decode kernel rotates by itself")
         _call("attention", "lsb_paged_attention_generic", *common, _i(_dt(qkv)),
-              _i(ctx.n_requests), _i(ctx.max_q_len), *tail, _stream(out))
+              _i(ctx.n_requests), _i(ctx.max_q_len), *tail, _f(softcap), _p(slopes), _stream(out))
         return
     R = ctx.n_requests
     n_decode, first, last = _batch_shape(ctx)

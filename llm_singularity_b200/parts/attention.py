@@ -41,6 +41,12 @@ class PagedAttention(Part):
             self.kernels = self.kernels + ("attention_tc", "attention_tc5")
         self.q_size = s.num_heads * s.head_dim
         self.kv_size = s.num_kv_heads * s.head_dim
+        self.softcap = float(getattr(s, "logit_softcap", None) or 0.0)
+        self.slopes = None
+        if getattr(s, "linear_bias", False):
+            # head h of n: 2^(-8 (h + 1) / n), the geometric sequence of the linear-bias scheme
+            self.slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / s.num_heads) for h in range(s.num_heads)],
+                                       dtype=torch.float32, device=rt.device)
 
     @classmethod
     def params(cls, spec) -> Dict[str, ParamSpec]:
@@ -60,6 +66,15 @@ class PagedAttention(Part):
     def cache_spec(self):
         return PagedKVSpec(self.spec.num_kv_heads, self.spec.head_dim, self.spec.window)
 
+    def _modifiers(self) -> dict:
+        """Keyword arguments for the attention operations: only what the spec asks for."""
+        mods = {}
+        if self.softcap:
+            mods["softcap"] = self.softcap
+        if self.slopes is not None:
+            mods["slopes"] = self.slopes
+        return mods
+
     def forward(self, x, ctx, cache, writes_cache: bool = True, into=None):
         s, ops = self.spec, self.rt.ops
         qkv = ops.linear(x, self.wqkv)
@@ -70,11 +85,12 @@ class PagedAttention(Part):
             ops.rope_kv_store(qkv, s.num_heads, s.num_kv_heads, s.head_dim, ctx, cache, None, 0,
                               store=writes_cache)
             ops.paged_attention(qkv, s.num_heads, s.num_kv_heads, s.head_dim, ctx, cache,
-                                s.scale, s.window or 0, out)
+                                s.scale, s.window or 0, out, **self._modifiers())
         else:
             inv_freq, rotary_dim = table
             ops.rope_store_attention(qkv, s.num_heads, s.num_kv_heads, s.head_dim, ctx, cache,
-                                     inv_freq, rotary_dim, writes_cache, s.scale, s.window or 0, out)
+                                     inv_freq, rotary_dim, writes_cache, s.scale, s.window or 0, out,
+                                     **self._modifiers())
         if into is not None:
             return ops.linear(out, self.wo, into=into)
         return ops.linear(out, self.wo)

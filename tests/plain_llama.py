@@ -114,11 +114,13 @@ def apply_rope(x, positions, inv_freq):
     return torch.cat([x0 * cos - x1 * sin, x0 * sin + x1 * cos], dim=-1)
 
 
-def causal_attention(q, k, v, scale, window=None):
+def causal_attention(q, k, v, scale, window=None, softcap=None, slopes=None):
     """q [n, nh, hd], k/v [n, nkv, hd]; query head h reads kv head h // (nh/nkv)
     (kernels/src/attention.cu:46); scores (q.k) * scale over keys at positions <= the
     query's own (models/llama/llama_model.cpp:599-615: per-row length start+t+1), softmax,
-    weighted sum of values (attention.cu:79-113,161-170).  ``window``: also key > pos - window."""
+    weighted sum of values (attention.cu:79-113,161-170).  ``window``: also key > pos - window.
+    Not in the reference, for parts of other architectures: ``softcap`` replaces a scaled score s
+    by softcap * tanh(s / softcap); ``slopes[h]`` times the distance to the key is subtracted."""
     n, nh, hd = q.shape
     nkv = k.shape[1]
     group = nh // nkv
@@ -127,6 +129,10 @@ def causal_attention(q, k, v, scale, window=None):
         g = h // group
         s = (q[:, h, :] @ k[:, g, :].T) * scale                 # [n, n]
         i = torch.arange(n, device=q.device)
+        if softcap:
+            s = softcap * torch.tanh(s / softcap)
+        if slopes is not None:
+            s = s - float(slopes[h]) * (i[:, None] - i[None, :]).to(s.dtype)
         mask = i[None, :] <= i[:, None]
         if window is not None:
             mask &= i[None, :] > i[:, None] - window

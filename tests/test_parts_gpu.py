@@ -43,7 +43,7 @@ def test_norm_part(dtype):
     assert (out2.double() - want[[4, 1]]).abs().max() <= _tol(dtype, 4)
 
 
-def _attention_setup(dtype, window=None, scaling=None, nh=6, nkv=2, hd=48, H=72, page=8):
+def _attention_setup(dtype, window=None, scaling=None, nh=6, nkv=2, hd=48, H=72, page=8, **more):
     from llm_singularity_b200.cache import CacheManager
     from llm_singularity_b200.config.specs import AttentionSpec, Llama3RopeScaling, RotarySpec
     from llm_singularity_b200.parts import MIXERS
@@ -51,7 +51,7 @@ def _attention_setup(dtype, window=None, scaling=None, nh=6, nkv=2, hd=48, H=72,
     sc = Llama3RopeScaling(8.0, 1.0, 4.0, 32) if scaling else None
     spec = AttentionSpec(hidden_size=H, num_heads=nh, num_kv_heads=nkv, head_dim=hd,
                          scale=1 / math.sqrt(hd), window=window,
-                         position=RotarySpec(head_dim=hd, rotary_dim=hd, theta=20000.0, scaling=sc))
+                         position=RotarySpec(head_dim=hd, rotary_dim=hd, theta=20000.0, scaling=sc), **more)
     att = MIXERS.build(spec, rt)
     ws = {"q_proj": _w(nh * hd, H, dtype=dtype, seed=1, std=0.3), "k_proj": _w(nkv * hd, H, dtype=dtype, seed=2, std=0.3),
           "v_proj": _w(nkv * hd, H, dtype=dtype, seed=3), "o_proj": _w(H, nh * hd, dtype=dtype, seed=4)}
@@ -60,7 +60,7 @@ def _attention_setup(dtype, window=None, scaling=None, nh=6, nkv=2, hd=48, H=72,
     return rt, att, ws, cache, sc
 
 
-def _plain_attention(x, ws, nh, nkv, hd, theta, sc, window):
+def _plain_attention(x, ws, nh, nkv, hd, theta, sc, window, softcap=None, slopes=None):
     n = x.shape[0]
     d = {k: v.double().cpu() for k, v in ws.items()}
     q = (x @ d["q_proj"].T).view(n, nh, hd)
@@ -71,7 +71,7 @@ def _plain_attention(x, ws, nh, nkv, hd, theta, sc, window):
                                        original_max_position_embeddings=sc.original_max_position_embeddings)
     inv = plain_llama.rope_inv_freq(hd, theta, scd)
     q, k = plain_llama.apply_rope(q, range(n), inv), plain_llama.apply_rope(k, range(n), inv)
-    a = plain_llama.causal_attention(q, k, v, 1 / math.sqrt(hd), window)
+    a = plain_llama.causal_attention(q, k, v, 1 / math.sqrt(hd), window, softcap, slopes)
     return a.reshape(n, nh * hd) @ d["o_proj"].T
 
 
@@ -105,6 +105,44 @@ def test_attention_part_in_portions_and_decode(dtype, window, scaling):
         assert cache.groups[0].pool.num_used <= -(-window // 8) + 1      # only the window's pages
     cache.close("s")
     cache.check_invariants()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("hd, softcap, bias", [(48, 5.0, False), (64, None, True), (64, 3.0, True)])
+def test_attention_part_with_score_modifiers(dtype, hd, softcap, bias):
+    """A soft cap on the scores and a linear position bias per head (neither is Llama's: what another
+    architecture's attention would set in its spec), in portions and decode tokens through the cache,
+    against plain attention with the same modifiers.  Head size 64 in bfloat16 would run the tensor-core
+    kernels; a spec with a modifier goes to the generic kernel, and it must show in the result: the
+    queries are large enough that the cap moves the scores by far more than the tolerance."""
+    from llm_singularity_b200.engine.batch import ContextBuilder
+    nh, nkv, H = 4, 2, 64
+    rt, att, ws, cache, sc = _attention_setup(dtype, None, None, nh=nh, nkv=nkv, hd=hd, H=H,
+                                              logit_softcap=softcap, linear_bias=bias)
+    x = _rand(40, H, dtype=dtype, seed=11) * (3 if softcap else 1)    # (large scores only where the cap bounds them)
+    slopes = [2.0 ** (-8.0 * (h + 1) / nh) for h in range(nh)] if bias else None
+    want = _plain_attention(x.double().cpu(), ws, nh, nkv, hd, 20000.0, sc, None, softcap, slopes)
+    plain = _plain_attention(x.double().cpu(), ws, nh, nkv, hd, 20000.0, sc, None)
+    builder = ContextBuilder("cuda", 64, 3)
+    cache.open("s")
+    outs, pos = [], 0
+    for n in [17, 1, 1, 9, 1, 11]:
+        assert cache.reserve("s", pos + n)
+        ups = dict(cache.take_updates(0))
+        if ups:
+            idx = torch.tensor(list(ups.keys()), dtype=torch.int32, device="cuda")
+            val = torch.tensor(list(ups.values()), dtype=torch.int32, device="cuda")
+            rt.ops.scatter_i32(cache.groups[0].dev_table, idx, val)
+        ctx, _ = builder.build([[0] * n], [pos], [cache.slot("s")], [[]])
+        outs.append(att.forward(x[pos:pos + n].contiguous(), ctx, cache.view(0, ctx)))
+        pos += n
+        cache.commit("s", pos)
+    got = torch.cat(outs).double().cpu()
+    rt.ops.check_status()
+    tol = _tol(dtype, want.abs().max().item() + 1)
+    assert (got - want).abs().max() <= tol
+    assert (plain - want).abs().max() > 0.1 * want.abs().max()   # the modifiers matter at these sizes
+    cache.close("s")
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
