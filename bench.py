@@ -178,12 +178,19 @@ def run_ours(args):
             runner.step([StepEntry(rid, [t], [0]) for rid, t in zip(ids, feed)], after=greedy)
         return runner.after_result
 
+    SETTLE = 96
+
     def time_decode(batch, steps, warmup, windows=1):
         """``windows`` timed windows of exactly ``steps`` decode steps each (the requests are
         refilled to the same lengths before each), after ``warmup`` steps; returns the median
         window's milliseconds per step, every window's, the launches of one window and the mean
-        context length inside a window."""
-        start = ctx_len - (steps + warmup + 2)
+        context length inside a window.
+
+        Filling the requests is a burst of prompt steps, and the first sixty-odd decode steps
+        after one run 4 - 8 % slower than the steady state (8 x 4096: 0.82 - 0.85 ms a step in the
+        first 64 steps, 0.79 from then on): ``SETTLE`` untimed decode steps follow every fill,
+        before the warm-up steps, so that a window measures decoding and not the fill before it."""
+        start = ctx_len - (steps + warmup + SETTLE + 2)
         ids = fill(batch, start)
         feed = torch.randint(0, V, (batch,), generator=g).tolist()
         runner.cuda_graphs, keep = False, runner.cuda_graphs
@@ -191,14 +198,14 @@ def run_ours(args):
         decode_steps(ids, 1, feed)                  # one step launched kernel by kernel: counted
         per_step = kernels.launch_count() - n0
         runner.cuda_graphs = keep
-        decode_steps(ids, max(warmup - 1, 2), feed)
+        decode_steps(ids, SETTLE + max(warmup - 1, 2), feed)
         all_ms = []
         for w in range(windows):
             if w:                                   # same lengths again: close, refill, warm up
                 for rid in ids:
                     runner.close(rid)
                 ids = fill(batch, start)
-                decode_steps(ids, warmup, feed)
+                decode_steps(ids, SETTLE + warmup, feed)
             torch.cuda.synchronize()
             e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             launches0 = kernels.launch_count()
@@ -255,14 +262,14 @@ def run_ours(args):
     # while the last still prefill: leave room for that, and let none finish inside the timed
     # region (the batch must stay at --batch requests throughout)
     slack = 4 * args.batch + 8
-    prompts = [torch.randint(0, V, (ctx_len - (args.steps + args.warmup) - slack,), generator=g).tolist()
+    prompts = [torch.randint(0, V, (ctx_len - (args.steps + args.warmup + SETTLE) - slack,), generator=g).tolist()
                for _ in range(args.batch)]
     for p in prompts:
-        eng.add_request(p, max_new_tokens=args.steps + args.warmup + slack, temperature=0.0,
+        eng.add_request(p, max_new_tokens=args.steps + args.warmup + SETTLE + slack, temperature=0.0,
                         ignore_eos=True)
     while any(not r.generated for r in eng._requests.values()):
         eng.step()                                   # prefill until every request decodes
-    for _ in range(args.warmup - 1):
+    for _ in range(SETTLE + args.warmup - 1):        # (the same settling after the prompts as above)
         eng.step()
     torch.cuda.synchronize()
     t0 = time.perf_counter()
@@ -294,7 +301,8 @@ def run_ours(args):
                    "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size,
                    "vocab": V, "tied_embeddings": True, "kv_page_tokens": page,
-                   "prefill_tokens": PREFILL_TOKENS, "l2": "inputs larger than L2, no flush",
+                   "prefill_tokens": PREFILL_TOKENS, "settle_steps_after_fill": SETTLE,
+                   "l2": "inputs larger than L2, no flush",
                    "peaks": peak_src},
         "clocks": clocks,
         "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": h2d,
