@@ -141,7 +141,7 @@ decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
                         int table_stride, bf16* __restrict__ out, float* __restrict__ part_o,
                         float* __restrict__ part_ml, int nh, int nkv, int page_size, int num_pages,
                         float scale, int window, int splits, int cluster_merge,
-                        const float* __restrict__ inv_freq, int store_kv) {
+                        const float* __restrict__ inv_freq, int rotary_dim, int store_kv) {
     constexpr int CPR = HD / 8, KS = HD / 16;
     constexpr int kStageElems = 2 * kChunk * HD;             // K rows then V rows
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -179,9 +179,10 @@ decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
     const int page0 = div_page(c0 * kChunk, page_size, page_shift);
     const int n_pages_here = c1 > c0 ? div_page(c1 * kChunk - 1, page_size, page_shift) - page0 + 1 : 0;
     const bool cached = n_pages_here <= kBtCache;
+    const int half = rotary_dim >> 1;                        // rotated pairs: dims (i, i + half), i < half
     if (inv_freq && single)
-        for (int i = threadIdx.x; i < HD / 2; i += kThreads)
-            sincosf((float)p * inv_freq[i], &sCS[HD / 2 + i], &sCS[i]);
+        for (int i = threadIdx.x; i < half; i += kThreads)
+            sincosf((float)p * inv_freq[i], &sCS[half + i], &sCS[i]);
 
     if (single && cached)                                    // from L2: another SM wrote it
         for (int idx = threadIdx.x; idx < n_pages_here; idx += kThreads)
@@ -252,22 +253,30 @@ decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
     const bf16* tok = qkv + (size_t)qs * qkv_stride;          // this token's row of the projection
     if (inv_freq) {
         // The projection comes unrotated: the rotation of the queries and of the new key happens
-        // here (split-half pairs (i, i + HD/2), angle p * inv_freq[i] in 32-bit, as the separate
-        // rotary kernel forms it), and the block whose key range holds position p writes the new
-        // key and value into their page before anybody's copies start.
-        constexpr int HC = CPR / 2;                             // 16-byte chunks per half row
+        // here (split-half pairs (i, i + rotary_dim / 2), angle p * inv_freq[i] in 32-bit, as the
+        // separate rotary kernel forms it; dims from rotary_dim on pass through), and the block
+        // whose key range holds position p writes the new key and value into their page before
+        // anybody's copies start.
+        const int HC = half >> 3;                               // 16-byte chunks per rotated half
+        const int per_row = CPR - HC;                           // work items a row: HC pairs, then the plain chunks
         __syncthreads();                                        // the sines and cosines formed above
-        for (int idx = threadIdx.x; idx < 16 * HC; idx += kThreads) {
-            const int row = idx / HC, c = idx - row * HC;
-            uint4 vlo = make_uint4(0, 0, 0, 0), vhi = make_uint4(0, 0, 0, 0);
-            if (row < G) {
-                const bf16* src = tok + (size_t)(g * G + row) * HD;
-                vlo = *reinterpret_cast<const uint4*>(src + c * 8);
-                vhi = *reinterpret_cast<const uint4*>(src + HD / 2 + c * 8);
-                rotate8(vlo, vhi, sCS + c * 8, sCS + HD / 2 + c * 8);
+        for (int idx = threadIdx.x; idx < 16 * per_row; idx += kThreads) {
+            const int row = idx / per_row, c = idx - row * per_row;
+            const bf16* src = tok + (size_t)(g * G + row) * HD;
+            if (c < HC) {
+                uint4 vlo = make_uint4(0, 0, 0, 0), vhi = make_uint4(0, 0, 0, 0);
+                if (row < G) {
+                    vlo = *reinterpret_cast<const uint4*>(src + c * 8);
+                    vhi = *reinterpret_cast<const uint4*>(src + half + c * 8);
+                    rotate8(vlo, vhi, sCS + c * 8, sCS + half + c * 8);
+                }
+                *reinterpret_cast<uint4*>(tile_ptr<HD>(sQ, row, c)) = vlo;
+                *reinterpret_cast<uint4*>(tile_ptr<HD>(sQ, row, c + HC)) = vhi;
+            } else {
+                uint4 v = make_uint4(0, 0, 0, 0);
+                if (row < G) v = *reinterpret_cast<const uint4*>(src + (c + HC) * 8);
+                *reinterpret_cast<uint4*>(tile_ptr<HD>(sQ, row, c + HC)) = v;
             }
-            *reinterpret_cast<uint4*>(tile_ptr<HD>(sQ, row, c)) = vlo;
-            *reinterpret_cast<uint4*>(tile_ptr<HD>(sQ, row, c + HC)) = vhi;
         }
         const int pc = p / kChunk;
         if (store_kv && pc >= c0 && pc < c1) {
@@ -281,10 +290,14 @@ decode_attention_kernel(const bf16* __restrict__ qkv, int qkv_stride,
                     const int c = threadIdx.x;
                     const bf16* src = tok + (size_t)(nh + g) * HD;
                     uint4 vlo = *reinterpret_cast<const uint4*>(src + c * 8);
-                    uint4 vhi = *reinterpret_cast<const uint4*>(src + HD / 2 + c * 8);
-                    rotate8(vlo, vhi, sCS + c * 8, sCS + HD / 2 + c * 8);
+                    uint4 vhi = *reinterpret_cast<const uint4*>(src + half + c * 8);
+                    rotate8(vlo, vhi, sCS + c * 8, sCS + half + c * 8);
                     *reinterpret_cast<uint4*>(k_pages + dst + c * 8) = vlo;
-                    *reinterpret_cast<uint4*>(k_pages + dst + HD / 2 + c * 8) = vhi;
+                    *reinterpret_cast<uint4*>(k_pages + dst + half + c * 8) = vhi;
+                } else if (threadIdx.x < per_row) {               // the key's dims beyond the rotated ones
+                    const int c = threadIdx.x + HC;
+                    *reinterpret_cast<uint4*>(k_pages + dst + c * 8) =
+                        *reinterpret_cast<const uint4*>(tok + (size_t)(nh + g) * HD + c * 8);
                 } else if (threadIdx.x >= 32 && threadIdx.x < 32 + CPR) {
                     const int c = threadIdx.x - 32;
                     *reinterpret_cast<uint4*>(v_pages + dst + c * 8) =
@@ -824,8 +837,8 @@ static int decode_launch(const void* qkv, int qkv_stride, void* k_pages, void* v
                          const int* q_start, const int* kv_len, const int* table_rows,
                          const int* block_table, int table_stride, void* out, float* scratch,
                          int n_requests, int nh, int nkv, int hd, int page_size, int num_pages,
-                         float scale, int window, int splits, const float* inv_freq, int store_kv,
-                         int max_cluster_size, cudaStream_t stream) {
+                         float scale, int window, int splits, const float* inv_freq, int rotary_dim,
+                         int store_kv, int max_cluster_size, cudaStream_t stream) {
     if (n_requests <= 0) return 0;
     if (nkv <= 0 || nh % nkv || nh / nkv > 16 || splits < 1 || n_requests > 65535 || nkv > 65535)
         return (int)cudaErrorInvalidValue;
@@ -846,7 +859,8 @@ static int decode_launch(const void* qkv, int qkv_stride, void* k_pages, void* v
             in_cluster ? splits : 1,                                                               \
             (const bf16*)qkv, qkv_stride, (bf16*)k_pages, (bf16*)v_pages, q_start,                \
             kv_len, table_rows, block_table, table_stride, (bf16*)out, part_o, part_ml, nh, nkv,  \
-            page_size, num_pages, scale, window, splits, in_cluster ? 1 : 0, inv_freq, store_kv);  \
+            page_size, num_pages, scale, window, splits, in_cluster ? 1 : 0, inv_freq, rotary_dim,  \
+            store_kv);                                                                             \
         if (rc) return rc;                                                                         \
         if (splits > 1 && !in_cluster)                                                             \
             rc = lsb_launch(decode_merge_kernel<HD>, dim3(nh, n_requests), dim3(64), 0, stream, 1, \
@@ -867,23 +881,26 @@ LSB_API int lsb_decode_attention(const void* qkv, int qkv_stride, const void* k_
                                  float scale, int window, int splits, cudaStream_t stream) {
     return decode_launch(qkv, qkv_stride, const_cast<void*>(k_pages), const_cast<void*>(v_pages), q_start,
                          kv_len, table_rows, block_table, table_stride, out, scratch, n_requests, nh, nkv,
-                         hd, page_size, num_pages, scale, window, splits, nullptr, 0, 0, stream);
+                         hd, page_size, num_pages, scale, window, splits, nullptr, 0, 0, 0, stream);
 }
 
 // The same over a projection that has not been rotated yet: the kernel rotates the queries and the
-// new key by `inv_freq` (hd / 2 entries: the whole head is rotary) at position kv_len - 1 and,
-// if `store_kv`, writes the new key and value into their page.  Replaces the separate rotary kernel
+// new key by `inv_freq` (rotary_dim / 2 entries; rotary_dim a multiple of 16, at most hd: the dims
+// from there on pass through) at position kv_len - 1 and, if `store_kv`, writes the new key and
+// value into their page.  Replaces the separate rotary kernel
 // for single decode tokens.
 LSB_API int lsb_decode_attention_rope(const void* qkv, int qkv_stride, void* k_pages, void* v_pages,
                                       const int* q_start, const int* kv_len, const int* table_rows,
                                       const int* block_table, int table_stride, void* out, float* scratch,
                                       int n_requests, int nh, int nkv, int hd, int page_size,
                                       int num_pages, float scale, int window, int splits,
-                                      const float* inv_freq, int store_kv, cudaStream_t stream) {
-    if (!inv_freq) return (int)cudaErrorInvalidValue;
+                                      const float* inv_freq, int rotary_dim, int store_kv,
+                                      cudaStream_t stream) {
+    if (!inv_freq || rotary_dim < 16 || rotary_dim % 16 || rotary_dim > hd)
+        return (int)cudaErrorInvalidValue;
     return decode_launch(qkv, qkv_stride, k_pages, v_pages, q_start, kv_len, table_rows, block_table,
                          table_stride, out, scratch, n_requests, nh, nkv, hd, page_size, num_pages,
-                         scale, window, splits, inv_freq, store_kv, 0, stream);
+                         scale, window, splits, inv_freq, rotary_dim, store_kv, 0, stream);
 }
 
 // Prompt portions (and, unless skip_single, single tokens too).  bf16, hd 64 or 128.
@@ -967,5 +984,6 @@ LSB_API int lsb_decode_attention_noalloc(const void* qkv, int qkv_stride, const 
     }
     return decode_launch(qkv, qkv_stride, const_cast<void*>(k_pages), const_cast<void*>(v_pages), q_start,
                          kv_len, table_rows, block_table, table_stride, out, scratch, n_requests, nh, nkv,
-                         hd, page_size, num_pages, scale, window, splits, nullptr, 0, kNoAllocCluster, stream);
+                         hd, page_size, num_pages, scale, window, splits, nullptr, 0, 0, kNoAllocCluster,
+                         stream);
 }

@@ -639,13 +639,13 @@ def rope_store_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cac
                          slopes: Optional[torch.Tensor] = None) -> None:
     """``rope_kv_store`` followed by ``paged_attention``, as one operation.  Where the decode
     kernel can do the rotation and the cache write of single tokens itself (tensor-core path,
-    the whole head rotary, no score modifier), the separate kernel runs only for the tokens of
-    prompt portions, or not at all."""
+    the rotated part of the head a multiple of 16 wide, no score modifier), the separate kernel
+    runs only for the tokens of prompt portions, or not at all."""
     if softcap or slopes is not None:
         rope_kv_store(qkv, nh, nkv, hd, ctx, cache, inv_freq, rotary_dim, store)
         paged_attention(qkv, nh, nkv, hd, ctx, cache, scale, window, out, softcap=softcap, slopes=slopes)
         return
-    fuse = (FUSE_DECODE_ROPE and rotary_dim == hd and inv_freq is not None
+    fuse = (FUSE_DECODE_ROPE and 0 < rotary_dim <= hd and rotary_dim % 16 == 0 and inv_freq is not None
             and tensor_core_attention_ok(qkv.dtype, hd, nh, nkv))
     n_decode = _batch_shape(ctx)[0] if fuse else 0
     if not n_decode:
@@ -661,7 +661,7 @@ def rope_store_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cac
             _stream_op(lambda: fork.record(main))             # qkv is whole here
             _stream_op(lambda: side.wait_event(fork))
             paged_attention(qkv, nh, nkv, hd, ctx, cache, scale, window, out,
-                            decode_rope=(inv_freq, store), only="single", stream=side.cuda_stream)
+                            decode_rope=(inv_freq, store, rotary_dim), only="single", stream=side.cuda_stream)
             _stream_op(lambda: join.record(side))
             rope_kv_store(qkv, nh, nkv, hd, ctx, cache, inv_freq, rotary_dim, store, skip_single=True)
             paged_attention(qkv, nh, nkv, hd, ctx, cache, scale, window, out, only="portions")
@@ -670,9 +670,10 @@ def rope_store_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cac
         rope_kv_store(qkv, nh, nkv, hd, ctx, cache, inv_freq, rotary_dim, store, skip_single=True)
     else:
         _req(inv_freq, "inv_freq", torch.float32, 1)
-        if inv_freq.shape[0] != hd // 2 or qkv.shape[1] != (nh + 2 * nkv) * hd:
+        if inv_freq.shape[0] != rotary_dim // 2 or qkv.shape[1] != (nh + 2 * nkv) * hd:
             raise KernelError("rope: inv_freq or qkv do not fit the head size")
-    paged_attention(qkv, nh, nkv, hd, ctx, cache, scale, window, out, decode_rope=(inv_freq, store))
+    paged_attention(qkv, nh, nkv, hd, ctx, cache, scale, window, out,
+                    decode_rope=(inv_freq, store, rotary_dim))
 
 
 def paged_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache, scale: float,
@@ -687,8 +688,8 @@ def paged_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache, s
 
     bfloat16 with head size 64 or 128 runs on the tensor cores: single decode tokens in the
     split-KV kernel, prompt portions in the tiled kernel.  Everything else (32-bit, other head
-    sizes) runs the generic kernel.  ``decode_rope = (inv_freq, store)`` says that single tokens
-    come unrotated and not yet in the cache (see ``rope_store_attention``).  ``only``: "single"
+    sizes) runs the generic kernel.  ``decode_rope = (inv_freq, store, rotary_dim)`` says that
+    single tokens come unrotated and not yet in the cache (see ``rope_store_attention``).  ``only``: "single"
     or "portions" launches just that kernel; ``stream``: a raw stream to launch on instead of the
     current one."""
     _req(qkv, "qkv", dim=2)
@@ -748,7 +749,7 @@ def paged_attention(qkv: torch.Tensor, nh: int, nkv: int, hd: int, ctx, cache, s
                   _i(splits), on)
         else:
             _call("attention_tc", "lsb_decode_attention_rope", *common, _p(scratch), _i(R), *tail,
-                  _i(splits), _p(decode_rope[0]), _i(1 if decode_rope[1] else 0), on)
+                  _i(splits), _p(decode_rope[0]), _i(decode_rope[2]), _i(1 if decode_rope[1] else 0), on)
     if n_decode < R and only != "single":
         # prompt portions: tcgen05 kernel for long ones (128-row tiles), mma.sync kernel otherwise
         # The grid has a slab of blocks per request, and blocks that find a single token leave at

@@ -504,23 +504,29 @@ def test_rope_kv_store_reports_a_page_that_is_not_held(ops):
 
 
 # ------------------------------------------------------------------- attention
-@pytest.mark.parametrize("nh, nkv, hd, page, window", [(8, 2, 64, 16, 0), (32, 8, 64, 16, 0), (6, 2, 128, 32, 0),
-                                                       (16, 1, 64, 8, 0), (4, 4, 64, 4, 0), (8, 2, 64, 16, 40)])
+@pytest.mark.parametrize("nh, nkv, hd, page, window, rotary",
+                         [(8, 2, 64, 16, 0, 64), (32, 8, 64, 16, 0, 64), (6, 2, 128, 32, 0, 128),
+                          (16, 1, 64, 8, 0, 64), (4, 4, 64, 4, 0, 64), (8, 2, 64, 16, 40, 64),
+                          (8, 2, 64, 16, 0, 32), (6, 3, 64, 8, 0, 16), (6, 2, 128, 32, 0, 32),
+                          (4, 4, 128, 16, 40, 96), (18, 2, 128, 16, 0, 64)])
 @pytest.mark.parametrize("q_lens, kv_lens", [([1, 1, 1, 1], [1, 16, 17, 700]), ([1, 9, 1, 130], [33, 20, 4097, 130]),
                                              ([1], [5000])])
-def test_decode_kernel_rotates_and_stores_like_the_separate_kernel(ops, nh, nkv, hd, page, window,
-                                                                    q_lens, kv_lens):
+def test_decode_kernel_rotates_and_stores_like_the_separate_kernel(ops, monkeypatch, nh, nkv, hd, page,
+                                                                    window, rotary, q_lens, kv_lens):
     """rope_store_attention (single tokens rotated and stored inside the decode kernel) against
     rope_kv_store followed by paged_attention on copies of the same inputs: same outputs, same
-    pages; also with store off."""
+    pages; also with store off, and with only the first `rotary` dims of a head rotated."""
     from llm_singularity_b200.parts.rotary import rotary_inv_freq
     dtype = torch.bfloat16
     R = len(q_lens)
     rows = list(reversed(range(R)))
     ctx = _make_ctx(q_lens, kv_lens, table_rows=rows)
     T = sum(q_lens)
-    inv = rotary_inv_freq(hd, 500000.0).float().cuda()
+    inv = rotary_inv_freq(rotary, 500000.0).float().cuda()
     scale = 1.0 / math.sqrt(hd)
+    called = []
+    call = ops._call
+    monkeypatch.setattr(ops, "_call", lambda lib, name, *a: (called.append(name), call(lib, name, *a))[1])
     qkv0 = _rand(T, (nh + 2 * nkv) * hd, dtype=dtype, seed=3)
     results = []
     for fused in (False, True):
@@ -532,10 +538,12 @@ def test_decode_kernel_rotates_and_stores_like_the_separate_kernel(ops, nh, nkv,
             qkv = qkv0.clone()
             out = torch.empty(T, nh * hd, dtype=dtype, device="cuda")
             if fused:
-                ops.rope_store_attention(qkv, nh, nkv, hd, ctx, cache, inv, hd, store, scale, window, out)
+                ops.rope_store_attention(qkv, nh, nkv, hd, ctx, cache, inv, rotary, store, scale, window, out)
+                assert "lsb_decode_attention_rope" in called
             else:
-                ops.rope_kv_store(qkv, nh, nkv, hd, ctx, cache, inv, hd, store=store)
+                ops.rope_kv_store(qkv, nh, nkv, hd, ctx, cache, inv, rotary, store=store)
                 ops.paged_attention(qkv, nh, nkv, hd, ctx, cache, scale, window, out)
+                assert "lsb_decode_attention_rope" not in called
             ops.check_status()
             results.append((out.float().cpu(), cache.k_pages.float().cpu(), cache.v_pages.cpu()))
     for a, b in ((0, 2), (1, 3)):

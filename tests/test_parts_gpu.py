@@ -43,7 +43,7 @@ def test_norm_part(dtype):
     assert (out2.double() - want[[4, 1]]).abs().max() <= _tol(dtype, 4)
 
 
-def _attention_setup(dtype, window=None, scaling=None, nh=6, nkv=2, hd=48, H=72, page=8, **more):
+def _attention_setup(dtype, window=None, scaling=None, nh=6, nkv=2, hd=48, H=72, page=8, rotary=None, **more):
     from llm_singularity_b200.cache import CacheManager
     from llm_singularity_b200.config.specs import AttentionSpec, Llama3RopeScaling, RotarySpec
     from llm_singularity_b200.parts import MIXERS
@@ -51,7 +51,8 @@ def _attention_setup(dtype, window=None, scaling=None, nh=6, nkv=2, hd=48, H=72,
     sc = Llama3RopeScaling(8.0, 1.0, 4.0, 32) if scaling else None
     spec = AttentionSpec(hidden_size=H, num_heads=nh, num_kv_heads=nkv, head_dim=hd,
                          scale=1 / math.sqrt(hd), window=window,
-                         position=RotarySpec(head_dim=hd, rotary_dim=hd, theta=20000.0, scaling=sc), **more)
+                         position=RotarySpec(head_dim=hd, rotary_dim=rotary or hd, theta=20000.0, scaling=sc),
+                         **more)
     att = MIXERS.build(spec, rt)
     ws = {"q_proj": _w(nh * hd, H, dtype=dtype, seed=1, std=0.3), "k_proj": _w(nkv * hd, H, dtype=dtype, seed=2, std=0.3),
           "v_proj": _w(nkv * hd, H, dtype=dtype, seed=3), "o_proj": _w(H, nh * hd, dtype=dtype, seed=4)}
@@ -60,7 +61,7 @@ def _attention_setup(dtype, window=None, scaling=None, nh=6, nkv=2, hd=48, H=72,
     return rt, att, ws, cache, sc
 
 
-def _plain_attention(x, ws, nh, nkv, hd, theta, sc, window, softcap=None, slopes=None):
+def _plain_attention(x, ws, nh, nkv, hd, theta, sc, window, softcap=None, slopes=None, rotary=None):
     n = x.shape[0]
     d = {k: v.double().cpu() for k, v in ws.items()}
     q = (x @ d["q_proj"].T).view(n, nh, hd)
@@ -69,21 +70,26 @@ def _plain_attention(x, ws, nh, nkv, hd, theta, sc, window, softcap=None, slopes
     scd = None if sc is None else dict(rope_type="llama3", factor=sc.factor, low_freq_factor=sc.low_freq_factor,
                                        high_freq_factor=sc.high_freq_factor,
                                        original_max_position_embeddings=sc.original_max_position_embeddings)
-    inv = plain_llama.rope_inv_freq(hd, theta, scd)
-    q, k = plain_llama.apply_rope(q, range(n), inv), plain_llama.apply_rope(k, range(n), inv)
+    rot = rotary or hd
+    inv = plain_llama.rope_inv_freq(rot, theta, scd)
+    q, k = (torch.cat([plain_llama.apply_rope(t[..., :rot], range(n), inv), t[..., rot:]], dim=-1) for t in (q, k))
     a = plain_llama.causal_attention(q, k, v, 1 / math.sqrt(hd), window, softcap, slopes)
     return a.reshape(n, nh * hd) @ d["o_proj"].T
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("window, scaling", [(None, False), (None, True), (11, False)])
-def test_attention_part_in_portions_and_decode(dtype, window, scaling):
+@pytest.mark.parametrize("window, scaling, hd, rotary", [(None, False, 48, None), (None, True, 48, None),
+                                                         (11, False, 48, None), (None, False, 48, 20),
+                                                         (None, True, 64, 32), (11, False, 128, 48)])
+def test_attention_part_in_portions_and_decode(dtype, window, scaling, hd, rotary):
     """One sequence of 45 tokens fed as 20 + 2 + 1 + ... through the part's own cache equals plain
-    attention over the whole sequence; with a window, pages the window has passed are given back."""
+    attention over the whole sequence; with a window, pages the window has passed are given back.
+    Also with heads of which only the first `rotary` dims rotate (in bfloat16 the 64- and 128-wide
+    ones take the decode kernel's own rotation for their single tokens)."""
     from llm_singularity_b200.engine.batch import ContextBuilder
-    rt, att, ws, cache, sc = _attention_setup(dtype, window, scaling)
+    rt, att, ws, cache, sc = _attention_setup(dtype, window, scaling, hd=hd, rotary=rotary)
     x = _rand(45, 72, dtype=dtype, seed=9)
-    want = _plain_attention(x.double().cpu(), ws, 6, 2, 48, 20000.0, sc, window)
+    want = _plain_attention(x.double().cpu(), ws, 6, 2, hd, 20000.0, sc, window, rotary=rotary)
     builder = ContextBuilder("cuda", 64, 3)
     cache.open("s")
     outs, pos = [], 0
