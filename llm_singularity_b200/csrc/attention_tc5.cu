@@ -67,6 +67,29 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
     lsb_set_status(LSB_WAIT_TIMEOUT);
     return false;
 }
+// Is the phase complete?  Never blocks.
+__device__ __forceinline__ uint32_t mbar_test(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+                 "selp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
+    return ok;
+}
+// A warp waits through its first lane and arrives through it: thirty-two lanes on one barrier are
+// thirty-two operations on one shared-memory word.
+__device__ __forceinline__ bool warp_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int lane) {
+    int ok = 1;
+    if (lane == 0) ok = mbar_wait(bar, parity, abort_flag) ? 1 : 0;
+    ok = __shfl_sync(0xffffffffu, ok, 0);
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ void warp_arrive(uint64_t* bar, int lane) {
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar);
+}
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int c0, int c1) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
                  ::"r"(smem_addr(dst)), "l"(map), "r"(smem_addr(bar)), "r"(c0), "r"(c1) : "memory");
@@ -171,7 +194,7 @@ struct Smem {
     static constexpr int kQBytes = kRows * HD * 2;
     static constexpr int kKVBytes = kKeys * HD * 2;         // one of K or V, one stage
     static constexpr size_t kTotal = 1024 + kQBytes + 2 * kKvStages * kKVBytes +
-                                     kBtCache * 4 + 16 * 8 + 16;
+                                     kBtCache * 4 + 20 * 8 + 16;
 };
 
 template <int HD>
@@ -180,9 +203,9 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                              const __grid_constant__ CUtensorMap map_v, const AttnParams prm) {
     using L = Smem<HD>;
     constexpr int KB = L::kKB;
-    // tensor memory: S (kKeys columns of 32-bit scores), P twice (kKeys / 2 columns each: two
-    // bfloat16 per column), the O tile (HD columns)
-    constexpr uint32_t kTmemCols = (2 * kKeys + HD) <= 128 ? 128 : (2 * kKeys + HD) <= 256 ? 256 : 512;
+    // tensor memory: S twice (kKeys columns of 32-bit scores each: even and odd tiles), P twice
+    // (kKeys / 2 columns each: two bfloat16 per column), the O tile (HD columns)
+    constexpr uint32_t kTmemCols = (3 * kKeys + HD) <= 128 ? 128 : (3 * kKeys + HD) <= 256 ? 256 : 512;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* base = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
     unsigned char* sQ = base;                                // [KB][128 rows][128 B]
@@ -193,15 +216,15 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
     uint64_t* q_full = bars;                                 // TMA -> MMA
     uint64_t* kv_full = bars + 1;                            // [stages] TMA -> MMA
     uint64_t* kv_empty = kv_full + kKvStages;                // [stages] MMA -> TMA
-    uint64_t* s_full = kv_empty + kKvStages;                 // MMA -> softmax
+    uint64_t* s_full = kv_empty + kKvStages;                 // [2] MMA -> softmax: S of an even / odd tile
     // P of even and of odd tiles has a barrier each: a softmax warp may be a whole tile ahead of
     // another (S of the next tile comes early), and its arrival for tile t + 1 must not count
     // towards tile t, whose P a slower warp has yet to write.  Two tiles ahead it cannot be: P of
     // tile t + 2 waits for the P V product of tile t, which waits for every warp's P of tile t.
-    uint64_t* p_full = s_full + 1;                           // [2] softmax -> MMA (128 arrivals)
+    uint64_t* p_full = s_full + 2;                           // [2] softmax -> MMA (an arrival a warp)
     uint64_t* o_full = p_full + 2;                           // [2] MMA -> softmax: P V of an even / odd tile landed
-    uint64_t* s_free = o_full + 2;                           // softmax -> MMA: S is in registers (128 arrivals)
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_free + 1);
+    uint64_t* s_free = o_full + 2;                           // [2] softmax -> MMA: S is in registers (an arrival a warp)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(s_free + 2);
     __shared__ int abort_flag;
 
     lsb_pdl_launch_dependents();
@@ -231,12 +254,14 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         abort_flag = 0;
         mbar_init(q_full, 1);
         for (int s = 0; s < kKvStages; ++s) { mbar_init(&kv_full[s], 1); mbar_init(&kv_empty[s], 1); }
-        mbar_init(s_full, 1);
-        mbar_init(&p_full[0], 128);
-        mbar_init(&p_full[1], 128);
+        mbar_init(&s_full[0], 1);
+        mbar_init(&s_full[1], 1);
+        mbar_init(&p_full[0], 4);
+        mbar_init(&p_full[1], 4);
         mbar_init(&o_full[0], 1);
         mbar_init(&o_full[1], 1);
-        mbar_init(s_free, 128);
+        mbar_init(&s_free[0], 4);
+        mbar_init(&s_free[1], 4);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
@@ -257,9 +282,9 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const uint32_t tmem_s = *tmem_slot;                      // S: columns [0, 128)
-    const uint32_t tmem_p = tmem_s + kKeys;                  // P of even tiles, then of odd tiles
-    const uint32_t tmem_o = tmem_s + 2 * kKeys;              // O tile
+    const uint32_t tmem_s = *tmem_slot;                      // S of even tiles, then of odd tiles
+    const uint32_t tmem_p = tmem_s + 2 * kKeys;              // P of even tiles, then of odd tiles
+    const uint32_t tmem_o = tmem_s + 3 * kKeys;              // O tile
     const int n_tiles = t1 - t0;
 
     if (warp == 0) {
@@ -315,9 +340,9 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         if (lane == 0) {
             constexpr uint32_t idesc_qk = make_idesc(kKeys, 0);
             bool ok = mbar_wait(q_full, 0, &abort_flag);
-            // S of tile t + 1 is issued as soon as the softmax warps hold S of tile t in registers,
-            // ahead of the P V of tile t: the tensor pipe works on it while they exponentiate, and
-            // they find the next S waiting when they are done.
+            // S has two buffers: S of tile t + 2 is issued as soon as the softmax warps hold S of
+            // tile t in registers, so a tile's scores are complete long before they are wanted and
+            // the softmax warps can ask for them early (see there).
             // Descriptors are formed once: the issuer shares its scheduler with busy softmax warps
             // and gets few issue slots, so every instruction saved per tile shortens the wait for S.
             uint64_t da_q[KB], db_k0[KB];
@@ -332,21 +357,20 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 for (int kb = 0; kb < KB; ++kb) {
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
-                        umma_bf16(tmem_s, da_q[kb] + 2 * k, db_k0[kb] + stage + 2 * k, idesc_qk, (kb | k) ? 1u : 0u);
+                        umma_bf16(tmem_s + (uint32_t)((t & 1) * kKeys), da_q[kb] + 2 * k, db_k0[kb] + stage + 2 * k,
+                                  idesc_qk, (kb | k) ? 1u : 0u);
                 }
-                umma_commit(s_full);
+                umma_commit(&s_full[t & 1]);
             };
-            if (ok && n_tiles > 0) {
-                ok = mbar_wait(&kv_full[0], 0, &abort_flag);
-                if (ok) { tc_fence_after(); issue_s(0); }
-            }
-            for (int t = 0; t + 1 < n_tiles && ok; ++t) {
-                ok = mbar_wait(&kv_full[(t + 1) % kKvStages], (uint32_t)((t + 1) / kKvStages) & 1, &abort_flag);
+            for (int t = 0; t < n_tiles && ok; ++t) {
+                ok = mbar_wait(&kv_full[t % kKvStages], (uint32_t)(t / kKvStages) & 1, &abort_flag);
                 if (!ok) break;
-                ok = mbar_wait(s_free, (uint32_t)t & 1, &abort_flag);
-                if (!ok) break;
+                if (t >= 2) {                                  // this buffer's last S is in registers
+                    ok = mbar_wait(&s_free[t & 1], (uint32_t)((t >> 1) - 1) & 1, &abort_flag);
+                    if (!ok) break;
+                }
                 tc_fence_after();
-                issue_s(t + 1);
+                issue_s(t);
             }
         }
     } else if (warp == 6) {
@@ -389,23 +413,34 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         constexpr float kRescale = 8.f;
         float m = -INFINITY, l = 0.f;
         bool ok = true;
+        // A wait on a barrier that is long complete, a load from tensor memory and a store to it
+        // each take the warp 200 to 500 cycles from issue to result (measured alone: 200, 510 and
+        // 260), and a tile's chain of them was as long as its arithmetic.  So the warp asks early and
+        // looks late: whether the P buffer is free is asked before the maxima and looked at after
+        // them; whether the next S is complete is asked before the exponentials, and if it is, its
+        // load is issued behind the store of P, under the wait for that store.
+        uint32_t v[kKeys];
+        bool loaded = false;                                   // S of tile t is on its way to v already
         for (int t = 0; t < n_tiles && ok; ++t) {
-            ok = mbar_wait(s_full, (uint32_t)t & 1, &abort_flag);
-            tc_fence_after();
-            if (!ok || abort_flag) { ok = false; break; }
+            if (!loaded) {
+                ok = warp_wait(&s_full[t & 1], (uint32_t)(t >> 1) & 1, &abort_flag, lane);
+                if (!ok) break;
+#pragma unroll
+                for (int c0 = 0; c0 < kKeys; c0 += 32)
+                    tmem_ld_32x32(tmem_s + lane_sel + (uint32_t)((t & 1) * kKeys + c0),
+                                  *reinterpret_cast<uint32_t(*)[32]>(&v[c0]));
+            }
             const int key0 = (t0 + t) * kKeys;
             const bool full = key0 + kKeys - 1 <= p0 && rows == kRows &&
                               (prm.window <= 0 || key0 > p_last - prm.window);
+            // this tile's P buffer was read by the P V of the tile before the previous one
+            uint32_t p_free = 1;
+            if (t > 1 && lane == 0) p_free = mbar_test(&o_full[t & 1], (uint32_t)((t >> 1) - 1) & 1);
             // S of this row: kKeys values, read from TMEM once.  Tiles wholly below the diagonal (the
             // common case) skip the key tests; partial maxima / sums are independent so that a warp
             // with a scheduler to itself still finds instructions to issue.
-            uint32_t v[kKeys];
-#pragma unroll
-            for (int c0 = 0; c0 < kKeys; c0 += 32)
-                tmem_ld_32x32(tmem_s + lane_sel + c0, *reinterpret_cast<uint32_t(*)[32]>(&v[c0]));
             tmem_ld_wait();
-            tc_fence_before();
-            mbar_arrive(s_free);                               // the next S may overwrite this one
+            warp_arrive(&s_free[t & 1], lane);                 // S of the tile after the next may overwrite this one
             // columns of this tile the row may see: [c_lo, c_hi]
             const int c_hi = full ? kKeys - 1 : (live ? pos - key0 : -1);
             const int c_lo = (full || prm.window <= 0) ? 0 : pos - prm.window + 1 - key0;
@@ -432,17 +467,16 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 l *= corr;
             }
             const float mref = (m == -INFINITY) ? 0.f : m;
-            if (t > 1) {
-                // this tile's P buffer was read by the P V of the tile before the previous one
-                ok = mbar_wait(&o_full[t & 1], (uint32_t)((t >> 1) - 1) & 1, &abort_flag);
+            if (__shfl_sync(0xffffffffu, p_free, 0)) {
                 tc_fence_after();
-                if (!ok || abort_flag) { ok = false; break; }
+            } else {
+                ok = warp_wait(&o_full[t & 1], (uint32_t)((t >> 1) - 1) & 1, &abort_flag, lane);
+                if (!ok) break;
             }
             if (t > 0 && __any_sync(0xffffffffu, moved)) {
                 // O *= corr for this warp's 32 rows; the P V of the previous tile must have landed
-                ok = mbar_wait(&o_full[(t - 1) & 1], (uint32_t)((t - 1) >> 1) & 1, &abort_flag);
-                tc_fence_after();
-                if (!ok || abort_flag) { ok = false; break; }
+                ok = warp_wait(&o_full[(t - 1) & 1], (uint32_t)((t - 1) >> 1) & 1, &abort_flag, lane);
+                if (!ok) break;
 #pragma unroll 1
                 for (int c0 = 0; c0 < HD; c0 += 32) {
                     uint32_t ov[32];
@@ -454,6 +488,8 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
                 }
                 tmem_st_wait();
             }
+            uint32_t s_next = 0;
+            if (t + 1 < n_tiles && lane == 0) s_next = mbar_test(&s_full[(t + 1) & 1], (uint32_t)((t + 1) >> 1) & 1);
             // probabilities (masked scores are -inf: 2^-inf = 0), rounded to bfloat16, two to a
             // 32-bit column
             float la[4] = {0.f, 0.f, 0.f, 0.f};
@@ -472,15 +508,20 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             for (int c0 = 0; c0 < kKeys / 2; c0 += 32)
                 tmem_st_32x32(tmem_p + lane_sel + (uint32_t)((t & 1) * (kKeys / 2) + c0),
                               *reinterpret_cast<uint32_t(*)[32]>(&pw[c0]));
+            loaded = __shfl_sync(0xffffffffu, s_next, 0) != 0;
+            if (loaded) {
+                tc_fence_after();
+#pragma unroll
+                for (int c0 = 0; c0 < kKeys; c0 += 32)
+                    tmem_ld_32x32(tmem_s + lane_sel + (uint32_t)(((t + 1) & 1) * kKeys + c0),
+                                  *reinterpret_cast<uint32_t(*)[32]>(&v[c0]));
+            }
             tmem_st_wait();
-            tc_fence_before();
-            mbar_arrive(&p_full[t & 1]);
+            warp_arrive(&p_full[t & 1], lane);
         }
         // all tiles issued: the last P V closes the accumulator
         if (ok) {
-            ok = mbar_wait(&o_full[(n_tiles - 1) & 1], (uint32_t)((n_tiles - 1) >> 1) & 1, &abort_flag);
-            tc_fence_after();
-            ok = ok && !abort_flag;
+            ok = warp_wait(&o_full[(n_tiles - 1) & 1], (uint32_t)((n_tiles - 1) >> 1) & 1, &abort_flag, lane);
         }
         if (ok) {
             const float inv = l > 0.f ? 1.f / l : 0.f;
