@@ -46,6 +46,9 @@ class _Group:
         self.dev_table: Optional[torch.Tensor] = None
 
 
+_NO_INTS = np.empty(0, dtype=np.int32)
+
+
 class CacheManager:
     def __init__(self, cache_specs: Sequence[object], page_size: int, num_pages,
                  max_requests: int, max_pages_per_request: int, rt=None):
@@ -88,6 +91,7 @@ class CacheManager:
             grp.cache_ids = members[g]
             self.groups.append(grp)
         self._page_buf = (ctypes.c_int * max_pages_per_request)()
+        self._update_buf: Dict[int, np.ndarray] = {}
         if rt is not None:
             self._allocate_device(rt)
 
@@ -208,6 +212,22 @@ class CacheManager:
             raise self._fail()
         flat = buf[:]
         return list(zip(flat[0::2], flat[1::2]))
+
+    def take_update_arrays(self, group: int) -> Tuple[np.ndarray, np.ndarray]:
+        """The same as two int32 arrays (cells, values) with one entry per changed cell, its last
+        value; the arrays are the manager's own and hold until the next call for the group."""
+        n = self._lib.lsbm_num_updates(self._ptr, group)
+        if n == native.ERR:
+            raise self._fail()
+        if n == 0:
+            return _NO_INTS, _NO_INTS
+        buf = self._update_buf.get(group)
+        if buf is None or buf.shape[1] < n:
+            buf = self._update_buf[group] = np.empty((2, max(2 * n, 1024)), dtype=np.int32)
+        n = self._lib.lsbm_take_updates_last(self._ptr, group, buf[0].ctypes.data, buf[1].ctypes.data, buf.shape[1])
+        if n == native.ERR:
+            raise self._fail()
+        return buf[0, :n], buf[1, :n]
 
     def group_of(self, cache_id: int) -> int:
         return self._group_of[cache_id]

@@ -1,5 +1,6 @@
 """Loading the host runtime (``csrc/host_memory.cpp``: pools, block tables, slots, prefix tree;
-``csrc/host_scheduler.cpp``: the scheduler) and declaring its C interface.
+``csrc/host_scheduler.cpp``: the scheduler; ``csrc/host_step.cpp``: a step's metadata packed into
+one buffer) and declaring its C interface.
 
 The library is host code only; it is compiled at first use like the CUDA libraries and needs no
 GPU to run, so the cache manager and the scheduler can be exercised anywhere.
@@ -41,7 +42,10 @@ _SIGNATURES = {
     "lsbm_table": (POINTER(c_int32), [c_void_p, c_int]),
     "lsbm_num_updates": (c_int, [c_void_p, c_int]),
     "lsbm_take_updates": (c_int, [c_void_p, c_int, _IP, c_int]),
+    "lsbm_take_updates_last": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_int]),
     "lsbm_check": (c_int, [c_void_p]),
+    "lsbh_pack_step": (c_longlong, [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                    c_longlong, c_void_p, c_void_p]),
     "lsbp_enable": (c_int, [c_void_p]),
     "lsbp_match": (c_int, [c_void_p, _IP, c_longlong, _IP, c_int]),
     "lsbp_adopt": (c_longlong, [c_void_p, c_int, _IP, c_int]),

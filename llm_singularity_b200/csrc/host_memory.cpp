@@ -359,6 +359,30 @@ LSB_API int lsbm_take_updates(void* h, int group, int* out, int cap_pairs) {
     return n;
 }
 
+// The same as two arrays, cells and values, with one entry per cell: where a cell changed more than
+// once since the last call only its last value is given (the device applies the entries in no
+// particular order).  Returns the number of entries.
+LSB_API int lsbm_take_updates_last(void* h, int group, int* cells, int* values, int cap) {
+    if (no_group(M(h), group)) return kErr;
+    Group& g = M(h)->groups[group];
+    const int n = (int)(g.updates.size() / 2);
+    if (cap < n) return M(h)->fail("take_updates_last: buffer too small");
+    int out = 0;
+    // newest first: a cell seen already is an older write (few cells change twice, the scan of
+    // what was kept is short: a request's new pages, in order)
+    for (int i = n - 1; i >= 0; --i) {
+        const int32_t cell = g.updates[2 * i];
+        bool seen = false;
+        for (int j = 0; j < out && !seen; ++j) seen = cells[j] == cell;
+        if (seen) continue;
+        cells[out] = cell;
+        values[out] = g.updates[2 * i + 1];
+        ++out;
+    }
+    g.updates.clear();
+    return out;
+}
+
 // ----------------------------------------------------------------------------- prefix tree
 // A node owns one page per group: the keys and values of its chunk of tokens after the path above
 // it.  Only whole pages are shared and a match never covers the last token of a prompt, so there is

@@ -12,11 +12,14 @@ packed int32 buffer and one host-to-device copy per step.
 """
 from __future__ import annotations
 
+import itertools
 from dataclasses import dataclass, field
 from typing import Hashable, List, Optional, Sequence
 
 import numpy as np
 import torch
+
+from ..cache import native
 
 
 @dataclass
@@ -65,8 +68,11 @@ class ContextBuilder:
                       for _ in range(self.RING)]
         self._dev = [torch.empty(cap, dtype=torch.int32, device=self.device)
                      for _ in range(self.RING)]
+        self._host_np = [h.numpy() for h in self._host]
         self._events = [None] * self.RING
         self._turn = 0
+        self._offsets = np.zeros(8, dtype=np.int64)
+        self._summary = np.zeros(4, dtype=np.int64)
 
     def _grow(self, n: int) -> None:
         cap = max(n, 2 * self._cap)
@@ -77,6 +83,7 @@ class ContextBuilder:
                       for _ in range(self.RING)]
         self._dev = [torch.empty(cap, dtype=torch.int32, device=self.device)
                      for _ in range(self.RING)]
+        self._host_np = [h.numpy() for h in self._host]
         self._events = [None] * self.RING
 
     def build(self, tokens: List[Sequence[int]], starts: List[int], rows: List[int],
@@ -88,21 +95,18 @@ class ContextBuilder:
         ``static``: a persistent device buffer to fill instead of the ring's (so that the
         arrays keep their addresses from step to step, as a captured graph needs)."""
         R = len(tokens)
-        q_len = np.fromiter((len(t) for t in tokens), dtype=np.int32, count=R)
-        if R == 0 or (q_len <= 0).any():
+        if R == 0:
             raise ValueError("a step needs at least one entry, and every entry at least one token")
-        T = int(q_len.sum())
-        q_start = np.zeros(R + 1, dtype=np.int32)
-        np.cumsum(q_len, out=q_start[1:])
+        arrays = [t if isinstance(t, np.ndarray) and t.dtype == np.int32 else np.asarray(t, dtype=np.int32)
+                  for t in tokens]
+        q_len = np.fromiter(map(len, arrays), dtype=np.int32, count=R)
+        flat = np.ascontiguousarray(arrays[0]) if R == 1 else np.concatenate(arrays)
         starts_a = np.asarray(starts, dtype=np.int32)
-        kv_len = starts_a + q_len
-        want_rows: List[int] = []
-        for r in range(R):
-            for w in wants[r]:
-                if not 0 <= w < q_len[r]:
-                    raise ValueError(f"entry {r}: wanted place {w} outside its {q_len[r]} tokens")
-                want_rows.append(int(q_start[r]) + int(w))
-        W = len(want_rows)
+        rows_a = np.asarray(rows, dtype=np.int32)
+        want_count = np.fromiter(map(len, wants), dtype=np.int32, count=R)
+        W = int(want_count.sum())
+        wants_a = np.fromiter(itertools.chain.from_iterable(wants), dtype=np.int32, count=W)
+        T = int(flat.shape[0])
         extra = extra or []
         n = 3 * T + (R + 1) + 2 * R + W + sum(len(e) for e in extra)
         if n > self._cap:
@@ -112,47 +116,47 @@ class ContextBuilder:
         self._turn = (self._turn + 1) % self.RING
         if self._events[i] is not None:
             self._events[i].synchronize()
-        host = self._host[i].numpy()
-        o = 0
-
-        def put(arr):
-            nonlocal o
-            a = o
-            host[o:o + len(arr)] = arr
-            o += len(arr)
-            return a, o
-
-        flat = np.concatenate([np.asarray(t, dtype=np.int32) for t in tokens])
-        token_req = np.repeat(np.arange(R, dtype=np.int32), q_len)
-        positions = np.arange(T, dtype=np.int32) - np.repeat(q_start[:-1] - starts_a, q_len)
-        s_tok = put(flat)
-        s_pos = put(positions)
-        s_req = put(token_req)
-        s_qs = put(q_start)
-        s_kv = put(kv_len)
-        s_rows = put(np.asarray(rows, dtype=np.int32))
-        s_want = put(np.asarray(want_rows, dtype=np.int32))
-        s_extra = [put(e) for e in extra]
+        host = self._host_np[i]
+        # one pass in the host library writes tokens, positions, each token's entry, where each
+        # entry starts, its length after the step, its block-table row and the wanted rows
+        o = native.lib().lsbh_pack_step(R, q_len.ctypes.data, starts_a.ctypes.data, rows_a.ctypes.data,
+                                        flat.ctypes.data, want_count.ctypes.data, wants_a.ctypes.data,
+                                        host.ctypes.data, self._cap, self._offsets.ctypes.data,
+                                        self._summary.ctypes.data)
+        if o < 0:
+            r = -o - 2
+            if o == -1 or q_len[r] <= 0:
+                raise ValueError("a step needs at least one entry, and every entry at least one token")
+            bad = next(w for w in wants[r] if not 0 <= w < q_len[r])
+            raise ValueError(f"entry {r}: wanted place {bad} outside its {q_len[r]} tokens")
+        s_tok, s_pos, s_req, s_qs, s_kv, s_rows, s_want, end = (int(x) for x in self._offsets)
+        s_extra = []
+        for e in extra:
+            host[o:o + len(e)] = e
+            s_extra.append((o, o + len(e)))
+            o += len(e)
 
         dev = self._dev[i] if static is None else static
         if dev.numel() < o:
             raise ValueError(f"static metadata buffer holds {dev.numel()} ints, step needs {o}")
         dev[:o].copy_(self._host[i][:o], non_blocking=True)
         if self._cuda:
-            ev = torch.cuda.Event()
-            ev.record()
-            self._events[i] = ev
+            if self._events[i] is None:
+                self._events[i] = torch.cuda.Event()
+            self._events[i].record()
 
         ctx = StepContext()
-        ctx.token_ids = dev[s_tok[0]:s_tok[1]]
-        ctx.positions = dev[s_pos[0]:s_pos[1]]
-        ctx.token_req = dev[s_req[0]:s_req[1]]
-        ctx.q_start = dev[s_qs[0]:s_qs[1]]
-        ctx.kv_len = dev[s_kv[0]:s_kv[1]]
-        ctx.table_rows = dev[s_rows[0]:s_rows[1]]
-        ctx.want_rows = dev[s_want[0]:s_want[1]]
+        ctx.token_ids = dev[s_tok:s_pos]
+        ctx.positions = dev[s_pos:s_req]
+        ctx.token_req = dev[s_req:s_qs]
+        ctx.q_start = dev[s_qs:s_kv]
+        ctx.kv_len = dev[s_kv:s_rows]
+        ctx.table_rows = dev[s_rows:s_want]
+        ctx.want_rows = dev[s_want:end]
         ctx.n_tokens, ctx.n_requests, ctx.n_wanted = T, R, W
-        ctx.h_q_len, ctx.h_kv_len, ctx.h_q_start = q_len, kv_len, q_start
-        ctx.h_table_rows = np.asarray(rows, dtype=np.int32)
-        ctx.max_q_len, ctx.max_kv_len = int(q_len.max()), int(kv_len.max())
+        ctx.h_q_len = q_len
+        ctx.h_q_start = host[s_qs:s_kv].copy()
+        ctx.h_kv_len = host[s_kv:s_rows].copy()
+        ctx.h_table_rows = rows_a
+        ctx.max_q_len, ctx.max_kv_len = int(self._summary[2]), int(self._summary[3])
         return ctx, [dev[a:b] for a, b in s_extra]

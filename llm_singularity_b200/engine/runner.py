@@ -12,6 +12,7 @@ returns host vectors (models/llama/llama_model.cpp:298-726; app/main.cpp:295-337
 """
 from __future__ import annotations
 
+import array
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -46,6 +47,26 @@ def parse_dtype(dtype) -> torch.dtype:
 def _build_model(spec: ModelSpec, rt: Runtime, arch=None):
     build = getattr(arch, "build", None) if arch is not None else None
     return build(spec, rt) if build else DecoderModel(spec, rt)
+
+
+def _token_array(tokens) -> Optional[np.ndarray]:
+    """The tokens as an int32 array; None if one does not fit 32 bits.  A list of thousands of
+    Python ints goes through ``array``, which converts it several times faster than numpy does."""
+    if isinstance(tokens, np.ndarray):
+        if tokens.dtype == np.int32:
+            return tokens
+        if tokens.size and not (-2 ** 31 <= int(tokens.min()) and int(tokens.max()) < 2 ** 31):
+            return None
+        return tokens.astype(np.int32)
+    try:
+        return np.frombuffer(array.array("i", tokens), dtype=np.int32)
+    except OverflowError:
+        return None
+    except TypeError:
+        a = np.asarray(tokens)
+        if a.dtype.kind not in "iu":
+            raise
+        return _token_array(a)
 
 
 def expected_tensors_of(spec: ModelSpec) -> Dict[str, Tuple[Tuple[int, ...], str, str]]:
@@ -164,11 +185,10 @@ class ModelRunner:
         V = self.spec.embedding.vocab_size
         # (a prompt portion comes as a list of thousands of Python ints: turned into an array once,
         # checked and later packed as an array)
-        arrays = [np.asarray(e.tokens, dtype=np.int64) for e in entries]
-        for e, a in zip(entries, arrays):
-            if a.size and not (0 <= int(a.min()) and int(a.max()) < V):
+        tokens = [_token_array(e.tokens) for e in entries]
+        for e, a in zip(entries, tokens):
+            if a is None or (a.size and not (0 <= int(a.min()) and int(a.max()) < V)):
                 raise ValueError(f"request {e.request!r}: token id outside [0, {V})")
-        tokens = [a.astype(np.int32) for a in arrays]
         # pages for the whole step or for none of it: lengths first, then the pools' room for all
         # entries together (every group hands out the same number of pages), then the reservations
         for e, s in zip(entries, starts):
@@ -303,11 +323,7 @@ class ModelRunner:
         cache = self.cache
         extra: List[np.ndarray] = []
         for gi in range(len(cache.groups)):
-            ups = cache.take_updates(gi)
-            # later writes to one cell win: keep the last value per cell
-            last = dict(ups)
-            extra.append(np.fromiter(last.keys(), dtype=np.int32, count=len(last)))
-            extra.append(np.fromiter(last.values(), dtype=np.int32, count=len(last)))
+            extra.extend(cache.take_update_arrays(gi))        # later writes to one cell win
         if tokens is None:
             tokens = [e.tokens for e in entries]
         ctx, dev_extra = self._ctx.build(

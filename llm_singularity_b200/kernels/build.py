@@ -43,7 +43,7 @@ SOURCES: Dict[str, object] = {          # library -> its source file (or files)
     "sampling": "sampling.cu",
     "random_init": "random_init.cu",
     # host code only: pools, block tables, prefix tree; scheduler
-    "host_runtime": ("host_memory.cpp", "host_scheduler.cpp"),
+    "host_runtime": ("host_memory.cpp", "host_scheduler.cpp", "host_step.cpp"),
 }
 HEADERS = ["common.cuh", "attention_tc_noalloc.h", "stream_warm.cuh"]     # of the CUDA libraries
 HOST_HEADERS = ["host_memory.h"]                          # of the host runtime

@@ -1,6 +1,7 @@
 """Cache manager and prefix cache on the host (no GPU): no page lost, held twice or freed twice."""
 import random
 
+import numpy as np
 import pytest
 
 from llm_singularity_b200.cache import CacheManager, PageError, PagePool, NO_PAGE
@@ -98,6 +99,25 @@ def test_table_updates_are_reported_once():
     assert ups == [(0, 0), (1, 1)] and m.take_updates(0) == []
     m.close("a")
     assert m.take_updates(0) == [(0, NO_PAGE), (1, NO_PAGE)]
+
+
+def test_table_updates_as_arrays_keep_the_last_value_of_a_cell():
+    """A request that ends and another that takes its pages between two steps write the same cells
+    twice: the arrays give every cell once, with its last value."""
+    m = _manager(pages=4, max_pages=8)
+    m.open("a")
+    m.reserve("a", 5)
+    m.close("a")
+    m.open("b")
+    m.reserve("b", 9)
+    table = m.groups[0].table.copy()
+    cells, values = m.take_update_arrays(0)
+    assert len(set(cells.tolist())) == len(cells) == 3
+    flat = np.full(table.size, NO_PAGE, dtype=np.int32)
+    flat[cells] = values
+    assert (flat.reshape(table.shape) == table).all()
+    again = m.take_update_arrays(0)
+    assert len(again[0]) == 0 and len(again[1]) == 0 and m.take_updates(0) == []
 
 
 @pytest.mark.parametrize("seed", range(6))

@@ -265,6 +265,71 @@ def test_engine_shares_prompt_pages_between_live_requests_and_yields_the_same_to
     assert stats[1]["prefix_hit_pages"] >= 3 * 3 and stats[0]["prefix_hit_pages"] == 0
 
 
+@pytest.mark.parametrize("seed", range(4))
+def test_step_metadata_is_packed_like_the_plain_arrays(seed):
+    """ContextBuilder (one pass in the host library) against the arrays written out in numpy, for
+    random entries; lists and arrays of tokens alike; bad entries are refused by name."""
+    import numpy as np
+    import torch
+    from llm_singularity_b200.engine.batch import ContextBuilder
+    rng = np.random.default_rng(seed)
+    b = ContextBuilder("cpu", 64, 4)                     # small: the buffers have to grow
+    for _ in range(6):
+        R = int(rng.integers(1, 7))
+        q_len = rng.integers(1, 40, R)
+        starts = rng.integers(0, 500, R)
+        rows = rng.permutation(16)[:R]
+        tokens = [rng.integers(0, 1000, n).astype(np.int32) for n in q_len]
+        as_given = [t.tolist() if i % 2 else t for i, t in enumerate(tokens)]
+        wants = [sorted(set(rng.integers(0, n, int(rng.integers(0, 4))).tolist())) for n in q_len]
+        more = [rng.integers(0, 99, 5).astype(np.int32), np.empty(0, dtype=np.int32)]
+        ctx, extra = b.build(as_given, starts.tolist(), rows.tolist(), wants, more)
+        q_start = np.concatenate([[0], np.cumsum(q_len)])
+        assert ctx.token_ids.tolist() == np.concatenate(tokens).tolist()
+        assert ctx.positions.tolist() == [s + i for s, n in zip(starts, q_len) for i in range(n)]
+        assert ctx.token_req.tolist() == [r for r, n in enumerate(q_len) for _ in range(n)]
+        assert ctx.q_start.tolist() == q_start.tolist() == ctx.h_q_start.tolist()
+        assert ctx.kv_len.tolist() == (starts + q_len).tolist() == ctx.h_kv_len.tolist()
+        assert ctx.table_rows.tolist() == rows.tolist() == ctx.h_table_rows.tolist()
+        assert ctx.want_rows.tolist() == [int(q_start[r]) + w for r in range(R) for w in wants[r]]
+        assert (ctx.n_tokens, ctx.n_requests, ctx.n_wanted) == (int(q_len.sum()), R, sum(map(len, wants)))
+        assert ctx.max_q_len == q_len.max() and ctx.max_kv_len == (starts + q_len).max()
+        assert ctx.h_q_len.tolist() == q_len.tolist()
+        assert [e.tolist() for e in extra] == [m.tolist() for m in more]
+        assert all(t.dtype == torch.int32 for t in (ctx.token_ids, ctx.positions, ctx.want_rows))
+    with pytest.raises(ValueError, match="entry 1: wanted place 3 outside its 3 tokens"):
+        b.build([[1, 2], [3, 4, 5]], [0, 0], [0, 1], [[1], [0, 3]])
+    with pytest.raises(ValueError, match="entry 0: wanted place -1"):
+        b.build([[1, 2]], [0], [0], [[-1]])
+    with pytest.raises(ValueError, match="every entry at least one token"):
+        b.build([[1, 2], []], [0, 0], [0, 1], [[], []])
+    with pytest.raises(ValueError, match="at least one entry"):
+        b.build([], [], [], [])
+
+
+def test_token_lists_become_arrays_or_are_refused(model_dirs):
+    """Tokens come as lists, as arrays of any integer type or as any sequence; an id that does not
+    fit 32 bits is refused like any id outside the vocabulary, by the request's name."""
+    import numpy as np
+    from llm_singularity_b200.engine import StepEntry
+    from llm_singularity_b200.engine.runner import _token_array
+    assert _token_array([1, 2, 3]).tolist() == [1, 2, 3] and _token_array([1, 2, 3]).dtype == np.int32
+    assert _token_array(np.array([4, 5], dtype=np.int64)).dtype == np.int32
+    assert _token_array(range(3)).tolist() == [0, 1, 2]
+    assert _token_array([1, 2 ** 40]) is None and _token_array(np.array([2 ** 40])) is None
+    with pytest.raises(TypeError):
+        _token_array([1.5, 2])
+    runner = ModelRunner(model_dirs["tiny_a"], dtype="float32", device="cpu", page_size=16, num_pages=4,
+                         max_requests=2, max_model_len=64, ops=standin_ops)
+    runner.open("a")
+    for bad in ([1, 2 ** 40], [1, -1], [runner.vocab_size]):
+        with pytest.raises(ValueError, match="request 'a': token id outside"):
+            runner.step([StepEntry("a", bad, [])])
+    assert runner.cache.free_pages() == 4
+    out = runner.step([StepEntry("a", np.array([1, 2, 3], dtype=np.int64), [2])])
+    assert out.shape == (1, runner.vocab_size)
+
+
 def test_a_step_that_does_not_fit_reserves_nothing(model_dirs):
     """Pages are taken for all entries of a step or for none: a step whose second entry finds no
     room leaves the first entry's request as it was (no page held back, no table update queued),
