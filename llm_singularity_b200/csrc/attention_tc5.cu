@@ -149,6 +149,32 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// The larger of three; two 32-bit floats in a 64-bit register, and a multiply-add and a sum on
+// both at once (sm_100: half the instructions of a row's exponents and sums).
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float r;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+    return r;
+}
+__device__ __forceinline__ uint64_t pack2(float a, float b) {
+    uint64_t r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(a), "f"(b));
+    return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& a, float& b) {
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(a), "=f"(b) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+    uint64_t r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+    uint64_t r;
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+
 // K-major operand tile, 128-byte swizzle: rows of 128 bytes, groups of 8 rows 1024 bytes apart.
 __device__ __forceinline__ uint64_t desc_kmajor(const void* tile) {
     uint64_t d = (uint64_t)((smem_addr(tile) >> 4) & 0x3FFFu);
@@ -447,7 +473,8 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             float mxa[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
             if (full) {
 #pragma unroll
-                for (int x = 0; x < kKeys; ++x) mxa[x & 3] = fmaxf(mxa[x & 3], __uint_as_float(v[x]));
+                for (int x = 0; x < kKeys; x += 2)
+                    mxa[(x >> 1) & 3] = max3(mxa[(x >> 1) & 3], __uint_as_float(v[x]), __uint_as_float(v[x + 1]));
             } else {
 #pragma unroll
                 for (int x = 0; x < kKeys; ++x) {
@@ -492,17 +519,23 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
             if (t + 1 < n_tiles && lane == 0) s_next = mbar_test(&s_full[(t + 1) & 1], (uint32_t)((t + 1) >> 1) & 1);
             // probabilities (masked scores are -inf: 2^-inf = 0), rounded to bfloat16, two to a
             // 32-bit column
-            float la[4] = {0.f, 0.f, 0.f, 0.f};
+            uint64_t la[4] = {0ull, 0ull, 0ull, 0ull};         // pairs of partial sums
+            const uint64_t sc2 = pack2(sc, sc), mref2 = pack2(-mref, -mref);
             uint32_t pw[kKeys / 2];
 #pragma unroll
             for (int x = 0; x < kKeys; x += 2) {
-                const float pa = fast_exp2(fmaf(__uint_as_float(v[x]), sc, -mref));
-                const float pb = fast_exp2(fmaf(__uint_as_float(v[x + 1]), sc, -mref));
-                la[(x >> 1) & 3] += pa + pb;
+                float ea, eb;
+                unpack2(fma2(pack2(__uint_as_float(v[x]), __uint_as_float(v[x + 1])), sc2, mref2), ea, eb);
+                const float pa = fast_exp2(ea), pb = fast_exp2(eb);
+                la[(x >> 1) & 3] = add2(la[(x >> 1) & 3], pack2(pa, pb));
                 __nv_bfloat162 hb = __floats2bfloat162_rn(pa, pb);
                 pw[x >> 1] = *reinterpret_cast<uint32_t*>(&hb);
             }
-            l += (la[0] + la[1]) + (la[2] + la[3]);
+            {
+                float s0, s1;
+                unpack2(add2(add2(la[0], la[1]), add2(la[2], la[3])), s0, s1);
+                l += s0 + s1;
+            }
             // P stays in tensor memory: the P V product takes it from there as its A operand
 #pragma unroll
             for (int c0 = 0; c0 < kKeys / 2; c0 += 32)
