@@ -89,7 +89,7 @@ def run_bench(eng, args) -> dict:
                 eng.step()
             times.append(_sync_time(dev) - t0)
         best = min(times[1:])
-        out.update(seconds=round(best, 6), prompt_tokens=args.prompt_len, runs=len(times),
+        out.update(seconds=round(best, 9), prompt_tokens=args.prompt_len, runs=len(times),
                    prompt_tokens_per_s=round(args.prompt_len / best, 1))
     elif args.bench == "decode":
         n_new = max(2, args.max_new_tokens)
@@ -104,7 +104,7 @@ def run_bench(eng, args) -> dict:
         for _ in range(n_new - 4):
             made += len(eng.step())
         dt = _sync_time(dev) - t0
-        out.update(seconds=round(dt, 6), decode_steps=n_new - 4, generated_tokens=made,
+        out.update(seconds=round(dt, 9), decode_steps=n_new - 4, generated_tokens=made,
                    generated_tokens_per_s=round(made / dt, 1))
         while eng.has_work():
             eng.step()
@@ -119,7 +119,7 @@ def run_bench(eng, args) -> dict:
         while eng.has_work():
             made += sum(1 for _, tok, _ in eng.step() if tok >= 0)
         dt = _sync_time(dev) - t0
-        out.update(seconds=round(dt, 6), prompt_tokens=sum(lens), generated_tokens=made,
+        out.update(seconds=round(dt, 9), prompt_tokens=sum(lens), generated_tokens=made,
                    generated_tokens_per_s=round(made / dt, 1),
                    total_tokens_per_s=round((made + sum(lens)) / dt, 1))
     out["stats"] = eng.stats()

@@ -75,13 +75,14 @@ def expected_tensors_of(spec: ModelSpec) -> Dict[str, Tuple[Tuple[int, ...], str
     return {n: (ps.shape, ps.role, ps.init) for n, (_, _, ps) in shell.expected_tensors().items()}
 
 
-class _DecodeGraph:
-    """What a captured decode step of one batch size keeps: its metadata buffer at a fixed
-    address, the captured graph and the logits tensor the graph writes."""
+class _StepGraph:
+    """What a captured step of one shape (the entries' token counts and wanted places) keeps: its
+    metadata buffer at a fixed address, the captured graph and the logits tensor the graph writes."""
 
-    def __init__(self, n_requests: int, n_groups: int, device):
-        self.cap = 2 * n_requests + 8                    # block-table cells changed per step
-        n = 3 * n_requests + (n_requests + 1) + 3 * n_requests + n_groups * (1 + 2 * self.cap) \
+    def __init__(self, n_requests: int, n_tokens: int, n_wanted: int, n_groups: int, page_size: int, device):
+        # block-table cells changed per step: new pages of the step's tokens, pages given back
+        self.cap = 2 * n_requests + n_tokens // page_size + 8
+        n = 3 * n_tokens + (n_requests + 1) + 2 * n_requests + n_wanted + n_groups * (1 + 2 * self.cap) \
             + 2 * n_requests                             # and which tokens come from the device
         self.meta = torch.zeros(n, dtype=torch.int32, device=device)
         self.graph = None
@@ -134,7 +135,15 @@ class ModelRunner:
         self.tokens_run = 0
         # decode-only steps are captured once per batch size and replayed (no per-kernel launch
         # cost); only if every part launches the same kernels whatever the host-side values are
-        self._graphs: Dict[tuple, "_DecodeGraph"] = {}     # (batch size, key of the step's ``after``)
+        # The same holds for a step with prompt portions whose shape (token count and wanted places
+        # of every entry) comes again: whole prompts of one length, the full portions of a long
+        # prompt.  Such a shape is captured when it is seen for the third time; the most recent
+        # ``max_shape_graphs`` are kept (each holds the activations of its step).
+        self._graphs: Dict[tuple, "_StepGraph"] = {}       # (batch size | shape, key of the step's ``after``)
+        self._shape_seen: Dict[tuple, int] = {}
+        self._shape_order: List[tuple] = []
+        self.max_shape_graphs = 4
+        self.shape_graphs = True
         self.after_result = None
         self._capture_stream = None
         self.cuda_graphs = (cuda_graphs and ops is None and self.rt.device.type == "cuda"
@@ -210,10 +219,11 @@ class ModelRunner:
             lens = np.fromiter((len(e.tokens) for e in entries), dtype=np.int32, count=len(entries))
             first = np.concatenate(([0], np.cumsum(lens[:-1]))).astype(np.int32)   # entry -> its first token
             moves = [first[np.asarray(which, dtype=np.int64)], np.asarray(places, dtype=np.int32)]
-        if self.cuda_graphs and all(len(e.tokens) == 1 and list(e.want) == [0] for e in entries):
-            logits = self._decode_with_graph(entries, starts, moves, None if feed is None else source, tokens,
-                                             after)
-            n_tokens = len(entries)
+        key = self._graph_key(entries, tokens, after) if self.cuda_graphs else None
+        if key is not None:
+            logits = self._step_with_graph(key, entries, starts, moves, None if feed is None else source,
+                                           tokens, after)
+            n_tokens = sum(len(t) for t in tokens)
         else:
             ctx, dev_moves = self.prepare_context(entries, starts, moves, tokens)
             if feed is not None:
@@ -227,32 +237,56 @@ class ModelRunner:
         return logits
 
     # ------------------------------------------------------------ decode graphs
-    def _decode_with_graph(self, entries: Sequence[StepEntry], starts: Sequence[int],
-                           moves: List[np.ndarray], source: Optional[torch.Tensor],
-                           tokens: Sequence[np.ndarray], after=None) -> torch.Tensor:
-        """A step of single decode tokens, all wanted: replay the graph captured for this batch
-        size.  The step's metadata and the block-table cells that changed are copied into buffers
-        at fixed addresses first; everything else happens inside the graph.  The returned logits
-        live in the graph's own memory and are overwritten by the next step of the same size."""
+    def _graph_key(self, entries: Sequence[StepEntry], tokens: Sequence[np.ndarray], after) -> Optional[tuple]:
+        """The key of the graph this step replays (or is about to be captured into), or None for a
+        step that is launched kernel by kernel."""
+        after_key = getattr(after, "key", None) if after is not None else None
+        if all(len(t) == 1 and list(e.want) == [0] for e, t in zip(entries, tokens)):
+            return (len(entries), after_key)
+        if not self.shape_graphs:
+            return None
+        key = (tuple(len(t) for t in tokens), tuple(tuple(e.want) for e in entries), after_key)
+        if key in self._graphs:
+            self._shape_order.remove(key)
+            self._shape_order.append(key)
+            return key
+        if len(self._shape_seen) > 4096:
+            self._shape_seen.clear()
+        seen = self._shape_seen[key] = self._shape_seen.get(key, 0) + 1
+        if seen < 2:
+            return None
+        del self._shape_seen[key]
+        while len(self._shape_order) >= self.max_shape_graphs:      # the least recently used goes
+            del self._graphs[self._shape_order.pop(0)]
+        self._shape_order.append(key)
+        return key
+
+    def _step_with_graph(self, key: tuple, entries: Sequence[StepEntry], starts: Sequence[int],
+                         moves: List[np.ndarray], source: Optional[torch.Tensor],
+                         tokens: Sequence[np.ndarray], after=None) -> torch.Tensor:
+        """A step whose shape has a graph: single decode tokens, all wanted (one graph a batch
+        size), or a shape with prompt portions that keeps coming.  The step's metadata and the
+        block-table cells that changed are copied into buffers at fixed addresses first;
+        everything else happens inside the graph (run once without capture, then captured, then
+        replayed).  The returned logits live in the graph's own memory and are overwritten by the
+        next step of the same shape."""
         cache, R = self.cache, len(entries)
-        key = (R, getattr(after, "key", None) if after is not None else None)
         st = self._graphs.get(key)
         if st is None:
-            st = self._graphs[key] = _DecodeGraph(R, len(cache.groups), self.rt.device)
+            st = self._graphs[key] = _StepGraph(R, sum(len(t) for t in tokens), sum(len(e.want) for e in entries),
+                                                len(cache.groups), self.page_size, self.rt.device)
         extra: List[np.ndarray] = []
         for gi in range(len(cache.groups)):
-            last = dict(cache.take_updates(gi))
-            if len(last) > st.cap:                       # rare (many requests closed): plain path
-                keys = list(last)
-                spill = {k: last.pop(k) for k in keys[st.cap:]}
-                idx = torch.tensor(list(spill), dtype=torch.int32, device=self.rt.device)
-                val = torch.tensor(list(spill.values()), dtype=torch.int32, device=self.rt.device)
+            cells, values = cache.take_update_arrays(gi)
+            if len(cells) > st.cap:                      # rare (many requests closed): plain path
+                idx = torch.from_numpy(cells[st.cap:].copy()).to(self.rt.device)
+                val = torch.from_numpy(values[st.cap:].copy()).to(self.rt.device)
                 self.rt.ops.scatter_i32(cache.groups[gi].dev_table, idx, val)
+                cells, values = cells[:st.cap], values[:st.cap]
             packed = np.zeros(1 + 2 * st.cap, dtype=np.int32)
-            packed[0] = len(last)
-            packed[1:1 + len(last)] = np.fromiter(last.keys(), dtype=np.int32, count=len(last))
-            packed[1 + st.cap:1 + st.cap + len(last)] = np.fromiter(last.values(), dtype=np.int32,
-                                                                    count=len(last))
+            packed[0] = len(cells)
+            packed[1:1 + len(cells)] = cells
+            packed[1 + st.cap:1 + st.cap + len(cells)] = values
             extra.append(packed)
         ctx, dev_extra = self._ctx.build(
             tokens, list(starts), [cache.slot(e.request) for e in entries],
@@ -265,7 +299,7 @@ class ModelRunner:
             for gi, g in enumerate(cache.groups):
                 self.rt.ops.scatter_i32_counted(g.dev_table, dev_extra[gi], st.cap)
             logits = self.model.forward(ctx, cache)
-            st.after_result = after(logits) if after is not None else None
+            st.after_result = after(logits) if after is not None and logits.shape[0] else None
             return logits
 
         if st.graph is None:

@@ -291,3 +291,66 @@ def test_a_swapped_block_table_cell_is_caught_at_the_tolerance_in_use(model_dirs
     runner.check_kernels()
     assert all(d > tol for d in wrong), f"swapped pages went unseen: {wrong} within {tol:.2e}"
     assert all(d <= tol for d in right), f"{right} > {tol:.2e}"
+
+
+# ------------------------------------------------- steps with prompt portions, replayed from a graph
+@pytest.mark.parametrize("name", ["tiny_d", "tiny_e"])
+def test_steps_of_a_shape_that_comes_again_are_replayed_from_a_graph(model_dirs, name):
+    """A step whose entries have the same token counts and wanted places as one before is captured
+    at its third occurrence and replayed from then on, wherever its requests stand in their
+    sequences and whatever their pages: the same bits as a runner that launches every such step
+    kernel by kernel (whole prompts and later portions of them), and rows within rounding of it
+    where single tokens ride along (their attention is split otherwise in a captured step).  At
+    most ``max_shape_graphs`` are kept; a shape that was dropped is captured again."""
+    from llm_singularity_b200.engine import ModelRunner, StepEntry
+    d = model_dirs[name]
+    kw = dict(dtype="bfloat16", page_size=8, num_pages=400, max_requests=8, max_tokens_per_step=512,
+              max_model_len=400)
+    graphs, plain = ModelRunner(d, **kw), ModelRunner(d, **kw)
+    plain.shape_graphs = False
+    graphs.max_shape_graphs = 2
+    V = graphs.vocab_size
+    assert graphs.cuda_graphs
+
+    def both(entries):
+        a = graphs.step([StepEntry(*e) for e in entries]).float().cpu()
+        b = plain.step([StepEntry(*e) for e in entries]).float().cpu()
+        return a, b
+
+    for r in range(8):
+        assert graphs.open(r) and plain.open(r)
+    # three shapes by turns, six rounds: a whole portion of 150 tokens with two places wanted, two
+    # portions side by side, and a portion beside two single tokens
+    seqs = {r: tiny_models.random_tokens(V, 400, 50 + r) for r in range(8)}
+    pos = {r: 0 for r in range(8)}
+
+    def take(r, n):
+        t = seqs[r][pos[r]:pos[r] + n]
+        pos[r] += n
+        return t
+
+    for r in (4, 5):                                       # the two that will bring single tokens
+        both([(r, take(r, 33), [])])
+    replays = []
+    for rnd in range(6):
+        a, b = both([(rnd % 4, take(rnd % 4, 150), [3, 149])])
+        assert torch.equal(a, b), f"round {rnd}: a whole portion"
+        a, b = both([(6, take(6, 40), [39]), (7, take(7, 24), [])])
+        assert torch.equal(a, b), f"round {rnd}: two portions"
+        a, b = both([(4, take(4, 1), [0]), (5, take(5, 1), [0]), (rnd % 4, take(rnd % 4, 30), [29])])
+        assert (a - b).abs().max() <= 2e-2 * b.abs().max(), f"round {rnd}: single tokens beside a portion"
+        replays.append(graphs.graph_replays)
+    # with room for two shapes and three by turns every shape is captured again and again:
+    # seen, run once, captured and replayed; with room for all of them they stay
+    assert replays[-1] >= 4 and plain.graph_replays == 0
+    assert len(graphs._shape_order) <= 2
+    graphs.max_shape_graphs = 4
+    before = graphs.graph_replays
+    for rnd in range(5):
+        a, b = both([(rnd % 4, take(rnd % 4, 9), [8])])
+        assert torch.equal(a, b)
+    assert graphs.graph_replays - before == 3              # rounds 2, 3 and 4
+    graphs.check_kernels(); plain.check_kernels()
+    for r in range(8):
+        graphs.close(r); plain.close(r)
+    graphs.cache.check_invariants()
