@@ -12,7 +12,8 @@
 captured graph and prints where one step's time goes: for every kernel of one layer in the middle
 of the model, the time from the previous kernel's end to its own end (kernels overlap: each starts
 under its predecessor), and the step's total by kernel.  ``prefill_step`` does the same for one
-prompt of ``--tokens`` tokens run as one step.
+prompt of ``--tokens`` tokens run as one step (a shape that comes again: from its third time on the
+runner replays it from a graph, as it would a portion of a long prompt).
 
 Times are CUDA-event times on the launching stream after warm-up, with a buffer larger than the
 L2 cache read between iterations (``--no-flush`` to keep it warm).  The same command line is
@@ -191,7 +192,8 @@ def _prefill_step(a) -> None:
         times.append(e0.elapsed_time(e1))
     times.sort()
     print(f"prefill step T={a.tokens} layers={a.layers} hidden={a.hidden}: median {times[len(times) // 2] * 1e3:.1f} us, "
-          f"best {times[0] * 1e3:.1f} us (CUDA events, launched kernel by kernel)")
+          f"best {times[0] * 1e3:.1f} us (CUDA events around ModelRunner.step; the step's shape has come "
+          f"before, so it is replayed from its graph: {r.graph_replays} replays so far)")
     _timeline(step, "step")
 
 

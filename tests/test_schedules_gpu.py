@@ -301,7 +301,8 @@ def test_steps_of_a_shape_that_comes_again_are_replayed_from_a_graph(model_dirs,
     sequences and whatever their pages: the same bits as a runner that launches every such step
     kernel by kernel (whole prompts and later portions of them), and rows within rounding of it
     where single tokens ride along (their attention is split otherwise in a captured step).  At
-    most ``max_shape_graphs`` are kept; a shape that was dropped is captured again."""
+    most ``max_shape_graphs`` are kept; a shape that was dropped is captured again.  (Steps of up
+    to three entries here; by default only a portion alone in its step is captured.)"""
     from llm_singularity_b200.engine import ModelRunner, StepEntry
     d = model_dirs[name]
     kw = dict(dtype="bfloat16", page_size=8, num_pages=400, max_requests=8, max_tokens_per_step=512,
@@ -309,6 +310,7 @@ def test_steps_of_a_shape_that_comes_again_are_replayed_from_a_graph(model_dirs,
     graphs, plain = ModelRunner(d, **kw), ModelRunner(d, **kw)
     plain.shape_graphs = False
     graphs.max_shape_graphs = 2
+    graphs.shape_graph_entries = 3                         # the default is 1: a portion alone in its step
     V = graphs.vocab_size
     assert graphs.cuda_graphs
 
