@@ -1004,10 +1004,13 @@ LSB_API int lsb_gemm_tc(const void* x, const void* w, void* out, int out_f32, in
             default: return (int)cudaErrorInvalidValue;
         }
     } else {
+        // 32 and 64 rows: four stages, so that the blocks of the next product (often split over a
+        // cluster) find room beside these and start under their ends (a decode step of 32 or 64
+        // rows at 1,024 tokens of context: 2 % shorter than with six and eight stages)
         switch (bn) {
             case 16: rc = launch<16, 8>(mp, mq, prm, grid, stream); break;
-            case 32: rc = launch<32, 8>(mp, mq, prm, grid, stream); break;
-            case 64: rc = launch<64, 6>(mp, mq, prm, grid, stream); break;
+            case 32: rc = launch<32, 4>(mp, mq, prm, grid, stream); break;
+            case 64: rc = launch<64, 4>(mp, mq, prm, grid, stream); break;
             case 128: rc = launch<128, 6>(mp, mq, prm, grid, stream); break;
             case 256: rc = launch<256, 4>(mp, mq, prm, grid, stream); break;
             default: return (int)cudaErrorInvalidValue;
