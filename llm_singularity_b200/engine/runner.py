@@ -173,7 +173,9 @@ class ModelRunner:
     # -------------------------------------------------------------------- step
     def step(self, entries: Sequence[StepEntry], feed=None, after=None) -> torch.Tensor:
         """Run the entries' tokens as one batch from the cache; returns the logits at the wanted
-        places, float32 [wanted, vocab] on the device, in the order of the entries.
+        places, float32 [wanted, vocab] on the device, in the order of the entries.  (After a step
+        of single tokens, all wanted, they are the captured graph's own rows: the next such step of
+        the same batch size writes over them, so keep a copy if you need them longer.)
 
         ``after``: a callable run on the logits right behind the model (sampling on the device);
         what it returns is kept in ``after_result``.  In a decode step that is replayed from a
@@ -274,8 +276,9 @@ class ModelRunner:
         size), or a shape with prompt portions that keeps coming.  The step's metadata and the
         block-table cells that changed are copied into buffers at fixed addresses first;
         everything else happens inside the graph (run once without capture, then captured, then
-        replayed).  The returned logits live in the graph's own memory and are overwritten by the
-        next step of the same shape."""
+        replayed).  The logits of a decode step live in the graph's own memory and are overwritten
+        by the next step of the same batch size; those of a step with prompt portions are copied
+        out."""
         cache, R = self.cache, len(entries)
         st = self._graphs.get(key)
         if st is None:
@@ -346,6 +349,10 @@ class ModelRunner:
         st.graph.replay()
         self.graph_replays += 1
         self.after_result = st.after_result
+        if len(key) == 3:
+            # a shape with prompt portions: the caller gets rows of its own (who asks for the logits
+            # of prompt positions tends to keep them); decode steps hand out the graph's rows
+            return st.logits.clone()
         return st.logits
 
     def check_kernels(self) -> None:
