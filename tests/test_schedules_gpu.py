@@ -321,7 +321,7 @@ def test_steps_of_a_shape_that_comes_again_are_replayed_from_a_graph(model_dirs,
 
     for r in range(8):
         assert graphs.open(r) and plain.open(r)
-    # three shapes by turns, six rounds: a whole portion of 150 tokens with two places wanted, two
+    # three shapes by turns, six turns: a whole portion of 150 tokens with two places wanted, two
     # portions side by side, and a portion beside two single tokens
     seqs = {r: tiny_models.random_tokens(V, 400, 50 + r) for r in range(8)}
     pos = {r: 0 for r in range(8)}
@@ -334,13 +334,13 @@ def test_steps_of_a_shape_that_comes_again_are_replayed_from_a_graph(model_dirs,
     for r in (4, 5):                                       # the two that will bring single tokens
         both([(r, take(r, 33), [])])
     replays = []
-    for rnd in range(6):
-        a, b = both([(rnd % 4, take(rnd % 4, 150), [3, 149])])
-        assert torch.equal(a, b), f"round {rnd}: a whole portion"
+    for turn in range(6):
+        a, b = both([(turn % 4, take(turn % 4, 150), [3, 149])])
+        assert torch.equal(a, b), f"turn {turn}: a whole portion"
         a, b = both([(6, take(6, 40), [39]), (7, take(7, 24), [])])
-        assert torch.equal(a, b), f"round {rnd}: two portions"
-        a, b = both([(4, take(4, 1), [0]), (5, take(5, 1), [0]), (rnd % 4, take(rnd % 4, 30), [29])])
-        assert (a - b).abs().max() <= 2e-2 * b.abs().max(), f"round {rnd}: single tokens beside a portion"
+        assert torch.equal(a, b), f"turn {turn}: two portions"
+        a, b = both([(4, take(4, 1), [0]), (5, take(5, 1), [0]), (turn % 4, take(turn % 4, 30), [29])])
+        assert (a - b).abs().max() <= 2e-2 * b.abs().max(), f"turn {turn}: single tokens beside a portion"
         replays.append(graphs.graph_replays)
     # with room for two shapes and three by turns every shape is captured again and again:
     # seen, run once, captured and replayed; with room for all of them they stay
@@ -348,10 +348,10 @@ def test_steps_of_a_shape_that_comes_again_are_replayed_from_a_graph(model_dirs,
     assert len(graphs._shape_order) <= 2
     graphs.max_shape_graphs = 4
     before = graphs.graph_replays
-    for rnd in range(5):
-        a, b = both([(rnd % 4, take(rnd % 4, 9), [8])])
+    for turn in range(5):
+        a, b = both([(turn % 4, take(turn % 4, 9), [8])])
         assert torch.equal(a, b)
-    assert graphs.graph_replays - before == 3              # rounds 2, 3 and 4
+    assert graphs.graph_replays - before == 3              # turns 2, 3 and 4
     graphs.check_kernels(); plain.check_kernels()
     for r in range(8):
         graphs.close(r); plain.close(r)
