@@ -41,6 +41,28 @@ def test_greedy_generation_matches_plain(model_dirs, name, dtype):
     eng.runner.cache.check_invariants()
 
 
+@pytest.mark.parametrize("name", ["tiny_b", "tiny_d"])
+def test_prompts_of_one_length_one_after_another_are_replayed_and_right(model_dirs, name):
+    """Six prompts of the same length, each generated alone: from the third on the prompt step is
+    replayed from a graph (with the sampler behind the model inside it), other tokens and other
+    pages every time; every continuation is held to the plain implementation."""
+    cfg, w = plain_llama.load_model_dir(model_dirs[name])
+    vocab = tiny_models.CONFIGS[name]["vocab_size"]
+    eng = _engine(model_dirs[name], name, "bfloat16", max_batch_size=1, prefix_cache=False)
+    compared = 0
+    for i in range(6):
+        prompt = tiny_models.random_tokens(vocab, 37, 700 + i)
+        out = eng.generate([prompt], max_new_tokens=6, ignore_eos=True)[0]
+        compared += check_greedy(cfg, w, prompt, out, 0.05, f"{name}, prompt {i}")
+    assert compared >= 12
+    if eng.runner.cuda_graphs:
+        # four replays of the prompt's shape, and the decode steps of batch size 1
+        assert eng.runner.graph_replays >= 4 + 6 * 3
+        assert any(len(k) == 3 for k in eng.runner._graphs)
+    eng.runner.check_kernels()
+    eng.runner.cache.check_invariants()
+
+
 def test_few_pages_preempt_and_still_give_the_same_tokens(model_dirs):
     name = "tiny_a"
     prompts = [tiny_models.random_tokens(256, n, 400 + n) for n in (30, 25, 28)]
