@@ -13,6 +13,7 @@ returns host vectors (models/llama/llama_model.cpp:298-726; app/main.cpp:295-337
 from __future__ import annotations
 
 import array
+import gc
 from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 
 import numpy as np
@@ -328,18 +329,35 @@ class ModelRunner:
                 if side is None:
                     side = self._capture_stream = torch.cuda.Stream(self.rt.device)
                 side.wait_stream(main)
-                with torch.cuda.stream(side):
-                    graph.capture_begin()
-                    try:
-                        st.logits = run()
-                    finally:
-                        graph.capture_end()
+                # No cyclic garbage collection while the stream captures: collecting an engine
+                # that is no longer used (its graphs, streams and events) makes calls that a
+                # capture does not survive, at whatever moment the collector happens to run.
+                collecting = gc.isenabled()
+                gc.disable()
+                try:
+                    with torch.cuda.stream(side):
+                        graph.capture_begin()
+                        try:
+                            st.logits = run()
+                        finally:
+                            graph.capture_end()
+                finally:
+                    if collecting:
+                        gc.enable()
                 main.wait_stream(side)
             except RuntimeError as e:
-                # a driver that cannot capture these launches: decode kernel by kernel from now on
+                # these launches could not be captured: such steps go kernel by kernel from now on
+                # (a shape with prompt portions that fails leaves the decode graphs alone)
                 import warnings
-                warnings.warn(f"CUDA graph capture failed ({e}); decode steps run without graphs")
-                self.cuda_graphs = False
+                if len(key) == 3:
+                    warnings.warn(f"CUDA graph capture failed ({e}); steps with prompt portions run without graphs")
+                    self.shape_graphs = False
+                    for k in self._shape_order:
+                        self._graphs.pop(k, None)
+                    self._shape_order.clear()
+                else:
+                    warnings.warn(f"CUDA graph capture failed ({e}); decode steps run without graphs")
+                    self.cuda_graphs = False
                 torch.cuda.synchronize(self.rt.device)
                 logits = run()
                 self.after_result = st.after_result
