@@ -265,8 +265,10 @@ class ModelRunner:
         if seen < 2:
             return None
         del self._shape_seen[key]
+        if key in self._shape_order:                 # promoted before, never captured (its step failed)
+            self._shape_order.remove(key)
         while len(self._shape_order) >= self.max_shape_graphs:      # the least recently used goes
-            del self._graphs[self._shape_order.pop(0)]
+            self._graphs.pop(self._shape_order.pop(0), None)
         self._shape_order.append(key)
         return key
 
