@@ -43,6 +43,8 @@ struct Group {
     std::vector<int32_t> table;      // [slots * max_pages], host mirror of the device table
     std::vector<int32_t> first_live; // per slot: pages [0, first_live) were released behind the window
     std::vector<int32_t> updates;    // (flat index, value) pairs not yet taken
+    std::vector<uint32_t> taken;     // per cell: the call of take_updates_last that last gave it out
+    uint32_t take_call = 0;
 };
 
 struct Request {
@@ -368,13 +370,17 @@ LSB_API int lsbm_take_updates_last(void* h, int group, int* cells, int* values, 
     const int n = (int)(g.updates.size() / 2);
     if (cap < n) return M(h)->fail("take_updates_last: buffer too small");
     int out = 0;
-    // newest first: a cell seen already is an older write (few cells change twice, the scan of
-    // what was kept is short: a request's new pages, in order)
+    // newest first: a cell that this call has given out already is an older write
+    if (g.taken.size() != g.table.size()) g.taken.assign(g.table.size(), 0u);
+    if (++g.take_call == 0) {                       // the counter came round: start afresh
+        std::fill(g.taken.begin(), g.taken.end(), 0u);
+        g.take_call = 1;
+    }
     for (int i = n - 1; i >= 0; --i) {
         const int32_t cell = g.updates[2 * i];
-        bool seen = false;
-        for (int j = 0; j < out && !seen; ++j) seen = cells[j] == cell;
-        if (seen) continue;
+        if (cell < 0 || (size_t)cell >= g.taken.size()) return M(h)->fail("take_updates_last: a cell outside the table");
+        if (g.taken[cell] == g.take_call) continue;
+        g.taken[cell] = g.take_call;
         cells[out] = cell;
         values[out] = g.updates[2 * i + 1];
         ++out;

@@ -120,6 +120,44 @@ def test_table_updates_as_arrays_keep_the_last_value_of_a_cell():
     assert len(again[0]) == 0 and len(again[1]) == 0 and m.take_updates(0) == []
 
 
+@pytest.mark.parametrize("seed", range(3))
+def test_update_arrays_equal_the_pairs_with_later_writes_winning(seed):
+    """Two managers driven alike under random opening, growing and closing of requests: the arrays
+    of one are, as a mapping, the pairs of the other with later writes to a cell winning; also
+    when hundreds of cells change between two calls."""
+    rng = random.Random(seed)
+    a, b = _manager(pages=64, max_pages=32, slots=6), _manager(pages=64, max_pages=32, slots=6)
+    live = {}
+    for step in range(300):
+        for m in (a, b):
+            m_rng = random.Random(seed * 1000 + step)
+            op = m_rng.random()
+            names = sorted(live)
+            if op < 0.3 and len(live) < 6:
+                name = f"r{step}"
+                m.open(name)
+                if m is b:
+                    live[name] = 0
+            elif op < 0.8 and names:
+                name = names[m_rng.randrange(len(names))]
+                grow = live[name] + m_rng.randrange(1, 60)
+                if grow <= 32 * 4 and m.reserve(name, grow):
+                    m.commit(name, grow)
+                    if m is b:
+                        live[name] = grow
+            elif names:
+                name = names[m_rng.randrange(len(names))]
+                m.close(name)
+                if m is b:
+                    del live[name]
+        if rng.random() < 0.15 or step == 299:
+            pairs = dict(a.take_updates(0))
+            cells, values = b.take_update_arrays(0)
+            assert len(set(cells.tolist())) == len(cells)
+            assert dict(zip(cells.tolist(), values.tolist())) == pairs
+    a.check_invariants(); b.check_invariants()
+
+
 @pytest.mark.parametrize("seed", range(6))
 def test_random_orders_keep_every_page_accounted_for(seed):
     rng = random.Random(seed)
