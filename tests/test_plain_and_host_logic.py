@@ -330,6 +330,44 @@ def test_token_lists_become_arrays_or_are_refused(model_dirs):
     assert out.shape == (1, runner.vocab_size)
 
 
+def test_which_steps_get_a_graph(model_dirs):
+    """The runner's decision alone (no device needed): single tokens that are all wanted share a
+    graph per batch size; a step of one entry with prompt tokens gets one from its second
+    occurrence on; steps of more entries only if asked for; the least recently used shape goes when
+    there are more than ``max_shape_graphs``."""
+    import numpy as np
+    from llm_singularity_b200.engine import StepEntry
+    runner = ModelRunner(model_dirs["tiny_a"], dtype="float32", device="cpu", page_size=16, num_pages=4,
+                         max_requests=2, max_model_len=64, ops=standin_ops)
+    assert not runner.cuda_graphs                      # (no device here: nothing is ever captured)
+
+    def key(*entries):
+        es = [StepEntry(f"r{i}", list(range(n)), list(want)) for i, (n, want) in enumerate(entries)]
+        return runner._graph_key(es, [np.zeros(n, dtype=np.int32) for n, _ in entries], None)
+
+    assert key((1, [0]), (1, [0]), (1, [0])) == (3, None)
+    assert key((1, [])) is None and key((1, [])) == ((1,), ((),), None)     # a token nobody wants: a shape
+    portion = (40, [39])
+    assert key(portion) is None                        # first seen
+    k = key(portion)
+    assert k == ((40,), ((39,),), None)
+    runner._graphs[k] = object()                       # (what capturing it would leave)
+    assert key(portion) == k and key(portion) == k
+    assert key((40, [39]), (1, [0])) is None and key((40, [39]), (1, [0])) is None      # two entries: never
+    runner.shape_graph_entries = 2
+    assert key((40, [39]), (1, [0])) is None and key((40, [39]), (1, [0])) is not None
+    runner.shape_graph_entries = 1
+    runner.max_shape_graphs = 2
+    runner._shape_order[:] = [k]
+    for n in (50, 60):
+        key((n, [0])); kn = key((n, [0]))
+        runner._graphs[kn] = object()
+    assert k not in runner._graphs and len(runner._shape_order) == 2           # the oldest went
+    assert key(portion) is None                        # and starts again from nothing
+    runner.shape_graphs = False
+    assert key(portion) is None and key(portion) is None
+
+
 def test_a_step_that_does_not_fit_reserves_nothing(model_dirs):
     """Pages are taken for all entries of a step or for none: a step whose second entry finds no
     room leaves the first entry's request as it was (no page held back, no table update queued),
