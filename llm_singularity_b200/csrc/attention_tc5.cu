@@ -440,9 +440,12 @@ prefill_attention_tc5_kernel(const __grid_constant__ CUtensorMap map_q, const __
         float m = -INFINITY, l = 0.f;
         bool ok = true;
         // A wait on a barrier that is long complete, a load from tensor memory and a store to it
-        // each take the warp 160 to 200 cycles from issue to result (measured alone, in a loop of
-        // nothing else: 200, 160 and 165), and a tile's chain of them (two waits, a load, a store)
-        // was as long as its exponentials.  So the warp asks early and looks late: whether the P buffer is free is asked before the maxima and looked at after
+        // each take the warp about a hundred cycles from issue to result when nothing else runs
+        // (107, 88 and 77: measure/tc_latency.cu), and several times that in this loop, beside the
+        // other block's warps and the products' traffic (clock stamps in a copy of this kernel: 300
+        // to 500 cycles for a wait on a barrier that was complete when it was asked).  A tile's chain
+        // of them (two waits, a load, a store) was as long as its exponentials.  So the warp asks
+        // early and looks late: whether the P buffer is free is asked before the maxima and looked at after
         // them; whether the next S is complete is asked before the exponentials, and if it is, its
         // load is issued behind the store of P, under the wait for that store.
         uint32_t v[kKeys];

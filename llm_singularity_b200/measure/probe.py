@@ -13,7 +13,9 @@ captured graph and prints where one step's time goes: for every kernel of one la
 of the model, the time from the previous kernel's end to its own end (kernels overlap: each starts
 under its predecessor), and the step's total by kernel.  ``prefill_step`` does the same for one
 prompt of ``--tokens`` tokens run as one step (a shape that comes again: from its third time on the
-runner replays it from a graph, as it would a portion of a long prompt).
+runner replays it from a graph, as it would a portion of a long prompt).  ``tc_latency`` builds and
+runs ``tc_latency.cu``: the cost of single tcgen05 operations that the attention kernel's loop is
+made of.
 
 Times are CUDA-event times on the launching stream after warm-up, with a buffer larger than the
 L2 cache read between iterations (``--no-flush`` to keep it warm).  The same command line is
@@ -197,10 +199,26 @@ def _prefill_step(a) -> None:
     _timeline(step, "step")
 
 
+def _tc_latency() -> int:
+    """Compile ``tc_latency.cu`` (beside this file) into a temporary folder and run it: what a
+    ``tcgen05.mma`` costs its issuing thread, and what a warp waits for a barrier test, a load from
+    tensor memory and a store to it to answer."""
+    import os
+    import subprocess
+    import tempfile
+    from ..kernels.build import find_nvcc
+    src = os.path.join(os.path.dirname(os.path.abspath(__file__)), "tc_latency.cu")
+    with tempfile.TemporaryDirectory() as d:
+        exe = os.path.join(d, "tc_latency")
+        subprocess.run([find_nvcc(), "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
+                        "-o", exe, src], check=True)
+        return subprocess.run([exe], timeout=120).returncode
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="probe", description=__doc__.split("\n\n")[0])
     ap.add_argument("op", choices=["gemm", "decode_attention", "prefill_attention", "add_rmsnorm", "rope",
-                                   "decode_step", "prefill_step"])
+                                   "decode_step", "prefill_step", "tc_latency"])
     ap.add_argument("--m", type=int, default=8)
     ap.add_argument("--n", type=int, default=16384)
     ap.add_argument("--k", type=int, default=2048)
@@ -227,6 +245,8 @@ def main(argv=None) -> int:
     ap.add_argument("--sample", action="store_true", help="decode_step: with greedy sampling inside the graph")
     ap.add_argument("--no-flush", action="store_true")
     a = ap.parse_args(argv)
+    if a.op == "tc_latency":
+        return _tc_latency()
     from .. import kernels as K
     torch.manual_seed(0)
     nh, nkv, hd = a.heads, a.kv_heads, a.head_dim
